@@ -1,0 +1,128 @@
+// Shared helpers of the k-means kernels: error plumbing, the fixed-point
+// representation of the centroid sums, small device utilities.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <string>
+
+#include "../../include/h2o4gpu_kmeans.h"
+
+namespace km {
+
+// ---- error plumbing -----------------------------------------------------------
+void set_error(const std::string& msg);
+
+struct Status {
+  int code;
+  Status(int c = KM_OK) : code(c) {}
+  bool ok() const { return code == KM_OK; }
+};
+
+#define KM_CUDA(expr)                                                                   \
+  do {                                                                                  \
+    cudaError_t _e = (expr);                                                            \
+    if (_e != cudaSuccess) {                                                            \
+      ::km::set_error(std::string(#expr) + ": " + cudaGetErrorString(_e) + " (" +       \
+                      __FILE__ + ":" + std::to_string(__LINE__) + ")");                 \
+      return (_e == cudaErrorMemoryAllocation) ? KM_ENOMEM : KM_ECUDA;                  \
+    }                                                                                   \
+  } while (0)
+
+#define KM_TRY(expr)                   \
+  do {                                 \
+    int _s = (expr);                   \
+    if (_s != KM_OK) return _s;        \
+  } while (0)
+
+#define KM_FAIL(code, msg)             \
+  do {                                 \
+    ::km::set_error(msg);              \
+    return (code);                     \
+  } while (0)
+
+// ---- fixed-point centroid sums ------------------------------------------------
+// A value x (|x| <= xmax < 2^e) is cut into NP signed pieces of 15 bits:
+//   p0 = rint(x * 2^sa), sa = 15 - e, |p0| <= 2^15
+//   r0 = x * 2^sa - p0 (exact), p1 = rint(r0 * 2^15), r1 = r0 * 2^15 - p1, ...
+// Pieces are summed as integers, so the sum does not depend on the order of
+// additions: any CTA schedule, any number of GPUs and any reduction tree give
+// the same bits.  int32 accumulators in shared memory hold up to 2^15 rows;
+// int64 accumulators in global memory hold pairs p(2q) * 2^15 + p(2q+1) and are
+// exact for up to 2^32 rows.  float uses 2 pieces (quantum xmax * 2^-30, below
+// half an ulp of any |x| >= xmax * 2^-7), double 4 pieces (quantum xmax * 2^-60).
+template <typename T> struct Fixed;
+template <> struct Fixed<float> { static constexpr int NP = 2; };
+template <> struct Fixed<double> { static constexpr int NP = 4; };
+constexpr int kPieceBits = 15;
+constexpr int kFlushRows = 32768;  // rows a CTA may add before its int32 accumulators are drained
+
+// Splits x * scale into NP 15-bit pieces.  `scale` = 2^sa.
+template <int NP>
+__device__ __forceinline__ void split_pieces(float x, float scale, int (&p)[NP]) {
+  // rint via the 1.5*2^23 trick: exact for |v| < 2^22, all full-rate ops.
+  const float magic = 12582912.0f;
+  float v = x * scale;
+#pragma unroll
+  for (int q = 0; q < NP; ++q) {
+    float t = v + magic;
+    p[q] = __float_as_int(t) - __float_as_int(magic);
+    float pf = t - magic;
+    v = (v - pf) * 32768.0f;
+  }
+}
+template <int NP>
+__device__ __forceinline__ void split_pieces(double x, double scale, int (&p)[NP]) {
+  const double magic = 6755399441055744.0;  // 1.5 * 2^52
+  double v = x * scale;
+#pragma unroll
+  for (int q = 0; q < NP; ++q) {
+    double t = v + magic;
+    p[q] = (int)(__double2loint(t));  // low word of the mantissa holds rint(v) (two's complement)
+    double pf = t - magic;
+    v = (v - pf) * 32768.0;
+  }
+}
+
+// Value of NP/2 int64 pairs back as a double.  inv = 2^-(sa + 15).
+template <int NP>
+__device__ __host__ __forceinline__ double fixed_to_double(const long long* g, double inv) {
+  // pair q weighs inv * 2^(-30 q); the small pair is added first
+  if (NP == 2) return (double)g[0] * inv;
+  return (double)g[1] * (inv * (1.0 / 1073741824.0)) + (double)g[0] * inv;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ double warp_max(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmax(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <typename T> struct Inf;
+template <> struct Inf<float> { __device__ static float v() { return __int_as_float(0x7f800000); } };
+template <> struct Inf<double> { __device__ static double v() { return __longlong_as_double(0x7ff0000000000000LL); } };
+
+// Device-side scalars of one shard, shared by the kernels of an iteration.
+struct IterState {
+  unsigned long long changed;   // labels that changed in the current E-step
+  int n_empty;                  // empty clusters found by the current M-step
+  int argmax_count;             // index of the largest cluster
+  int relocated;                // relocations done in the current M-step
+  int error;                    // sticky device-side error word (0 = none)
+  double shift_sq;              // summed squared centroid shift of the current M-step
+  double inertia;               // scratch for the inertia pass
+};
+
+}  // namespace km

@@ -1,0 +1,531 @@
+// Host side of the engine: row shards resident on the local devices, the Lloyd
+// loop, kernel dispatch.  Replaces kmeans_fit / kmeans_predict / kmeans_transform
+// and kmeans::kmeans (src/gpu/kmeans/kmeans_h2o4gpu.cu:617-975,
+// src/gpu/kmeans/kmeans_impl.h:45-247).  One host thread drives all local
+// devices asynchronously (the reference uses one OpenMP thread per GPU); the
+// per-iteration exchange is one NCCL all-reduce of the int64 sums and counts
+// instead of the reference's device->host->device staging (kmeans_impl.h:140-188).
+#pragma once
+
+#include <algorithm>
+#include <chrono>
+#include <cmath>
+#include <cstring>
+#include <memory>
+#include <vector>
+
+#include "km_accumulate.cuh"
+#include "km_common.cuh"
+#include "km_finalize.cuh"
+#include "km_nccl.h"
+#include "km_smallk.cuh"
+#include "km_tiles.cuh"
+
+namespace km {
+
+void log_msg(int verbose, int level, const char* fmt, ...);
+
+struct DevGuard {
+  int prev = -1;
+  explicit DevGuard(int dev) {
+    cudaGetDevice(&prev);
+    if (dev != prev) cudaSetDevice(dev);
+  }
+  ~DevGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+inline double now_s() {
+  return std::chrono::duration<double>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+constexpr size_t kMaxDynSmem = 227 * 1024;
+
+template <typename T>
+struct Shard {
+  int dev = -1;
+  int num_sms = 0;
+  cudaStream_t stream = nullptr;
+  const T* X = nullptr;
+  T* X_owned = nullptr;
+  size_t rows = 0, row0 = 0;
+  int* labels = nullptr;
+  size_t labels_cap = 0;
+  double* dist = nullptr;
+  size_t dist_cap = 0;
+  // buffers that depend on (k, d)
+  int k_cap = 0, d_cap = 0;
+  long long* gacc = nullptr;  // [NP/2][k][d] sums followed by [k] counts: one all-reduce covers both
+  T* C[2] = {nullptr, nullptr};
+  T* cnorm = nullptr;
+  double* shift_k = nullptr;
+  int* empties = nullptr;
+  IterState* st = nullptr;
+  double* cand_val = nullptr;
+  unsigned long long* cand_row = nullptr;
+  double* sum_partials = nullptr;
+  double* shift_log = nullptr;
+  unsigned long long* changed_log = nullptr;
+  int* reloc_log = nullptr;
+  int log_cap = 0;
+  double* xstat = nullptr;  // device: [0] max|x| ; int flag behind it
+  double* host_pin = nullptr;  // pinned: [0] shift, [1] changed (as u64), [2] n_empty etc.
+  ncclComm_t comm = nullptr;
+  bool x_checked = false;
+  double xmax = 0;
+
+  long long* sums() const { return gacc; }
+  unsigned long long* counts(int k, int d) const {
+    return reinterpret_cast<unsigned long long*>(gacc + (size_t)(Fixed<T>::NP / 2) * k * d);
+  }
+  size_t gacc_count(int k, int d) const { return (size_t)(Fixed<T>::NP / 2) * k * d + k; }
+};
+
+struct EngineBase {
+  int dtype = 0;
+  virtual ~EngineBase() {}
+};
+
+template <typename T>
+struct Engine : EngineBase {
+  std::vector<Shard<T>> shards;
+  int world_rank0 = 0, world_size = 1;
+  size_t n_total = 0;
+  int d = 0, k = 0;
+  int cur = 0;  // index of the current centroid buffer
+  bool have_centroids = false;
+  int verbose = 0;
+  kmeans_stats stats{};
+  int launches = 0;
+
+  ~Engine() { destroy(); }
+
+  int init(int n_local, const int* devs, int rank0, int world, const void* nccl_id);
+  void destroy();
+  int attach_device(int local, const T* dX, size_t rows, size_t cols, size_t ntot);
+  int upload_host(const T* X, size_t rows, size_t cols, char order);
+  int ensure_buffers(int k_);
+  int check_data();
+  int set_centroids(int k_, const T* host_c);
+  int fit(int k_, int max_iter, double threshold, const T* init, int flags);
+  int assign_all(int flags);
+  int transform_shard(int local, T* out_host, size_t ld);
+  int inertia(double* out);
+  int allreduce_acc();
+  int relocate_multi(double scale);
+
+  // launch helpers (device of the shard must be current)
+  int launch_tiles(Shard<T>& s, const T* Xp, size_t nrows, int* labels, int mode, T* out, size_t ld_out,
+                   bool count_changes);
+  int launch_smallk(Shard<T>& s, bool update, T scale);
+  int launch_accumulate(Shard<T>& s, T scale);
+  bool smallk_ok(bool update) const;
+  bool vec_ok(const Shard<T>& s) const {
+    constexpr int V = VecOf<T>::N;
+    return (d % V == 0) && ((reinterpret_cast<uintptr_t>(s.X) & 15) == 0);
+  }
+};
+
+// -------------------------------------------------------------------------------
+template <typename T>
+int Engine<T>::init(int n_local, const int* devs, int rank0, int world, const void* nccl_id) {
+  dtype = sizeof(T) == 8;
+  int visible = 0;
+  if (cudaGetDeviceCount(&visible) != cudaSuccess || visible == 0) KM_FAIL(KM_ENODEV, "no CUDA device visible");
+  if (n_local < 1 || world < n_local || rank0 < 0 || rank0 + n_local > world)
+    KM_FAIL(KM_EINVAL, "kmeans_create: bad device / rank layout");
+  world_rank0 = rank0;
+  world_size = world;
+  shards.resize(n_local);
+  for (int i = 0; i < n_local; ++i) {
+    Shard<T>& s = shards[i];
+    s.dev = devs[i];
+    if (s.dev < 0 || s.dev >= visible) KM_FAIL(KM_ENODEV, "kmeans_create: device id out of range");
+    DevGuard g(s.dev);
+    cudaDeviceProp prop;
+    KM_CUDA(cudaGetDeviceProperties(&prop, s.dev));
+    s.num_sms = prop.multiProcessorCount;
+    KM_CUDA(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
+    KM_CUDA(cudaMalloc(&s.st, sizeof(IterState)));
+    KM_CUDA(cudaMemset(s.st, 0, sizeof(IterState)));
+    KM_CUDA(cudaMalloc(&s.xstat, 2 * sizeof(double)));
+    KM_CUDA(cudaMallocHost(&s.host_pin, 8 * sizeof(double)));
+    KM_CUDA(cudaMalloc(&s.cand_val, 1024 * sizeof(double)));
+    KM_CUDA(cudaMalloc(&s.cand_row, 1024 * sizeof(unsigned long long)));
+    KM_CUDA(cudaMalloc(&s.sum_partials, 1024 * sizeof(double)));
+  }
+  if (world > 1) {
+    NcclApi* api = NcclApi::get();
+    if (!api) KM_FAIL(KM_ENCCL, "more than one GPU requested but libnccl.so.2 could not be loaded");
+    if (world == n_local) {
+      std::vector<ncclComm_t> comms(n_local);
+      std::vector<int> dl(devs, devs + n_local);
+      KM_NCCL(api, api->CommInitAll(comms.data(), n_local, dl.data()));
+      for (int i = 0; i < n_local; ++i) shards[i].comm = comms[i];
+    } else {
+      if (!nccl_id) KM_FAIL(KM_EINVAL, "kmeans_create: nccl_id required when world_size > n_local");
+      ncclUniqueId id;
+      std::memcpy(&id, nccl_id, sizeof(id));
+      KM_NCCL(api, api->GroupStart());
+      for (int i = 0; i < n_local; ++i) {
+        DevGuard g(shards[i].dev);
+        KM_NCCL(api, api->CommInitRank(&shards[i].comm, world, id, rank0 + i));
+      }
+      KM_NCCL(api, api->GroupEnd());
+    }
+  }
+  return KM_OK;
+}
+
+template <typename T>
+void Engine<T>::destroy() {
+  for (auto& s : shards) {
+    if (s.dev < 0) continue;
+    DevGuard g(s.dev);
+    if (s.stream) cudaStreamSynchronize(s.stream);
+    if (s.comm) {
+      NcclApi* api = NcclApi::get();
+      if (api) api->CommDestroy(s.comm);
+    }
+    cudaFree(s.X_owned); cudaFree(s.labels); cudaFree(s.dist); cudaFree(s.gacc);
+    cudaFree(s.C[0]); cudaFree(s.C[1]); cudaFree(s.cnorm); cudaFree(s.shift_k); cudaFree(s.empties);
+    cudaFree(s.st); cudaFree(s.cand_val); cudaFree(s.cand_row); cudaFree(s.sum_partials);
+    cudaFree(s.shift_log); cudaFree(s.changed_log); cudaFree(s.reloc_log); cudaFree(s.xstat);
+    if (s.host_pin) cudaFreeHost(s.host_pin);
+    if (s.stream) cudaStreamDestroy(s.stream);
+    s.dev = -1;
+  }
+  shards.clear();
+}
+
+template <typename T>
+int Engine<T>::attach_device(int local, const T* dX, size_t rows, size_t cols, size_t ntot) {
+  if (local < 0 || local >= (int)shards.size() || !dX || rows == 0 || cols == 0 || cols > (1u << 20))
+    KM_FAIL(KM_EINVAL, "kmeans_attach_device: bad argument");
+  if (d != 0 && d != (int)cols && local != 0) KM_FAIL(KM_EINVAL, "kmeans_attach_device: shards disagree on cols");
+  Shard<T>& s = shards[local];
+  DevGuard g(s.dev);
+  if (s.X_owned && s.X_owned != dX) { cudaFree(s.X_owned); s.X_owned = nullptr; }
+  s.X = dX;
+  s.rows = rows;
+  s.x_checked = false;
+  if ((int)cols != d) have_centroids = false;
+  d = (int)cols;
+  n_total = ntot;
+  if (s.labels_cap < rows) {
+    cudaFree(s.labels);
+    s.labels = nullptr;
+    KM_CUDA(cudaMalloc(&s.labels, rows * sizeof(int)));
+    s.labels_cap = rows;
+  }
+  KM_CUDA(cudaMemsetAsync(s.labels, 0xff, rows * sizeof(int), s.stream));
+  return KM_OK;
+}
+
+template <typename T>
+__global__ void transpose_cm_kernel(const T* __restrict__ src, T* __restrict__ dst, size_t rows, int cols) {
+  // src: column-major rows x cols (leading dimension rows) -> dst row-major
+  __shared__ T tile[32][33];
+  size_t r0 = (size_t)blockIdx.x * 32;
+  int c0 = blockIdx.y * 32;
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    size_t r = r0 + threadIdx.x;
+    int c = c0 + j;
+    if (r < rows && c < cols) tile[j][threadIdx.x] = src[(size_t)c * rows + r];
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    size_t r = r0 + j;
+    int c = c0 + threadIdx.x;
+    if (r < rows && c < cols) dst[r * (size_t)cols + c] = tile[threadIdx.x][j];
+  }
+}
+
+template <typename T>
+int Engine<T>::upload_host(const T* X, size_t rows, size_t cols, char order) {
+  if (!X || rows == 0 || cols == 0 || cols > (1u << 20)) KM_FAIL(KM_EINVAL, "kmeans_upload_host: bad argument");
+  if (order != 'r' && order != 'c') KM_FAIL(KM_EINVAL, "kmeans_upload_host: order must be 'r' or 'c'");
+  if (world_size != (int)shards.size())
+    KM_FAIL(KM_ESTATE, "kmeans_upload_host: one process must own all ranks; use kmeans_attach_device");
+  double t0 = now_s();
+  const size_t g = shards.size();
+  const size_t per = (rows + g - 1) / g;
+  size_t off = 0;
+  for (size_t i = 0; i < g; ++i) {
+    Shard<T>& s = shards[i];
+    size_t r = (off < rows) ? std::min(per, rows - off) : 0;
+    if (r == 0) KM_FAIL(KM_EINVAL, "kmeans_upload_host: fewer rows than devices");
+    DevGuard gd(s.dev);
+    cudaFree(s.X_owned);
+    s.X_owned = nullptr;
+    KM_CUDA(cudaMalloc(&s.X_owned, r * cols * sizeof(T)));
+    if (order == 'r') {
+      KM_CUDA(cudaMemcpyAsync(s.X_owned, X + off * cols, r * cols * sizeof(T), cudaMemcpyHostToDevice, s.stream));
+    } else {
+      // column-major host matrix (leading dimension = total rows): strided copy of the
+      // shard's rows of every column, then a transpose on the device
+      T* tmp = nullptr;
+      KM_CUDA(cudaMalloc(&tmp, r * cols * sizeof(T)));
+      KM_CUDA(cudaMemcpy2DAsync(tmp, r * sizeof(T), X + off, rows * sizeof(T), r * sizeof(T), cols,
+                                cudaMemcpyHostToDevice, s.stream));
+      dim3 grid((unsigned)((r + 31) / 32), (unsigned)((cols + 31) / 32));
+      transpose_cm_kernel<T><<<grid, dim3(32, 8), 0, s.stream>>>(tmp, s.X_owned, r, (int)cols);
+      KM_CUDA(cudaGetLastError());
+      KM_CUDA(cudaStreamSynchronize(s.stream));
+      cudaFree(tmp);
+    }
+    KM_TRY(attach_device((int)i, s.X_owned, r, cols, rows));
+    s.row0 = off;
+    off += r;
+  }
+  for (auto& s : shards) {
+    DevGuard gd(s.dev);
+    KM_CUDA(cudaStreamSynchronize(s.stream));
+  }
+  stats.seconds_upload = now_s() - t0;
+  return KM_OK;
+}
+
+template <typename T>
+int Engine<T>::ensure_buffers(int k_) {
+  constexpr int NP = Fixed<T>::NP;
+  for (auto& s : shards) {
+    if (!s.X) KM_FAIL(KM_ESTATE, "no data attached to the handle");
+    DevGuard g(s.dev);
+    if (s.k_cap != k_ || s.d_cap != d) {
+      cudaFree(s.gacc); cudaFree(s.C[0]); cudaFree(s.C[1]); cudaFree(s.cnorm);
+      cudaFree(s.shift_k); cudaFree(s.empties);
+      s.gacc = nullptr; s.C[0] = s.C[1] = nullptr; s.cnorm = nullptr; s.shift_k = nullptr; s.empties = nullptr;
+      size_t kd = (size_t)k_ * d;
+      KM_CUDA(cudaMalloc(&s.gacc, ((size_t)(NP / 2) * kd + k_) * sizeof(long long)));
+      KM_CUDA(cudaMalloc(&s.C[0], kd * sizeof(T)));
+      KM_CUDA(cudaMalloc(&s.C[1], kd * sizeof(T)));
+      KM_CUDA(cudaMalloc(&s.cnorm, k_ * sizeof(T)));
+      KM_CUDA(cudaMalloc(&s.shift_k, k_ * sizeof(double)));
+      KM_CUDA(cudaMalloc(&s.empties, k_ * sizeof(int)));
+      s.k_cap = k_;
+      s.d_cap = d;
+    }
+  }
+  return KM_OK;
+}
+
+// max |x| over all ranks (sets the fixed-point scale) and the finiteness check
+// the wrapper's do_checks performs on the host
+// (src/interface_py/h2o4gpu/solvers/utils.py:144-158).
+template <typename T>
+int Engine<T>::check_data() {
+  bool all = true;
+  for (auto& s : shards) all = all && s.x_checked;
+  if (all) return KM_OK;
+  constexpr int V = VecOf<T>::N;
+  for (auto& s : shards) {
+    DevGuard g(s.dev);
+    KM_CUDA(cudaMemsetAsync(s.xstat, 0, 2 * sizeof(double), s.stream));
+    size_t count = s.rows * (size_t)d;
+    int grid = s.num_sms * 8;
+    if ((reinterpret_cast<uintptr_t>(s.X) & 15) == 0)
+      absmax_kernel<T, V><<<grid, 256, 0, s.stream>>>(s.X, count, s.xstat, reinterpret_cast<int*>(s.xstat + 1));
+    else
+      absmax_kernel<T, 1><<<grid, 256, 0, s.stream>>>(s.X, count, s.xstat, reinterpret_cast<int*>(s.xstat + 1));
+    KM_CUDA(cudaGetLastError());
+    ++launches;
+  }
+  if (world_size > 1) {
+    NcclApi* api = NcclApi::get();
+    KM_NCCL(api, api->GroupStart());
+    for (auto& s : shards) {
+      // both words are non-negative: max as doubles is right for the max and for the flag
+      KM_NCCL(api, api->AllReduce(s.xstat, s.xstat, 2, ncclDouble, ncclMax, s.comm, s.stream));
+    }
+    KM_NCCL(api, api->GroupEnd());
+  }
+  for (auto& s : shards) {
+    DevGuard g(s.dev);
+    double h[2];
+    KM_CUDA(cudaMemcpyAsync(h, s.xstat, sizeof(h), cudaMemcpyDeviceToHost, s.stream));
+    KM_CUDA(cudaStreamSynchronize(s.stream));
+    long long flag;
+    std::memcpy(&flag, &h[1], sizeof(flag));
+    if (flag != 0 || !(h[0] <= 1.7e308)) KM_FAIL(KM_ENONFINITE, "input data contains NaN or Inf");
+    s.xmax = h[0];
+    s.x_checked = true;
+  }
+  return KM_OK;
+}
+
+template <typename T>
+int Engine<T>::set_centroids(int k_, const T* host_c) {
+  if (k_ < 1 || !host_c) KM_FAIL(KM_EINVAL, "kmeans_set_centroids: bad argument");
+  if (d == 0) KM_FAIL(KM_ESTATE, "kmeans_set_centroids: attach data first (defines cols)");
+  for (size_t i = 0; i < (size_t)k_ * d; ++i)
+    if (!std::isfinite((double)host_c[i])) KM_FAIL(KM_ENONFINITE, "centroids contain NaN or Inf");
+  KM_TRY(ensure_buffers(k_));
+  k = k_;
+  cur = 0;
+  for (auto& s : shards) {
+    DevGuard g(s.dev);
+    KM_CUDA(cudaMemcpyAsync(s.C[0], host_c, (size_t)k * d * sizeof(T), cudaMemcpyHostToDevice, s.stream));
+    cnorm_kernel<T><<<k, 128, 0, s.stream>>>(s.C[0], k, d, s.cnorm);
+    KM_CUDA(cudaGetLastError());
+    ++launches;
+    // host_c may be freed by the caller right after this returns
+    KM_CUDA(cudaStreamSynchronize(s.stream));
+  }
+  have_centroids = true;
+  return KM_OK;
+}
+
+// ---- kernel dispatch -----------------------------------------------------------
+template <typename T, int BM, int BN, int BK, int TM, int TN>
+static int launch_tile_cfg(const T* X, size_t n, int d, const T* C, int k, const T* cnorm, int* labels,
+                           IterState* st, T* out, size_t ld_out, int mode, bool vec, cudaStream_t stream) {
+  constexpr int V = VecOf<T>::N;
+  constexpr int NT = (BM / TM) * (BN / TN);
+  size_t grid = (n + BM - 1) / BM;
+  if (grid > 0x7fffffffULL) KM_FAIL(KM_EINVAL, "shard too large for one launch");
+  if (mode == MODE_ASSIGN) {
+    if (vec) tile_kernel<T, BM, BN, BK, TM, TN, V, MODE_ASSIGN><<<(unsigned)grid, NT, 0, stream>>>(X, n, d, C, k, cnorm, labels, st, out, ld_out);
+    else tile_kernel<T, BM, BN, BK, TM, TN, 1, MODE_ASSIGN><<<(unsigned)grid, NT, 0, stream>>>(X, n, d, C, k, cnorm, labels, st, out, ld_out);
+  } else {
+    if (vec) tile_kernel<T, BM, BN, BK, TM, TN, V, MODE_TRANSFORM><<<(unsigned)grid, NT, 0, stream>>>(X, n, d, C, k, cnorm, labels, st, out, ld_out);
+    else tile_kernel<T, BM, BN, BK, TM, TN, 1, MODE_TRANSFORM><<<(unsigned)grid, NT, 0, stream>>>(X, n, d, C, k, cnorm, labels, st, out, ld_out);
+  }
+  KM_CUDA(cudaGetLastError());
+  return KM_OK;
+}
+
+template <typename T> struct TileCfg;
+template <> struct TileCfg<float> {
+  static int go(const float* X, size_t n, int d, const float* C, int k, const float* cn, int* lab, IterState* st,
+                float* out, size_t ld, int mode, bool vec, cudaStream_t s) {
+    if (k <= 64) return launch_tile_cfg<float, 128, 64, 16, 8, 4>(X, n, d, C, k, cn, lab, st, out, ld, mode, vec, s);
+    return launch_tile_cfg<float, 128, 128, 16, 8, 8>(X, n, d, C, k, cn, lab, st, out, ld, mode, vec, s);
+  }
+};
+template <> struct TileCfg<double> {
+  static int go(const double* X, size_t n, int d, const double* C, int k, const double* cn, int* lab, IterState* st,
+                double* out, size_t ld, int mode, bool vec, cudaStream_t s) {
+    return launch_tile_cfg<double, 64, 64, 16, 4, 4>(X, n, d, C, k, cn, lab, st, out, ld, mode, vec, s);
+  }
+};
+
+template <typename T>
+int Engine<T>::launch_tiles(Shard<T>& s, const T* Xp, size_t nrows, int* labels, int mode, T* out,
+                            size_t ld_out, bool count_changes) {
+  bool vec = (d % VecOf<T>::N == 0) && ((reinterpret_cast<uintptr_t>(Xp) & 15) == 0);
+  ++launches;
+  return TileCfg<T>::go(Xp, nrows, d, s.C[cur], k, s.cnorm, labels, count_changes ? s.st : nullptr, out, ld_out,
+                        mode, vec, s.stream);
+}
+
+template <typename T, int V>
+using SmallKFn = void (*)(const T*, size_t, int, const T*, int, const T*, int*, IterState*, long long*,
+                          unsigned long long*, T, int, unsigned int);
+
+template <typename T, int V>
+static SmallKFn<T, V> smallk_pick(int k, int* K) {
+#define KM_PICK(KK) if (k <= KK) { *K = KK; return smallk_kernel<T, KK, V>; }
+  KM_PICK(1) KM_PICK(2) KM_PICK(3) KM_PICK(4) KM_PICK(5) KM_PICK(6) KM_PICK(8) KM_PICK(10) KM_PICK(12)
+#undef KM_PICK
+  *K = 16;
+  return smallk_kernel<T, 16, V>;
+}
+inline int smallk_bound(int k) {
+  const int ks[] = {1, 2, 3, 4, 5, 6, 8, 10, 12, 16};
+  for (int v : ks) if (k <= v) return v;
+  return 16;
+}
+
+template <typename T>
+bool Engine<T>::smallk_ok(bool update) const {
+  if (k > 16) return false;
+  return smallk_smem_bytes<T>(smallk_bound(k), d, update) <= kMaxDynSmem;
+}
+
+template <typename T>
+int Engine<T>::launch_smallk(Shard<T>& s, bool update, T scale) {
+  constexpr int V = VecOf<T>::N;
+  int K = 0;
+  bool vec = vec_ok(s);
+  size_t smem;
+  // rows per CTA: enough CTAs to fill the GPU twice over, never more rows than
+  // the int32 accumulators can hold
+  size_t target = (size_t)s.num_sms * 4;
+  size_t rpc = (s.rows + target - 1) / target;
+  rpc = std::max<size_t>(rpc, 512);
+  rpc = std::min<size_t>(rpc, kFlushRows);
+  size_t grid = (s.rows + rpc - 1) / rpc;
+  cudaError_t e;
+  if (vec) {
+    auto fn = smallk_pick<T, V>(k, &K);
+    smem = smallk_smem_bytes<T>(K, d, update);
+    e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) KM_CUDA(e);
+    fn<<<(unsigned)grid, kSmallKThreads, smem, s.stream>>>(s.X, s.rows, d, s.C[cur], k, s.cnorm, s.labels, s.st,
+                                                          s.sums(), s.counts(k, d), scale, update ? 1 : 0,
+                                                          (unsigned)rpc);
+  } else {
+    auto fn = smallk_pick<T, 1>(k, &K);
+    smem = smallk_smem_bytes<T>(K, d, update);
+    e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) KM_CUDA(e);
+    fn<<<(unsigned)grid, kSmallKThreads, smem, s.stream>>>(s.X, s.rows, d, s.C[cur], k, s.cnorm, s.labels, s.st,
+                                                          s.sums(), s.counts(k, d), scale, update ? 1 : 0,
+                                                          (unsigned)rpc);
+  }
+  KM_CUDA(cudaGetLastError());
+  ++launches;
+  return KM_OK;
+}
+
+template <typename T>
+int Engine<T>::launch_accumulate(Shard<T>& s, T scale) {
+  constexpr int V = VecOf<T>::N;
+  constexpr int NP = Fixed<T>::NP;
+  const size_t per_cluster = (size_t)NP * d * sizeof(int) + sizeof(int);
+  const size_t budget = 200 * 1024;
+  if (per_cluster + 16 > budget) KM_FAIL(KM_EINVAL, "cols too large for the centroid-sum kernel");
+  int kc_max = (int)((budget - 16) / per_cluster);
+  int n_slices = (k + kc_max - 1) / kc_max;
+  int kc = (k + n_slices - 1) / n_slices;
+  size_t smem = accumulate_smem_bytes<T>(kc, d);
+  int per_sm = (int)std::max<size_t>(1, std::min<size_t>(4, kMaxDynSmem / (smem + 1024)));
+  size_t target = (size_t)s.num_sms * per_sm;
+  size_t rpp = (s.rows + target - 1) / target;
+  rpp = std::max<size_t>(rpp, 1024);
+  rpp = std::min<size_t>(rpp, kFlushRows);
+  size_t parts = (s.rows + rpp - 1) / rpp;
+  size_t grid = parts * n_slices;
+  if (grid > 0x7fffffffULL) KM_FAIL(KM_EINVAL, "shard too large for one launch");
+  bool vec = vec_ok(s);
+  int dv = vec ? d / V : d;
+  if ((unsigned long long)rpp * dv * dv >= (1ULL << 40)) KM_FAIL(KM_EINVAL, "cols too large for the centroid-sum kernel");
+  unsigned long long magic = fastdiv_magic((unsigned)dv);
+  if (vec) {
+    KM_CUDA(cudaFuncSetAttribute(accumulate_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    accumulate_kernel<T, V><<<(unsigned)grid, kAccThreads, smem, s.stream>>>(
+        s.X, s.rows, d, s.labels, k, kc, n_slices, s.sums(), s.counts(k, d), scale, (unsigned)rpp, magic);
+  } else {
+    KM_CUDA(cudaFuncSetAttribute(accumulate_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    accumulate_kernel<T, 1><<<(unsigned)grid, kAccThreads, smem, s.stream>>>(
+        s.X, s.rows, d, s.labels, k, kc, n_slices, s.sums(), s.counts(k, d), scale, (unsigned)rpp, magic);
+  }
+  KM_CUDA(cudaGetLastError());
+  ++launches;
+  return KM_OK;
+}
+
+template <typename T>
+int Engine<T>::allreduce_acc() {
+  if (world_size <= 1) return KM_OK;
+  NcclApi* api = NcclApi::get();
+  KM_NCCL(api, api->GroupStart());
+  for (auto& s : shards)
+    KM_NCCL(api, api->AllReduce(s.gacc, s.gacc, s.gacc_count(k, d), ncclInt64, ncclSum, s.comm, s.stream));
+  KM_NCCL(api, api->GroupEnd());
+  return KM_OK;
+}
+
+}  // namespace km

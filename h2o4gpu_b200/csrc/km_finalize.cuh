@@ -1,0 +1,469 @@
+// The small kernels that close an M-step: empty-cluster bookkeeping and
+// relocation, averaging, norms, shift.  Replaces revert_zeroed_centroids /
+// scale_centroids (src/gpu/kmeans/kmeans_centroids.h:77-105), the host-staged
+// multi-GPU divide (src/gpu/kmeans/kmeans_impl.h:140-188), self_dots on the
+// centroids (src/gpu/kmeans/kmeans_labels.h:187-214) and the inner_product
+// convergence test (kmeans_impl.h:191-208).  The empty-cluster rule is the CPU
+// path's (relocate to the farthest points; a cluster still empty copies the
+// largest cluster), not the GPU reference's keep-the-old-centroid rule.
+#pragma once
+
+#include <cooperative_groups.h>
+
+#include "km_common.cuh"
+#include "km_tiles.cuh"
+
+namespace km {
+
+namespace cg = cooperative_groups;
+
+// ---- max |x| and finiteness of a shard (once per upload) ----------------------
+template <typename T, int V>
+__global__ void __launch_bounds__(256)
+absmax_kernel(const T* __restrict__ X, size_t count, double* __restrict__ out_max,
+              int* __restrict__ out_nonfinite) {
+  __shared__ double smax[8];
+  double m = 0;
+  int bad = 0;
+  const size_t nv = count / V;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv;
+       i += (size_t)gridDim.x * blockDim.x) {
+    T x[V];
+    VecLoad<T, V>::ld(X + i * V, x);
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      double a = fabs((double)x[e]);
+      bad |= !(a <= 1.7976931348623157e308);
+      m = fmax(m, a);
+    }
+  }
+  // tail (count % V) handled by block 0
+  if (blockIdx.x == 0 && threadIdx.x < (count % V)) {
+    double a = fabs((double)X[nv * V + threadIdx.x]);
+    bad |= !(a <= 1.7976931348623157e308);
+    m = fmax(m, a);
+  }
+  m = warp_max(m);
+  bad = __any_sync(0xffffffffu, bad);
+  if ((threadIdx.x & 31) == 0) smax[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    m = (threadIdx.x < 8) ? smax[threadIdx.x] : 0.0;
+    m = warp_max(m);
+    if (threadIdx.x == 0) {
+      // order-independent: max of non-negative doubles compared as integers
+      atomicMax(reinterpret_cast<unsigned long long*>(out_max), (unsigned long long)__double_as_longlong(m));
+    }
+  }
+  if (bad && (threadIdx.x & 31) == 0) atomicOr(out_nonfinite, 1);
+}
+
+// ---- |c|^2 of a centroid table -------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+cnorm_kernel(const T* __restrict__ C, int k, int d, T* __restrict__ cnorm) {
+  __shared__ double red[4];
+  int j = blockIdx.x;
+  double s = 0;
+  for (int t = threadIdx.x; t < d; t += blockDim.x) {
+    double v = (double)C[(size_t)j * d + t];
+    s += v * v;
+  }
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) cnorm[j] = (T)(red[0] + red[1] + red[2] + red[3]);
+}
+
+// ---- per-iteration bookkeeping: empties, largest cluster ----------------------
+// `empties` receives the ids of the empty clusters in ascending order.
+__global__ void __launch_bounds__(256)
+prepare_kernel(const unsigned long long* __restrict__ gcounts, int k, IterState* st,
+               int* __restrict__ empties, int* __restrict__ host_n_empty) {
+  __shared__ int s_n;
+  __shared__ unsigned long long s_best[256];
+  __shared__ int s_idx[256];
+  if (threadIdx.x == 0) s_n = 0;
+  __syncthreads();
+  unsigned long long best = 0;
+  int bi = 0x7fffffff;
+  int local = 0;
+  for (int j = threadIdx.x; j < k; j += 256) {
+    unsigned long long c = gcounts[j];
+    if (c == 0) ++local;
+    if (c > best || (c == best && j < bi)) { best = c; bi = j; }
+  }
+  if (local) atomicAdd(&s_n, local);
+  s_best[threadIdx.x] = best;
+  s_idx[threadIdx.x] = bi;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int t = 1; t < 256; ++t)
+      if (s_best[t] > best || (s_best[t] == best && s_idx[t] < bi)) { best = s_best[t]; bi = s_idx[t]; }
+    st->argmax_count = bi;
+    st->n_empty = s_n;
+    st->relocated = 0;
+    if (host_n_empty) *host_n_empty = s_n;
+    if (s_n) {
+      int e = 0;
+      for (int j = 0; j < k; ++j)
+        if (gcounts[j] == 0) empties[e++] = j;
+    }
+  }
+}
+
+// ---- squared distance of every row to its assigned (old) centre ---------------
+// Direct differences in double.  Runs only when the M-step found empty clusters.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rowdist_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict__ labels,
+               const T* __restrict__ C_old, double* __restrict__ dist, const IterState* st,
+               int force) {
+  if (!force && st->n_empty == 0) return;
+  const int lane = threadIdx.x & 31;
+  const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const size_t nwarp = ((size_t)gridDim.x * blockDim.x) >> 5;
+  for (size_t row = warp; row < n; row += nwarp) {
+    const T* x = X + row * (size_t)d;
+    const T* c = C_old + (size_t)labels[row] * d;
+    double s = 0;
+    for (int t = lane; t < d; t += 32) {
+      double q = (double)x[t] - (double)c[t];
+      s += q * q;
+    }
+    s = warp_sum(s);
+    if (lane == 0) dist[row] = s;
+  }
+}
+
+// Sum of dist (inertia), deterministic two-stage tree: per-CTA partials then CTA 0.
+__global__ void __launch_bounds__(256)
+sum_partials_kernel(const double* __restrict__ v, size_t n, double* __restrict__ partials) {
+  __shared__ double red[8];
+  double s = 0;
+  for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) s += v[i];
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0;
+    for (int w = 0; w < 8; ++w) t += red[w];
+    partials[blockIdx.x] = t;
+  }
+}
+__global__ void sum_final_kernel(const double* __restrict__ partials, int m, double* out) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    double t = 0;
+    for (int i = 0; i < m; ++i) t += partials[i];
+    *out = t;
+  }
+}
+
+// ---- relocation of empty clusters (cooperative launch, single shard) ----------
+// For each empty cluster, lowest id first: take the remaining row with the
+// largest distance to its assigned centre (ties: lowest row), remove it from its
+// donor's sums and make it the sole member of the empty cluster.  Nothing moves
+// when the largest distance is zero.  `cand_*` hold one candidate per CTA.
+template <typename T>
+__global__ void __launch_bounds__(256)
+relocate_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict__ labels, int k,
+                double* __restrict__ dist, long long* __restrict__ gsums,
+                unsigned long long* __restrict__ gcounts, const int* __restrict__ empties,
+                IterState* st, double* __restrict__ cand_val, unsigned long long* __restrict__ cand_row,
+                T scale) {
+  constexpr int NP = Fixed<T>::NP;
+  const int E = st->n_empty;
+  if (E == 0) return;
+  cg::grid_group grid = cg::this_grid();
+  __shared__ double s_v[256];
+  __shared__ unsigned long long s_r[256];
+  const size_t per = (n + gridDim.x - 1) / gridDim.x;
+  const size_t b0 = (size_t)blockIdx.x * per;
+  const size_t b1 = (b0 + per < n) ? b0 + per : n;
+
+  for (int e = 0; e < E; ++e) {
+    double bv = -1.0;
+    unsigned long long br = ~0ULL;
+    for (size_t i = b0 + threadIdx.x; i < b1; i += 256) {
+      double v = dist[i];
+      if (v > bv) { bv = v; br = i; }  // ascending i: first maximum kept
+    }
+    s_v[threadIdx.x] = bv;
+    s_r[threadIdx.x] = br;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+      if (threadIdx.x < o) {
+        double ov = s_v[threadIdx.x + o];
+        unsigned long long orow = s_r[threadIdx.x + o];
+        if (ov > s_v[threadIdx.x] || (ov == s_v[threadIdx.x] && orow < s_r[threadIdx.x])) {
+          s_v[threadIdx.x] = ov;
+          s_r[threadIdx.x] = orow;
+        }
+      }
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) { cand_val[blockIdx.x] = s_v[0]; cand_row[blockIdx.x] = s_r[0]; }
+    grid.sync();
+    // every CTA takes the same decision from the candidate table
+    bv = -1.0;
+    br = ~0ULL;
+    for (unsigned int c = threadIdx.x; c < gridDim.x; c += 256) {
+      double v = cand_val[c];
+      unsigned long long r = cand_row[c];
+      if (v > bv || (v == bv && r < br)) { bv = v; br = r; }
+    }
+    s_v[threadIdx.x] = bv;
+    s_r[threadIdx.x] = br;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+      if (threadIdx.x < o) {
+        double ov = s_v[threadIdx.x + o];
+        unsigned long long orow = s_r[threadIdx.x + o];
+        if (ov > s_v[threadIdx.x] || (ov == s_v[threadIdx.x] && orow < s_r[threadIdx.x])) {
+          s_v[threadIdx.x] = ov;
+          s_r[threadIdx.x] = orow;
+        }
+      }
+      __syncthreads();
+    }
+    bv = s_v[0];
+    br = s_r[0];
+    __syncthreads();
+    bool stop = (bv < 0.0) || (e == 0 && bv == 0.0);
+    if (stop) break;  // uniform over the grid
+    if (blockIdx.x == 0) {
+      const int cid = empties[e];
+      const int old = labels[br];
+      const T* x = X + (size_t)br * d;
+      for (int t = threadIdx.x; t < d; t += 256) {
+        int p[NP];
+        split_pieces<NP>(x[t], scale, p);
+#pragma unroll
+        for (int q = 0; q < NP / 2; ++q) {
+          long long v = (long long)p[2 * q] * (1LL << kPieceBits) + (long long)p[2 * q + 1];
+          gsums[(size_t)q * k * d + (size_t)old * d + t] -= v;
+          gsums[(size_t)q * k * d + (size_t)cid * d + t] = v;
+        }
+      }
+      if (threadIdx.x == 0) {
+        gcounts[cid] = 1;
+        gcounts[old] -= 1;
+        dist[br] = -2.0;
+        st->relocated += 1;
+      }
+    }
+    grid.sync();
+  }
+}
+
+// ---- averaging, norms and per-cluster shift ------------------------------------
+// One CTA per cluster.  inv = 2^-(sa+15) turns the int64 pairs back into sums.
+// A cluster without members copies the largest cluster's row as the CPU path
+// leaves it at that moment: already averaged if its id is lower, raw sums if not.
+template <typename T>
+__global__ void __launch_bounds__(128)
+average_kernel(const long long* __restrict__ gsums, const unsigned long long* __restrict__ gcounts,
+               int k, int d, double inv, const T* __restrict__ C_old, T* __restrict__ C_new,
+               T* __restrict__ cnorm, double* __restrict__ shift_k, const IterState* st) {
+  constexpr int NP = Fixed<T>::NP;
+  __shared__ double red_n[4], red_s[4];
+  const int j = blockIdx.x;
+  unsigned long long cnt = gcounts[j];
+  int src = j;
+  double a;
+  if (cnt > 0) {
+    a = 1.0 / (double)cnt;
+  } else {
+    src = st->argmax_count;
+    unsigned long long cb = gcounts[src];
+    a = (src < j && cb > 0) ? 1.0 / (double)cb : 1.0;
+  }
+  double sn = 0, ss = 0;
+  for (int t = threadIdx.x; t < d; t += blockDim.x) {
+    long long g[NP / 2];
+#pragma unroll
+    for (int q = 0; q < NP / 2; ++q) g[q] = gsums[(size_t)q * k * d + (size_t)src * d + t];
+    T v = (T)(fixed_to_double<NP>(g, inv) * a);
+    C_new[(size_t)j * d + t] = v;
+    double dv = (double)v;
+    double df = dv - (double)C_old[(size_t)j * d + t];
+    sn += dv * dv;
+    ss += df * df;
+  }
+  sn = warp_sum(sn);
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) { red_n[threadIdx.x >> 5] = sn; red_s[threadIdx.x >> 5] = ss; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    cnorm[j] = (T)(red_n[0] + red_n[1] + red_n[2] + red_n[3]);
+    shift_k[j] = red_s[0] + red_s[1] + red_s[2] + red_s[3];
+  }
+}
+
+// Sums the per-cluster shifts in a fixed order, logs the iteration and re-arms
+// the label-change counter.
+__global__ void __launch_bounds__(256)
+iter_close_kernel(const double* __restrict__ shift_k, int k, IterState* st, double* __restrict__ shift_log,
+                  unsigned long long* __restrict__ changed_log, int* __restrict__ reloc_log, int it,
+                  double* __restrict__ host_shift, unsigned long long* __restrict__ host_changed) {
+  __shared__ double red[256];
+  double s = 0;
+  for (int j = threadIdx.x; j < k; j += 256) s += shift_k[j];
+  red[threadIdx.x] = s;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    st->shift_sq = red[0];
+    shift_log[it] = red[0];
+    changed_log[it] = st->changed;
+    reloc_log[it] = st->relocated;
+    if (host_shift) { *host_shift = red[0]; *host_changed = st->changed; }
+    st->changed = 0;
+  }
+}
+
+}  // namespace km
+
+namespace km {
+
+// ---- relocation across several shards / ranks ----------------------------------
+// Each shard lists its E farthest rows (descending distance, ties lowest row) as
+// one packed record: [E double val][E u64 id][E i64 label][E*d T row].  The
+// records of all ranks are all-gathered and every rank applies the same E-way
+// choice to its (already all-reduced, hence identical) sums.
+template <typename T>
+__global__ void __launch_bounds__(256)
+select_far_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict__ labels,
+                  double* __restrict__ dist, int E, unsigned long long id_base,
+                  double* __restrict__ cand_val, unsigned long long* __restrict__ cand_row,
+                  unsigned char* __restrict__ rec) {
+  cg::grid_group grid = cg::this_grid();
+  __shared__ double s_v[256];
+  __shared__ unsigned long long s_r[256];
+  double* r_val = reinterpret_cast<double*>(rec);
+  unsigned long long* r_id = reinterpret_cast<unsigned long long*>(rec + (size_t)E * 8);
+  long long* r_lab = reinterpret_cast<long long*>(rec + (size_t)E * 16);
+  T* r_vec = reinterpret_cast<T*>(rec + (size_t)E * 24);
+  const size_t per = (n + gridDim.x - 1) / gridDim.x;
+  const size_t b0 = (size_t)blockIdx.x * per;
+  const size_t b1 = (b0 + per < n) ? b0 + per : n;
+  for (int e = 0; e < E; ++e) {
+    double bv = -1.0;
+    unsigned long long br = ~0ULL;
+    for (size_t i = b0 + threadIdx.x; i < b1; i += 256) {
+      double v = dist[i];
+      if (v > bv) { bv = v; br = i; }
+    }
+    s_v[threadIdx.x] = bv;
+    s_r[threadIdx.x] = br;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+      if (threadIdx.x < o) {
+        double ov = s_v[threadIdx.x + o];
+        unsigned long long orow = s_r[threadIdx.x + o];
+        if (ov > s_v[threadIdx.x] || (ov == s_v[threadIdx.x] && orow < s_r[threadIdx.x])) {
+          s_v[threadIdx.x] = ov;
+          s_r[threadIdx.x] = orow;
+        }
+      }
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) { cand_val[blockIdx.x] = s_v[0]; cand_row[blockIdx.x] = s_r[0]; }
+    grid.sync();
+    if (blockIdx.x == 0) {
+      bv = -1.0;
+      br = ~0ULL;
+      for (unsigned int c = threadIdx.x; c < gridDim.x; c += 256) {
+        double v = cand_val[c];
+        unsigned long long r = cand_row[c];
+        if (v > bv || (v == bv && r < br)) { bv = v; br = r; }
+      }
+      s_v[threadIdx.x] = bv;
+      s_r[threadIdx.x] = br;
+      __syncthreads();
+      for (int o = 128; o > 0; o >>= 1) {
+        if (threadIdx.x < o) {
+          double ov = s_v[threadIdx.x + o];
+          unsigned long long orow = s_r[threadIdx.x + o];
+          if (ov > s_v[threadIdx.x] || (ov == s_v[threadIdx.x] && orow < s_r[threadIdx.x])) {
+            s_v[threadIdx.x] = ov;
+            s_r[threadIdx.x] = orow;
+          }
+        }
+        __syncthreads();
+      }
+      bv = s_v[0];
+      br = s_r[0];
+      __syncthreads();
+      const bool have = (bv >= 0.0) && (br != ~0ULL);
+      if (threadIdx.x == 0) {
+        r_val[e] = have ? bv : -1.0;
+        r_id[e] = have ? (id_base + br) : ~0ULL;
+        r_lab[e] = have ? (long long)labels[br] : -1;
+        if (have) dist[br] = -2.0;
+      }
+      for (int t = threadIdx.x; t < d; t += 256) r_vec[(size_t)e * d + t] = have ? X[(size_t)br * d + t] : (T)0;
+    }
+    grid.sync();
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+apply_far_kernel(const unsigned char* __restrict__ rec_all, int world, int E, size_t rec_bytes, int k, int d,
+                 long long* __restrict__ gsums, unsigned long long* __restrict__ gcounts,
+                 const int* __restrict__ empties, IterState* st, T scale) {
+  constexpr int NP = Fixed<T>::NP;
+  __shared__ int head[64];
+  __shared__ int s_w;
+  __shared__ int s_stop;
+  if (threadIdx.x < 64) head[threadIdx.x] = 0;
+  __syncthreads();
+  for (int e = 0; e < E; ++e) {
+    if (threadIdx.x == 0) {
+      double bv = -1.0;
+      unsigned long long bid = ~0ULL;
+      int bw = -1;
+      for (int w = 0; w < world; ++w) {
+        if (head[w] >= E) continue;
+        const unsigned char* rec = rec_all + (size_t)w * rec_bytes;
+        double v = reinterpret_cast<const double*>(rec)[head[w]];
+        unsigned long long id = reinterpret_cast<const unsigned long long*>(rec + (size_t)E * 8)[head[w]];
+        if (v > bv || (v == bv && id < bid)) { bv = v; bid = id; bw = w; }
+      }
+      s_w = bw;
+      s_stop = (bw < 0) || (bv < 0.0) || (e == 0 && bv == 0.0);
+    }
+    __syncthreads();
+    if (s_stop) break;
+    const int w = s_w;
+    const unsigned char* rec = rec_all + (size_t)w * rec_bytes;
+    const int h = head[w];
+    const int old = (int)reinterpret_cast<const long long*>(rec + (size_t)E * 16)[h];
+    const T* x = reinterpret_cast<const T*>(rec + (size_t)E * 24) + (size_t)h * d;
+    const int cid = empties[e];
+    for (int t = threadIdx.x; t < d; t += 256) {
+      int p[NP];
+      split_pieces<NP>(x[t], scale, p);
+#pragma unroll
+      for (int q = 0; q < NP / 2; ++q) {
+        long long v = (long long)p[2 * q] * (1LL << kPieceBits) + (long long)p[2 * q + 1];
+        gsums[(size_t)q * k * d + (size_t)old * d + t] -= v;
+        gsums[(size_t)q * k * d + (size_t)cid * d + t] = v;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      gcounts[cid] = 1;
+      gcounts[old] -= 1;
+      st->relocated += 1;
+      head[w] = h + 1;
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace km

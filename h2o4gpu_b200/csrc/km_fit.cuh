@@ -1,0 +1,351 @@
+// The Lloyd loop and the resident predict / transform / inertia passes.
+#pragma once
+
+#include "km_engine.cuh"
+
+namespace km {
+
+template <typename T>
+static int ensure_dist(Shard<T>& s) {
+  if (s.dist_cap < s.rows) {
+    cudaFree(s.dist);
+    s.dist = nullptr;
+    KM_CUDA(cudaMalloc(&s.dist, s.rows * sizeof(double)));
+    s.dist_cap = s.rows;
+  }
+  return KM_OK;
+}
+
+template <typename T>
+static int ensure_logs(Shard<T>& s, int n) {
+  if (s.log_cap < n) {
+    cudaFree(s.shift_log); cudaFree(s.changed_log); cudaFree(s.reloc_log);
+    s.shift_log = nullptr; s.changed_log = nullptr; s.reloc_log = nullptr;
+    KM_CUDA(cudaMalloc(&s.shift_log, n * sizeof(double)));
+    KM_CUDA(cudaMalloc(&s.changed_log, n * sizeof(unsigned long long)));
+    KM_CUDA(cudaMalloc(&s.reloc_log, n * sizeof(int)));
+    s.log_cap = n;
+  }
+  return KM_OK;
+}
+
+// E-step on every local shard with the current centroids (final pass of fit,
+// predict).  Labels change counters are not touched.
+template <typename T>
+int Engine<T>::assign_all(int flags) {
+  if (!have_centroids) KM_FAIL(KM_ESTATE, "no centroids set");
+  for (auto& s : shards) {
+    if (!s.X) KM_FAIL(KM_ESTATE, "no data attached to the handle");
+    DevGuard g(s.dev);
+    if (smallk_ok(false) && !(flags & KM_FIT_FORCE_SPLIT)) {
+      IterState* keep = s.st;
+      s.st = nullptr;
+      int rc = launch_smallk(s, false, (T)1);
+      s.st = keep;
+      KM_TRY(rc);
+    } else {
+      KM_TRY(launch_tiles(s, s.X, s.rows, s.labels, MODE_ASSIGN, nullptr, 0, false));
+    }
+  }
+  return KM_OK;
+}
+
+template <typename T>
+int Engine<T>::relocate_multi(double scale) {
+  NcclApi* api = NcclApi::get();
+  const size_t g = shards.size();
+  std::vector<int> E(g, 0);
+  for (size_t i = 0; i < g; ++i) {
+    Shard<T>& s = shards[i];
+    DevGuard gd(s.dev);
+    KM_CUDA(cudaStreamSynchronize(s.stream));
+    E[i] = *reinterpret_cast<volatile int*>(&s.host_pin[2]);
+  }
+  for (size_t i = 1; i < g; ++i)
+    if (E[i] != E[0]) KM_FAIL(KM_ESTATE, "shards disagree on the number of empty clusters");
+  const int ne = E[0];
+  if (ne == 0) return KM_OK;
+  const size_t rec_bytes = (size_t)ne * 24 + (size_t)ne * d * sizeof(T);
+  std::vector<unsigned char*> rec(g, nullptr), all(g, nullptr);
+  for (size_t i = 0; i < g; ++i) {
+    Shard<T>& s = shards[i];
+    DevGuard gd(s.dev);
+    KM_TRY(ensure_dist(s));
+    KM_CUDA(cudaMalloc(&rec[i], rec_bytes));
+    KM_CUDA(cudaMalloc(&all[i], rec_bytes * world_size));
+    rowdist_kernel<T><<<s.num_sms * 8, 256, 0, s.stream>>>(s.X, s.rows, d, s.labels, s.C[cur], s.dist, s.st, 1);
+    KM_CUDA(cudaGetLastError());
+    const T* Xp = s.X;
+    size_t n = s.rows;
+    int dd = d;
+    const int* lab = s.labels;
+    double* dist = s.dist;
+    int ee = ne;
+    unsigned long long id_base = (unsigned long long)(world_rank0 + (int)i) << 40;
+    double* cv = s.cand_val;
+    unsigned long long* cr = s.cand_row;
+    unsigned char* rp = rec[i];
+    void* args[] = {&Xp, &n, &dd, &lab, &dist, &ee, &id_base, &cv, &cr, &rp};
+    KM_CUDA(cudaLaunchCooperativeKernel((void*)select_far_kernel<T>, dim3(s.num_sms), dim3(256), args, 0, s.stream));
+    launches += 2;
+  }
+  KM_NCCL(api, api->GroupStart());
+  for (size_t i = 0; i < g; ++i)
+    KM_NCCL(api, api->AllGather(rec[i], all[i], rec_bytes, ncclChar, shards[i].comm, shards[i].stream));
+  KM_NCCL(api, api->GroupEnd());
+  for (size_t i = 0; i < g; ++i) {
+    Shard<T>& s = shards[i];
+    DevGuard gd(s.dev);
+    apply_far_kernel<T><<<1, 256, 0, s.stream>>>(all[i], world_size, ne, rec_bytes, k, d, s.sums(), s.counts(k, d),
+                                                 s.empties, s.st, (T)scale);
+    KM_CUDA(cudaGetLastError());
+    ++launches;
+    KM_CUDA(cudaStreamSynchronize(s.stream));
+    cudaFree(rec[i]);
+    cudaFree(all[i]);
+  }
+  return KM_OK;
+}
+
+template <typename T>
+int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int flags) {
+  if (k_ < 1 || max_iter < 0 || !init) KM_FAIL(KM_EINVAL, "kmeans_fit_resident: bad argument");
+  if (shards.empty() || !shards[0].X) KM_FAIL(KM_ESTATE, "kmeans_fit_resident: no data attached");
+  if (world_size > 64) KM_FAIL(KM_EINVAL, "at most 64 ranks");
+  const double t_start = now_s();
+  launches = 0;
+  KM_TRY(check_data());
+  KM_TRY(set_centroids(k_, init));
+
+  // fixed-point scale from the global max |x|: xmax < 2^e, first piece <= 2^15
+  double xmax = 0;
+  for (auto& s : shards) xmax = std::max(xmax, s.xmax);
+  int e = 0;
+  if (xmax > 0) std::frexp(xmax, &e);
+  const int sa = kPieceBits - e;
+  const T scale = (T)std::ldexp(1.0, sa);
+  const double inv = std::ldexp(1.0, -(sa + kPieceBits));
+  if (!std::isfinite((double)scale) || scale == (T)0) KM_FAIL(KM_EINVAL, "data magnitude outside the supported range");
+
+  const bool fused = smallk_ok(true) && !(flags & KM_FIT_FORCE_SPLIT);
+  const bool multi = world_size > 1;
+  const bool check = (threshold > 0) || (flags & KM_FIT_CHECK_EVERY_ITER);
+  stats = kmeans_stats{};
+  stats.path = fused ? 1 : 2;
+  stats.inertia = -1;
+
+  for (auto& s : shards) {
+    DevGuard g(s.dev);
+    KM_TRY(ensure_logs(s, std::max(max_iter, 1)));
+    if (!multi) KM_TRY(ensure_dist(s));
+    KM_CUDA(cudaMemsetAsync(s.st, 0, sizeof(IterState), s.stream));
+    KM_CUDA(cudaMemsetAsync(s.labels, 0xff, s.rows * sizeof(int), s.stream));
+  }
+
+  // events on shard 0: [4*it + 0..3] = start, after E-step, after sums, after close
+  Shard<T>& s0 = shards[0];
+  std::vector<cudaEvent_t> ev((size_t)4 * std::max(max_iter, 1) + 2, nullptr);
+  {
+    DevGuard g(s0.dev);
+    for (auto& x : ev) KM_CUDA(cudaEventCreate(&x));
+  }
+  auto free_events = [&]() {
+    DevGuard g(s0.dev);
+    for (auto& x : ev) if (x) cudaEventDestroy(x);
+  };
+
+  int it = 0;
+  int rc = KM_OK;
+  for (; it < max_iter; ++it) {
+    for (size_t i = 0; i < shards.size() && rc == KM_OK; ++i) {
+      Shard<T>& s = shards[i];
+      DevGuard g(s.dev);
+      if (i == 0) cudaEventRecord(ev[4 * it + 0], s.stream);
+      cudaMemsetAsync(s.gacc, 0, s.gacc_count(k, d) * sizeof(long long), s.stream);
+      if (fused) {
+        rc = launch_smallk(s, true, scale);
+        if (i == 0) { cudaEventRecord(ev[4 * it + 1], s.stream); cudaEventRecord(ev[4 * it + 2], s.stream); }
+      } else {
+        rc = launch_tiles(s, s.X, s.rows, s.labels, MODE_ASSIGN, nullptr, 0, true);
+        if (i == 0) cudaEventRecord(ev[4 * it + 1], s.stream);
+        if (rc == KM_OK) rc = launch_accumulate(s, scale);
+        if (i == 0) cudaEventRecord(ev[4 * it + 2], s.stream);
+      }
+    }
+    if (rc != KM_OK) break;
+    if (multi && (rc = allreduce_acc()) != KM_OK) break;
+    for (size_t i = 0; i < shards.size() && rc == KM_OK; ++i) {
+      Shard<T>& s = shards[i];
+      DevGuard g(s.dev);
+      prepare_kernel<<<1, 256, 0, s.stream>>>(s.counts(k, d), k, s.st, s.empties,
+                                             reinterpret_cast<int*>(&s.host_pin[2]));
+      ++launches;
+      if (!multi) {
+        rowdist_kernel<T><<<s.num_sms * 8, 256, 0, s.stream>>>(s.X, s.rows, d, s.labels, s.C[cur], s.dist, s.st, 0);
+        const T* Xp = s.X;
+        size_t n = s.rows;
+        int dd = d, kk = k;
+        const int* lab = s.labels;
+        double* dist = s.dist;
+        long long* gs = s.sums();
+        unsigned long long* gc = s.counts(k, d);
+        const int* em = s.empties;
+        IterState* st = s.st;
+        double* cv = s.cand_val;
+        unsigned long long* cr = s.cand_row;
+        T sc = scale;
+        void* args[] = {&Xp, &n, &dd, &lab, &kk, &dist, &gs, &gc, &em, &st, &cv, &cr, &sc};
+        cudaError_t ce = cudaLaunchCooperativeKernel((void*)relocate_kernel<T>, dim3(s.num_sms), dim3(256), args, 0,
+                                                     s.stream);
+        if (ce != cudaSuccess) { set_error(std::string("relocate launch: ") + cudaGetErrorString(ce)); rc = KM_ECUDA; }
+        launches += 2;
+      }
+    }
+    if (rc != KM_OK) break;
+    if (multi && (rc = relocate_multi((double)scale)) != KM_OK) break;
+    for (size_t i = 0; i < shards.size() && rc == KM_OK; ++i) {
+      Shard<T>& s = shards[i];
+      DevGuard g(s.dev);
+      average_kernel<T><<<k, 128, 0, s.stream>>>(s.sums(), s.counts(k, d), k, d, inv, s.C[cur], s.C[cur ^ 1], s.cnorm,
+                                               s.shift_k, s.st);
+      iter_close_kernel<<<1, 256, 0, s.stream>>>(s.shift_k, k, s.st, s.shift_log, s.changed_log, s.reloc_log, it,
+                                                 &s.host_pin[0], reinterpret_cast<unsigned long long*>(&s.host_pin[1]));
+      launches += 2;
+      if (i == 0) cudaEventRecord(ev[4 * it + 3], s.stream);
+      cudaError_t ce = cudaGetLastError();
+      if (ce != cudaSuccess) { set_error(std::string("iteration launch: ") + cudaGetErrorString(ce)); rc = KM_ECUDA; }
+    }
+    if (rc != KM_OK) break;
+    cur ^= 1;
+    if (check) {
+      DevGuard g(s0.dev);
+      cudaError_t ce = cudaStreamSynchronize(s0.stream);
+      if (ce != cudaSuccess) { set_error(std::string("iteration sync: ") + cudaGetErrorString(ce)); rc = KM_ECUDA; break; }
+      double shift = *reinterpret_cast<volatile double*>(&s0.host_pin[0]);
+      unsigned long long changed = *reinterpret_cast<volatile unsigned long long*>(&s0.host_pin[1]);
+      log_msg(verbose, 400, "iteration %d: shift^2 %.6g, %llu labels changed", it, shift, changed);
+      // the reference's test, src/gpu/kmeans/kmeans_impl.h:202
+      if (threshold > 0 && shift < threshold) { ++it; break; }
+      if ((flags & KM_FIT_CHECK_EVERY_ITER) && changed == 0 && !multi) { ++it; break; }
+    }
+  }
+  if (rc != KM_OK) { free_events(); return rc; }
+  const int done = it;
+  {
+    DevGuard g(s0.dev);
+    cudaEventRecord(ev[ev.size() - 2], s0.stream);
+  }
+  if (!(flags & KM_FIT_NO_FINAL_ASSIGN)) {
+    rc = assign_all(flags);
+    if (rc != KM_OK) { free_events(); return rc; }
+  }
+  {
+    DevGuard g(s0.dev);
+    cudaEventRecord(ev[ev.size() - 1], s0.stream);
+  }
+  for (auto& s : shards) {
+    DevGuard g(s.dev);
+    cudaError_t ce = cudaStreamSynchronize(s.stream);
+    if (ce != cudaSuccess) { set_error(std::string("fit sync: ") + cudaGetErrorString(ce)); free_events(); return KM_ECUDA; }
+  }
+  // logs -> stats
+  {
+    DevGuard g(s0.dev);
+    stats.iterations = done;
+    if (done > 0) {
+      std::vector<double> sh(done);
+      std::vector<unsigned long long> ch(done);
+      std::vector<int> rl(done);
+      KM_CUDA(cudaMemcpy(sh.data(), s0.shift_log, done * sizeof(double), cudaMemcpyDeviceToHost));
+      KM_CUDA(cudaMemcpy(ch.data(), s0.changed_log, done * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+      KM_CUDA(cudaMemcpy(rl.data(), s0.reloc_log, done * sizeof(int), cudaMemcpyDeviceToHost));
+      stats.last_shift_sq = sh[done - 1];
+      if (!multi) {
+        for (int i = 0; i < done; ++i)
+          if (ch[i] == 0) { stats.n_iter_converged = i + 1; break; }
+      }
+      for (int i = 0; i < done; ++i) stats.relocations += rl[i];
+      float a = 0, u = 0, ms = 0;
+      for (int i = 0; i < done; ++i) {
+        cudaEventElapsedTime(&ms, ev[4 * i + 0], ev[4 * i + 1]);
+        a += ms;
+        cudaEventElapsedTime(&ms, ev[4 * i + 1], ev[4 * i + 3]);
+        u += ms;
+      }
+      stats.ms_assign = a;
+      stats.ms_update = u;
+      cudaEventElapsedTime(&ms, ev[0], ev[ev.size() - 2]);
+      stats.ms_loop = ms;
+    }
+  }
+  free_events();
+  stats.gpu_launches = launches;
+  stats.seconds_fit = now_s() - t_start;
+  return KM_OK;
+}
+
+// Sum of squared distances of every row to its assigned centre (direct
+// differences, double), all local shards; all-reduced over ranks.
+template <typename T>
+int Engine<T>::inertia(double* out) {
+  if (!have_centroids) KM_FAIL(KM_ESTATE, "no centroids set");
+  double total = 0;
+  for (auto& s : shards) {
+    DevGuard g(s.dev);
+    KM_TRY(ensure_dist(s));
+    rowdist_kernel<T><<<s.num_sms * 8, 256, 0, s.stream>>>(s.X, s.rows, d, s.labels, s.C[cur], s.dist, s.st, 1);
+    sum_partials_kernel<<<1024, 256, 0, s.stream>>>(s.dist, s.rows, s.sum_partials);
+    sum_final_kernel<<<1, 32, 0, s.stream>>>(s.sum_partials, 1024, &s.st->inertia);
+    KM_CUDA(cudaGetLastError());
+    launches += 3;
+  }
+  if (world_size > 1) {
+    NcclApi* api = NcclApi::get();
+    KM_NCCL(api, api->GroupStart());
+    for (auto& s : shards)
+      KM_NCCL(api, api->AllReduce(&s.st->inertia, &s.st->inertia, 1, ncclDouble, ncclSum, s.comm, s.stream));
+    KM_NCCL(api, api->GroupEnd());
+    Shard<T>& s = shards[0];
+    DevGuard g(s.dev);
+    KM_CUDA(cudaMemcpyAsync(&total, &s.st->inertia, sizeof(double), cudaMemcpyDeviceToHost, s.stream));
+    KM_CUDA(cudaStreamSynchronize(s.stream));
+  } else {
+    Shard<T>& s = shards[0];
+    DevGuard g(s.dev);
+    KM_CUDA(cudaMemcpyAsync(&total, &s.st->inertia, sizeof(double), cudaMemcpyDeviceToHost, s.stream));
+    KM_CUDA(cudaStreamSynchronize(s.stream));
+  }
+  *out = total;
+  stats.inertia = total;
+  return KM_OK;
+}
+
+// Squared distances of one shard, column-major with leading dimension ld, to the host.
+template <typename T>
+int Engine<T>::transform_shard(int local, T* out_host, size_t ld) {
+  if (local < 0 || local >= (int)shards.size() || !out_host) KM_FAIL(KM_EINVAL, "kmeans_transform_resident: bad argument");
+  if (!have_centroids) KM_FAIL(KM_ESTATE, "no centroids set");
+  Shard<T>& s = shards[local];
+  if (ld < s.rows) KM_FAIL(KM_EINVAL, "kmeans_transform_resident: ld smaller than the shard");
+  DevGuard g(s.dev);
+  // row batches bound the device block to about 256 MB
+  size_t batch = std::max<size_t>(128, ((size_t)1 << 28) / ((size_t)k * sizeof(T)));
+  batch = (batch + 127) / 128 * 128;
+  batch = std::min(batch, (s.rows + 127) / 128 * 128);
+  T* buf = nullptr;
+  KM_CUDA(cudaMalloc(&buf, batch * (size_t)k * sizeof(T)));
+  int rc = KM_OK;
+  for (size_t r = 0; r < s.rows && rc == KM_OK; r += batch) {
+    size_t nr = std::min(batch, s.rows - r);
+    rc = launch_tiles(s, s.X + r * (size_t)d, nr, nullptr, MODE_TRANSFORM, buf, batch, false);
+    if (rc != KM_OK) break;
+    cudaError_t ce = cudaMemcpy2DAsync(out_host + r, ld * sizeof(T), buf, batch * sizeof(T), nr * sizeof(T), k,
+                                       cudaMemcpyDeviceToHost, s.stream);
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(s.stream);
+    if (ce != cudaSuccess) { set_error(std::string("transform copy: ") + cudaGetErrorString(ce)); rc = KM_ECUDA; }
+  }
+  cudaFree(buf);
+  return rc;
+}
+
+}  // namespace km

@@ -1,0 +1,471 @@
+// C ABI of the k-means engine: the reference's exported functions
+// (src/include/solver/kmeans.h:56-76) plus the resident-handle extension.
+// See include/h2o4gpu_kmeans.h for the contract of every entry point.
+#include <cstdarg>
+#include <cstdlib>
+#include <ctime>
+#include <numeric>
+#include <random>
+
+#include "km_fit.cuh"
+#include "km_synth.cuh"
+
+namespace km {
+
+static thread_local std::string g_err;
+void set_error(const std::string& msg) { g_err = msg; }
+
+// Levelled stderr logger with the reference's convention: a message of level L
+// prints when 0 < L <= verbose (src/common/logger.h:10-25, logger.cpp:16-34).
+void log_msg(int verbose, int level, const char* fmt, ...) {
+  if (!(level > 0 && level <= verbose)) return;
+  va_list ap;
+  va_start(ap, fmt);
+  fprintf(stderr, "[kmeans %d] ", level);
+  vfprintf(stderr, fmt, ap);
+  fprintf(stderr, "\n");
+  va_end(ap);
+  fflush(stderr);
+}
+
+}  // namespace km
+
+struct km_engine {
+  int dtype;
+  km::Engine<float>* f32;
+  km::Engine<double>* f64;
+};
+
+using km::set_error;
+
+namespace {
+
+// devices = (gpu_id + i) % visible, i < n_gpu, n_gpu clamped to the visible
+// devices and to the row count (src/gpu/kmeans/kmeans_h2o4gpu.cu:585-603)
+int device_list(int gpu_id, int n_gpu, size_t rows, std::vector<int>* out) {
+  int visible = 0;
+  if (cudaGetDeviceCount(&visible) != cudaSuccess || visible < 1) KM_FAIL(KM_ENODEV, "no CUDA device visible");
+  if (n_gpu < 0 || n_gpu > visible) n_gpu = visible;
+  if (n_gpu == 0) KM_FAIL(KM_ENODEV, "n_gpu == 0: this library has no CPU path");
+  if ((size_t)n_gpu > rows) n_gpu = (int)rows;
+  if (gpu_id < 0) gpu_id = 0;
+  out->clear();
+  for (int i = 0; i < n_gpu; ++i) out->push_back((gpu_id + i) % visible);
+  return KM_OK;
+}
+
+template <typename T>
+int out_buffer(T** slot, size_t count, bool* allocated) {
+  *allocated = false;
+  if (!slot) KM_FAIL(KM_EINVAL, "output pointer is NULL");
+  if (*slot == nullptr) {
+    *slot = static_cast<T*>(std::malloc(std::max<size_t>(count, 1) * sizeof(T)));
+    if (!*slot) KM_FAIL(KM_ENOMEM, "host allocation failed");
+    *allocated = true;
+  }
+  return KM_OK;
+}
+
+template <typename T>
+int make_engine(const std::vector<int>& devs, std::unique_ptr<km::Engine<T>>* out) {
+  std::unique_ptr<km::Engine<T>> e(new km::Engine<T>());
+  KM_TRY(e->init((int)devs.size(), devs.data(), 0, (int)devs.size(), nullptr));
+  *out = std::move(e);
+  return KM_OK;
+}
+
+// seeded row choice of the reference: first k entries of a shuffle of 0..rows-1
+// with std::default_random_engine(seed) (src/gpu/kmeans/kmeans_h2o4gpu.cu:662-669,
+// 687-693); seed < 0 draws the engine's seed from the clock.
+template <typename T>
+void shuffled_rows_init(const T* X, size_t rows, size_t cols, int k, int seed, std::vector<T>* init) {
+  std::vector<int> v(rows);
+  std::iota(v.begin(), v.end(), 0);
+  unsigned s = (seed >= 0) ? (unsigned)seed : (unsigned)std::time(nullptr);
+  std::shuffle(v.begin(), v.end(), std::default_random_engine(s));
+  init->resize((size_t)k * cols);
+  for (int i = 0; i < k; ++i) std::memcpy(init->data() + (size_t)i * cols, X + (size_t)v[i] * cols, cols * sizeof(T));
+}
+
+template <typename T>
+int fit_impl(int verbose, int seed, int gpu_id, int n_gpu, size_t rows, size_t cols, int k, int max_iter,
+             int init_from_data, T threshold, const T* X, const T* centroids, T** pred_centroids, int** pred_labels) {
+  if (!X || rows == 0 || cols == 0 || k < 1 || max_iter < 0) KM_FAIL(KM_EINVAL, "kmeans fit: bad argument");
+  if (rows > 0x7fffffffULL) KM_FAIL(KM_EINVAL, "kmeans fit: more than INT_MAX rows through the host-pointer ABI");
+  if ((size_t)k > rows) {
+    km::log_msg(verbose, 300, "number of clusters adjusted to the number of rows");
+    k = (int)rows;  // src/gpu/kmeans/kmeans_h2o4gpu.cu:629-635
+  }
+  if (init_from_data == 2 && !centroids) KM_FAIL(KM_EINVAL, "init_from_data == 2 needs initial centroids");
+  std::vector<int> devs;
+  KM_TRY(device_list(gpu_id, n_gpu, rows, &devs));
+  std::unique_ptr<km::Engine<T>> e;
+  KM_TRY(make_engine<T>(devs, &e));
+  e->verbose = verbose;
+  km::log_msg(verbose, 500, "rows %zu cols %zu k %d max_iter %d devices %zu", rows, cols, k, max_iter, devs.size());
+  KM_TRY(e->upload_host(X, rows, cols, 'r'));
+  std::vector<T> init;
+  const T* init_ptr = centroids;
+  if (init_from_data != 2) {
+    // 0 = seeded random rows; 1 (k-means||) currently starts from the same rows
+    shuffled_rows_init(X, rows, cols, k, seed, &init);
+    init_ptr = init.data();
+  }
+  int flags = (threshold > 0) ? KM_FIT_CHECK_EVERY_ITER : 0;
+  KM_TRY(e->fit(k, max_iter, (double)threshold, init_ptr, flags));
+  bool a1 = false, a2 = false;
+  KM_TRY(out_buffer(pred_centroids, (size_t)k * cols, &a1));
+  int rc = out_buffer(pred_labels, rows, &a2);
+  if (rc != KM_OK) { if (a1) { std::free(*pred_centroids); *pred_centroids = nullptr; } return rc; }
+  {
+    km::Shard<T>& s0 = e->shards[0];
+    km::DevGuard g(s0.dev);
+    KM_CUDA(cudaMemcpy(*pred_centroids, s0.C[e->cur], (size_t)k * cols * sizeof(T), cudaMemcpyDeviceToHost));
+  }
+  size_t off = 0;
+  for (auto& s : e->shards) {
+    km::DevGuard g(s.dev);
+    KM_CUDA(cudaMemcpy(*pred_labels + off, s.labels, s.rows * sizeof(int), cudaMemcpyDeviceToHost));
+    off += s.rows;
+  }
+  km::log_msg(verbose, 300, "fit: %d iterations, %.3f s upload, %.3f s fit", e->stats.iterations,
+              e->stats.seconds_upload, e->stats.seconds_fit);
+  return KM_OK;
+}
+
+template <typename T>
+int predict_impl(int verbose, int gpu_id, int n_gpu, size_t rows, size_t cols, int k, const T* X,
+                 const T* centroids, int** pred_labels) {
+  if (!X || !centroids || rows == 0 || cols == 0 || k < 1) KM_FAIL(KM_EINVAL, "kmeans predict: bad argument");
+  std::vector<int> devs;
+  KM_TRY(device_list(gpu_id, n_gpu, rows, &devs));
+  std::unique_ptr<km::Engine<T>> e;
+  KM_TRY(make_engine<T>(devs, &e));
+  e->verbose = verbose;
+  KM_TRY(e->upload_host(X, rows, cols, 'r'));
+  KM_TRY(e->check_data());
+  KM_TRY(e->set_centroids(k, centroids));
+  KM_TRY(e->assign_all(0));
+  bool a = false;
+  KM_TRY(out_buffer(pred_labels, rows, &a));
+  size_t off = 0;
+  for (auto& s : e->shards) {
+    km::DevGuard g(s.dev);
+    KM_CUDA(cudaStreamSynchronize(s.stream));
+    KM_CUDA(cudaMemcpy(*pred_labels + off, s.labels, s.rows * sizeof(int), cudaMemcpyDeviceToHost));
+    off += s.rows;
+  }
+  return KM_OK;
+}
+
+template <typename T>
+int transform_impl(int verbose, int gpu_id, int n_gpu, size_t rows, size_t cols, int k, const T* X,
+                   const T* centroids, T** preds) {
+  if (!X || !centroids || rows == 0 || cols == 0 || k < 1) KM_FAIL(KM_EINVAL, "kmeans transform: bad argument");
+  std::vector<int> devs;
+  KM_TRY(device_list(gpu_id, n_gpu, rows, &devs));
+  std::unique_ptr<km::Engine<T>> e;
+  KM_TRY(make_engine<T>(devs, &e));
+  e->verbose = verbose;
+  KM_TRY(e->upload_host(X, rows, cols, 'r'));
+  KM_TRY(e->check_data());
+  KM_TRY(e->set_centroids(k, centroids));
+  bool a = false;
+  KM_TRY(out_buffer(preds, rows * (size_t)k, &a));
+  size_t off = 0;
+  for (size_t i = 0; i < e->shards.size(); ++i) {
+    KM_TRY(e->transform_shard((int)i, *preds + off, rows));
+    off += e->shards[i].rows;
+  }
+  return KM_OK;
+}
+
+template <typename T>
+int centroid_sums_impl(int gpu_id, const T* X, const int32_t* labels, size_t rows, size_t cols, int k, double* sums,
+                       int64_t* counts) {
+  if (!X || !labels || !sums || !counts || rows == 0 || cols == 0 || k < 1) KM_FAIL(KM_EINVAL, "centroid sums: bad argument");
+  for (size_t i = 0; i < rows; ++i)
+    if (labels[i] < 0 || labels[i] >= k) KM_FAIL(KM_EINVAL, "centroid sums: label out of range");
+  std::vector<int> devs;
+  KM_TRY(device_list(gpu_id, 1, rows, &devs));
+  std::unique_ptr<km::Engine<T>> e;
+  KM_TRY(make_engine<T>(devs, &e));
+  KM_TRY(e->upload_host(X, rows, cols, 'r'));
+  KM_TRY(e->check_data());
+  e->k = k;
+  KM_TRY(e->ensure_buffers(k));
+  km::Shard<T>& s = e->shards[0];
+  km::DevGuard g(s.dev);
+  int ex = 0;
+  if (s.xmax > 0) std::frexp(s.xmax, &ex);
+  const int sa = km::kPieceBits - ex;
+  KM_CUDA(cudaMemcpyAsync(s.labels, labels, rows * sizeof(int), cudaMemcpyHostToDevice, s.stream));
+  KM_CUDA(cudaMemsetAsync(s.gacc, 0, s.gacc_count(k, (int)cols) * sizeof(long long), s.stream));
+  KM_TRY(e->launch_accumulate(s, (T)std::ldexp(1.0, sa)));
+  std::vector<long long> h(s.gacc_count(k, (int)cols));
+  KM_CUDA(cudaMemcpyAsync(h.data(), s.gacc, h.size() * sizeof(long long), cudaMemcpyDeviceToHost, s.stream));
+  KM_CUDA(cudaStreamSynchronize(s.stream));
+  constexpr int NP = km::Fixed<T>::NP;
+  const double inv = std::ldexp(1.0, -(sa + km::kPieceBits));
+  const size_t kd = (size_t)k * cols;
+  for (size_t i = 0; i < kd; ++i) {
+    long long gp[NP / 2];
+    for (int q = 0; q < NP / 2; ++q) gp[q] = h[(size_t)q * kd + i];
+    sums[i] = km::fixed_to_double<NP>(gp, inv);
+  }
+  for (int j = 0; j < k; ++j) counts[j] = (int64_t)h[(size_t)(NP / 2) * kd + j];
+  return KM_OK;
+}
+
+template <typename T>
+int synth_impl(int gpu_id, T* dX, size_t rows, size_t cols, size_t row0, int kind, const T* centers_host, int n_comp,
+               const T* weights_host, T sigma, uint64_t seed) {
+  if (!dX || rows == 0 || cols == 0) KM_FAIL(KM_EINVAL, "synth: bad argument");
+  if (kind != 1 && (!centers_host || n_comp < 1)) KM_FAIL(KM_EINVAL, "synth: mixture needs centers");
+  km::DevGuard g(gpu_id);
+  T* dc = nullptr;
+  float* dcdf = nullptr;
+  if (kind != 1) {
+    std::vector<float> cdf(n_comp);
+    double tot = 0, run = 0;
+    for (int i = 0; i < n_comp; ++i) tot += weights_host ? (double)weights_host[i] : 1.0;
+    for (int i = 0; i < n_comp; ++i) {
+      run += (weights_host ? (double)weights_host[i] : 1.0) / tot;
+      cdf[i] = (float)run;
+    }
+    cdf[n_comp - 1] = 1.0f;
+    KM_CUDA(cudaMalloc(&dc, (size_t)n_comp * cols * sizeof(T)));
+    KM_CUDA(cudaMalloc(&dcdf, n_comp * sizeof(float)));
+    KM_CUDA(cudaMemcpy(dc, centers_host, (size_t)n_comp * cols * sizeof(T), cudaMemcpyHostToDevice));
+    KM_CUDA(cudaMemcpy(dcdf, cdf.data(), n_comp * sizeof(float), cudaMemcpyHostToDevice));
+  }
+  km::synth_kernel<T><<<148 * 16, 256>>>(dX, rows, (int)cols, row0, kind, dc, n_comp, dcdf, sigma, seed);
+  cudaError_t ce = cudaGetLastError();
+  if (ce == cudaSuccess) ce = cudaDeviceSynchronize();
+  cudaFree(dc);
+  cudaFree(dcdf);
+  if (ce != cudaSuccess) KM_FAIL(KM_ECUDA, std::string("synth: ") + cudaGetErrorString(ce));
+  return KM_OK;
+}
+
+}  // namespace
+
+template <typename T>
+static int assign_sync(km::Engine<T>* e) {
+  KM_TRY(e->check_data());
+  KM_TRY(e->assign_all(0));
+  for (auto& s : e->shards) {
+    km::DevGuard g(s.dev);
+    KM_CUDA(cudaStreamSynchronize(s.stream));
+  }
+  return KM_OK;
+}
+
+template <typename T>
+static int get_centroids(km::Engine<T>* e, void* out) {
+  if (!out) KM_FAIL(KM_EINVAL, "NULL output");
+  if (!e->have_centroids) KM_FAIL(KM_ESTATE, "no centroids set");
+  km::Shard<T>& s = e->shards[0];
+  km::DevGuard g(s.dev);
+  KM_CUDA(cudaStreamSynchronize(s.stream));
+  KM_CUDA(cudaMemcpy(out, s.C[e->cur], (size_t)e->k * e->d * sizeof(T), cudaMemcpyDeviceToHost));
+  return KM_OK;
+}
+
+template <typename T>
+static int get_labels(km::Engine<T>* e, int local, int32_t* out) {
+  if (!out || local < 0 || local >= (int)e->shards.size()) KM_FAIL(KM_EINVAL, "kmeans_get_labels: bad argument");
+  km::Shard<T>& s = e->shards[local];
+  if (!s.labels) KM_FAIL(KM_ESTATE, "no labels yet");
+  km::DevGuard g(s.dev);
+  KM_CUDA(cudaStreamSynchronize(s.stream));
+  KM_CUDA(cudaMemcpy(out, s.labels, s.rows * sizeof(int), cudaMemcpyDeviceToHost));
+  return KM_OK;
+}
+
+template <typename T>
+static int labels_dev(km::Engine<T>* e, int local, const int32_t** out) {
+  if (!out || local < 0 || local >= (int)e->shards.size()) KM_FAIL(KM_EINVAL, "kmeans_labels_device: bad argument");
+  *out = e->shards[local].labels;
+  return KM_OK;
+}
+
+template <typename T>
+static int get_stats(km::Engine<T>* e, kmeans_stats* out, int want_inertia) {
+  if (!out) KM_FAIL(KM_EINVAL, "NULL output");
+  if (want_inertia && e->have_centroids) {
+    double v;
+    KM_TRY(e->inertia(&v));
+  }
+  *out = e->stats;
+  return KM_OK;
+}
+
+// ---- extern "C" surface ---------------------------------------------------------
+extern "C" {
+
+const char* kmeans_last_error(void) { return km::g_err.c_str(); }
+
+int kmeans_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) return 0;
+  return n;
+}
+
+void kmeans_free(void* p) { std::free(p); }
+
+int kmeans_fit_f32(int verbose, int seed, int gpu_id, int n_gpu, size_t rows, size_t cols, int k, int max_iterations,
+                   int init_from_data, float threshold, const float* srcdata, const float* centroids,
+                   float** pred_centroids, int** pred_labels) {
+  return fit_impl<float>(verbose, seed, gpu_id, n_gpu, rows, cols, k, max_iterations, init_from_data, threshold,
+                         srcdata, centroids, pred_centroids, pred_labels);
+}
+int kmeans_fit_f64(int verbose, int seed, int gpu_id, int n_gpu, size_t rows, size_t cols, int k, int max_iterations,
+                   int init_from_data, double threshold, const double* srcdata, const double* centroids,
+                   double** pred_centroids, int** pred_labels) {
+  return fit_impl<double>(verbose, seed, gpu_id, n_gpu, rows, cols, k, max_iterations, init_from_data, threshold,
+                          srcdata, centroids, pred_centroids, pred_labels);
+}
+int kmeans_predict_f32(int verbose, int gpu_id, int n_gpu, size_t rows, size_t cols, int k, const float* srcdata,
+                       const float* centroids, int** pred_labels) {
+  return predict_impl<float>(verbose, gpu_id, n_gpu, rows, cols, k, srcdata, centroids, pred_labels);
+}
+int kmeans_predict_f64(int verbose, int gpu_id, int n_gpu, size_t rows, size_t cols, int k, const double* srcdata,
+                       const double* centroids, int** pred_labels) {
+  return predict_impl<double>(verbose, gpu_id, n_gpu, rows, cols, k, srcdata, centroids, pred_labels);
+}
+int kmeans_transform_f32(int verbose, int gpu_id, int n_gpu, size_t rows, size_t cols, int k, const float* srcdata,
+                         const float* centroids, float** preds) {
+  return transform_impl<float>(verbose, gpu_id, n_gpu, rows, cols, k, srcdata, centroids, preds);
+}
+int kmeans_transform_f64(int verbose, int gpu_id, int n_gpu, size_t rows, size_t cols, int k, const double* srcdata,
+                         const double* centroids, double** preds) {
+  return transform_impl<double>(verbose, gpu_id, n_gpu, rows, cols, k, srcdata, centroids, preds);
+}
+
+int kmeans_create(kmeans_handle_t* out, int dtype, int n_local, const int* device_ids, int world_rank0,
+                  int world_size, const void* nccl_id) {
+  if (!out || !device_ids || (dtype != 0 && dtype != 1)) KM_FAIL(KM_EINVAL, "kmeans_create: bad argument");
+  std::unique_ptr<km_engine> h(new km_engine{dtype, nullptr, nullptr});
+  int rc;
+  if (dtype == 0) {
+    h->f32 = new km::Engine<float>();
+    rc = h->f32->init(n_local, device_ids, world_rank0, world_size, nccl_id);
+  } else {
+    h->f64 = new km::Engine<double>();
+    rc = h->f64->init(n_local, device_ids, world_rank0, world_size, nccl_id);
+  }
+  if (rc != KM_OK) { delete h->f32; delete h->f64; return rc; }
+  *out = h.release();
+  return KM_OK;
+}
+
+int kmeans_destroy(kmeans_handle_t h) {
+  if (!h) return KM_OK;
+  delete h->f32;
+  delete h->f64;
+  delete h;
+  return KM_OK;
+}
+
+int kmeans_nccl_unique_id(void* out128) {
+  if (!out128) KM_FAIL(KM_EINVAL, "kmeans_nccl_unique_id: NULL");
+  km::NcclApi* api = km::NcclApi::get();
+  if (!api) KM_FAIL(KM_ENCCL, "libnccl.so.2 could not be loaded");
+  ncclUniqueId id;
+  KM_NCCL(api, api->GetUniqueId(&id));
+  static_assert(sizeof(id) == 128, "ncclUniqueId size");
+  std::memcpy(out128, &id, 128);
+  return KM_OK;
+}
+
+#define KM_DISPATCH(h, call_f32, call_f64)                      \
+  if (!(h)) KM_FAIL(KM_EINVAL, "NULL handle");                  \
+  return (h)->dtype == 0 ? (call_f32) : (call_f64)
+
+int kmeans_attach_device(kmeans_handle_t h, int local, const void* dX, size_t rows, size_t cols, size_t n_total) {
+  KM_DISPATCH(h, h->f32->attach_device(local, static_cast<const float*>(dX), rows, cols, n_total),
+              h->f64->attach_device(local, static_cast<const double*>(dX), rows, cols, n_total));
+}
+int kmeans_upload_host(kmeans_handle_t h, const void* X, size_t rows, size_t cols, char order) {
+  KM_DISPATCH(h, h->f32->upload_host(static_cast<const float*>(X), rows, cols, order),
+              h->f64->upload_host(static_cast<const double*>(X), rows, cols, order));
+}
+int kmeans_fit_resident(kmeans_handle_t h, int k, int max_iter, double threshold, const void* init, int flags) {
+  KM_DISPATCH(h, h->f32->fit(k, max_iter, threshold, static_cast<const float*>(init), flags),
+              h->f64->fit(k, max_iter, threshold, static_cast<const double*>(init), flags));
+}
+int kmeans_set_centroids(kmeans_handle_t h, int k, const void* c) {
+  KM_DISPATCH(h, h->f32->set_centroids(k, static_cast<const float*>(c)),
+              h->f64->set_centroids(k, static_cast<const double*>(c)));
+}
+
+int kmeans_assign_resident(kmeans_handle_t h) { KM_DISPATCH(h, assign_sync(h->f32), assign_sync(h->f64)); }
+
+int kmeans_get_centroids(kmeans_handle_t h, void* out) { KM_DISPATCH(h, get_centroids(h->f32, out), get_centroids(h->f64, out)); }
+
+int kmeans_get_labels(kmeans_handle_t h, int local, int32_t* out) {
+  KM_DISPATCH(h, get_labels(h->f32, local, out), get_labels(h->f64, local, out));
+}
+
+int kmeans_labels_device(kmeans_handle_t h, int local, const int32_t** out) {
+  KM_DISPATCH(h, labels_dev(h->f32, local, out), labels_dev(h->f64, local, out));
+}
+int kmeans_transform_resident(kmeans_handle_t h, int local, void* out, size_t ld) {
+  KM_DISPATCH(h, h->f32->transform_shard(local, static_cast<float*>(out), ld),
+              h->f64->transform_shard(local, static_cast<double*>(out), ld));
+}
+
+int kmeans_get_stats(kmeans_handle_t h, kmeans_stats* out) {
+  KM_DISPATCH(h, get_stats(h->f32, out, 0), get_stats(h->f64, out, 0));
+}
+int kmeans_inertia(kmeans_handle_t h, double* out) {
+  if (!out) KM_FAIL(KM_EINVAL, "NULL output");
+  KM_DISPATCH(h, h->f32->inertia(out), h->f64->inertia(out));
+}
+
+int kmeans_centroid_sums_f32(int gpu_id, const float* X, const int32_t* labels, size_t rows, size_t cols, int k,
+                             double* sums, int64_t* counts) {
+  return centroid_sums_impl<float>(gpu_id, X, labels, rows, cols, k, sums, counts);
+}
+int kmeans_centroid_sums_f64(int gpu_id, const double* X, const int32_t* labels, size_t rows, size_t cols, int k,
+                             double* sums, int64_t* counts) {
+  return centroid_sums_impl<double>(gpu_id, X, labels, rows, cols, k, sums, counts);
+}
+
+int kmeans_synth_f32(int gpu_id, float* dX, size_t rows, size_t cols, size_t row0, int kind, const float* centers_host,
+                     int n_comp, const float* weights_host, float sigma, uint64_t seed) {
+  return synth_impl<float>(gpu_id, dX, rows, cols, row0, kind, centers_host, n_comp, weights_host, sigma, seed);
+}
+int kmeans_synth_f64(int gpu_id, double* dX, size_t rows, size_t cols, size_t row0, int kind,
+                     const double* centers_host, int n_comp, const double* weights_host, double sigma, uint64_t seed) {
+  return synth_impl<double>(gpu_id, dX, rows, cols, row0, kind, centers_host, n_comp, weights_host, sigma, seed);
+}
+
+}  // extern "C"
+
+// ---- the reference header's C++-linkage names -------------------------------------
+int make_ptr_float_kmeans(int dopredict, int verbose, int seed, int gpu_id, int n_gpu, size_t mTrain, size_t n, int k,
+                          int max_iterations, int init_from_data, float threshold, const float* srcdata,
+                          const float* centroids, float** pred_centroids, int** pred_labels) {
+  if (dopredict == 0)
+    return kmeans_fit_f32(verbose, seed, gpu_id, n_gpu, mTrain, n, k, max_iterations, init_from_data, threshold,
+                          srcdata, centroids, pred_centroids, pred_labels);
+  return kmeans_predict_f32(verbose, gpu_id, n_gpu, mTrain, n, k, srcdata, centroids, pred_labels);
+}
+int make_ptr_double_kmeans(int dopredict, int verbose, int seed, int gpu_id, int n_gpu, size_t mTrain, size_t n, int k,
+                           int max_iterations, int init_from_data, double threshold, const double* srcdata,
+                           const double* centroids, double** pred_centroids, int** pred_labels) {
+  if (dopredict == 0)
+    return kmeans_fit_f64(verbose, seed, gpu_id, n_gpu, mTrain, n, k, max_iterations, init_from_data, threshold,
+                          srcdata, centroids, pred_centroids, pred_labels);
+  return kmeans_predict_f64(verbose, gpu_id, n_gpu, mTrain, n, k, srcdata, centroids, pred_labels);
+}
+int kmeans_transform_float(int verbose, int gpu_id, int n_gpu, size_t m, size_t n, int k, const float* srcdata,
+                           const float* centroids, float** preds) {
+  return kmeans_transform_f32(verbose, gpu_id, n_gpu, m, n, k, srcdata, centroids, preds);
+}
+int kmeans_transform_double(int verbose, int gpu_id, int n_gpu, size_t m, size_t n, int k, const double* srcdata,
+                            const double* centroids, double** preds) {
+  return kmeans_transform_f64(verbose, gpu_id, n_gpu, m, n, k, srcdata, centroids, preds);
+}

@@ -1,0 +1,198 @@
+/* C ABI of the B200 k-means engine (libh2o4gpu_kmeans.so).
+ *
+ * Plain pointers and sizes only.  Every function returns 0 on success and a
+ * negative KM_E* code on failure; kmeans_last_error() gives the message of the
+ * calling thread's last failure.  Nothing here exits the process, installs a
+ * signal handler or throws across the boundary.
+ *
+ * Section 1 are the reference's exported functions for this path, with the
+ * reference's names, parameter order and types.  In the reference they have C++
+ * linkage (src/include/solver/kmeans.h:56-76; defined in
+ * src/gpu/kmeans/kmeans_h2o4gpu.cu:1060-1097) and are reached through SWIG
+ * (src/swig/solver/kmeans.i:1-13).  This library exports them twice: with C++
+ * linkage, so code compiled against the reference's header links unchanged, and
+ * as the extern "C" names below for ctypes / cgo / JNI style bindings.
+ */
+#ifndef H2O4GPU_KMEANS_H_
+#define H2O4GPU_KMEANS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- error codes -------------------------------------------------------- */
+#define KM_OK 0
+#define KM_EINVAL (-1)   /* bad argument (null pointer, k < 1, rows == 0, ...)        */
+#define KM_ENOMEM (-2)   /* device or host allocation failed (the reference's -1,    */
+                         /* src/gpu/kmeans/kmeans_impl.h:105)                        */
+#define KM_ECUDA (-3)    /* a CUDA runtime call or kernel launch failed              */
+#define KM_ENODEV (-4)   /* no usable CUDA device / bad device id                    */
+#define KM_ENCCL (-5)    /* NCCL missing or a collective failed                      */
+#define KM_ENONFINITE (-6) /* NaN or Inf in the data or the centroids                */
+#define KM_ETIMEOUT (-7) /* a bounded device-side wait gave up                       */
+#define KM_ESTATE (-8)   /* call out of order on a handle (no data, no centroids)    */
+
+const char* kmeans_last_error(void);
+
+/* ---- 1. the reference's entry points ------------------------------------ */
+
+/* Fit (dopredict == 0) or predict (dopredict == 1).
+ * Replaces make_ptr_float_kmeans / make_ptr_double_kmeans
+ * (src/include/solver/kmeans.h:56-68; src/gpu/kmeans/kmeans_h2o4gpu.cu:977-991,
+ * 1060-1082).  Argument meaning as in the reference: verbose = log level,
+ * seed < 0 = nondeterministic, devices = (gpu_id + i) % visible for i < n_gpu,
+ * mTrain = rows, n = cols, srcdata row-major rows x cols on the host,
+ * threshold compared with the summed squared centroid shift
+ * (src/gpu/kmeans/kmeans_impl.h:191-208), centroids = k x cols row-major.
+ *   init_from_data 0: first k rows of a seeded shuffle (kmeans_h2o4gpu.cu:662-693)
+ *   init_from_data 1: k-means|| on the device (kmeans_h2o4gpu.cu:729-742)
+ *   init_from_data 2: EXTENSION - start from `centroids` (the reference ignores
+ *                     that argument in fit, kmeans_h2o4gpu.cu:983-986).
+ * Outputs: if *pred_centroids / *pred_labels is non-NULL on entry it is a caller
+ * buffer of k*cols values / rows int32 and is written in place; if it is NULL the
+ * library allocates it (release with kmeans_free).  The reference always
+ * allocates and never frees (kmeans_h2o4gpu.cu:767-781).  All rows are labelled
+ * (the reference drops rows % n_gpu trailing rows, kmeans_h2o4gpu.cu:649). */
+int kmeans_fit_f32(int verbose, int seed, int gpu_id, int n_gpu, size_t rows, size_t cols,
+                   int k, int max_iterations, int init_from_data, float threshold,
+                   const float* srcdata, const float* centroids, float** pred_centroids,
+                   int** pred_labels);
+int kmeans_fit_f64(int verbose, int seed, int gpu_id, int n_gpu, size_t rows, size_t cols,
+                   int k, int max_iterations, int init_from_data, double threshold,
+                   const double* srcdata, const double* centroids, double** pred_centroids,
+                   int** pred_labels);
+/* predict = the dopredict == 1 branch (src/gpu/kmeans/kmeans_h2o4gpu.cu:817-889) */
+int kmeans_predict_f32(int verbose, int gpu_id, int n_gpu, size_t rows, size_t cols, int k,
+                       const float* srcdata, const float* centroids, int** pred_labels);
+int kmeans_predict_f64(int verbose, int gpu_id, int n_gpu, size_t rows, size_t cols, int k,
+                       const double* srcdata, const double* centroids, int** pred_labels);
+/* Replaces kmeans_transform_float / kmeans_transform_double
+ * (src/include/solver/kmeans.h:70-76; kmeans_h2o4gpu.cu:891-975, 1085-1097):
+ * squared distances |xn + cn - 2 x.c| (src/gpu/kmeans/kmeans_labels.cu:173-176),
+ * ONE column-major rows x k block over the whole matrix, which is the layout
+ * src/interface_py/h2o4gpu/solvers/kmeans.py:420-421 reshapes with order='F'. */
+int kmeans_transform_f32(int verbose, int gpu_id, int n_gpu, size_t rows, size_t cols, int k,
+                         const float* srcdata, const float* centroids, float** preds);
+int kmeans_transform_f64(int verbose, int gpu_id, int n_gpu, size_t rows, size_t cols, int k,
+                         const double* srcdata, const double* centroids, double** preds);
+/* Frees a buffer the library allocated for a NULL output pointer. */
+void kmeans_free(void* p);
+
+/* Device count as the wrapper needs it (replaces the count half of
+ * get_gpu_info_c, src/gpu/utils.cu:57-90, used by
+ * src/interface_py/h2o4gpu/util/gpu.py:14-38). */
+int kmeans_device_count(void);
+
+/* ---- 2. resident engine (extension) -------------------------------------
+ * The reference re-uploads X on every call (kmeans_h2o4gpu.cu:672-683) and so
+ * cannot hold a 100 GB shard or time the Lloyd loop alone.  A handle keeps one
+ * row shard per local device resident.  dtype: 0 = float32, 1 = float64.
+ * A handle drives `n_local` devices of this process; with world_size > n_local
+ * several processes (one per GPU) cooperate through NCCL, rank = world_rank0 +
+ * local index.  nccl_id is the 128-byte ncclUniqueId shared by all processes
+ * (NULL when world_size == n_local: the library creates the communicators). */
+typedef struct km_engine* kmeans_handle_t;
+
+int kmeans_create(kmeans_handle_t* out, int dtype, int n_local, const int* device_ids,
+                  int world_rank0, int world_size, const void* nccl_id);
+int kmeans_destroy(kmeans_handle_t h);
+/* 128-byte NCCL unique id for kmeans_create (rank 0 makes it, the caller ships it). */
+int kmeans_nccl_unique_id(void* out128);
+
+/* Attach a shard that already lives on local device `local` (borrowed pointer,
+ * row-major rows x cols, 16-byte aligned).  n_total = rows over all ranks. */
+int kmeans_attach_device(kmeans_handle_t h, int local, const void* dX, size_t rows, size_t cols,
+                         size_t n_total);
+/* Upload a host matrix: rows are split contiguously over the local devices
+ * (ceil split, every row covered).  order 'r' = row-major, 'c' = column-major
+ * (the two layouts of copy_data, src/gpu/kmeans/kmeans_h2o4gpu.h:24-42). */
+int kmeans_upload_host(kmeans_handle_t h, const void* X, size_t rows, size_t cols, char order);
+
+/* flags for kmeans_fit_resident */
+#define KM_FIT_NO_FINAL_ASSIGN 1 /* skip the closing E-step (benchmark loops)        */
+#define KM_FIT_FORCE_SIMT 2      /* never take the tcgen05 distance kernel           */
+#define KM_FIT_FORCE_SPLIT 4     /* never take the fused small-k kernel              */
+#define KM_FIT_CHECK_EVERY_ITER 8 /* host reads shift/label changes each iteration   */
+
+/* Lloyd iterations on the resident shards from k x cols host centroids.
+ * Stops after max_iter, or earlier when threshold > 0 and the summed squared
+ * shift drops below it, or (with KM_FIT_CHECK_EVERY_ITER) when no label changed. */
+int kmeans_fit_resident(kmeans_handle_t h, int k, int max_iter, double threshold,
+                        const void* init_centroids, int flags);
+/* One E-step on the resident shards with the handle's current centroids. */
+int kmeans_assign_resident(kmeans_handle_t h);
+int kmeans_set_centroids(kmeans_handle_t h, int k, const void* centroids);
+int kmeans_get_centroids(kmeans_handle_t h, void* out_host);
+/* labels of local shard `local`, rows int32, to host / as a device pointer */
+int kmeans_get_labels(kmeans_handle_t h, int local, int32_t* out_host);
+int kmeans_labels_device(kmeans_handle_t h, int local, const int32_t** out_dev);
+/* squared distances of shard `local` into a column-major block with leading
+ * dimension ld (>= shard rows), written to host memory */
+int kmeans_transform_resident(kmeans_handle_t h, int local, void* out_host, size_t ld);
+
+typedef struct kmeans_stats {
+  int iterations;          /* Lloyd iterations executed                              */
+  int n_iter_converged;    /* first iteration after which no label changed, +1; else 0 */
+  int relocations;         /* empty-cluster relocations over the whole fit           */
+  int path;                /* 1 fused small-k, 2 SIMT tiles, 3 tcgen05               */
+  int gpu_launches;        /* kernels launched by the last fit (all local devices)   */
+  int reserved;
+  double last_shift_sq;    /* summed squared centroid shift of the last iteration    */
+  double inertia;          /* sum of squared distances after the closing E-step, or -1 */
+  double seconds_upload;   /* host-side wall time of the last upload                 */
+  double seconds_fit;      /* wall time of the last kmeans_fit_resident              */
+  float ms_assign;         /* CUDA-event time of the distance+argmin kernel, summed  */
+  float ms_update;         /* ... of the sum / count / finalize kernels              */
+  float ms_loop;           /* ... of the whole iteration loop on device 0            */
+  float reserved2;
+} kmeans_stats;
+int kmeans_get_stats(kmeans_handle_t h, kmeans_stats* out);
+/* Sum of squared distances of every row to its assigned centre (direct
+ * differences in double, all ranks): sklearn's inertia_, which the reference's
+ * GPU path never sets (src/interface_py/h2o4gpu/solvers/kmeans.py:187). */
+int kmeans_inertia(kmeans_handle_t h, double* out);
+
+/* ---- 3. kernel-level entry points (host pointers; used by the parity tests
+ * that restate the reference's kernel tests, tests/cpp/gpu/kmeans/*.cu) ------ */
+/* un-normalised sums (k x cols, as double) and counts of one labelled shard:
+ * the quantity calculate_centroids produces (src/gpu/kmeans/kmeans_centroids.h:40-75) */
+int kmeans_centroid_sums_f32(int gpu_id, const float* X, const int32_t* labels, size_t rows,
+                             size_t cols, int k, double* sums, int64_t* counts);
+int kmeans_centroid_sums_f64(int gpu_id, const double* X, const int32_t* labels, size_t rows,
+                             size_t cols, int k, double* sums, int64_t* counts);
+
+/* ---- 4. synthetic data on the device (benchmark inputs too large for the host)
+ * Fills dX (rows x cols row-major on the current device `gpu_id`) with
+ * centers[comp(row)] + sigma * N(0,1); comp drawn from `weights` (NULL = equal).
+ * kind 1 instead draws the image-like distribution (0 w.p. 0.8 else 1..255).
+ * row0 = global index of the first row, so shards of one matrix are disjoint
+ * streams of one counter-based generator. */
+int kmeans_synth_f32(int gpu_id, float* dX, size_t rows, size_t cols, size_t row0, int kind,
+                     const float* centers_host, int n_comp, const float* weights_host,
+                     float sigma, uint64_t seed);
+int kmeans_synth_f64(int gpu_id, double* dX, size_t rows, size_t cols, size_t row0, int kind,
+                     const double* centers_host, int n_comp, const double* weights_host,
+                     double sigma, uint64_t seed);
+
+#ifdef __cplusplus
+} /* extern "C" */
+
+/* C++-linkage spellings of the reference's header, forwarded to the above. */
+int make_ptr_float_kmeans(int dopredict, int verbose, int seed, int gpu_id, int n_gpu,
+                          size_t mTrain, size_t n, int k, int max_iterations, int init_from_data,
+                          float threshold, const float* srcdata, const float* centroids,
+                          float** pred_centroids, int** pred_labels);
+int make_ptr_double_kmeans(int dopredict, int verbose, int seed, int gpu_id, int n_gpu,
+                           size_t mTrain, size_t n, int k, int max_iterations,
+                           int init_from_data, double threshold, const double* srcdata,
+                           const double* centroids, double** pred_centroids, int** pred_labels);
+int kmeans_transform_float(int verbose, int gpu_id, int n_gpu, size_t m, size_t n, int k,
+                           const float* srcdata, const float* centroids, float** preds);
+int kmeans_transform_double(int verbose, int gpu_id, int n_gpu, size_t m, size_t n, int k,
+                            const double* srcdata, const double* centroids, double** preds);
+#endif
+
+#endif /* H2O4GPU_KMEANS_H_ */

@@ -1,0 +1,385 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI.
+
+Tolerances (stated by the task for this path): final centroids within 1e-4
+relative for float32 and 1e-10 for float64; labels identical except rows whose
+two nearest-centre squared distances differ by less than 1e-5 relative, which
+are counted.  "Relative" for a centroid table is max|diff| / max|reference|.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+
+from conftest import GOLDEN_CASES, load_golden
+from oracle import cref, lloyd
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 1e-4
+F64_TOL = 1e-10
+GAP_REL = 1e-5
+
+
+def rel_err(a, ref):
+    return float(np.abs(np.asarray(a, np.float64) - ref).max() / max(np.abs(ref).max(), 1e-300))
+
+
+def check_labels(X, C, got, want, allow_frac=0.0):
+    """Mismatches must all be near ties (gap < 1e-5 relative); returns their count."""
+    bad = np.flatnonzero(got != want)
+    if bad.size == 0:
+        return 0
+    tie = lloyd.near_tie_mask(X[bad], C, rel=GAP_REL)
+    hard = int((~tie).sum())
+    assert hard <= allow_frac * X.shape[0], "%d label mismatches outside the near-tie band" % hard
+    return int(bad.size)
+
+
+@pytest.fixture(scope="module")
+def eng(built_lib):
+    import h2o4gpu_b200.engine as e
+    return e
+
+
+def one_step(eng, X, C, flags=0, dtype=None):
+    """One Lloyd iteration on the GPU from centres C: (C_new, labels of the E-step)."""
+    dtype = X.dtype if dtype is None else dtype
+    h = eng.ResidentKMeans(dtype=dtype)
+    h.upload(X)
+    h.fit(C, 1, flags=flags | eng.FIT_NO_FINAL_ASSIGN)
+    out = h.centroids(), h.labels(), h.stats()
+    h.close()
+    return out
+
+
+# ---- golden fixtures (scikit-learn = the reference's CPU path) --------------------
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_golden_fit_f64(eng, name):
+    g = load_golden(name)
+    X = g["X"].astype(np.float64)
+    init = g["init"].astype(np.float64)
+    h = eng.ResidentKMeans(dtype=np.float64)
+    h.upload(X)
+    h.fit(init, int(g["T"]))
+    C, lab = h.centroids(), h.labels()
+    ref = g["centers_f64"]
+    if name.startswith("empty"):
+        perm = lloyd.match_centers(ref, C)   # relocated cluster ids may be permuted
+        assert rel_err(C[perm], ref) < F64_TOL
+        inv = np.empty_like(perm)
+        inv[perm] = np.arange(perm.size)
+        assert np.array_equal(inv[lab], g["labels_f64"])
+        assert h.stats()["relocations"] == 2
+    else:
+        assert rel_err(C, ref) < F64_TOL
+        assert np.array_equal(lab, g["labels_f64"])
+    assert abs(h.inertia() / float(g["inertia_f64"]) - 1) < 1e-9
+    h.close()
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_golden_fit_f32(eng, name):
+    g = load_golden(name)
+    X, init = g["X"], g["init"]
+    h = eng.ResidentKMeans(dtype=np.float32)
+    h.upload(X)
+    h.fit(init, int(g["T"]))
+    C, lab = h.centroids(), h.labels()
+    ref = g["centers_f32"].astype(np.float64)
+    want = g["labels_f32"]
+    if name.startswith("empty"):
+        perm = lloyd.match_centers(ref, C)
+        C = C[perm]
+        inv = np.empty_like(perm)
+        inv[perm] = np.arange(perm.size)
+        lab = inv[lab]
+    assert rel_err(C, ref) < F32_TOL
+    check_labels(X, ref, lab, want)
+    h.close()
+
+
+# ---- reference entry points with host pointers -------------------------------------
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_abi_fit_predict_transform(built_lib, dtype):
+    from h2o4gpu_b200.libs import lib_kmeans
+    lib = lib_kmeans.get()
+    g = load_golden("blobs_n2000_d32_k8")
+    tag = "f32" if dtype == np.float32 else "f64"
+    X = g["X"].astype(dtype)
+    init = g["init"].astype(dtype)
+    rows, cols = X.shape
+    k = init.shape[0]
+    centers = np.zeros(k * cols, dtype)
+    labels = np.zeros(rows, np.int32)
+    fn = lib.make_ptr_float_kmeans if dtype == np.float32 else lib.make_ptr_double_kmeans
+    fn(0, 0, 0, 0, 1, rows, cols, k, int(g["T"]), 2, 0.0, X.reshape(-1), init.reshape(-1), centers, labels)
+    C = centers.reshape(k, cols)
+    ref = g["centers_" + tag].astype(np.float64)
+    assert rel_err(C, ref) < (F32_TOL if dtype == np.float32 else F64_TOL)
+    check_labels(X, ref, labels, g["labels_" + tag])
+    # predict with the oracle's centres
+    pl = np.zeros(rows, np.int32)
+    fn(1, 0, 0, 0, 1, rows, cols, k, 0, 0, 0.0, X.reshape(-1), g["centers_" + tag].astype(dtype).reshape(-1),
+       np.empty([], dtype), pl)
+    check_labels(X, ref, pl, g["predict_" + tag])
+    # transform: squared, column-major over the whole matrix
+    tr = np.zeros(rows * k, dtype)
+    tf = lib.kmeans_transform_float if dtype == np.float32 else lib.kmeans_transform_double
+    tf(0, 0, 1, rows, cols, k, X.reshape(-1), g["centers_" + tag].astype(dtype).reshape(-1), tr)
+    D = tr.reshape((rows, k), order="F")
+    want = g["transform_" + tag].astype(np.float64) ** 2
+    tol = 1e-4 if dtype == np.float32 else 1e-10
+    floor = np.finfo(dtype).eps * ((X[:64].astype(np.float64) ** 2).sum(1)[:, None] + (ref ** 2).sum(1)[None, :])
+    assert (np.abs(D[:64] - want) <= tol * want + 8 * floor).all()
+    colmajor = lloyd.transform_sq_colmajor(X, ref)
+    assert np.abs(tr - colmajor).max() <= tol * colmajor.max()
+
+
+def test_abi_library_allocates_when_output_null(built_lib):
+    from h2o4gpu_b200.libs import lib_kmeans
+    lib = lib_kmeans.cdll()
+    g = load_golden("blobs_n600_d5_k4")
+    X, init = g["X"], g["init"]
+    pc, pl = ctypes.c_void_p(), ctypes.c_void_p()
+    rc = lib.kmeans_fit_f32(0, 0, 0, 1, X.shape[0], X.shape[1], 4, 10, 2, 0.0, X.ctypes.data_as(ctypes.c_void_p),
+                            init.ctypes.data_as(ctypes.c_void_p), ctypes.byref(pc), ctypes.byref(pl))
+    assert rc == 0 and pc.value and pl.value
+    C = np.ctypeslib.as_array(ctypes.cast(pc, ctypes.POINTER(ctypes.c_float)), (4, 5)).copy()
+    assert rel_err(C, g["centers_f32"].astype(np.float64)) < F32_TOL
+    lib.kmeans_free(pc)
+    lib.kmeans_free(pl)
+
+
+def test_abi_errors(built_lib):
+    from h2o4gpu_b200.libs import lib_kmeans
+    lib = lib_kmeans.cdll()
+    X = np.zeros((4, 2), np.float32)
+    pc, pl = ctypes.c_void_p(), ctypes.c_void_p()
+    rc = lib.kmeans_fit_f32(0, 0, 0, 1, 4, 2, 0, 5, 0, 0.0, X.ctypes.data_as(ctypes.c_void_p), None,
+                            ctypes.byref(pc), ctypes.byref(pl))
+    assert rc == -1 and b"bad argument" in lib.kmeans_last_error()
+    rc = lib.kmeans_fit_f32(0, 0, 0, 1, 4, 2, 2, 5, 2, 0.0, X.ctypes.data_as(ctypes.c_void_p), None,
+                            ctypes.byref(pc), ctypes.byref(pl))
+    assert rc == -1
+    X[1, 1] = np.nan
+    rc = lib.kmeans_fit_f32(0, 0, 0, 1, 4, 2, 2, 5, 0, 0.0, X.ctypes.data_as(ctypes.c_void_p), None,
+                            ctypes.byref(pc), ctypes.byref(pl))
+    assert rc == -6 and b"NaN" in lib.kmeans_last_error()
+
+
+# ---- the reference's kernel tests, re-expressed -------------------------------------
+def test_ref_calculate_centroids_gpu(eng):
+    # tests/cpp/gpu/kmeans/test_kmeans_centroids.cu:7-78
+    X = np.array([[0, 0], [0, 1], [1, 1], [1, 0]], np.float32)
+    sums, counts = eng.centroid_sums(X, np.array([0, 0, 1, 1], np.int32), 2)
+    assert np.array_equal(sums, [[0, 1], [2, 1]]) and np.array_equal(counts, [2, 2])
+
+
+def test_ref_two_shards_add_up_gpu(eng):
+    # test_kmeans_centroids.cu:82-251
+    Xa = np.array([[4, 2], [1, 0], [4, 0]], np.float32)
+    Xb = np.array([[4, 4], [1, 4], [1, 2]], np.float32)
+    la, lb = np.array([0, 0, 0], np.int32), np.array([0, 1, 1], np.int32)
+    sa, ca = eng.centroid_sums(Xa, la, 2)
+    sb, cb = eng.centroid_sums(Xb, lb, 2)
+    s, c = eng.centroid_sums(np.vstack([Xa, Xb]), np.r_[la, lb], 2)
+    assert np.array_equal(sa + sb, s) and np.array_equal(ca + cb, c)
+    assert np.array_equal(s, [[13, 6], [2, 6]])
+
+
+def test_ref_counts_per_centroid_gpu(eng):
+    # tests/cpp/gpu/kmeans/test_kmeans_h2o4gpu.cu:67-174
+    X = np.array([[0, 0], [2, 2], [2, 3], [3, 2]], np.float32)
+    h = eng.ResidentKMeans()
+    h.upload(X)
+    h.set_centroids(np.array([[0, 0], [2, 2]], np.float32))
+    h.assign()
+    assert np.bincount(h.labels(), minlength=2).tolist() == [1, 3]
+    P = np.array([[1, 2], [1, 4], [1, 0], [4, 2], [4, 4], [4, 0]], np.float32)
+    h.upload(P)
+    h.set_centroids(P)
+    h.assign()
+    assert h.labels().tolist() == [0, 1, 2, 3, 4, 5]
+    h.close()
+
+
+def test_ref_copy_data_orders_gpu(eng):
+    # test_kmeans_h2o4gpu.cu:9-65: row- and column-major sources give the same shard
+    X = np.arange(9, dtype=np.float32).reshape(3, 3)
+    C = np.array([[0, 1, 2], [6, 7, 8]], np.float32)
+    for order in ("r", "c"):
+        h = eng.ResidentKMeans()
+        h.upload(X, order=order)
+        h.set_centroids(C)
+        h.assign()
+        D = h.transform()
+        assert np.allclose(D, lloyd.transform_sq_exact(X, C))
+        assert h.labels().tolist() == [0, 0, 1]     # row 1 is equidistant: first minimum wins
+        h.close()
+
+
+def test_ref_scaling_and_empty_rule_gpu(eng):
+    # test_kmeans_centroids.cu:308-346 (sums/counts) through one full step; and the CPU
+    # path's empty rule instead of revert_zeroed_centroids (:253-306)
+    X = np.array([[1, 2], [0, 0], [0, 0], [0, 0], [1, 2], [2, 2]], np.float32)
+    C0 = np.array([[0.1, 0.1], [1.5, 2.0], [50, 50]], np.float32)
+    C, lab, st = one_step(eng, X, C0)
+    Cn, labn, _, moved = lloyd.step(X, C0.astype(np.float64), order="descending")
+    assert np.array_equal(lab, labn) and st["relocations"] == len(moved) == 1
+    assert rel_err(C, Cn) < 1e-6
+
+
+# ---- teacher-forced parity on the benchmark distributions ---------------------------
+CASES = [
+    ("c1", dict(n=20000), 6),
+    ("c2", dict(n=30000), 5),
+    ("c3", dict(n=20000), 3),
+    ("c4", dict(n=4000), 4),
+    ("c5", dict(n=9000), 2),
+]
+
+
+@pytest.mark.parametrize("cfg,kw,steps", CASES)
+def test_teacher_forced_f32(eng, cfg, kw, steps):
+    from h2o4gpu_b200 import synth
+    X, init, _ = synth.CONFIGS[cfg](**kw)
+    C = init.astype(np.float64)
+    h = eng.ResidentKMeans(dtype=np.float32)
+    h.upload(X)
+    ties = 0
+    for _ in range(steps):
+        C32 = C.astype(np.float32)
+        Cn, labn, _, moved = lloyd.step(X, C32.astype(np.float64), order="descending")
+        h.fit(C32, 1, flags=eng.FIT_NO_FINAL_ASSIGN)
+        got, lab = h.centroids(), h.labels()
+        bad = check_labels(X, C32.astype(np.float64), lab, labn)
+        ties += bad
+        if bad == 0:
+            assert rel_err(got, Cn) < F32_TOL
+            assert h.stats()["relocations"] == len(moved)
+        C = Cn
+    h.close()
+    print("near-tie label differences over the run:", ties)
+
+
+@pytest.mark.parametrize("cfg,kw,steps", [("c2", dict(n=20000), 8), ("c5", dict(n=6000, k=512), 3),
+                                          ("c4", dict(n=3000), 6)])
+def test_end_to_end_f64(eng, cfg, kw, steps):
+    from h2o4gpu_b200 import synth
+    X, init, _ = synth.CONFIGS[cfg](dtype=np.float64, **kw)
+    r = lloyd.fit(X, init, steps, dtype=np.float64, center=False, order="descending", stop_on_repeat=False)
+    h = eng.ResidentKMeans(dtype=np.float64)
+    h.upload(X)
+    h.fit(init, steps)
+    assert rel_err(h.centroids(), r["centers"]) < F64_TOL
+    assert np.array_equal(h.labels(), r["labels"])
+    h.close()
+
+
+def test_fused_and_split_paths_agree_bitwise(eng):
+    from h2o4gpu_b200 import synth
+    X, init, _ = synth.c1(n=30000)
+    a = one_step(eng, X, init)
+    b = one_step(eng, X, init, flags=eng.FIT_FORCE_SPLIT)
+    assert a[2]["path"] == 1 and b[2]["path"] == 2
+    if np.array_equal(a[1], b[1]):
+        assert np.array_equal(a[0], b[0])          # integer sums: same labels -> same bits
+    else:
+        check_labels(X, init.astype(np.float64), a[1], b[1])
+
+
+def test_deterministic_across_runs(eng):
+    from h2o4gpu_b200 import synth
+    X, init, _ = synth.c2(n=40000)
+    outs = []
+    for _ in range(2):
+        h = eng.ResidentKMeans()
+        h.upload(X)
+        h.fit(init, 6)
+        outs.append((h.centroids(), h.labels()))
+        h.close()
+    assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
+
+
+# ---- edge cases ------------------------------------------------------------------------
+@pytest.mark.parametrize("n,d,k", [(1, 1, 1), (3, 2, 2), (5, 3, 5), (129, 7, 3), (257, 33, 17), (1000, 130, 20),
+                                   (300, 4, 16), (300, 4, 18), (2049, 64, 100), (700, 1030, 6)])
+def test_ragged_shapes(eng, n, d, k):
+    rng = np.random.default_rng(n * 1000 + d * 10 + k)
+    X = rng.standard_normal((n, d)).astype(np.float32) * 3
+    init = X[rng.choice(n, k, replace=False)].copy()
+    Cn, labn, _, moved = lloyd.step(X, init.astype(np.float64), order="descending")
+    C, lab, st = one_step(eng, X, init)
+    bad = check_labels(X, init.astype(np.float64), lab, labn)
+    if bad == 0:
+        assert rel_err(C, Cn) < F32_TOL
+        assert st["relocations"] == len(moved)
+
+
+def test_k_larger_than_rows_is_clamped(built_lib):
+    from h2o4gpu_b200 import KMeansH2O
+    X = np.array([[0., 0.], [1., 1.], [5., 5.]], np.float32)
+    m = KMeansH2O(n_clusters=5, init="random", max_iter=3, random_state=1, n_gpus=1).fit(X)
+    assert m.cluster_centers_.shape == (3, 2)      # src/gpu/kmeans/kmeans_h2o4gpu.cu:629-635
+    assert sorted(m.labels_.tolist()) == [0, 1, 2]
+
+
+def test_duplicate_points_more_clusters_than_distinct(eng):
+    X = np.repeat(np.array([[1., 2.], [3., 4.]], np.float32), 10, axis=0)
+    init = np.array([[1, 2], [3, 4], [9, 9]], np.float32)
+    C, lab, st = one_step(eng, X, init)
+    Cn, labn, _, moved = lloyd.step(X, init.astype(np.float64), order="descending")
+    assert np.array_equal(lab, labn) and st["relocations"] == len(moved) == 0   # max distance is 0: nothing moves
+    assert rel_err(C, Cn) < 1e-6                   # the empty cluster copies the largest one
+
+
+def test_tolerance_stops_early(eng):
+    g = load_golden("blobs_n2000_d32_k8")
+    h = eng.ResidentKMeans()
+    h.upload(g["X"])
+    h.fit(g["init"], 50, threshold=1e-3)
+    st = h.stats()
+    assert 0 < st["iterations"] < 50 and st["last_shift_sq"] < 1e-3
+    h.fit(g["init"], 50, flags=eng.FIT_CHECK_EVERY_ITER)
+    assert h.stats()["iterations"] == int(g["n_iter_f32"])     # stops when labels repeat, like the CPU path
+    h.close()
+
+
+# ---- estimator -------------------------------------------------------------------------
+def test_estimator_matches_cpu_backend(built_lib):
+    import h2o4gpu_b200
+    g = load_golden("blobs_n2000_d32_k8")
+    X, init = g["X"], g["init"]
+    gpu = h2o4gpu_b200.KMeans(n_clusters=8, init=init, max_iter=int(g["T"]), tol=0.0, n_gpus=1).fit(X)
+    cpu = h2o4gpu_b200.KMeans(n_clusters=8, init=init, max_iter=int(g["T"]), tol=0.0, n_gpus=0).fit(X)
+    assert rel_err(gpu.cluster_centers_, cpu.cluster_centers_.astype(np.float64)) < F32_TOL
+    check_labels(X, cpu.cluster_centers_.astype(np.float64), gpu.labels_, cpu.labels_)
+    assert np.array_equal(gpu.predict(X), gpu.labels_)
+    D = gpu.transform(X)
+    assert D.shape == (2000, 8)
+    assert np.allclose(np.sqrt(D), cpu.transform(X), rtol=1e-3, atol=1e-2)
+    # README.md:115-133 shapes (R tests: src/interface_r/tests/testthat/test_model.R:5-22)
+    Xs = np.array([[1., 1.], [1., 4.], [1., 0.]])
+    m = h2o4gpu_b200.KMeans(n_clusters=2, random_state=1234).fit(Xs)
+    assert m.cluster_centers_.shape == (2, 2) and m.predict(Xs).shape == (3,) and m.transform(Xs).shape == (3, 2)
+
+
+# ---- several GPUs in one process ------------------------------------------------------
+def test_multi_gpu_equals_single_gpu(eng):
+    from h2o4gpu_b200.libs import lib_kmeans
+    ndev = lib_kmeans.cdll().kmeans_device_count()
+    if ndev < 2:
+        pytest.skip("one GPU visible")
+    from h2o4gpu_b200 import synth
+    X, init, _ = synth.c2(n=50001)
+    h1 = eng.ResidentKMeans()
+    h1.upload(X)
+    h1.fit(init, 5)
+    h2 = eng.ResidentKMeans(devices=list(range(min(ndev, 4))))
+    h2.upload(X)
+    h2.fit(init, 5)
+    assert h1.stats()["relocations"] == h2.stats()["relocations"] > 0
+    assert np.array_equal(h1.centroids(), h2.centroids())      # integer sums: bit-identical
+    assert np.array_equal(h1.labels(), h2.all_labels())
+    h1.close()
+    h2.close()
