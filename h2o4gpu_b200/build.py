@@ -43,7 +43,7 @@ def build(force=False, verbose=False):
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
            "-shared", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
-           "-o", LIB] + _nccl_include() + [os.path.join(CSRC, s) for s in SOURCES] + ["-ldl", "-lcuda"]
+           "-o", LIB] + _nccl_include() + [os.path.join(CSRC, s) for s in SOURCES] + ["-ldl"]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
         print(" ".join(cmd))

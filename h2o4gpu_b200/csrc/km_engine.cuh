@@ -19,7 +19,10 @@
 #include "km_finalize.cuh"
 #include "km_nccl.h"
 #include "km_smallk.cuh"
+#include "km_tc_host.cuh"
 #include "km_tiles.cuh"
+
+#include <type_traits>
 
 namespace km {
 
@@ -46,6 +49,8 @@ template <typename T>
 struct Shard {
   int dev = -1;
   int num_sms = 0;
+  int cc_major = 0;
+  tc::Plan tcp;  // tensor-core path (float only)
   cudaStream_t stream = nullptr;
   const T* X = nullptr;
   T* X_owned = nullptr;
@@ -114,6 +119,10 @@ struct Engine : EngineBase {
   int inertia(double* out);
   int allreduce_acc();
   int relocate_multi(double scale);
+  bool tc_ok(int flags) const;
+  int tc_refresh(Shard<T>& s);  // split the current centroids for the tensor-core kernel
+  int launch_assign(Shard<T>& s, bool use_tc, bool count_changes);
+  int tc_mask_hi = 1;
 
   // launch helpers (device of the shard must be current)
   int launch_tiles(Shard<T>& s, const T* Xp, size_t nrows, int* labels, int mode, T* out, size_t ld_out,
@@ -146,6 +155,7 @@ int Engine<T>::init(int n_local, const int* devs, int rank0, int world, const vo
     cudaDeviceProp prop;
     KM_CUDA(cudaGetDeviceProperties(&prop, s.dev));
     s.num_sms = prop.multiProcessorCount;
+    s.cc_major = prop.major;
     KM_CUDA(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
     KM_CUDA(cudaMalloc(&s.st, sizeof(IterState)));
     KM_CUDA(cudaMemset(s.st, 0, sizeof(IterState)));
@@ -188,6 +198,7 @@ void Engine<T>::destroy() {
       NcclApi* api = NcclApi::get();
       if (api) api->CommDestroy(s.comm);
     }
+    s.tcp.release();
     cudaFree(s.X_owned); cudaFree(s.labels); cudaFree(s.dist); cudaFree(s.gacc);
     cudaFree(s.C[0]); cudaFree(s.C[1]); cudaFree(s.cnorm); cudaFree(s.shift_k); cudaFree(s.empties);
     cudaFree(s.st); cudaFree(s.cand_val); cudaFree(s.cand_row); cudaFree(s.sum_partials);
@@ -515,6 +526,38 @@ int Engine<T>::launch_accumulate(Shard<T>& s, T scale) {
   KM_CUDA(cudaGetLastError());
   ++launches;
   return KM_OK;
+}
+
+// The tcgen05 kernel serves float32 shards with d in {32, 64} and 16 < k <= 128 on
+// compute capability 10.x; everything else runs on the SIMT kernels.
+template <typename T>
+bool Engine<T>::tc_ok(int flags) const {
+  if (!std::is_same<T, float>::value || (flags & KM_FIT_FORCE_SIMT)) return false;
+  if (!tc::shape_ok(k, d)) return false;
+  for (const auto& s : shards)
+    if (s.cc_major != 10 || (reinterpret_cast<uintptr_t>(s.X) & 15) != 0) return false;
+  return true;
+}
+
+template <typename T>
+int Engine<T>::tc_refresh(Shard<T>& s) {
+  if constexpr (std::is_same<T, float>::value) {
+    KM_TRY(tc::setup(s.tcp, s.X, s.rows, k, d));
+    KM_TRY(tc::prep(s.tcp, s.C[cur], s.cnorm, s.stream));
+    ++launches;
+  }
+  return KM_OK;
+}
+
+template <typename T>
+int Engine<T>::launch_assign(Shard<T>& s, bool use_tc, bool count_changes) {
+  if constexpr (std::is_same<T, float>::value) {
+    if (use_tc) {
+      ++launches;
+      return tc::launch(s.tcp, s.labels, s.st, count_changes, s.num_sms, tc_mask_hi, s.stream);
+    }
+  }
+  return launch_tiles(s, s.X, s.rows, s.labels, MODE_ASSIGN, nullptr, 0, count_changes);
 }
 
 template <typename T>

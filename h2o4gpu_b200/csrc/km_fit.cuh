@@ -44,7 +44,9 @@ int Engine<T>::assign_all(int flags) {
       s.st = keep;
       KM_TRY(rc);
     } else {
-      KM_TRY(launch_tiles(s, s.X, s.rows, s.labels, MODE_ASSIGN, nullptr, 0, false));
+      const bool use_tc = tc_ok(flags);
+      if (use_tc) KM_TRY(tc_refresh(s));
+      KM_TRY(launch_assign(s, use_tc, false));
     }
   }
   return KM_OK;
@@ -128,10 +130,12 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
   if (!std::isfinite((double)scale) || scale == (T)0) KM_FAIL(KM_EINVAL, "data magnitude outside the supported range");
 
   const bool fused = smallk_ok(true) && !(flags & KM_FIT_FORCE_SPLIT);
+  const bool use_tc = !fused && tc_ok(flags);
+  if (const char* e = std::getenv("H2O4GPU_KM_TC_MASK_HI")) tc_mask_hi = std::atoi(e);
   const bool multi = world_size > 1;
   const bool check = (threshold > 0) || (flags & KM_FIT_CHECK_EVERY_ITER);
   stats = kmeans_stats{};
-  stats.path = fused ? 1 : 2;
+  stats.path = fused ? 1 : (use_tc ? 3 : 2);
   stats.inertia = -1;
 
   for (auto& s : shards) {
@@ -140,6 +144,7 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
     if (!multi) KM_TRY(ensure_dist(s));
     KM_CUDA(cudaMemsetAsync(s.st, 0, sizeof(IterState), s.stream));
     KM_CUDA(cudaMemsetAsync(s.labels, 0xff, s.rows * sizeof(int), s.stream));
+    if (use_tc) KM_TRY(tc_refresh(s));
   }
 
   // events on shard 0: [4*it + 0..3] = start, after E-step, after sums, after close
@@ -166,7 +171,7 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
         rc = launch_smallk(s, true, scale);
         if (i == 0) { cudaEventRecord(ev[4 * it + 1], s.stream); cudaEventRecord(ev[4 * it + 2], s.stream); }
       } else {
-        rc = launch_tiles(s, s.X, s.rows, s.labels, MODE_ASSIGN, nullptr, 0, true);
+        rc = launch_assign(s, use_tc, true);
         if (i == 0) cudaEventRecord(ev[4 * it + 1], s.stream);
         if (rc == KM_OK) rc = launch_accumulate(s, scale);
         if (i == 0) cudaEventRecord(ev[4 * it + 2], s.stream);
@@ -217,6 +222,13 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
     }
     if (rc != KM_OK) break;
     cur ^= 1;
+    if (use_tc) {
+      for (size_t i = 0; i < shards.size() && rc == KM_OK; ++i) {
+        DevGuard g(shards[i].dev);
+        rc = tc_refresh(shards[i]);
+      }
+      if (rc != KM_OK) break;
+    }
     if (check) {
       DevGuard g(s0.dev);
       cudaError_t ce = cudaStreamSynchronize(s0.stream);
@@ -247,6 +259,17 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
     DevGuard g(s.dev);
     cudaError_t ce = cudaStreamSynchronize(s.stream);
     if (ce != cudaSuccess) { set_error(std::string("fit sync: ") + cudaGetErrorString(ce)); free_events(); return KM_ECUDA; }
+  }
+  for (auto& s : shards) {
+    DevGuard g(s.dev);
+    IterState hs;
+    cudaError_t ce = cudaMemcpy(&hs, s.st, sizeof(hs), cudaMemcpyDeviceToHost);
+    if (ce != cudaSuccess) { set_error(std::string("fit state: ") + cudaGetErrorString(ce)); free_events(); return KM_ECUDA; }
+    if (hs.error != 0) {
+      set_error("a bounded device-side wait gave up (code " + std::to_string(hs.error) + ")");
+      free_events();
+      return KM_ETIMEOUT;
+    }
   }
   // logs -> stats
   {
