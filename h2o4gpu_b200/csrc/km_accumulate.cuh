@@ -66,14 +66,15 @@ accumulate_kernel(const T* __restrict__ X, size_t n, int d, const int* __restric
     for (unsigned int base = tid; base < items; base += kAccThreads * UNROLL) {
       T x[UNROLL][V];
       int lab[UNROLL];
-      unsigned int col[UNROLL];
+      unsigned int col[UNROLL], rowu[UNROLL];
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         unsigned int idx = base + u * kAccThreads;
         lab[u] = -1;
         if (idx < items) {
           unsigned int row = (unsigned int)(((unsigned long long)idx * dv_magic) >> 40);
-          col[u] = (idx - row * dv) * V;
+          col[u] = idx - row * dv;  // vector index within the row
+          rowu[u] = row;
           VecLoad<T, V>::ld(Xp + (size_t)idx * V, x[u]);
           lab[u] = Lp[row];
           if (col[u] == 0) atomicAdd(&cnt[lab[u]], 1);
@@ -82,14 +83,7 @@ accumulate_kernel(const T* __restrict__ X, size_t n, int d, const int* __restric
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         if (lab[u] < 0) continue;
-        int* a = acc + (size_t)lab[u] * d + col[u];
-#pragma unroll
-        for (int e = 0; e < V; ++e) {
-          int p[NP];
-          split_pieces<NP>(x[u][e], scale, p);
-#pragma unroll
-          for (int q = 0; q < NP; ++q) atomicAdd(a + q * pstride + e, p[q]);
-        }
+        add_vec_fixed<T, V, NP>(acc + (size_t)lab[u] * d, pstride, dv, (int)col[u], (int)rowu[u] & (V - 1), x[u], scale);
       }
     }
   } else {
@@ -117,13 +111,7 @@ accumulate_kernel(const T* __restrict__ X, size_t n, int d, const int* __restric
           for (int idx = l; idx < dv; idx += lpr) {
             T x[V];
             VecLoad<T, V>::ld(xr + (size_t)idx * V, x);
-#pragma unroll
-            for (int e = 0; e < V; ++e) {
-              int p[NP];
-              split_pieces<NP>(x[e], scale, p);
-#pragma unroll
-              for (int q = 0; q < NP; ++q) atomicAdd(a + q * pstride + idx * V + e, p[q]);
-            }
+            add_vec_fixed<T, V, NP>(a, pstride, dv, idx, g & (V - 1), x, scale);
           }
         }
         for (int i = 0; i < groups && mask; ++i) mask &= mask - 1;
@@ -134,11 +122,13 @@ accumulate_kernel(const T* __restrict__ X, size_t n, int d, const int* __restric
 
   const int kloc = c1 - c0;
   for (int i = tid; i < kloc * d; i += kAccThreads) {
+    const int c = i / d;
+    const int col = pos_to_col(i - c * d, dv, V);
 #pragma unroll
     for (int q = 0; q < NP / 2; ++q) {
       long long v = (long long)acc[(size_t)(2 * q) * pstride + i] * (1LL << kPieceBits) +
                     (long long)acc[(size_t)(2 * q + 1) * pstride + i];
-      if (v) atomicAdd(reinterpret_cast<unsigned long long*>(gsums + (size_t)q * k * d + (size_t)c0 * d + i),
+      if (v) atomicAdd(reinterpret_cast<unsigned long long*>(gsums + (size_t)q * k * d + (size_t)(c0 + c) * d + col),
                        (unsigned long long)v);
     }
   }

@@ -2,7 +2,7 @@
 //
 // Scores |c|^2 - 2 x.c for a 128-row tile of X against all centroids are formed
 // on the 5th-generation tensor cores as a 3xTF32 product so that fp32 accuracy
-// is kept:   x = xh + xl,  -2c = bh + bl  (h = upper 11 significand bits)
+// is kept:   x = xh + xl,  -2c = bh + bl  (h = nearest TF32 value, l = rounded rest)
 //            acc = xh.bh + xl.bh + xh.bl          (fp32 accumulation in TMEM)
 // and the epilogue adds |c|^2 and takes the running argmin, so the rows x k
 // distance matrix never exists.  Replaces calculate_distances + relabel
@@ -13,14 +13,14 @@
 //   warp 0      TMA producer: raw fp32 X tiles (128 x d, 128B-swizzled panels of
 //               32 columns) into a 4-stage shared-memory ring; the split
 //               centroid table (bh, bl) is loaded once per CTA and stays resident.
-//   warps 2-5   converters: thread r reads row r of the tile (conflict-free
+//   warps 2-9   converters (two groups of four, alternating tiles): thread r reads row r of the tile (conflict-free
 //               thanks to the swizzle), splits it and writes xh / xl into TMEM
 //               with tcgen05.st - the A operand of the MMA lives in TMEM, so
 //               the tensor core reads only the centroid panels from shared memory.
 //   warp 1      MMA issuer: 3 * d/8 tcgen05.mma (M=128, N=kpad, K=8) per tile into
 //               one of two TMEM accumulators; tcgen05.commit releases the A
 //               buffer and publishes the accumulator.
-//   warps 6-9   epilogue: tcgen05.ld, + |c|^2, argmin (first minimum wins),
+//   warps 10-17 epilogue (two groups, one per accumulator): tcgen05.ld, + |c|^2, argmin (first minimum wins),
 //               label store, changed-label count.
 // Every mbarrier wait is bounded (wall-clock limit); on a timeout the CTA sets an
 // error word, drains its copies, frees its TMEM and returns.
@@ -34,12 +34,13 @@ namespace km {
 namespace tc {
 
 constexpr int kBM = 128;
-constexpr int kThreads = 320;
+constexpr int kThreads = 576;  // producer, MMA issuer, 2 x 4 converter warps, 2 x 4 epilogue warps
 constexpr int kStages = 4;
 constexpr int kMaxD = 64;
 constexpr int kMaxNPad = 128;
 constexpr int kTmemCols = 512;
-constexpr unsigned long long kWaitLimitNs = 2000000000ULL;  // 2 s
+constexpr unsigned long long kWaitLimitNs = 2000000000ULL;  // 2 s (abort drain loops)
+constexpr long long kWaitLimitClk = 6000000000LL;          // about 3 s of SM clocks
 
 enum Bar { FULL = 0, EMPTY = kStages, A_READY = 2 * kStages, A_EMPTY = 2 * kStages + 2,
            ACC_FULL = 2 * kStages + 4, ACC_EMPTY = 2 * kStages + 6, B_FULL = 2 * kStages + 8,
@@ -47,7 +48,8 @@ enum Bar { FULL = 0, EMPTY = kStages, A_READY = 2 * kStages, A_EMPTY = 2 * kStag
 
 inline size_t smem_bytes(int d, int npad) {
   size_t P = d / 32;
-  return 1024 + 2 * P * (size_t)npad * 128 + (size_t)kStages * P * 16384 + (size_t)npad * 4 + NUM_BARS * 8 + 64;
+  return 1024 + 2 * P * (size_t)npad * 128 + (size_t)kStages * P * 16384 + (size_t)npad * 4 + 2 * kBM * 4 +
+         NUM_BARS * 8 + 64;
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -81,12 +83,17 @@ __device__ __forceinline__ unsigned long long gtime_ns() {
 // one gave up); the caller leaves its loop.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
   if (mbar_try(bar, parity)) return true;
-  const unsigned long long t0 = gtime_ns();
+  // Back off between polls: a spinning warp would otherwise take issue slots from
+  // the warps doing the arithmetic on the same scheduler.
+  long long t0 = 0;
   for (unsigned int it = 1;; ++it) {
+    __nanosleep(it < 64 ? 20 : 100);
     if (mbar_try(bar, parity)) return true;
-    if ((it & 255u) == 0) {
+    if ((it & 4095u) == 0) {
       if (*abort_flag) return false;
-      if (gtime_ns() - t0 > kWaitLimitNs) {
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kWaitLimitClk) {
         *abort_flag = code;
         return false;
       }
@@ -158,6 +165,12 @@ __device__ __forceinline__ void tmem_wait_ld(uint32_t (&v)[32]) {
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// x rounded to the nearest TF32 value (11 significand bits, ties away from zero);
+// the low 13 bits of the result are zero, so the tensor core reads it exactly.
+__device__ __forceinline__ float tf32_rn(float x) {
+  return __uint_as_float((__float_as_uint(x) + 0x00001000u) & 0xffffe000u);
+}
+
 // Split centroid table for the tensor-core kernel: bh/bl = split(-2 c), rows
 // k..npad-1 zero with |c|^2 = +inf so that padding never wins the argmin.
 __global__ void __launch_bounds__(64)
@@ -166,20 +179,25 @@ prep_kernel(const float* __restrict__ C, const float* __restrict__ cnorm, int k,
   const int j = blockIdx.x;
   for (int t = threadIdx.x; t < d; t += blockDim.x) {
     float v = (j < k) ? -2.0f * C[(size_t)j * d + t] : 0.0f;
-    float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+    float h = tf32_rn(v);
     bhi[(size_t)j * d + t] = h;
-    blo[(size_t)j * d + t] = v - h;
+    blo[(size_t)j * d + t] = tf32_rn(v - h);
   }
-  if (threadIdx.x == 0) cnorm_pad[j] = (j < k) ? cnorm[j] : __int_as_float(0x7f800000);
+  if (threadIdx.x == 0) {
+    cnorm_pad[j] = (j < k) ? cnorm[j] : __int_as_float(0x7f800000);
+    // slot npad (zeroed before the launch) receives max |c|^2; non-negative floats order as ints
+    if (j < k) atomicMax(reinterpret_cast<int*>(cnorm_pad + npad), __float_as_int(cnorm[j]));
+  }
 }
 
-// mask_hi: 1 = store the upper part of x with its low 13 bits cleared, 0 = store x
-// itself and rely on the tensor core ignoring those bits.
+// Both halves of every operand are rounded to TF32 before they reach the tensor
+// core, so the result does not depend on how the hardware treats the low 13 bits
+// (measured on B200: it ignores them).  mask_hi is kept for experiments.
 __global__ void __launch_bounds__(kThreads, 1)
 assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmBhi,
                  const __grid_constant__ CUtensorMap tmBlo, const float* __restrict__ cnorm_pad,
                  int* __restrict__ labels, size_t n, int n_tiles, int d, int npad, IterState* st,
-                 int* __restrict__ err, int mask_hi) {
+                 int count_changes, unsigned int* __restrict__ amb_rows, float tol_rel, int mask_hi) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_u32 = smem_u32(smem_raw);
   const uint32_t base = (raw_u32 + 1023u) & ~1023u;
@@ -191,9 +209,11 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   const uint32_t off_stage = 2u * P * b_panel;
   const uint32_t stage_bytes = (uint32_t)P * 16384u;
   const uint32_t off_cn = off_stage + kStages * stage_bytes;
-  const uint32_t off_bar = (off_cn + (uint32_t)npad * 4u + 7u) & ~7u;
+  const uint32_t off_xn = off_cn + (uint32_t)npad * 4u;
+  const uint32_t off_bar = (off_xn + 2u * kBM * 4u + 7u) & ~7u;
   const uint32_t off_misc = off_bar + NUM_BARS * 8;
   float* cn_s = reinterpret_cast<float*>(sm + off_cn);
+  float* xn_s = reinterpret_cast<float*>(sm + off_xn);  // [2][128] |x|^2 of the rows in A buffer b
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(sm + off_misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + off_misc + 4);
   auto bar = [&](int i) { return base + off_bar + (uint32_t)i * 8u; };
@@ -225,6 +245,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  const float cn_max = cnorm_pad[npad];  // largest |c|^2, stored behind the padded table
   // TMEM columns: accumulators at 0 and 128; A buffers b at 256 + 128 b (xh) and + 64 (xl)
   const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(npad >> 3) << 17) | ((128u >> 4) << 24);
 
@@ -282,7 +303,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
               const uint64_t bd = smem_desc_sw128(base + b_off + p * b_panel + kk * 32u);
-              tc_mma_ts(acc, a_col + p * 32u + kk * 8u, bd, idesc, accumulate);
+              if (!(mask_hi & 2)) tc_mma_ts(acc, a_col + p * 32u + kk * 8u, bd, idesc, accumulate);
               accumulate = 1;
             }
           }
@@ -298,15 +319,17 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           if (gtime_ns() - t0 > kWaitLimitNs) break;
       }
     }
-  } else if (warp < 6) {
+  } else if (warp < 10) {
     // ------------------------------ converters --------------------------------
+    // two groups of four warps; group g serves the tiles with i % 2 == g, i.e. A buffer g
+    const int grp = (warp - 2) >> 2;
     const int q = warp & 3;
     const int row = q * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    const uint32_t hi_mask = mask_hi ? 0xffffe000u : 0xffffffffu;
     bool ok = true;
     int i = 0;
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++i) {
+      if ((i & 1) != grp) continue;
       const int s = i % kStages;
       const uint32_t ph = (uint32_t)(i / kStages) & 1u;
       const int b = i & 1;
@@ -318,6 +341,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       tc_fence_after();
       const uint8_t* stage = sm + off_stage + s * stage_bytes;
       const uint32_t a_hi = tmem_base + lane_addr + 256u + (uint32_t)b * 128u;
+      float xn = 0.0f;
       for (int p = 0; p < P; ++p) {
         uint32_t hi[32], lo[32];
         const uint8_t* rowp = stage + p * 16384 + row * 128;
@@ -327,17 +351,22 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           const float xs[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const uint32_t bits = __float_as_uint(xs[e]);
-            const float h = __uint_as_float(bits & 0xffffe000u);
-            hi[c * 4 + e] = bits & hi_mask;
-            lo[c * 4 + e] = __float_as_uint(xs[e] - h);
+            const float h = tf32_rn(xs[e]);
+            xn = fmaf(xs[e], xs[e], xn);
+            hi[c * 4 + e] = __float_as_uint(h);
+            lo[c * 4 + e] = __float_as_uint(tf32_rn(xs[e] - h));
           }
         }
-        tmem_st16(a_hi + p * 32u, hi, 0);
-        tmem_st16(a_hi + p * 32u + 16u, hi, 16);
-        tmem_st16(a_hi + 64u + p * 32u, lo, 0);
-        tmem_st16(a_hi + 64u + p * 32u + 16u, lo, 16);
+        if (!(mask_hi & 8)) {
+          tmem_st16(a_hi + p * 32u, hi, 0);
+          tmem_st16(a_hi + p * 32u + 16u, hi, 16);
+          tmem_st16(a_hi + 64u + p * 32u, lo, 0);
+          tmem_st16(a_hi + 64u + p * 32u + 16u, lo, 16);
+        } else if (hi[3] == 0x12345u && lo[7] == 0x54321u) {
+          labels[0] = 0;  // keeps the loads alive
+        }
       }
+      xn_s[b * kBM + row] = xn;
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar(EMPTY + s));
@@ -345,6 +374,8 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     }
   } else {
     // ------------------------------ epilogue ----------------------------------
+    // two groups of four warps; group g drains accumulator g
+    const int grp = (warp - 10) >> 2;
     const int q = warp & 3;
     const int row_in_tile = q * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
@@ -352,6 +383,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     bool ok = true;
     int i = 0;
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++i) {
+      if ((i & 1) != grp) continue;
       const int b = i & 1;
       const uint32_t phb = (uint32_t)(i >> 1) & 1u;
       ok = mbar_wait(bar(ACC_FULL + b), phb, abort_flag, 7);
@@ -359,41 +391,76 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       if (!ok) break;
       tc_fence_after();
       const uint32_t acc = tmem_base + lane_addr + (uint32_t)b * 128u;
-      float best = __int_as_float(0x7f800000);
-      int bidx = 0;
-      for (int c0 = 0; c0 < npad; c0 += 32) {
-        uint32_t v[32];
+      const float kInf = __int_as_float(0x7f800000);
+      // four interleaved (best, second, index) chains keep the compare/select
+      // dependency short; chain q sees columns j with j % 4 == q in ascending order
+      float bst[4] = {kInf, kInf, kInf, kInf}, sec[4] = {kInf, kInf, kInf, kInf};
+      int bix[4] = {0, 0, 0, 0};
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = 0;
-        const bool two = (c0 + 16 < npad);
-        tmem_ld16(acc + c0, v, 0);
-        if (two) tmem_ld16(acc + c0 + 16, v, 16);
-        tmem_wait_ld(v);
-        const int lim = two ? 32 : 16;
+      for (int ch = 0; ch < kMaxNPad / 32; ++ch) {
+        constexpr int kChunk = 32;
+        const int c0 = ch * kChunk;  // compile-time after unrolling: column indices are immediates
+        if (c0 < npad && !(mask_hi & 4)) {
+          uint32_t v[32];
+          const bool two = (c0 + 16 < npad);
+          tmem_ld16(acc + c0, v, 0);
+          if (two) tmem_ld16(acc + c0 + 16, v, 16);
+          tmem_wait_ld(v);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          if (j < lim) {
-            const float sc = __uint_as_float(v[j]) + cn_s[c0 + j];
-            if (sc < best) { best = sc; bidx = c0 + j; }
+          for (int j4 = 0; j4 < 8; ++j4) {
+            if (j4 < 4 || two) {
+              const float4 cn4 = *reinterpret_cast<const float4*>(cn_s + c0 + j4 * 4);
+              const float cn[4] = {cn4.x, cn4.y, cn4.z, cn4.w};
+#pragma unroll
+              for (int qq = 0; qq < 4; ++qq) {
+                const float sc = __uint_as_float(v[j4 * 4 + qq]) + cn[qq];
+                sec[qq] = fminf(sec[qq], fmaxf(sc, bst[qq]));
+                const bool lt = sc < bst[qq];
+                bst[qq] = lt ? sc : bst[qq];
+                bix[qq] = lt ? (c0 + j4 * 4 + qq) : bix[qq];
+              }
+            }
           }
         }
       }
+      const float xn = xn_s[b * kBM + row_in_tile];
       tc_fence_before();
       mbar_arrive(bar(ACC_EMPTY + b));
+      float best = bst[0], second = sec[0];
+      int bidx = bix[0];
+#pragma unroll
+      for (int qq = 1; qq < 4; ++qq) {
+        if (bst[qq] < best || (bst[qq] == best && bix[qq] < bidx)) {
+          second = fminf(second, best);
+          best = bst[qq];
+          bidx = bix[qq];
+        } else {
+          second = fminf(second, bst[qq]);
+        }
+        second = fminf(second, sec[qq]);
+      }
       const size_t row = (size_t)tile * kBM + row_in_tile;
       if (row < n) {
-        changed += (labels[row] != bidx);
-        labels[row] = bidx;
+        // rows whose two best scores are closer than the error bound of the 3xTF32
+        // product are left to the exact re-evaluation pass
+        const float tol = tol_rel * (xn + cn_max);
+        if (amb_rows != nullptr && !(second - best > tol)) {
+          const unsigned int pos = atomicAdd(&st->amb_count, 1u);
+          amb_rows[pos] = (unsigned int)row;
+        } else {
+          changed += (labels[row] != bidx);
+          labels[row] = bidx;
+        }
       }
     }
-    if (st) {
+    if (count_changes) {
       changed = __reduce_add_sync(0xffffffffu, changed);
       if (lane == 0 && changed) atomicAdd(&st->changed, (unsigned long long)changed);
     }
   }
 
   __syncthreads();
-  if (tid == 0 && *abort_flag) atomicMax(err, *abort_flag);
+  if (tid == 0 && *abort_flag) atomicMax(&st->error, *abort_flag);
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)

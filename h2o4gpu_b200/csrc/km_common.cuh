@@ -86,6 +86,37 @@ __device__ __forceinline__ void split_pieces(double x, double scale, int (&p)[NP
   }
 }
 
+// Shared-memory accumulators of one cluster hold column `col` at position
+//   pos = (col % V) * dv + col / V        (dv = d / V, V = elements per vector load)
+// so that the lanes of a warp, which own consecutive vectors of a row, hit
+// consecutive banks.  When several rows share a warp step, row r starts with
+// element (r % V) of its vector, which spreads the rows over different banks.
+// adds x[0..V) (vector c4 of its row) into the cluster whose piece-0 base is a0.
+template <typename T, int V, int NP>
+__device__ __forceinline__ void add_vec_fixed(int* a0, size_t pstride, int dv, int c4, int rot, const T (&x)[V],
+                                              T scale) {
+  T y[V];
+#pragma unroll
+  for (int e = 0; e < V; ++e) y[e] = x[e];
+  if (V == 4) {
+    if (rot & 1) { T t = y[0]; y[0] = y[1]; y[1] = y[2]; y[2] = y[3]; y[3] = t; }
+    if (rot & 2) { T t = y[0]; y[0] = y[2]; y[2] = t; t = y[1]; y[1] = y[3]; y[3] = t; }
+  } else if (V == 2) {
+    if (rot & 1) { T t = y[0]; y[0] = y[1]; y[1] = t; }
+  }
+#pragma unroll
+  for (int ee = 0; ee < V; ++ee) {
+    const int e = (ee + rot) & (V - 1);
+    int p[NP];
+    split_pieces<NP>(y[ee], scale, p);
+    int* a = a0 + e * dv + c4;
+#pragma unroll
+    for (int q = 0; q < NP; ++q) atomicAdd(a + q * pstride, p[q]);
+  }
+}
+// column of position `pos`
+__device__ __forceinline__ int pos_to_col(int pos, int dv, int V) { return (pos % dv) * V + pos / dv; }
+
 // Value of NP/2 int64 pairs back as a double.  inv = 2^-(sa + 15).
 template <int NP>
 __device__ __host__ __forceinline__ double fixed_to_double(const long long* g, double inv) {
@@ -121,6 +152,8 @@ struct IterState {
   int argmax_count;             // index of the largest cluster
   int relocated;                // relocations done in the current M-step
   int error;                    // sticky device-side error word (0 = none)
+  unsigned int amb_count;       // rows handed to the exact re-evaluation pass in the current E-step
+  unsigned int pad0;
   double shift_sq;              // summed squared centroid shift of the current M-step
   double inertia;               // scratch for the inertia pass
 };

@@ -18,6 +18,7 @@
 #include "km_common.cuh"
 #include "km_finalize.cuh"
 #include "km_nccl.h"
+#include "km_refine.cuh"
 #include "km_smallk.cuh"
 #include "km_tc_host.cuh"
 #include "km_tiles.cuh"
@@ -51,6 +52,9 @@ struct Shard {
   int num_sms = 0;
   int cc_major = 0;
   tc::Plan tcp;  // tensor-core path (float only)
+  unsigned int* amb_rows = nullptr;  // rows handed to the exact re-evaluation pass
+  size_t amb_cap = 0;
+  unsigned int* amb_log = nullptr;
   cudaStream_t stream = nullptr;
   const T* X = nullptr;
   T* X_owned = nullptr;
@@ -123,6 +127,7 @@ struct Engine : EngineBase {
   int tc_refresh(Shard<T>& s);  // split the current centroids for the tensor-core kernel
   int launch_assign(Shard<T>& s, bool use_tc, bool count_changes);
   int tc_mask_hi = 1;
+  float tc_tol_rel = tc::kTolRel;
 
   // launch helpers (device of the shard must be current)
   int launch_tiles(Shard<T>& s, const T* Xp, size_t nrows, int* labels, int mode, T* out, size_t ld_out,
@@ -199,6 +204,7 @@ void Engine<T>::destroy() {
       if (api) api->CommDestroy(s.comm);
     }
     s.tcp.release();
+    cudaFree(s.amb_rows); cudaFree(s.amb_log);
     cudaFree(s.X_owned); cudaFree(s.labels); cudaFree(s.dist); cudaFree(s.gacc);
     cudaFree(s.C[0]); cudaFree(s.C[1]); cudaFree(s.cnorm); cudaFree(s.shift_k); cudaFree(s.empties);
     cudaFree(s.st); cudaFree(s.cand_val); cudaFree(s.cand_row); cudaFree(s.sum_partials);
@@ -542,6 +548,13 @@ bool Engine<T>::tc_ok(int flags) const {
 template <typename T>
 int Engine<T>::tc_refresh(Shard<T>& s) {
   if constexpr (std::is_same<T, float>::value) {
+    if (s.rows > 0xffffffffULL) KM_FAIL(KM_EINVAL, "shard too large for the tensor-core kernel");
+    if (s.amb_cap < s.rows) {
+      cudaFree(s.amb_rows);
+      s.amb_rows = nullptr;
+      KM_CUDA(cudaMalloc(&s.amb_rows, s.rows * sizeof(unsigned int)));
+      s.amb_cap = s.rows;
+    }
     KM_TRY(tc::setup(s.tcp, s.X, s.rows, k, d));
     KM_TRY(tc::prep(s.tcp, s.C[cur], s.cnorm, s.stream));
     ++launches;
@@ -553,8 +566,13 @@ template <typename T>
 int Engine<T>::launch_assign(Shard<T>& s, bool use_tc, bool count_changes) {
   if constexpr (std::is_same<T, float>::value) {
     if (use_tc) {
-      ++launches;
-      return tc::launch(s.tcp, s.labels, s.st, count_changes, s.num_sms, tc_mask_hi, s.stream);
+      launches += 2;
+      KM_TRY(tc::launch(s.tcp, s.labels, s.st, count_changes, s.amb_rows, tc_tol_rel, s.num_sms, tc_mask_hi,
+                        s.stream));
+      refine_kernel<float><<<s.num_sms * 2, 256, 0, s.stream>>>(s.X, d, s.C[cur], k, s.amb_rows, s.st, s.labels,
+                                                               count_changes ? 1 : 0);
+      KM_CUDA(cudaGetLastError());
+      return KM_OK;
     }
   }
   return launch_tiles(s, s.X, s.rows, s.labels, MODE_ASSIGN, nullptr, 0, count_changes);

@@ -304,7 +304,8 @@ average_kernel(const long long* __restrict__ gsums, const unsigned long long* __
 // the label-change counter.
 __global__ void __launch_bounds__(256)
 iter_close_kernel(const double* __restrict__ shift_k, int k, IterState* st, double* __restrict__ shift_log,
-                  unsigned long long* __restrict__ changed_log, int* __restrict__ reloc_log, int it,
+                  unsigned long long* __restrict__ changed_log, int* __restrict__ reloc_log,
+                  unsigned int* __restrict__ amb_log, int it,
                   double* __restrict__ host_shift, unsigned long long* __restrict__ host_changed) {
   __shared__ double red[256];
   double s = 0;
@@ -320,6 +321,8 @@ iter_close_kernel(const double* __restrict__ shift_k, int k, IterState* st, doub
     shift_log[it] = red[0];
     changed_log[it] = st->changed;
     reloc_log[it] = st->relocated;
+    amb_log[it] = st->amb_count;
+    st->amb_count = 0;
     if (host_shift) { *host_shift = red[0]; *host_changed = st->changed; }
     st->changed = 0;
   }

@@ -19,8 +19,9 @@ static int ensure_dist(Shard<T>& s) {
 template <typename T>
 static int ensure_logs(Shard<T>& s, int n) {
   if (s.log_cap < n) {
-    cudaFree(s.shift_log); cudaFree(s.changed_log); cudaFree(s.reloc_log);
-    s.shift_log = nullptr; s.changed_log = nullptr; s.reloc_log = nullptr;
+    cudaFree(s.shift_log); cudaFree(s.changed_log); cudaFree(s.reloc_log); cudaFree(s.amb_log);
+    s.shift_log = nullptr; s.changed_log = nullptr; s.reloc_log = nullptr; s.amb_log = nullptr;
+    KM_CUDA(cudaMalloc(&s.amb_log, n * sizeof(unsigned int)));
     KM_CUDA(cudaMalloc(&s.shift_log, n * sizeof(double)));
     KM_CUDA(cudaMalloc(&s.changed_log, n * sizeof(unsigned long long)));
     KM_CUDA(cudaMalloc(&s.reloc_log, n * sizeof(int)));
@@ -45,7 +46,10 @@ int Engine<T>::assign_all(int flags) {
       KM_TRY(rc);
     } else {
       const bool use_tc = tc_ok(flags);
-      if (use_tc) KM_TRY(tc_refresh(s));
+      if (use_tc) {
+        KM_TRY(tc_refresh(s));
+        KM_CUDA(cudaMemsetAsync(&s.st->amb_count, 0, sizeof(unsigned int), s.stream));
+      }
       KM_TRY(launch_assign(s, use_tc, false));
     }
   }
@@ -132,6 +136,7 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
   const bool fused = smallk_ok(true) && !(flags & KM_FIT_FORCE_SPLIT);
   const bool use_tc = !fused && tc_ok(flags);
   if (const char* e = std::getenv("H2O4GPU_KM_TC_MASK_HI")) tc_mask_hi = std::atoi(e);
+  if (const char* e = std::getenv("H2O4GPU_KM_TC_TOL")) tc_tol_rel = (float)std::atof(e);
   const bool multi = world_size > 1;
   const bool check = (threshold > 0) || (flags & KM_FIT_CHECK_EVERY_ITER);
   stats = kmeans_stats{};
@@ -213,7 +218,8 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
       DevGuard g(s.dev);
       average_kernel<T><<<k, 128, 0, s.stream>>>(s.sums(), s.counts(k, d), k, d, inv, s.C[cur], s.C[cur ^ 1], s.cnorm,
                                                s.shift_k, s.st);
-      iter_close_kernel<<<1, 256, 0, s.stream>>>(s.shift_k, k, s.st, s.shift_log, s.changed_log, s.reloc_log, it,
+      iter_close_kernel<<<1, 256, 0, s.stream>>>(s.shift_k, k, s.st, s.shift_log, s.changed_log, s.reloc_log,
+                                                 s.amb_log, it,
                                                  &s.host_pin[0], reinterpret_cast<unsigned long long*>(&s.host_pin[1]));
       launches += 2;
       if (i == 0) cudaEventRecord(ev[4 * it + 3], s.stream);
@@ -279,6 +285,9 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
       std::vector<double> sh(done);
       std::vector<unsigned long long> ch(done);
       std::vector<int> rl(done);
+      std::vector<unsigned int> am(done);
+      KM_CUDA(cudaMemcpy(am.data(), s0.amb_log, done * sizeof(unsigned int), cudaMemcpyDeviceToHost));
+      for (int i = 0; i < done; ++i) stats.refined_rows += (long long)am[i];
       KM_CUDA(cudaMemcpy(sh.data(), s0.shift_log, done * sizeof(double), cudaMemcpyDeviceToHost));
       KM_CUDA(cudaMemcpy(ch.data(), s0.changed_log, done * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
       KM_CUDA(cudaMemcpy(rl.data(), s0.reloc_log, done * sizeof(int), cudaMemcpyDeviceToHost));

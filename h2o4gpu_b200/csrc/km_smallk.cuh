@@ -139,13 +139,7 @@ smallk_kernel(const T* __restrict__ X, size_t n, int d, const T* __restrict__ C,
         for (int idx = l; idx < dv; idx += lpr) {
           T x[V];
           VecLoad<T, V>::ld(X + row[r] * (size_t)d + (size_t)idx * V, x);
-#pragma unroll
-          for (int e = 0; e < V; ++e) {
-            int p[NP];
-            split_pieces<NP>(x[e], scale, p);
-#pragma unroll
-            for (int q = 0; q < NP; ++q) atomicAdd(a + (size_t)q * K * d + idx * V + e, p[q]);
-          }
+          add_vec_fixed<T, V, NP>(a, (size_t)K * d, dv, idx, g & (V - 1), x, scale);
         }
       }
     }
@@ -158,11 +152,13 @@ smallk_kernel(const T* __restrict__ X, size_t n, int d, const T* __restrict__ C,
   if (update) {
     // drain: pair q of the global sums = piece(2q) * 2^15 + piece(2q+1)
     for (int i = tid; i < k * d; i += kSmallKThreads) {
+      const int c = i / d;
+      const int col = pos_to_col(i - c * d, dv, V);
 #pragma unroll
       for (int q = 0; q < NP / 2; ++q) {
         long long v = (long long)acc[(size_t)(2 * q) * K * d + i] * (1LL << kPieceBits) +
                       (long long)acc[(size_t)(2 * q + 1) * K * d + i];
-        if (v) atomicAdd(reinterpret_cast<unsigned long long*>(gsums + (size_t)q * k * d + i),
+        if (v) atomicAdd(reinterpret_cast<unsigned long long*>(gsums + (size_t)q * k * d + (size_t)c * d + col),
                          (unsigned long long)v);
       }
     }

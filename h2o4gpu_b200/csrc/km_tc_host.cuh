@@ -65,7 +65,7 @@ inline int setup(Plan& pl, const float* X, size_t rows, int k, int d) {
     pl.release();
     KM_CUDA(cudaMalloc(&pl.bhi, (size_t)npad * d * sizeof(float)));
     KM_CUDA(cudaMalloc(&pl.blo, (size_t)npad * d * sizeof(float)));
-    KM_CUDA(cudaMalloc(&pl.cn, (size_t)npad * sizeof(float)));
+    KM_CUDA(cudaMalloc(&pl.cn, (size_t)(npad + 1) * sizeof(float)));
   }
   pl.npad = npad; pl.k = k; pl.d = d; pl.x_base = X; pl.x_rows = rows;
   KM_TRY(make_map(&pl.tmX, X, rows, d, kBM));
@@ -78,19 +78,25 @@ inline int setup(Plan& pl, const float* X, size_t rows, int k, int d) {
 }
 
 inline int prep(Plan& pl, const float* C, const float* cnorm, cudaStream_t stream) {
+  KM_CUDA(cudaMemsetAsync(pl.cn + pl.npad, 0, sizeof(float), stream));
   prep_kernel<<<pl.npad, 64, 0, stream>>>(C, cnorm, pl.k, pl.d, pl.npad, pl.bhi, pl.blo, pl.cn);
   KM_CUDA(cudaGetLastError());
   return KM_OK;
 }
 
-inline int launch(Plan& pl, int* labels, IterState* st, bool count_changes, int num_sms, int mask_hi,
-                  cudaStream_t stream) {
+// tol_rel: a row goes to the exact pass when second - best <= tol_rel * (|x|^2 + max|c|^2).
+// The 3xTF32 product with both halves rounded to nearest stays below 2^-23 of that
+// bound in the worst mismatch measured; 2^-20 leaves a factor of ~16.
+constexpr float kTolRel = 9.5367431640625e-07f;
+
+inline int launch(Plan& pl, int* labels, IterState* st, bool count_changes, unsigned int* amb_rows, float tol_rel,
+                  int num_sms, int mask_hi, cudaStream_t stream) {
   const size_t tiles = (pl.x_rows + kBM - 1) / kBM;
   if (tiles > 0x7fffffffULL / kBM) KM_FAIL(KM_EINVAL, "shard too large for the tensor-core kernel");
   const int grid = (int)std::min<size_t>(tiles, (size_t)num_sms);
   assign_tc_kernel<<<grid, kThreads, smem_bytes(pl.d, pl.npad), stream>>>(
-      pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, labels, pl.x_rows, (int)tiles, pl.d, pl.npad,
-      count_changes ? st : nullptr, &st->error, mask_hi);
+      pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, labels, pl.x_rows, (int)tiles, pl.d, pl.npad, st, count_changes ? 1 : 0,
+      amb_rows, tol_rel, mask_hi);
   KM_CUDA(cudaGetLastError());
   return KM_OK;
 }

@@ -35,7 +35,7 @@ class Stats(ctypes.Structure):
                 ("last_shift_sq", _c.c_double), ("inertia", _c.c_double),
                 ("seconds_upload", _c.c_double), ("seconds_fit", _c.c_double),
                 ("ms_assign", _c.c_float), ("ms_update", _c.c_float), ("ms_loop", _c.c_float),
-                ("reserved2", _c.c_float)]
+                ("reserved2", _c.c_float), ("refined_rows", _c.c_longlong)]
 
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_ if not n.startswith("reserved")}

@@ -148,6 +148,9 @@ typedef struct kmeans_stats {
   float ms_update;         /* ... of the sum / count / finalize kernels              */
   float ms_loop;           /* ... of the whole iteration loop on device 0            */
   float reserved2;
+  long long refined_rows;  /* rows (device 0, summed over iterations) whose two best */
+                           /* scores were within the fast kernel's error bound and   */
+                           /* were re-evaluated exactly                              */
 } kmeans_stats;
 int kmeans_get_stats(kmeans_handle_t h, kmeans_stats* out);
 /* Sum of squared distances of every row to its assigned centre (direct
