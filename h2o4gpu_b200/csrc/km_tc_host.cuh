@@ -71,8 +71,12 @@ inline int setup(Plan& pl, const float* X, size_t rows, int k, int d) {
   KM_TRY(make_map(&pl.tmX, X, rows, d, kBM));
   KM_TRY(make_map(&pl.tmBhi, pl.bhi, npad, d, npad));
   KM_TRY(make_map(&pl.tmBlo, pl.blo, npad, d, npad));
-  KM_CUDA(cudaFuncSetAttribute(assign_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               (int)smem_bytes(d, npad)));
+  if (d == 32)
+    KM_CUDA(cudaFuncSetAttribute(assign_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem_bytes(d, npad)));
+  else
+    KM_CUDA(cudaFuncSetAttribute(assign_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem_bytes(d, npad)));
   pl.ready = true;
   return KM_OK;
 }
@@ -94,9 +98,14 @@ inline int launch(Plan& pl, int* labels, IterState* st, bool count_changes, unsi
   const size_t tiles = (pl.x_rows + kBM - 1) / kBM;
   if (tiles > 0x7fffffffULL / kBM) KM_FAIL(KM_EINVAL, "shard too large for the tensor-core kernel");
   const int grid = (int)std::min<size_t>(tiles, (size_t)num_sms);
-  assign_tc_kernel<<<grid, kThreads, smem_bytes(pl.d, pl.npad), stream>>>(
-      pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, labels, pl.x_rows, (int)tiles, pl.d, pl.npad, st, count_changes ? 1 : 0,
-      amb_rows, tol_rel, mask_hi);
+  if (pl.d == 32)
+    assign_tc_kernel<32><<<grid, kThreads, smem_bytes(pl.d, pl.npad), stream>>>(
+        pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, labels, pl.x_rows, (int)tiles, pl.npad, st, count_changes ? 1 : 0,
+        amb_rows, tol_rel, mask_hi);
+  else
+    assign_tc_kernel<64><<<grid, kThreads, smem_bytes(pl.d, pl.npad), stream>>>(
+        pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, labels, pl.x_rows, (int)tiles, pl.npad, st, count_changes ? 1 : 0,
+        amb_rows, tol_rel, mask_hi);
   KM_CUDA(cudaGetLastError());
   return KM_OK;
 }

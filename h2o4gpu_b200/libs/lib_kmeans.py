@@ -16,7 +16,7 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libh2o4gpu_kmeans.so")
+LIB_PATH = os.environ.get("H2O4GPU_KM_LIB") or os.path.join(os.path.dirname(_HERE), "lib", "libh2o4gpu_kmeans.so")
 
 _c = ctypes
 _sz = _c.c_size_t
