@@ -13,15 +13,14 @@
 //   warp 0      TMA producer: raw fp32 X tiles (128 x d, 128B-swizzled panels of
 //               32 columns) into a 4-stage shared-memory ring; the split
 //               centroid table (bh, bl) is loaded once per CTA and stays resident.
-//   warps 2-9   converters (two groups of four, alternating tiles): thread r reads row r of the tile (conflict-free
+//   warps 4-11  converters (two groups of four, alternating tiles): thread r reads row r of the tile (conflict-free
 //               thanks to the swizzle), splits it and writes xh / xl into TMEM
 //               with tcgen05.st - the A operand of the MMA lives in TMEM, so
 //               the tensor core reads only the centroid panels from shared memory.
-//   warp 1      MMA issuer: 3 * d/8 tcgen05.mma (M=128, N=kpad, K=8) per tile into
-//               one of two TMEM accumulators; tcgen05.commit releases the A
+//   warps 1-2   MMA issuers, one per A buffer / accumulator: 3 * d/8 tcgen05.mma
+//               (M=128, N=kpad, K=8) per tile; tcgen05.commit releases the A
 //               buffer and publishes the accumulator.
-//   warps 10-25 epilogue (two groups of eight, one group per accumulator; two warps share a
-//               row block and split the columns): tcgen05.ld, + |c|^2, argmin (first minimum wins),
+//   warps 12-19 epilogue (two groups of four, one per accumulator): tcgen05.ld, + |c|^2, argmin (first minimum wins),
 //               label store, changed-label count.
 // Every mbarrier wait is bounded (wall-clock limit); on a timeout the CTA sets an
 // error word, drains its copies, frees its TMEM and returns.
@@ -34,25 +33,10 @@
 namespace km {
 namespace tc {
 
-#ifdef KM_TC_PROFILE
-// debug build only: per-CTA clock totals of the waits of each role
-__device__ long long g_tc_prof[160][24];
-__device__ long long g_tc_trace[64][12];
-#define KM_TRACE(ev) do { if (blockIdx.x == 0 && i < 64) g_tc_trace[i][ev] = clock64(); } while (0)
-#define KM_PROF_T0() const long long _pt0 = clock64()
-#define KM_PROF_ADD(slot) do { if (lane == 0) g_tc_prof[blockIdx.x][slot] += clock64() - _pt0; } while (0)
-#ifdef KM_TC_TRACE_ONLY
-#define KM_PROF_SCOPE(slot, stmt) do { stmt; } while (0)
-#else
-#define KM_PROF_SCOPE(slot, stmt) do { const long long _t = clock64(); stmt; if (lane == 0) g_tc_prof[blockIdx.x][slot] += clock64() - _t; } while (0)
-#endif
-#else
-#define KM_PROF_SCOPE(slot, stmt) do { stmt; } while (0)
-#define KM_TRACE(ev) do { } while (0)
-#endif
+
 
 constexpr int kBM = 128;
-constexpr int kThreads = 832;  // producer, MMA issuer, 2 x 4 converter warps, 2 x 8 epilogue warps
+constexpr int kThreads = 640;  // producer, 2 MMA issuers, spare, 2 x 4 converter warps, 2 x 4 epilogue warps
 constexpr int kStages = 4;
 constexpr int kMaxD = 64;
 constexpr int kMaxNPad = 128;
@@ -62,12 +46,12 @@ constexpr long long kWaitLimitClk = 6000000000LL;          // about 3 s of SM cl
 
 enum Bar { FULL = 0, EMPTY = kStages, A_READY = 2 * kStages, A_EMPTY = 2 * kStages + 2,
            ACC_FULL = 2 * kStages + 4, ACC_EMPTY = 2 * kStages + 6, B_FULL = 2 * kStages + 8,
-           PART_FULL = 2 * kStages + 9, PART_EMPTY = 2 * kStages + 11, NUM_BARS = 2 * kStages + 13 };
+           NUM_BARS = 2 * kStages + 9 };
 
 inline size_t smem_bytes(int d, int npad) {
   size_t P = d / 32;
   return 1024 + 2 * P * (size_t)npad * 128 + (size_t)kStages * P * 16384 + (size_t)npad * 4 + 2 * kBM * 4 +
-         2 * kBM * 12 + NUM_BARS * 8 + 64;
+         NUM_BARS * 8 + 64;
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -99,24 +83,27 @@ __device__ __forceinline__ unsigned long long gtime_ns() {
 }
 // Bounded wait.  Returns false when the CTA is aborting (this wait or another
 // one gave up); the caller leaves its loop.
+// try_wait that lets the hardware park the warp for up to `ns` nanoseconds (it wakes
+// as soon as the phase completes), so waiting costs no issue slots.
+__device__ __forceinline__ bool mbar_try_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-  if (mbar_try(bar, parity)) return true;
-  // Back off between polls: a spinning warp would otherwise take issue slots from
-  // the warps doing the arithmetic on the same scheduler.
-  long long t0 = 0;
-  for (unsigned int it = 1;; ++it) {
-    __nanosleep(it < 64 ? 20 : 100);
-    if (mbar_try(bar, parity)) return true;
-    if ((it & 4095u) == 0) {
-      if (*abort_flag) return false;
-      const long long now = clock64();
-      if (t0 == 0) t0 = now;
-      if (now - t0 > kWaitLimitClk) {
-        *abort_flag = code;
-        return false;
-      }
-    }
+  // 150000 parked waits of at most 20 us each: gives up after about 3 s
+  for (unsigned int it = 0; it < 150000u; ++it) {
+    if (mbar_try_hint(bar, parity, 20000u)) return true;
+    if (*abort_flag) return false;
   }
+  *abort_flag = code;
+  return false;
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
@@ -209,18 +196,17 @@ prep_kernel(const float* __restrict__ C, const float* __restrict__ cnorm, int k,
   }
 }
 
-// Both halves of every operand are rounded to TF32 before they reach the tensor
-// core, so the result does not depend on how the hardware treats the low 13 bits
-// (measured on B200: it ignores them).  mask_hi is kept for experiments.
+// Operand halves: xh is x itself (the tensor core ignores the low 13 bits of an
+// fp32 operand - measured on B200 - so it sees x truncated to TF32), xl is
+// x - trunc(x) rounded to TF32; -2c is split by rounding on both halves.
+// dbg: bit 1 (2) = do not issue the MMAs, bit 2 (4) = skip the epilogue arithmetic,
+// bit 3 (8) = skip the TMEM stores (timing experiments only).
 template <int D>
 __global__ void __launch_bounds__(kThreads, 1)
 assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmBhi,
                  const __grid_constant__ CUtensorMap tmBlo, const float* __restrict__ cnorm_pad,
                  int* __restrict__ labels, size_t n, int n_tiles, int npad, IterState* st,
-                 int count_changes, unsigned int* __restrict__ amb_rows, float tol_rel, int mask_hi) {
-#ifdef KM_TC_PROFILE
-  const long long _kstart = clock64();
-#endif
+                 int count_changes, unsigned int* __restrict__ amb_rows, float tol_rel, int dbg) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_u32 = smem_u32(smem_raw);
   const uint32_t base = (raw_u32 + 1023u) & ~1023u;
@@ -230,11 +216,10 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   const uint32_t b_panel = (uint32_t)npad * 128u;
   const uint32_t off_blo = (uint32_t)P * b_panel;
   const uint32_t off_stage = 2u * P * b_panel;
-  const uint32_t stage_bytes = (uint32_t)P * 16384u;
+  constexpr uint32_t stage_bytes = (uint32_t)P * 16384u;
   const uint32_t off_cn = off_stage + kStages * stage_bytes;
   const uint32_t off_xn = off_cn + (uint32_t)npad * 4u;
-  const uint32_t off_part = off_xn + 2u * kBM * 4u;  // [2 groups][3][128] partial argmin of the upper columns
-  const uint32_t off_bar = (off_part + 2u * kBM * 12u + 7u) & ~7u;
+  const uint32_t off_bar = (off_xn + 2u * kBM * 4u + 7u) & ~7u;
   const uint32_t off_misc = off_bar + NUM_BARS * 8;
   float* cn_s = reinterpret_cast<float*>(sm + off_cn);
   float* xn_s = reinterpret_cast<float*>(sm + off_xn);  // [2][128] |x|^2 of the rows in A buffer b
@@ -252,9 +237,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       mbar_init(bar(A_READY + b), 128);
       mbar_init(bar(A_EMPTY + b), 1);
       mbar_init(bar(ACC_FULL + b), 1);
-      mbar_init(bar(ACC_EMPTY + b), 256);
-      mbar_init(bar(PART_FULL + b), 128);
-      mbar_init(bar(PART_EMPTY + b), 128);
+      mbar_init(bar(ACC_EMPTY + b), 128);
     }
     mbar_init(bar(B_FULL), 1);
     *abort_flag = 0;
@@ -288,12 +271,12 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++i) {
         const int s = i % kStages;
         const uint32_t ph = (uint32_t)(i / kStages) & 1u;
-        if (i >= kStages) KM_PROF_SCOPE(0, ok = mbar_wait(bar(EMPTY + s), ph ^ 1u, abort_flag, 1));
+        if (i >= kStages) ok = mbar_wait(bar(EMPTY + s), ph ^ 1u, abort_flag, 1);
         if (!ok) break;
         mbar_expect_tx(bar(FULL + s), stage_bytes);
+#pragma unroll
         for (int p = 0; p < P; ++p)
           tma_load_2d(base + off_stage + s * stage_bytes + p * 16384u, &tmX, p * 32, tile * kBM, bar(FULL + s));
-        KM_TRACE(8);
       }
       if (!ok) {
         // aborting: let the copies already issued land before the CTA exits
@@ -306,8 +289,12 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer --------------------------------
+  } else if (warp == 1 || warp == 2) {
+    // ------------------------------ MMA issuers -------------------------------
+    // Two issuing threads on two schedulers, one per A buffer / accumulator: the
+    // issue rate of a single thread (about ten scalar instructions per MMA) would
+    // otherwise cap the tensor pipe below its rate for these short K = 8 MMAs.
+    const int grp = warp - 1;
     if (lane == 0) {
       bool ok = mbar_wait(bar(B_FULL), 0, abort_flag, 2);
       // the centroid panels never move: one shared-memory descriptor per (panel, k-step)
@@ -319,22 +306,15 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           bdesc_hi[p * 4 + kk] = smem_desc_sw128(base + p * b_panel + kk * 32u);
           bdesc_lo[p * 4 + kk] = smem_desc_sw128(base + off_blo + p * b_panel + kk * 32u);
         }
-      int i = 0;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++i) {
-        const int b = i & 1;
+      const uint32_t acc = tmem_base + (uint32_t)grp * 128u;
+      const uint32_t a_hi = tmem_base + 256u + (uint32_t)grp * 128u;
+      int i = grp;
+      for (int tile = blockIdx.x + grp * gridDim.x; tile < n_tiles && ok; tile += 2 * gridDim.x, i += 2) {
         const uint32_t phb = (uint32_t)(i >> 1) & 1u;
-        KM_PROF_SCOPE(1, ok = mbar_wait(bar(A_READY + b), phb, abort_flag, 3));
-        KM_TRACE(2);
-        if (ok && i >= 2) KM_PROF_SCOPE(2, ok = mbar_wait(bar(ACC_EMPTY + b), phb ^ 1u, abort_flag, 4));
-        KM_TRACE(3);
+        ok = mbar_wait(bar(A_READY + grp), phb, abort_flag, 3);
+        if (ok && i >= 2) ok = mbar_wait(bar(ACC_EMPTY + grp), phb ^ 1u, abort_flag, 4);
         if (!ok) break;
-        KM_PROF_SCOPE(16, tc_fence_after());
-#ifdef KM_TC_PROFILE
-        const long long _m0 = clock64();
-#endif
-        const uint32_t acc = tmem_base + (uint32_t)b * 128u;
-        const uint32_t a_hi = tmem_base + 256u + (uint32_t)b * 128u;
-        // straight-line issue: descriptors were built once, operand addresses are immediates
+        tc_fence_after();
 #pragma unroll
         for (int term = 0; term < 3; ++term) {
 #pragma unroll
@@ -343,73 +323,70 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             for (int kk = 0; kk < 4; ++kk) {
               const uint32_t a_col = a_hi + (term == 1 ? 64u : 0u) + p * 32u + kk * 8u;
               const uint64_t bd = (term == 2) ? bdesc_lo[p * 4 + kk] : bdesc_hi[p * 4 + kk];
-              if (!(mask_hi & 2)) tc_mma_ts(acc, a_col, bd, idesc, (term | p | kk) ? 1u : 0u);
+              if (!(dbg & 2) && !((dbg & 64) && term > 0))
+                tc_mma_ts((dbg & 128) ? (acc ^ ((uint32_t)(kk & 1) << 6)) : acc, a_col, bd, idesc, (term | p | kk) ? 1u : 0u);
             }
           }
         }
-#ifdef KM_TC_PROFILE
-        g_tc_prof[blockIdx.x][17] += clock64() - _m0;
-#endif
-        KM_PROF_SCOPE(18, tc_commit(bar(A_EMPTY + b)));
-        KM_PROF_SCOPE(19, tc_commit(bar(ACC_FULL + b)));
-        KM_TRACE(4);
+        tc_commit(bar(A_EMPTY + grp));
+        tc_commit(bar(ACC_FULL + grp));
       }
-      if (!ok && i > 0) {
+      if (!ok && i >= 2 + grp) {
         // aborting: the MMAs already issued must retire before TMEM is freed
-        const int j = i - 1;
+        const int j = i - 2;
         const unsigned long long t0 = gtime_ns();
-        while (!mbar_try(bar(ACC_FULL + (j & 1)), (uint32_t)(j >> 1) & 1u))
+        while (!mbar_try(bar(ACC_FULL + grp), (uint32_t)(j >> 1) & 1u))
           if (gtime_ns() - t0 > kWaitLimitNs) break;
       }
     }
-  } else if (warp < 10) {
+  } else if (warp == 3) {
+    // spare warp (keeps the role warps aligned to the four TMEM lane quadrants)
+  } else if (warp < 12) {
     // ------------------------------ converters --------------------------------
     // two groups of four warps; group g serves the tiles with i % 2 == g, i.e. A buffer g
-    const int grp = (warp - 2) >> 2;
+    const int grp = (warp - 4) >> 2;
     const int q = warp & 3;
     const int row = q * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    const uint32_t a_hi = tmem_base + lane_addr + 256u + (uint32_t)grp * 128u;
     bool ok = true;
-    int i = 0;
-    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++i) {
-      if ((i & 1) != grp) continue;
+    int i = grp;
+    for (int tile = blockIdx.x + grp * gridDim.x; tile < n_tiles && ok; tile += 2 * gridDim.x, i += 2) {
       const int s = i % kStages;
       const uint32_t ph = (uint32_t)(i / kStages) & 1u;
-      const int b = i & 1;
       const uint32_t phb = (uint32_t)(i >> 1) & 1u;
-      KM_PROF_SCOPE(3 + grp * 4, ok = mbar_wait(bar(FULL + s), ph, abort_flag, 5));
-      if (q == 0 && lane == 0) KM_TRACE(9);
-      if (ok && i >= 2) KM_PROF_SCOPE(4 + grp * 4, ok = mbar_wait(bar(A_EMPTY + b), phb ^ 1u, abort_flag, 6));
-#ifdef KM_TC_PROFILE
-      const long long _cw0 = clock64();
-      if (q == 0 && lane == 0) KM_TRACE(0);
-#endif
+      ok = mbar_wait(bar(FULL + s), ph, abort_flag, 5);
+      if (ok && i >= 2) ok = mbar_wait(bar(A_EMPTY + grp), phb ^ 1u, abort_flag, 6);
       ok = __all_sync(0xffffffffu, ok);  // the tcgen05.st below needs the whole warp
       if (!ok) break;
       tc_fence_after();
       const uint8_t* stage = sm + off_stage + s * stage_bytes;
-      const uint32_t a_hi = tmem_base + lane_addr + 256u + (uint32_t)b * 128u;
       float xn = 0.0f;
 #pragma unroll
       for (int p = 0; p < P; ++p) {
         const uint8_t* rowp = stage + p * 16384 + row * 128;
+        float4 xv[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          xv[c] = (dbg & 32) ? make_float4(1.f, 2.f, 3.f, 4.f)
+                             : *reinterpret_cast<const float4*>(rowp + ((c ^ (row & 7)) << 4));
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           uint32_t hi[16], lo[16];
 #pragma unroll
           for (int cc = 0; cc < 4; ++cc) {
-            const int c = half * 4 + cc;
-            const float4 x = *reinterpret_cast<const float4*>(rowp + ((c ^ (row & 7)) << 4));
+            const float4 x = xv[half * 4 + cc];
             const float xs[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const float h = tf32_rn(xs[e]);
+              const uint32_t bits = __float_as_uint(xs[e]);
+              const float h = __uint_as_float(bits & 0xffffe000u);
               xn = fmaf(xs[e], xs[e], xn);
-              hi[cc * 4 + e] = __float_as_uint(h);
+              hi[cc * 4 + e] = bits;
               lo[cc * 4 + e] = __float_as_uint(tf32_rn(xs[e] - h));
             }
           }
-          if (!(mask_hi & 8)) {
+          if (!(dbg & 8)) {
             tmem_st16(a_hi + p * 32u + half * 16u, hi);
             tmem_st16(a_hi + 64u + p * 32u + half * 16u, lo);
           } else if (hi[3] == 0x12345u && lo[7] == 0x54321u) {
@@ -417,86 +394,79 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           }
         }
       }
-      xn_s[b * kBM + row] = xn;
-#ifdef KM_TC_PROFILE
-      if (lane == 0 && q == 0) g_tc_prof[blockIdx.x][5 + grp * 4] += clock64() - _cw0;
-#endif
-      KM_PROF_SCOPE(6 + grp * 4, tmem_wait_st());
+      xn_s[grp * kBM + row] = xn;
+      tmem_wait_st();
       tc_fence_before();
-      if (q == 0 && lane == 0) KM_TRACE(1);
       mbar_arrive(bar(EMPTY + s));
-      mbar_arrive(bar(A_READY + b));
+      mbar_arrive(bar(A_READY + grp));
     }
   } else {
     // ------------------------------ epilogue ----------------------------------
-    // Two groups of eight warps; group g drains accumulator g.  Within a group the
-    // warps with hsel = 0 scan columns [0, 64) and those with hsel = 1 the rest; the
-    // upper half hands its (best, second, index) to the lower half through shared
-    // memory, which finishes the row.
-    const int ew = warp - 10;
-    const int grp = ew >> 3;
-    const int hsel = (ew >> 2) & 1;
+    // two groups of four warps; group g drains accumulator g
+    const int grp = (warp - 12) >> 2;
     const int q = warp & 3;
     const int row_in_tile = q * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    float* part = reinterpret_cast<float*>(sm + off_part) + grp * 3 * kBM;
+    const uint32_t acc = tmem_base + lane_addr + (uint32_t)grp * 128u;
     const float kInf = __int_as_float(0x7f800000);
     unsigned int changed = 0;
     bool ok = true;
-    int i = 0;
-    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++i) {
-      if ((i & 1) != grp) continue;
-      const int b = i & 1;
+    int i = grp;
+    for (int tile = blockIdx.x + grp * gridDim.x; tile < n_tiles && ok; tile += 2 * gridDim.x, i += 2) {
       const uint32_t phb = (uint32_t)(i >> 1) & 1u;
-      KM_PROF_SCOPE(11 + grp * 2, ok = mbar_wait(bar(ACC_FULL + b), phb, abort_flag, 7));
-#ifdef KM_TC_PROFILE
-      const long long _ew0 = clock64();
-      if (ew == grp * 8 && lane == 0) KM_TRACE(5);
-#endif
+      // the previous label is only needed for the change count at the very end: fetch
+      // it now so that its DRAM round trip hides behind the wait and the arithmetic
+      const size_t row = (size_t)tile * kBM + row_in_tile;
+      int old_label = -1;
+      if (count_changes && row < n) old_label = labels[row];
+      ok = mbar_wait(bar(ACC_FULL + grp), phb, abort_flag, 7);
       ok = __all_sync(0xffffffffu, ok);  // the tcgen05.ld below needs the whole warp
       if (!ok) break;
       tc_fence_after();
-      const uint32_t acc = tmem_base + lane_addr + (uint32_t)b * 128u;
       // four interleaved (best, second, index) chains keep the compare/select
       // dependency short; chain q sees columns j with j % 4 == q in ascending order
       float bst[4] = {kInf, kInf, kInf, kInf}, sec[4] = {kInf, kInf, kInf, kInf};
       int bix[4] = {0, 0, 0, 0};
+      // The load of chunk ch+1 is issued before the arithmetic on chunk ch, so its
+      // latency overlaps the compare/select work (tcgen05.wait::ld waits for all loads
+      // in flight, hence "wait, issue next, compute").
+      uint32_t va[32], vb[32];
+      if (!(dbg & 4)) {
+        tmem_ld16(acc, va, 0);
+        if (16 < npad) tmem_ld16(acc + 16, va, 16);
+      }
 #pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        if (hh != hsel) continue;
+      for (int ch = 0; ch < kMaxNPad / 32; ++ch) {
+        const int c0 = ch * 32;  // compile-time after unrolling: column indices are immediates
+        if (c0 < npad && !(dbg & 4)) {
+          uint32_t(&v)[32] = (ch & 1) ? vb : va;
+          uint32_t(&vn)[32] = (ch & 1) ? va : vb;
+          const bool two = (c0 + 16 < npad);
+          tmem_wait_ld(v);
+          if (c0 + 32 < npad) {
+            tmem_ld16(acc + c0 + 32, vn, 0);
+            if (c0 + 48 < npad) tmem_ld16(acc + c0 + 48, vn, 16);
+          }
 #pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
-          const int c0 = hh * 64 + ch * 32;  // compile-time after unrolling: column indices are immediates
-          if (c0 < npad && !(mask_hi & 4)) {
-            uint32_t v[32];
-            const bool two = (c0 + 16 < npad);
-            tmem_ld16(acc + c0, v, 0);
-            if (two) tmem_ld16(acc + c0 + 16, v, 16);
-            tmem_wait_ld(v);
+          for (int j4 = 0; j4 < 8; ++j4) {
+            if (j4 < 4 || two) {
+              const float4 cn4 = *reinterpret_cast<const float4*>(cn_s + c0 + j4 * 4);
+              const float cn[4] = {cn4.x, cn4.y, cn4.z, cn4.w};
 #pragma unroll
-            for (int j4 = 0; j4 < 8; ++j4) {
-              if (j4 < 4 || two) {
-                const float4 cn4 = *reinterpret_cast<const float4*>(cn_s + c0 + j4 * 4);
-                const float cn[4] = {cn4.x, cn4.y, cn4.z, cn4.w};
-#pragma unroll
-                for (int qq = 0; qq < 4; ++qq) {
-                  const float sc = __uint_as_float(v[j4 * 4 + qq]) + cn[qq];
-                  sec[qq] = fminf(sec[qq], fmaxf(sc, bst[qq]));
-                  const bool lt = sc < bst[qq];
-                  bst[qq] = lt ? sc : bst[qq];
-                  bix[qq] = lt ? (c0 + j4 * 4 + qq) : bix[qq];
-                }
+              for (int qq = 0; qq < 4; ++qq) {
+                const float sc = __uint_as_float(v[j4 * 4 + qq]) + cn[qq];
+                sec[qq] = fminf(sec[qq], fmaxf(sc, bst[qq]));
+                const bool lt = sc < bst[qq];
+                bst[qq] = lt ? sc : bst[qq];
+                bix[qq] = lt ? (c0 + j4 * 4 + qq) : bix[qq];
               }
             }
           }
         }
       }
+      const float xn = xn_s[grp * kBM + row_in_tile];
       tc_fence_before();
-      if (ew == grp * 8 && lane == 0) KM_TRACE(6);
-      mbar_arrive(bar(ACC_EMPTY + b));
-#ifdef KM_TC_PROFILE
-      if (lane == 0 && ew == grp * 8) g_tc_prof[blockIdx.x][12 + grp * 2] += clock64() - _ew0;
-#endif
+      mbar_arrive(bar(ACC_EMPTY + grp));
       float best = bst[0], second = sec[0];
       int bidx = bix[0];
 #pragma unroll
@@ -510,46 +480,17 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         }
         second = fminf(second, sec[qq]);
       }
-      const uint32_t pht = phb;  // this group's tile counter is i >> 1
-      if (hsel == 1) {
-        // (bounded waits instead of a named barrier: a warp that aborts must not strand its partners)
-        if (i >= 2) ok = mbar_wait(bar(PART_EMPTY + grp), pht ^ 1u, abort_flag, 8);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        part[row_in_tile] = best;
-        part[kBM + row_in_tile] = second;
-        part[2 * kBM + row_in_tile] = __int_as_float(bidx);
-        mbar_arrive(bar(PART_FULL + grp));
-      } else {
-        ok = mbar_wait(bar(PART_FULL + grp), pht, abort_flag, 9);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        const float ub = part[row_in_tile];
-        const float us = part[kBM + row_in_tile];
-        const int ui = __float_as_int(part[2 * kBM + row_in_tile]);
-        if (ub < best) {  // upper columns have larger indices: they win only when strictly smaller
-          second = fminf(best, us);
-          best = ub;
-          bidx = ui;
+      if (row < n && !(dbg & 16)) {
+        // rows whose two best scores are closer than the error bound of the 3xTF32
+        // product are left to the exact re-evaluation pass
+        const float tol = tol_rel * (xn + cn_max);
+        if (amb_rows != nullptr && !(second - best > tol)) {
+          const unsigned int pos = atomicAdd(&st->amb_count, 1u);
+          amb_rows[pos] = (unsigned int)row;
         } else {
-          second = fminf(second, ub);
+          changed += (old_label != bidx);
+          labels[row] = bidx;
         }
-        const float xn = xn_s[b * kBM + row_in_tile];
-        const size_t row = (size_t)tile * kBM + row_in_tile;
-        if (row < n) {
-          // rows whose two best scores are closer than the error bound of the 3xTF32
-          // product are left to the exact re-evaluation pass
-          const float tol = tol_rel * (xn + cn_max);
-          if (amb_rows != nullptr && !(second - best > tol)) {
-            const unsigned int pos = atomicAdd(&st->amb_count, 1u);
-            amb_rows[pos] = (unsigned int)row;
-          } else {
-            changed += (labels[row] != bidx);
-            labels[row] = bidx;
-          }
-        }
-        if (ew == grp * 8 && lane == 0) KM_TRACE(7);
-        mbar_arrive(bar(PART_EMPTY + grp));  // `part` has been read
       }
     }
     if (count_changes) {
@@ -559,9 +500,6 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   }
 
   __syncthreads();
-#ifdef KM_TC_PROFILE
-  if (tid == 0) g_tc_prof[blockIdx.x][15] += clock64() - _kstart;
-#endif
   if (tid == 0 && *abort_flag) atomicMax(&st->error, *abort_flag);
   if (warp == 1) {
     tc_fence_after();

@@ -89,9 +89,10 @@ inline int prep(Plan& pl, const float* C, const float* cnorm, cudaStream_t strea
 }
 
 // tol_rel: a row goes to the exact pass when second - best <= tol_rel * (|x|^2 + max|c|^2).
-// The 3xTF32 product with both halves rounded to nearest stays below 2^-23 of that
-// bound in the worst mismatch measured; 2^-20 leaves a factor of ~16.
-constexpr float kTolRel = 9.5367431640625e-07f;
+// Error of the 3xTF32 product: xh truncated (exact residual), xl and both halves of
+// -2c rounded to TF32 (2^-12 relative each), xl.bl dropped (2^-21 |x||b|): about
+// 2^-20.4 (|x|^2 + |c|^2) per score, twice that for a difference -> 2^-19.
+constexpr float kTolRel = 1.9073486328125e-06f;
 
 inline int launch(Plan& pl, int* labels, IterState* st, bool count_changes, unsigned int* amb_rows, float tol_rel,
                   int num_sms, int mask_hi, cudaStream_t stream) {

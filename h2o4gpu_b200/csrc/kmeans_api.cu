@@ -442,20 +442,6 @@ int kmeans_synth_f64(int gpu_id, double* dX, size_t rows, size_t cols, size_t ro
   return synth_impl<double>(gpu_id, dX, rows, cols, row0, kind, centers_host, n_comp, weights_host, sigma, seed);
 }
 
-#ifdef KM_TC_PROFILE
-int kmeans_debug_tc_trace(long long* out) {
-  cudaMemcpyFromSymbol(out, km::tc::g_tc_trace, sizeof(long long) * 64 * 12);
-  return 0;
-}
-int kmeans_debug_tc_profile(long long* out, int reset) {
-  cudaMemcpyFromSymbol(out, km::tc::g_tc_prof, sizeof(long long) * 160 * 24);
-  if (reset) {
-    static long long zeros[160 * 24];
-    cudaMemcpyToSymbol(km::tc::g_tc_prof, zeros, sizeof(zeros));
-  }
-  return 0;
-}
-#endif
 
 }  // extern "C"
 
