@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIBDIR, "libh2o4gpu_kmeans.so")
-SOURCES = ["kmeans_api.cu"]
+SOURCES = ["kmeans_api.cu", "kmeans_noalloc.cu"]
 
 
 def _nccl_include():

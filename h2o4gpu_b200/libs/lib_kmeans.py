@@ -68,6 +68,7 @@ SIGNATURES = {
     "kmeans_inertia": (_c.c_int, [_vp, _c.POINTER(_c.c_double)]),
     "kmeans_centroid_sums_f32": (_c.c_int, [_c.c_int, _vp, _vp, _sz, _sz, _c.c_int, _vp, _vp]),
     "kmeans_centroid_sums_f64": (_c.c_int, [_c.c_int, _vp, _vp, _sz, _sz, _c.c_int, _vp, _vp]),
+    "kmeans_centroid_sums_noalloc_f32": (_c.c_int, [_vp, _vp, _sz, _sz, _c.c_int, _vp, _vp, _vp]),
     "kmeans_synth_f32": (_c.c_int, [_c.c_int, _vp, _sz, _sz, _sz, _c.c_int, _vp, _c.c_int, _vp, _c.c_float, _c.c_uint64]),
     "kmeans_synth_f64": (_c.c_int, [_c.c_int, _vp, _sz, _sz, _sz, _c.c_int, _vp, _c.c_int, _vp, _c.c_double, _c.c_uint64]),
 }

@@ -167,6 +167,27 @@ int kmeans_centroid_sums_f32(int gpu_id, const float* X, const int32_t* labels, 
 int kmeans_centroid_sums_f64(int gpu_id, const double* X, const int32_t* labels, size_t rows,
                              size_t cols, int k, double* sums, int64_t* counts);
 
+/* No counterpart in the reference.  Same result as kmeans_centroid_sums_f32 for a
+ * shard that already lives on the current device, for callers that must not
+ * allocate device memory where they call it: between cudaStreamBeginCapture and
+ * EndCapture, in a serving loop whose memory budget is frozen, or where the
+ * implicit synchronisation of cudaMalloc / cudaFree is not acceptable.  All
+ * working memory is one static device array inside the library (229,440 bytes,
+ * held by every GPU that loads the library until the process exits), hence the
+ * limit k * cols <= 24576 and k <= 4096; larger sizes return KM_EINVAL.
+ * dX (rows x cols row-major), dLabels, dSums (k x cols doubles) and dCounts
+ * (k int64) are device pointers; `stream` is a cudaStream_t (NULL = default
+ * stream).  The work is enqueued on that stream and the call returns without
+ * waiting; it calls no cudaMalloc / cudaFree.  Rows whose label is outside [0, k)
+ * are skipped; the data must be finite.  The first call on a device looks up
+ * the array's address and raises a shared-memory limit: make it outside any
+ * stream capture.  Every call on a device uses the same array, which keeps the
+ * previous call's contents until the next call clears them: calls whose GPU
+ * work overlaps (other streams, concurrent graph replays) race and must be
+ * serialised by the caller. */
+int kmeans_centroid_sums_noalloc_f32(const float* dX, const int32_t* dLabels, size_t rows, size_t cols,
+                                     int k, double* dSums, long long* dCounts, void* stream);
+
 /* ---- 4. synthetic data on the device (benchmark inputs too large for the host)
  * Fills dX (rows x cols row-major on the current device `gpu_id`) with
  * centers[comp(row)] + sigma * N(0,1); comp drawn from `weights` (NULL = equal).
