@@ -15,6 +15,7 @@
 #include <vector>
 
 #include "km_accumulate.cuh"
+#include "km_accumulate_sorted.cuh"
 #include "km_common.cuh"
 #include "km_finalize.cuh"
 #include "km_nccl.h"
@@ -497,10 +498,53 @@ int Engine<T>::launch_smallk(Shard<T>& s, bool update, T scale) {
   return KM_OK;
 }
 
+template <int GS>
+static int launch_sorted_gs(const float* X, size_t rows, int d, const int* labels, int k, long long* gs,
+                            unsigned long long* gc, float scale30, const SortPlan& p, cudaStream_t stream) {
+  KM_CUDA(cudaFuncSetAttribute(sorted_accumulate_kernel<GS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)p.smem_bytes));
+  sorted_accumulate_kernel<GS><<<p.grid, kSortThreads, p.smem_bytes, stream>>>(X, rows, d, labels, k, gs, gc, scale30,
+                                                                              p.tile_rows, p.smem_acc);
+  KM_CUDA(cudaGetLastError());
+  return KM_OK;
+}
+
+// float shards with 16-byte rows: run-length kernel.  `scale` is 2^(15-e); the
+// run-length kernel quantises with 2^(30-e) in one step, which gives the same integers.
+template <typename T>
+static int try_sorted_accumulate(Shard<T>& s, int d, int k, T scale, bool vec, bool* done) {
+  *done = false;
+  if constexpr (std::is_same<T, float>::value) {
+    static const bool enabled = [] {
+      const char* e = std::getenv("H2O4GPU_KM_ACC_SORTED");
+      return !(e && e[0] == '0');
+    }();
+    SortPlan p;
+    if (!enabled || !vec || !sorted_accumulate_plan(s.rows, d, k, s.num_sms, kMaxDynSmem, &p)) return KM_OK;
+    const float scale30 = scale * 32768.0f;
+    const int dv = d / 4;
+    int rc;
+    if (dv <= 8) rc = launch_sorted_gs<8>(s.X, s.rows, d, s.labels, k, s.sums(), s.counts(k, d), scale30, p, s.stream);
+    else if (dv <= 16) rc = launch_sorted_gs<16>(s.X, s.rows, d, s.labels, k, s.sums(), s.counts(k, d), scale30, p, s.stream);
+    else if (dv <= 32) rc = launch_sorted_gs<32>(s.X, s.rows, d, s.labels, k, s.sums(), s.counts(k, d), scale30, p, s.stream);
+    else if (dv <= 64) rc = launch_sorted_gs<64>(s.X, s.rows, d, s.labels, k, s.sums(), s.counts(k, d), scale30, p, s.stream);
+    else if (dv <= 128) rc = launch_sorted_gs<128>(s.X, s.rows, d, s.labels, k, s.sums(), s.counts(k, d), scale30, p, s.stream);
+    else rc = launch_sorted_gs<256>(s.X, s.rows, d, s.labels, k, s.sums(), s.counts(k, d), scale30, p, s.stream);
+    KM_TRY(rc);
+    *done = true;
+  }
+  return KM_OK;
+}
+
 template <typename T>
 int Engine<T>::launch_accumulate(Shard<T>& s, T scale) {
   constexpr int V = VecOf<T>::N;
   constexpr int NP = Fixed<T>::NP;
+  {
+    bool done = false;
+    KM_TRY(try_sorted_accumulate<T>(s, d, k, scale, vec_ok(s), &done));
+    if (done) { ++launches; return KM_OK; }
+  }
   const size_t per_cluster = (size_t)NP * d * sizeof(int) + sizeof(int);
   const size_t budget = 200 * 1024;
   if (per_cluster + 16 > budget) KM_FAIL(KM_EINVAL, "cols too large for the centroid-sum kernel");
