@@ -1,0 +1,22 @@
+"""Small resident fit of the C2-shaped workload (d=64, k=100) for profiler captures:
+    python h2o4gpu_b200/ncu_case.py [rows] [iterations]"""
+import sys
+import numpy as np
+sys.path.insert(0, __import__('os').path.dirname(__import__('os').path.dirname(__import__('os').path.abspath(__file__))))
+import torch
+from h2o4gpu_b200 import engine
+n = int(sys.argv[1]) if len(sys.argv) > 1 else 2_000_000
+iters = int(sys.argv[2]) if len(sys.argv) > 2 else 3
+d, k = 64, 100
+dev = torch.device("cuda", 0)
+rng = np.random.default_rng(0)
+centers = rng.uniform(-10, 10, (100, d)).astype(np.float32)
+w = rng.dirichlet(np.ones(100)).astype(np.float32)
+X = torch.empty((n, d), dtype=torch.float32, device=dev)
+engine.synth_device(X.data_ptr(), n, d, np.float32, centers=centers, weights=w, sigma=1.0, seed=1)
+init = X[torch.from_numpy(np.sort(rng.choice(n, k, replace=False))).to(dev)].cpu().numpy()
+h = engine.ResidentKMeans()
+h.attach_device(0, X.data_ptr(), n, d)
+h.fit(init, iters, flags=engine.FIT_NO_FINAL_ASSIGN)
+print(h.stats())
+h.close()
