@@ -77,7 +77,8 @@ accumulate_kernel(const T* __restrict__ X, size_t n, int d, const int* __restric
           rowu[u] = row;
           VecLoad<T, V>::ld(Xp + (size_t)idx * V, x[u]);
           lab[u] = Lp[row];
-          if (col[u] == 0) atomicAdd(&cnt[lab[u]], 1);
+          if ((unsigned)lab[u] >= (unsigned)k) lab[u] = -1;  // cannot come from the E-step kernels; skipped
+          else if (col[u] == 0) atomicAdd(&cnt[lab[u]], 1);
         }
       }
 #pragma unroll

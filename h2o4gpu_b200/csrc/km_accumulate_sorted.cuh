@@ -98,7 +98,11 @@ sorted_accumulate_kernel(const float* __restrict__ X, size_t n, int d, const int
     // ---- counting sort of the tile's rows by label ----
     for (int i = tid; i < k; i += kSortThreads) hist[i] = 0;
     __syncthreads();
-    for (int i = tid; i < nr; i += kSortThreads) atomicAdd(&hist[labels[r0 + i]], 1);
+    // (labels outside [0, k) cannot come from the E-step kernels; such rows are skipped)
+    for (int i = tid; i < nr; i += kSortThreads) {
+      const int lab = labels[r0 + i];
+      if ((unsigned)lab < (unsigned)k) atomicAdd(&hist[lab], 1);
+    }
     __syncthreads();
     // exclusive scan of hist into offs (k <= 4096: each thread owns a contiguous chunk)
     {
@@ -124,18 +128,21 @@ sorted_accumulate_kernel(const float* __restrict__ X, size_t n, int d, const int
     __syncthreads();
     for (int i = tid; i < nr; i += kSortThreads) {
       const int lab = labels[r0 + i];
+      if ((unsigned)lab >= (unsigned)k) continue;
       const int pos = atomicAdd(&offs[lab], 1);
       sorted[pos] = ((unsigned)lab << 16) | (unsigned)i;     // tile_rows <= 65536, k <= 4096
     }
+
     // per-cluster counts of this tile
     for (int i = tid; i < k; i += kSortThreads)
       if (hist[i]) atomicAdd(gcounts + i, (unsigned long long)hist[i]);
     __syncthreads();
 
     // ---- walk the sorted list: group `grp` owns positions [p0, p1) ----
-    const int per_grp = (nr + G - 1) / G;
+    const int nsorted = offs[k - 1];  // rows with a valid label (all of them in normal operation)
+    const int per_grp = (nsorted + G - 1) / G;
     const int p0 = grp * per_grp;
-    const int p1 = min(nr, p0 + per_grp);
+    const int p1 = min(nsorted, p0 + per_grp);
     long long s[4] = {0, 0, 0, 0};
     int cur = -1;
     const float* Xt = X + r0 * (size_t)d;

@@ -1,57 +1,70 @@
 // Tensor-core distance + argmin kernel for sm_100a (tcgen05 / TMEM / TMA).
 //
 // Scores |c|^2 - 2 x.c for a 128-row tile of X against all centroids are formed
-// on the 5th-generation tensor cores as a 3xTF32 product so that fp32 accuracy
-// is kept:   x = xh + xl,  -2c = bh + bl  (h = nearest TF32 value, l = rounded rest)
-//            acc = xh.bh + xl.bh + xh.bl          (fp32 accumulation in TMEM)
-// and the epilogue adds |c|^2 and takes the running argmin, so the rows x k
-// distance matrix never exists.  Replaces calculate_distances + relabel
+// on the 5th-generation tensor cores as a three-term split product so that fp32
+// accuracy is kept:
+//      x * Sx = xh + xl,   -2c * Sb = bh + bl      (Sx, Sb powers of two)
+//      acc    = xh.bh + xl.bh + xh.bl              (fp32 accumulation in TMEM)
+// where every half is an IEEE half-precision number (11 significant bits, the
+// same as TF32): products of two halves are exact in fp32, so the split loses
+// only xl.bl (2^-22 relative) and the rounding of the low halves (2^-23).  The
+// power-of-two scales keep every operand inside the fp16 range; they cancel in
+// the comparison because |c|^2 is scaled by the same Sx*Sb.  Using kind::f16
+// (K = 16 per instruction) instead of kind::tf32 (K = 8) halves the number of
+// MMA instructions per tile (3 * d/16), which matters because for N = 112 the
+// tensor pipe is bound by a per-instruction cost, not by N.  The epilogue adds
+// |c|^2 and takes the running argmin, so the rows x k distance matrix never
+// exists.  Replaces calculate_distances + relabel
 // (src/gpu/kmeans/kmeans_labels.cu:115-244, kmeans_labels.h:360-392) for
 // float32, d in {32, 64}, 16 < k <= 128.
 //
 // Persistent CTAs (one per SM), warp-specialised:
 //   warp 0      TMA producer: raw fp32 X tiles (128 x d, 128B-swizzled panels of
-//               32 columns) into a 4-stage shared-memory ring; the split
-//               centroid table (bh, bl) is loaded once per CTA and stays resident.
-//   warps 4-11  converters (two groups of four, alternating tiles): thread r reads row r of the tile (conflict-free
-//               thanks to the swizzle), splits it and writes xh / xl into TMEM
-//               with tcgen05.st - the A operand of the MMA lives in TMEM, so
-//               the tensor core reads only the centroid panels from shared memory.
-//   warps 1-2   MMA issuers, one per A buffer / accumulator: 3 * d/8 tcgen05.mma
-//               (M=128, N=kpad, K=8) per tile; tcgen05.commit releases the A
-//               buffer and publishes the accumulator.
-//   warps 12-19 epilogue (two groups of four, one per accumulator): tcgen05.ld, + |c|^2, argmin (first minimum wins),
-//               label store, changed-label count.
-// Every mbarrier wait is bounded (wall-clock limit); on a timeout the CTA sets an
-// error word, drains its copies, frees its TMEM and returns.
+//               32 columns) into a 5-stage shared-memory ring; the split centroid
+//               table (bh, bl; fp16, one swizzled panel each) is loaded once per
+//               CTA and stays resident.
+//   warps 4-11  converters (two groups of four, alternating tiles): thread r
+//               reads row r of the tile (conflict-free thanks to the swizzle),
+//               splits it and writes packed xh / xl into TMEM with tcgen05.st -
+//               the A operand of the MMA lives in TMEM, so the tensor core reads
+//               only the centroid panels from shared memory.
+//   warps 1-2   MMA issuers, one per A buffer: 3 * d/16 tcgen05.mma.kind::f16
+//               (M=128, N=kpad, K=16) per tile into one of three TMEM
+//               accumulators; tcgen05.commit releases the A buffer and publishes
+//               the accumulator.
+//   warps 12-23 epilogue (three groups of four, one per accumulator): tcgen05.ld,
+//               + |c|^2, four interleaved (min, second-min, argmin) chains, label
+//               store, changed-label count; rows whose two best scores are within
+//               the error bound go to the exact re-evaluation list.
+// Every mbarrier wait is bounded; on a timeout the CTA sets an error word, drains
+// its copies, frees its TMEM and returns.
 #pragma once
 
 #include <cuda.h>
+#include <cuda_fp16.h>
 
 #include "km_common.cuh"
 
 namespace km {
 namespace tc {
 
-
-
 constexpr int kBM = 128;
-constexpr int kThreads = 640;  // producer, 2 MMA issuers, spare, 2 x 4 converter warps, 2 x 4 epilogue warps
-constexpr int kStages = 4;
+constexpr int kThreads = 768;  // producer, 2 MMA issuers, spare, 2 x 4 converter warps, 3 x 4 epilogue warps
+constexpr int kStages = 5;
+constexpr int kAcc = 3;        // TMEM accumulators
 constexpr int kMaxD = 64;
 constexpr int kMaxNPad = 128;
 constexpr int kTmemCols = 512;
 constexpr unsigned long long kWaitLimitNs = 2000000000ULL;  // 2 s (abort drain loops)
-constexpr long long kWaitLimitClk = 6000000000LL;          // about 3 s of SM clocks
 
 enum Bar { FULL = 0, EMPTY = kStages, A_READY = 2 * kStages, A_EMPTY = 2 * kStages + 2,
-           ACC_FULL = 2 * kStages + 4, ACC_EMPTY = 2 * kStages + 6, B_FULL = 2 * kStages + 8,
-           NUM_BARS = 2 * kStages + 9 };
+           ACC_FULL = 2 * kStages + 4, ACC_EMPTY = 2 * kStages + 4 + kAcc, B_FULL = 2 * kStages + 4 + 2 * kAcc,
+           NUM_BARS = 2 * kStages + 5 + 2 * kAcc };
 
+// shared memory: [bh panel][bl panel][stages][cn][barriers][misc]; d is 32 or 64
 inline size_t smem_bytes(int d, int npad) {
   size_t P = d / 32;
-  return 1024 + 2 * P * (size_t)npad * 128 + (size_t)kStages * P * 16384 + (size_t)npad * 4 + 2 * kBM * 4 +
-         NUM_BARS * 8 + 64;
+  return 1024 + 2 * (size_t)npad * 128 + (size_t)kStages * P * 16384 + (size_t)npad * 4 + NUM_BARS * 8 + 64;
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -81,8 +94,6 @@ __device__ __forceinline__ unsigned long long gtime_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait.  Returns false when the CTA is aborting (this wait or another
-// one gave up); the caller leaves its loop.
 // try_wait that lets the hardware park the warp for up to `ns` nanoseconds (it wakes
 // as soon as the phase completes), so waiting costs no issue slots.
 __device__ __forceinline__ bool mbar_try_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
@@ -96,6 +107,8 @@ __device__ __forceinline__ bool mbar_try_hint(uint32_t bar, uint32_t parity, uin
       : "memory");
   return ok != 0;
 }
+// Bounded wait.  Returns false when the CTA is aborting (this wait or another one
+// gave up); the caller leaves its loop.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
   // 150000 parked waits of at most 20 us each: gives up after about 3 s
   for (unsigned int it = 0; it < 150000u; ++it) {
@@ -120,13 +133,13 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-// D[tmem] (+)= A[tmem] * B[smem desc], kind::tf32, M=128
+// D[tmem] (+)= A[tmem] * B[smem desc], kind::f16 (fp16 inputs, fp32 accumulate), M=128, K=16
 __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
                                           uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
@@ -150,12 +163,10 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[32], int
       : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
-  const int o = 0;
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-      ::"r"(taddr), "r"(v[o + 0]), "r"(v[o + 1]), "r"(v[o + 2]), "r"(v[o + 3]), "r"(v[o + 4]), "r"(v[o + 5]),
-        "r"(v[o + 6]), "r"(v[o + 7]), "r"(v[o + 8]), "r"(v[o + 9]), "r"(v[o + 10]), "r"(v[o + 11]), "r"(v[o + 12]),
-        "r"(v[o + 13]), "r"(v[o + 14]), "r"(v[o + 15])
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
       : "memory");
 }
 // The loaded registers are operands of the wait so that no use of them can be
@@ -171,58 +182,66 @@ __device__ __forceinline__ void tmem_wait_ld(uint32_t (&v)[32]) {
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// x rounded to the nearest TF32 value (11 significand bits, ties away from zero);
-// the low 13 bits of the result are zero, so the tensor core reads it exactly.
-__device__ __forceinline__ float tf32_rn(float x) {
-  return __uint_as_float((__float_as_uint(x) + 0x00001000u) & 0xffffe000u);
+// |x|^2 of every row (float), once per upload: the error bound of a row's scores.
+__global__ void __launch_bounds__(256)
+rownorm_kernel(const float* __restrict__ X, size_t n, int d, float* __restrict__ xn) {
+  const int lane = threadIdx.x & 31;
+  const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const size_t nwarp = ((size_t)gridDim.x * blockDim.x) >> 5;
+  for (size_t row = warp; row < n; row += nwarp) {
+    const float* x = X + row * (size_t)d;
+    float s = 0.f;
+    for (int t = lane; t < d; t += 32) s = fmaf(x[t], x[t], s);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) xn[row] = s;
+  }
 }
 
-// Split centroid table for the tensor-core kernel: bh/bl = split(-2 c), rows
-// k..npad-1 zero with |c|^2 = +inf so that padding never wins the argmin.
+// Split centroid table: bh/bl = fp16 halves of (-2 c * sb), one row of 64 halves per
+// centroid (columns >= d and rows >= k zero); cn_pad[j] = |c_j|^2 * sx * sb, +inf for
+// padding rows; cn_pad[npad] = max_j |c_j|^2 (unscaled; zeroed before the launch).
 __global__ void __launch_bounds__(64)
-prep_kernel(const float* __restrict__ C, const float* __restrict__ cnorm, int k, int d, int npad,
-            float* __restrict__ bhi, float* __restrict__ blo, float* __restrict__ cnorm_pad) {
+prep_kernel(const float* __restrict__ C, const float* __restrict__ cnorm, int k, int d, int npad, float sb,
+            float sxsb, __half* __restrict__ bhi, __half* __restrict__ blo, float* __restrict__ cn_pad) {
   const int j = blockIdx.x;
-  for (int t = threadIdx.x; t < d; t += blockDim.x) {
-    float v = (j < k) ? -2.0f * C[(size_t)j * d + t] : 0.0f;
-    float h = tf32_rn(v);
-    bhi[(size_t)j * d + t] = h;
-    blo[(size_t)j * d + t] = tf32_rn(v - h);
-  }
-  if (threadIdx.x == 0) {
-    cnorm_pad[j] = (j < k) ? cnorm[j] : __int_as_float(0x7f800000);
-    // slot npad (zeroed before the launch) receives max |c|^2; non-negative floats order as ints
-    if (j < k) atomicMax(reinterpret_cast<int*>(cnorm_pad + npad), __float_as_int(cnorm[j]));
+  const int t = threadIdx.x;  // 64 threads = 64 columns
+  float v = (j < k && t < d) ? -2.0f * C[(size_t)j * d + t] * sb : 0.0f;
+  const __half h = __float2half_rn(v);
+  bhi[(size_t)j * 64 + t] = h;
+  blo[(size_t)j * 64 + t] = __float2half_rn(v - __half2float(h));
+  if (t == 0) {
+    cn_pad[j] = (j < k) ? cnorm[j] * sxsb : __int_as_float(0x7f800000);
+    // non-negative floats order as ints
+    if (j < k) atomicMax(reinterpret_cast<int*>(cn_pad + npad), __float_as_int(cnorm[j]));
   }
 }
 
-// Operand halves: xh is x itself (the tensor core ignores the low 13 bits of an
-// fp32 operand - measured on B200 - so it sees x truncated to TF32), xl is
-// x - trunc(x) rounded to TF32; -2c is split by rounding on both halves.
 // dbg: bit 1 (2) = do not issue the MMAs, bit 2 (4) = skip the epilogue arithmetic,
-// bit 3 (8) = skip the TMEM stores (timing experiments only).
+// bit 3 (8) = skip the TMEM stores (timing experiments only; labels stay valid;
+// 0 or 1 in production).
 template <int D>
 __global__ void __launch_bounds__(kThreads, 1)
 assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmBhi,
-                 const __grid_constant__ CUtensorMap tmBlo, const float* __restrict__ cnorm_pad,
-                 int* __restrict__ labels, size_t n, int n_tiles, int npad, IterState* st,
-                 int count_changes, unsigned int* __restrict__ amb_rows, float tol_rel, int dbg) {
+                 const __grid_constant__ CUtensorMap tmBlo, const float* __restrict__ cn_pad,
+                 const float* __restrict__ xnorm, int* __restrict__ labels, size_t n, int n_tiles, int npad,
+                 IterState* st, int count_changes, unsigned int* __restrict__ amb_rows, float tol_rel, float sx,
+                 float sxsb, int dbg) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_u32 = smem_u32(smem_raw);
   const uint32_t base = (raw_u32 + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (base - raw_u32);
 
-  constexpr int P = D / 32;  // 32-column panels per row tile
-  const uint32_t b_panel = (uint32_t)npad * 128u;
-  const uint32_t off_blo = (uint32_t)P * b_panel;
-  const uint32_t off_stage = 2u * P * b_panel;
+  constexpr int P = D / 32;    // 32-column fp32 panels per row tile
+  constexpr int KS = D / 16;   // K = 16 steps per term
+  const uint32_t b_panel = (uint32_t)npad * 128u;       // one fp16 panel: npad rows x 64 halves
+  const uint32_t off_blo = b_panel;
+  const uint32_t off_stage = 2u * b_panel;
   constexpr uint32_t stage_bytes = (uint32_t)P * 16384u;
   const uint32_t off_cn = off_stage + kStages * stage_bytes;
-  const uint32_t off_xn = off_cn + (uint32_t)npad * 4u;
-  const uint32_t off_bar = (off_xn + 2u * kBM * 4u + 7u) & ~7u;
+  const uint32_t off_bar = (off_cn + (uint32_t)npad * 4u + 7u) & ~7u;
   const uint32_t off_misc = off_bar + NUM_BARS * 8;
   float* cn_s = reinterpret_cast<float*>(sm + off_cn);
-  float* xn_s = reinterpret_cast<float*>(sm + off_xn);  // [2][128] |x|^2 of the rows in A buffer b
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(sm + off_misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + off_misc + 4);
   auto bar = [&](int i) { return base + off_bar + (uint32_t)i * 8u; };
@@ -233,17 +252,13 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(bar(FULL + s), 1); mbar_init(bar(EMPTY + s), 128); }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(bar(A_READY + b), 128);
-      mbar_init(bar(A_EMPTY + b), 1);
-      mbar_init(bar(ACC_FULL + b), 1);
-      mbar_init(bar(ACC_EMPTY + b), 128);
-    }
+    for (int b = 0; b < 2; ++b) { mbar_init(bar(A_READY + b), 128); mbar_init(bar(A_EMPTY + b), 1); }
+    for (int a = 0; a < kAcc; ++a) { mbar_init(bar(ACC_FULL + a), 1); mbar_init(bar(ACC_EMPTY + a), 128); }
     mbar_init(bar(B_FULL), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  for (int i = tid; i < npad; i += kThreads) cn_s[i] = cnorm_pad[i];
+  for (int i = tid; i < npad; i += kThreads) cn_s[i] = cn_pad[i];
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(base + off_misc),
                  "r"((uint32_t)kTmemCols)
@@ -254,18 +269,19 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  const float cn_max = cnorm_pad[npad];  // largest |c|^2, stored behind the padded table
-  // TMEM columns: accumulators at 0 and 128; A buffers b at 256 + 128 b (xh) and + 64 (xl)
-  const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(npad >> 3) << 17) | ((128u >> 4) << 24);
+  const float cn_max = cn_pad[npad];  // largest |c|^2 (unscaled), stored behind the padded table
+  // TMEM columns: accumulators at 0, 128, 256; A buffer b at 384 + 64 b: xh in 32 columns
+  // (two halves per column), xl in the next 32
+  constexpr uint32_t kACol = 384u;
+  // instruction descriptor: D = f32, A = B = f16, K-major, N = npad, M = 128
+  const uint32_t idesc = (1u << 4) | ((uint32_t)(npad >> 3) << 17) | ((128u >> 4) << 24);
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
-      mbar_expect_tx(bar(B_FULL), 2u * P * b_panel);
-      for (int p = 0; p < P; ++p) {
-        tma_load_2d(base + p * b_panel, &tmBhi, p * 32, 0, bar(B_FULL));
-        tma_load_2d(base + off_blo + p * b_panel, &tmBlo, p * 32, 0, bar(B_FULL));
-      }
+      mbar_expect_tx(bar(B_FULL), 2u * b_panel);
+      tma_load_2d(base, &tmBhi, 0, 0, bar(B_FULL));
+      tma_load_2d(base + off_blo, &tmBlo, 0, 0, bar(B_FULL));
       int i = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++i) {
@@ -291,51 +307,50 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     }
   } else if (warp == 1 || warp == 2) {
     // ------------------------------ MMA issuers -------------------------------
-    // Two issuing threads on two schedulers, one per A buffer / accumulator: the
-    // issue rate of a single thread (about ten scalar instructions per MMA) would
-    // otherwise cap the tensor pipe below its rate for these short K = 8 MMAs.
+    // Two issuing threads on two schedulers, one per A buffer: a single thread's
+    // issue rate (about ten scalar instructions per MMA) would otherwise cap the
+    // tensor pipe for these short MMAs.
     const int grp = warp - 1;
     if (lane == 0) {
       bool ok = mbar_wait(bar(B_FULL), 0, abort_flag, 2);
-      // the centroid panels never move: one shared-memory descriptor per (panel, k-step)
-      uint64_t bdesc_hi[P * 4], bdesc_lo[P * 4];
+      // the centroid panels never move: one shared-memory descriptor per k-step
+      uint64_t bdesc_hi[KS], bdesc_lo[KS];
 #pragma unroll
-      for (int p = 0; p < P; ++p)
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          bdesc_hi[p * 4 + kk] = smem_desc_sw128(base + p * b_panel + kk * 32u);
-          bdesc_lo[p * 4 + kk] = smem_desc_sw128(base + off_blo + p * b_panel + kk * 32u);
-        }
-      const uint32_t acc = tmem_base + (uint32_t)grp * 128u;
-      const uint32_t a_hi = tmem_base + 256u + (uint32_t)grp * 128u;
+      for (int kk = 0; kk < KS; ++kk) {
+        bdesc_hi[kk] = smem_desc_sw128(base + kk * 32u);
+        bdesc_lo[kk] = smem_desc_sw128(base + off_blo + kk * 32u);
+      }
+      const uint32_t a_hi = tmem_base + kACol + (uint32_t)grp * 64u;
       int i = grp;
+      int last_acc = 0;
+      uint32_t last_ph = 0;
       for (int tile = blockIdx.x + grp * gridDim.x; tile < n_tiles && ok; tile += 2 * gridDim.x, i += 2) {
         const uint32_t phb = (uint32_t)(i >> 1) & 1u;
+        const int a = i % kAcc;
+        const uint32_t pha = (uint32_t)(i / kAcc) & 1u;
         ok = mbar_wait(bar(A_READY + grp), phb, abort_flag, 3);
-        if (ok && i >= 2) ok = mbar_wait(bar(ACC_EMPTY + grp), phb ^ 1u, abort_flag, 4);
+        if (ok && i >= kAcc) ok = mbar_wait(bar(ACC_EMPTY + a), pha ^ 1u, abort_flag, 4);
         if (!ok) break;
         tc_fence_after();
+        const uint32_t acc = tmem_base + (uint32_t)a * 128u;
 #pragma unroll
         for (int term = 0; term < 3; ++term) {
 #pragma unroll
-          for (int p = 0; p < P; ++p) {
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-              const uint32_t a_col = a_hi + (term == 1 ? 64u : 0u) + p * 32u + kk * 8u;
-              const uint64_t bd = (term == 2) ? bdesc_lo[p * 4 + kk] : bdesc_hi[p * 4 + kk];
-              if (!(dbg & 2) && !((dbg & 64) && term > 0))
-                tc_mma_ts((dbg & 128) ? (acc ^ ((uint32_t)(kk & 1) << 6)) : acc, a_col, bd, idesc, (term | p | kk) ? 1u : 0u);
-            }
+          for (int kk = 0; kk < KS; ++kk) {
+            const uint32_t a_col = a_hi + (term == 1 ? 32u : 0u) + kk * 8u;
+            const uint64_t bd = (term == 2) ? bdesc_lo[kk] : bdesc_hi[kk];
+            if (!(dbg & 2)) tc_mma_ts(acc, a_col, bd, idesc, (term | kk) ? 1u : 0u);
           }
         }
         tc_commit(bar(A_EMPTY + grp));
-        tc_commit(bar(ACC_FULL + grp));
+        tc_commit(bar(ACC_FULL + a));
+        last_acc = a;
+        last_ph = pha;
       }
       if (!ok && i >= 2 + grp) {
         // aborting: the MMAs already issued must retire before TMEM is freed
-        const int j = i - 2;
         const unsigned long long t0 = gtime_ns();
-        while (!mbar_try(bar(ACC_FULL + grp), (uint32_t)(j >> 1) & 1u))
+        while (!mbar_try(bar(ACC_FULL + last_acc), last_ph))
           if (gtime_ns() - t0 > kWaitLimitNs) break;
       }
     }
@@ -348,7 +363,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     const int q = warp & 3;
     const int row = q * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    const uint32_t a_hi = tmem_base + lane_addr + 256u + (uint32_t)grp * 128u;
+    const uint32_t a_hi = tmem_base + lane_addr + kACol + (uint32_t)grp * 64u;
     bool ok = true;
     int i = grp;
     for (int tile = blockIdx.x + grp * gridDim.x; tile < n_tiles && ok; tile += 2 * gridDim.x, i += 2) {
@@ -361,40 +376,35 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       if (!ok) break;
       tc_fence_after();
       const uint8_t* stage = sm + off_stage + s * stage_bytes;
-      float xn = 0.0f;
 #pragma unroll
       for (int p = 0; p < P; ++p) {
         const uint8_t* rowp = stage + p * 16384 + row * 128;
         float4 xv[8];
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
-          xv[c] = (dbg & 32) ? make_float4(1.f, 2.f, 3.f, 4.f)
-                             : *reinterpret_cast<const float4*>(rowp + ((c ^ (row & 7)) << 4));
+        for (int c = 0; c < 8; ++c) xv[c] = *reinterpret_cast<const float4*>(rowp + ((c ^ (row & 7)) << 4));
+        // 32 floats -> 16 words of packed xh pairs and 16 words of packed xl pairs
+        uint32_t hi[16], lo[16];
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t hi[16], lo[16];
-#pragma unroll
-          for (int cc = 0; cc < 4; ++cc) {
-            const float4 x = xv[half * 4 + cc];
-            const float xs[4] = {x.x, x.y, x.z, x.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const uint32_t bits = __float_as_uint(xs[e]);
-              const float h = __uint_as_float(bits & 0xffffe000u);
-              xn = fmaf(xs[e], xs[e], xn);
-              hi[cc * 4 + e] = bits;
-              lo[cc * 4 + e] = __float_as_uint(tf32_rn(xs[e] - h));
-            }
-          }
-          if (!(dbg & 8)) {
-            tmem_st16(a_hi + p * 32u + half * 16u, hi);
-            tmem_st16(a_hi + 64u + p * 32u + half * 16u, lo);
-          } else if (hi[3] == 0x12345u && lo[7] == 0x54321u) {
-            labels[0] = 0;  // keeps the loads alive
-          }
+        for (int c = 0; c < 8; ++c) {
+          const float y0 = xv[c].x * sx, y1 = xv[c].y * sx, y2 = xv[c].z * sx, y3 = xv[c].w * sx;
+          const __half2 h01 = __floats2half2_rn(y0, y1);
+          const __half2 h23 = __floats2half2_rn(y2, y3);
+          const float2 f01 = __half22float2(h01);
+          const float2 f23 = __half22float2(h23);
+          const __half2 l01 = __floats2half2_rn(y0 - f01.x, y1 - f01.y);
+          const __half2 l23 = __floats2half2_rn(y2 - f23.x, y3 - f23.y);
+          hi[c * 2 + 0] = *reinterpret_cast<const uint32_t*>(&h01);
+          hi[c * 2 + 1] = *reinterpret_cast<const uint32_t*>(&h23);
+          lo[c * 2 + 0] = *reinterpret_cast<const uint32_t*>(&l01);
+          lo[c * 2 + 1] = *reinterpret_cast<const uint32_t*>(&l23);
+        }
+        if (!(dbg & 8)) {
+          tmem_st16(a_hi + p * 16u, hi);
+          tmem_st16(a_hi + 32u + p * 16u, lo);
+        } else if (hi[3] == 0x12345u && lo[7] == 0x54321u) {
+          labels[0] = 0;  // keeps the loads alive
         }
       }
-      xn_s[grp * kBM + row] = xn;
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar(EMPTY + s));
@@ -402,51 +412,45 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     }
   } else {
     // ------------------------------ epilogue ----------------------------------
-    // two groups of four warps; group g drains accumulator g
+    // three groups of four warps; group g owns accumulator g and takes the tiles with i % 3 == g
     const int grp = (warp - 12) >> 2;
     const int q = warp & 3;
     const int row_in_tile = q * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    const uint32_t acc = tmem_base + lane_addr + (uint32_t)grp * 128u;
     const float kInf = __int_as_float(0x7f800000);
     unsigned int changed = 0;
     bool ok = true;
     int i = grp;
-    for (int tile = blockIdx.x + grp * gridDim.x; tile < n_tiles && ok; tile += 2 * gridDim.x, i += 2) {
-      const uint32_t phb = (uint32_t)(i >> 1) & 1u;
-      // the previous label is only needed for the change count at the very end: fetch
-      // it now so that its DRAM round trip hides behind the wait and the arithmetic
+    for (int tile = blockIdx.x + grp * gridDim.x; tile < n_tiles && ok; tile += kAcc * gridDim.x, i += kAcc) {
+      const int a = grp;
+      const uint32_t pha = (uint32_t)(i / kAcc) & 1u;
+      // the previous label and |x|^2 are only needed at the very end: fetch them now so
+      // that their DRAM round trip hides behind the wait and the arithmetic
       const size_t row = (size_t)tile * kBM + row_in_tile;
       int old_label = -1;
-      if (count_changes && row < n) old_label = labels[row];
-      ok = mbar_wait(bar(ACC_FULL + grp), phb, abort_flag, 7);
+      float xn = 0.f;
+      if (row < n) {
+        xn = xnorm[row];
+        if (count_changes) old_label = labels[row];
+      }
+      ok = mbar_wait(bar(ACC_FULL + a), pha, abort_flag, 7);
       ok = __all_sync(0xffffffffu, ok);  // the tcgen05.ld below needs the whole warp
       if (!ok) break;
       tc_fence_after();
+      const uint32_t acc = tmem_base + lane_addr + (uint32_t)a * 128u;
       // four interleaved (best, second, index) chains keep the compare/select
       // dependency short; chain q sees columns j with j % 4 == q in ascending order
       float bst[4] = {kInf, kInf, kInf, kInf}, sec[4] = {kInf, kInf, kInf, kInf};
       int bix[4] = {0, 0, 0, 0};
-      // The load of chunk ch+1 is issued before the arithmetic on chunk ch, so its
-      // latency overlaps the compare/select work (tcgen05.wait::ld waits for all loads
-      // in flight, hence "wait, issue next, compute").
-      uint32_t va[32], vb[32];
-      if (!(dbg & 4)) {
-        tmem_ld16(acc, va, 0);
-        if (16 < npad) tmem_ld16(acc + 16, va, 16);
-      }
 #pragma unroll
       for (int ch = 0; ch < kMaxNPad / 32; ++ch) {
         const int c0 = ch * 32;  // compile-time after unrolling: column indices are immediates
         if (c0 < npad && !(dbg & 4)) {
-          uint32_t(&v)[32] = (ch & 1) ? vb : va;
-          uint32_t(&vn)[32] = (ch & 1) ? va : vb;
+          uint32_t v[32];
           const bool two = (c0 + 16 < npad);
+          tmem_ld16(acc + c0, v, 0);
+          if (two) tmem_ld16(acc + c0 + 16, v, 16);
           tmem_wait_ld(v);
-          if (c0 + 32 < npad) {
-            tmem_ld16(acc + c0 + 32, vn, 0);
-            if (c0 + 48 < npad) tmem_ld16(acc + c0 + 48, vn, 16);
-          }
 #pragma unroll
           for (int j4 = 0; j4 < 8; ++j4) {
             if (j4 < 4 || two) {
@@ -464,9 +468,8 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           }
         }
       }
-      const float xn = xn_s[grp * kBM + row_in_tile];
       tc_fence_before();
-      mbar_arrive(bar(ACC_EMPTY + grp));
+      mbar_arrive(bar(ACC_EMPTY + a));
       float best = bst[0], second = sec[0];
       int bidx = bix[0];
 #pragma unroll
@@ -480,10 +483,11 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         }
         second = fminf(second, sec[qq]);
       }
-      if (row < n && !(dbg & 16)) {
-        // rows whose two best scores are closer than the error bound of the 3xTF32
-        // product are left to the exact re-evaluation pass
-        const float tol = tol_rel * (xn + cn_max);
+      if (dbg & 4) { best = 0.f; second = 3.0e38f; }  // timing experiments: nothing is ambiguous
+      if (row < n) {
+        // rows whose two best scores are closer than the error bound of the split
+        // product are left to the exact re-evaluation pass (scores carry the factor sx*sb)
+        const float tol = tol_rel * (xn + cn_max) * sxsb;
         if (amb_rows != nullptr && !(second - best > tol)) {
           const unsigned int pos = atomicAdd(&st->amb_count, 1u);
           amb_rows[pos] = (unsigned int)row;

@@ -129,6 +129,8 @@ struct Engine : EngineBase {
   int launch_assign(Shard<T>& s, bool use_tc, bool count_changes);
   int tc_mask_hi = 1;
   float tc_tol_rel = tc::kTolRel;
+  float tc_sx = 1.f, tc_sb = 1.f;   // operand scales of the tensor-core kernel
+  double cbound = 0;                // bound on |centroid coordinate|: max(|x|, |initial centroids|)
 
   // launch helpers (device of the shard must be current)
   int launch_tiles(Shard<T>& s, const T* Xp, size_t nrows, int* labels, int mode, T* out, size_t ld_out,
@@ -377,8 +379,12 @@ template <typename T>
 int Engine<T>::set_centroids(int k_, const T* host_c) {
   if (k_ < 1 || !host_c) KM_FAIL(KM_EINVAL, "kmeans_set_centroids: bad argument");
   if (d == 0) KM_FAIL(KM_ESTATE, "kmeans_set_centroids: attach data first (defines cols)");
-  for (size_t i = 0; i < (size_t)k_ * d; ++i)
+  double cmax = 0;
+  for (size_t i = 0; i < (size_t)k_ * d; ++i) {
     if (!std::isfinite((double)host_c[i])) KM_FAIL(KM_ENONFINITE, "centroids contain NaN or Inf");
+    cmax = std::max(cmax, std::fabs((double)host_c[i]));
+  }
+  cbound = cmax;
   KM_TRY(ensure_buffers(k_));
   k = k_;
   cur = 0;
@@ -585,13 +591,20 @@ bool Engine<T>::tc_ok(int flags) const {
   if (!std::is_same<T, float>::value || (flags & KM_FIT_FORCE_SIMT)) return false;
   if (!tc::shape_ok(k, d)) return false;
   for (const auto& s : shards)
-    if (s.cc_major != 10 || (reinterpret_cast<uintptr_t>(s.X) & 15) != 0) return false;
-  return true;
+    if (s.cc_major != 10 || (reinterpret_cast<uintptr_t>(s.X) & 15) != 0 || !s.x_checked) return false;
+  double xmax = 0;
+  for (const auto& s : shards) xmax = std::max(xmax, s.xmax);
+  float sx, sb;
+  return tc::pick_scales(xmax, std::max(xmax, cbound), &sx, &sb);
 }
 
 template <typename T>
 int Engine<T>::tc_refresh(Shard<T>& s) {
   if constexpr (std::is_same<T, float>::value) {
+    double xmax = 0;
+    for (const auto& sh : shards) xmax = std::max(xmax, sh.xmax);
+    if (!tc::pick_scales(xmax, std::max(xmax, cbound), &tc_sx, &tc_sb))
+      KM_FAIL(KM_EINVAL, "data magnitude outside the range of the tensor-core kernel");
     if (s.rows > 0xffffffffULL) KM_FAIL(KM_EINVAL, "shard too large for the tensor-core kernel");
     if (s.amb_cap < s.rows) {
       cudaFree(s.amb_rows);
@@ -599,7 +612,9 @@ int Engine<T>::tc_refresh(Shard<T>& s) {
       KM_CUDA(cudaMalloc(&s.amb_rows, s.rows * sizeof(unsigned int)));
       s.amb_cap = s.rows;
     }
-    KM_TRY(tc::setup(s.tcp, s.X, s.rows, k, d));
+    KM_TRY(tc::setup(s.tcp, s.X, s.rows, k, d, s.num_sms, s.stream));
+    s.tcp.sx = tc_sx;
+    s.tcp.sb = tc_sb;
     KM_TRY(tc::prep(s.tcp, s.C[cur], s.cnorm, s.stream));
     ++launches;
   }
@@ -613,8 +628,15 @@ int Engine<T>::launch_assign(Shard<T>& s, bool use_tc, bool count_changes) {
       launches += 2;
       KM_TRY(tc::launch(s.tcp, s.labels, s.st, count_changes, s.amb_rows, tc_tol_rel, s.num_sms, tc_mask_hi,
                         s.stream));
-      refine_kernel<float><<<s.num_sms * 2, 256, 0, s.stream>>>(s.X, d, s.C[cur], k, s.amb_rows, s.st, s.labels,
-                                                               count_changes ? 1 : 0);
+      // (k <= 128 on this path: four centroids per lane)
+      const size_t rsm = refine_smem_bytes<float>(k, d);
+      static bool attr_set = false;
+      if (!attr_set) {
+        KM_CUDA(cudaFuncSetAttribute(refine_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        attr_set = true;
+      }
+      refine_kernel<float><<<s.num_sms * 2, kRefineThreads, rsm, s.stream>>>(s.X, d, s.C[cur], k, s.amb_rows, s.st,
+                                                                            s.labels, count_changes ? 1 : 0);
       KM_CUDA(cudaGetLastError());
       return KM_OK;
     }

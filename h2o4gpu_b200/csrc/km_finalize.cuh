@@ -97,10 +97,19 @@ prepare_kernel(const unsigned long long* __restrict__ gcounts, int k, IterState*
   s_best[threadIdx.x] = best;
   s_idx[threadIdx.x] = bi;
   __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (threadIdx.x < o) {
+      const unsigned long long ob = s_best[threadIdx.x + o];
+      const int oi = s_idx[threadIdx.x + o];
+      if (ob > s_best[threadIdx.x] || (ob == s_best[threadIdx.x] && oi < s_idx[threadIdx.x])) {
+        s_best[threadIdx.x] = ob;
+        s_idx[threadIdx.x] = oi;
+      }
+    }
+    __syncthreads();
+  }
   if (threadIdx.x == 0) {
-    for (int t = 1; t < 256; ++t)
-      if (s_best[t] > best || (s_best[t] == best && s_idx[t] < bi)) { best = s_best[t]; bi = s_idx[t]; }
-    st->argmax_count = bi;
+    st->argmax_count = s_idx[0];
     st->n_empty = s_n;
     st->relocated = 0;
     if (host_n_empty) *host_n_empty = s_n;

@@ -4,14 +4,28 @@
 // double precision and takes the argmin (first minimum wins), so labels agree
 // with exact arithmetic on the float inputs.  The list is short (a fraction of
 // a percent of the rows), bounded by the shard size in the worst case.
+//
+// The centroid table is staged once per CTA in shared memory, transposed
+// ([d][k], so the lanes of a warp read consecutive centroids of one column), with
+// |c|^2 in double; each lane carries up to kRefineCpl centroids as independent
+// FMA chains.
 #pragma once
 
 #include "km_common.cuh"
 
 namespace km {
 
+constexpr int kRefineThreads = 256;
+constexpr int kRefineCpl = 4;  // centroids per lane: k <= 32 * kRefineCpl
+
 template <typename T>
-__global__ void __launch_bounds__(256)
+inline size_t refine_smem_bytes(int k, int d) {
+  const int kp = (k + 31) / 32 * 32;
+  return (size_t)d * kp * sizeof(T) + (size_t)kp * sizeof(double) + 16;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kRefineThreads)
 refine_kernel(const T* __restrict__ X, int d, const T* __restrict__ C, int k,
               const unsigned int* __restrict__ amb_rows, IterState* st, int* __restrict__ labels,
               int count_changes) {
@@ -19,22 +33,50 @@ refine_kernel(const T* __restrict__ X, int d, const T* __restrict__ C, int k,
   const int lane = threadIdx.x & 31;
   const unsigned int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const unsigned int nwarp = (gridDim.x * blockDim.x) >> 5;
+  if (blockIdx.x * (kRefineThreads / 32) >= cnt) return;  // no row for this CTA (uniform)
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int kp = (k + 31) / 32 * 32;
+  double* cn_s = reinterpret_cast<double*>(smem_raw);            // [kp]
+  T* Ct = reinterpret_cast<T*>(cn_s + kp);                       // [d][kp]
+  for (int i = threadIdx.x; i < d * kp; i += kRefineThreads) {
+    const int t = i / kp, c = i - t * kp;
+    Ct[i] = (c < k) ? C[(size_t)c * d + t] : (T)0;
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < kp; c += kRefineThreads) {
+    double s = 0.0;
+    for (int t = 0; t < d; ++t) {
+      const double v = (double)Ct[t * kp + c];
+      s = fma(v, v, s);
+    }
+    cn_s[c] = s;
+  }
+  __syncthreads();
+
   unsigned int changed = 0;
   for (unsigned int e = warp; e < cnt; e += nwarp) {
     const size_t row = amb_rows[e];
     const T* x = X + row * (size_t)d;
+    double dot[kRefineCpl];
+#pragma unroll
+    for (int u = 0; u < kRefineCpl; ++u) dot[u] = 0.0;
+    for (int t = 0; t < d; ++t) {
+      const double xv = (double)x[t];
+      const T* ct = Ct + t * kp + lane;
+#pragma unroll
+      for (int u = 0; u < kRefineCpl; ++u)
+        if (u * 32 < kp) dot[u] = fma(xv, (double)ct[u * 32], dot[u]);
+    }
     double best = __longlong_as_double(0x7ff0000000000000LL);
     int bi = 0x7fffffff;
-    for (int c = lane; c < k; c += 32) {
-      const T* cv = C + (size_t)c * d;
-      double dot = 0.0, cn = 0.0;
-      for (int t = 0; t < d; ++t) {
-        const double cc = (double)cv[t];
-        dot = fma((double)x[t], cc, dot);
-        cn = fma(cc, cc, cn);
+#pragma unroll
+    for (int u = 0; u < kRefineCpl; ++u) {
+      const int c = u * 32 + lane;
+      if (c < k) {
+        const double s = cn_s[c] - 2.0 * dot[u];
+        if (s < best) { best = s; bi = c; }
       }
-      const double s = cn - 2.0 * dot;
-      if (s < best) { best = s; bi = c; }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {

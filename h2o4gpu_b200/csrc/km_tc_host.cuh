@@ -24,15 +24,17 @@ inline EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// rows x cols fp32 row-major, boxes of box_rows x 32 columns, 128-byte swizzle
-inline int make_map(CUtensorMap* map, const float* base, size_t rows, int cols, int box_rows) {
+// rows x cols row-major matrix of fp32 (elem 4) or fp16 (elem 2), boxes of box_rows rows x
+// 128 bytes, 128-byte swizzle
+inline int make_map(CUtensorMap* map, const void* base, size_t rows, int cols, int box_rows, int elem) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) KM_FAIL(KM_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t gstride[1] = {(cuuint64_t)cols * sizeof(float)};
-  cuuint32_t box[2] = {32u, (cuuint32_t)box_rows};
+  cuuint64_t gstride[1] = {(cuuint64_t)cols * elem};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / elem), (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1u, 1u};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), gdim, gstride, box, estr,
+  CUresult r = fn(map, elem == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                  const_cast<void*>(base), gdim, gstride, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) KM_FAIL(KM_ECUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
@@ -40,37 +42,74 @@ inline int make_map(CUtensorMap* map, const float* base, size_t rows, int cols, 
 }
 
 struct Plan {
-  float* bhi = nullptr;
-  float* blo = nullptr;
-  float* cn = nullptr;
+  __half* bhi = nullptr;   // [npad][64] upper halves of -2 c * sb
+  __half* blo = nullptr;   // [npad][64] lower halves
+  float* cn = nullptr;     // [npad] |c|^2 * sx * sb (+inf padding), [npad] max |c|^2
+  float* xnorm = nullptr;  // [rows] |x|^2
+  size_t xnorm_cap = 0;
+  const float* xnorm_of = nullptr;
+  size_t xnorm_rows = 0;
   int npad = 0, k = 0, d = 0;
   const float* x_base = nullptr;
   size_t x_rows = 0;
+  float sx = 1.f, sb = 1.f;
   CUtensorMap tmX, tmBhi, tmBlo;
   bool ready = false;
 
   void release() {
-    cudaFree(bhi); cudaFree(blo); cudaFree(cn);
-    bhi = blo = cn = nullptr;
+    cudaFree(bhi); cudaFree(blo); cudaFree(cn); cudaFree(xnorm);
+    bhi = blo = nullptr;
+    cn = xnorm = nullptr;
+    xnorm_cap = 0;
+    xnorm_of = nullptr;
     ready = false;
   }
 };
 
+// Power-of-two scales that put x * sx and 2 c * sb below 2^14 (fp16 overflows at 65504):
+// xmax bounds |x|, cbound bounds |c| (centroids are means of rows, or the caller's
+// initial table).  Returns false when the magnitudes cannot be scaled into range.
+inline bool pick_scales(double xmax, double cbound, float* sx, float* sb) {
+  int ex = 0, ec = 0;
+  if (xmax > 0) std::frexp(xmax, &ex);
+  if (cbound > 0) std::frexp(cbound, &ec);
+  const int px = 14 - ex, pb = 13 - ec;
+  if (px < -100 || px > 100 || pb < -100 || pb > 100 || px + pb < -120 || px + pb > 120) return false;
+  *sx = (float)std::ldexp(1.0, px);
+  *sb = (float)std::ldexp(1.0, pb);
+  return true;
+}
+
 inline bool shape_ok(int k, int d) { return (d == 32 || d == 64) && k > 16 && k <= kMaxNPad; }
 
-inline int setup(Plan& pl, const float* X, size_t rows, int k, int d) {
+inline int setup(Plan& pl, const float* X, size_t rows, int k, int d, int num_sms, cudaStream_t stream) {
   const int npad = (k + 15) / 16 * 16;
+  // |x|^2 per row, once per attached matrix
+  if (pl.xnorm_of != X || pl.xnorm_rows != rows) {
+    if (pl.xnorm_cap < rows) {
+      cudaFree(pl.xnorm);
+      pl.xnorm = nullptr;
+      KM_CUDA(cudaMalloc(&pl.xnorm, rows * sizeof(float)));
+      pl.xnorm_cap = rows;
+    }
+    rownorm_kernel<<<num_sms * 8, 256, 0, stream>>>(X, rows, d, pl.xnorm);
+    KM_CUDA(cudaGetLastError());
+    pl.xnorm_of = X;
+    pl.xnorm_rows = rows;
+  }
   if (pl.ready && pl.k == k && pl.d == d && pl.x_base == X && pl.x_rows == rows) return KM_OK;
   if (!(pl.bhi && pl.k == k && pl.d == d)) {
-    pl.release();
-    KM_CUDA(cudaMalloc(&pl.bhi, (size_t)npad * d * sizeof(float)));
-    KM_CUDA(cudaMalloc(&pl.blo, (size_t)npad * d * sizeof(float)));
+    cudaFree(pl.bhi); cudaFree(pl.blo); cudaFree(pl.cn);
+    pl.bhi = pl.blo = nullptr;
+    pl.cn = nullptr;
+    KM_CUDA(cudaMalloc(&pl.bhi, (size_t)npad * 64 * sizeof(__half)));
+    KM_CUDA(cudaMalloc(&pl.blo, (size_t)npad * 64 * sizeof(__half)));
     KM_CUDA(cudaMalloc(&pl.cn, (size_t)(npad + 1) * sizeof(float)));
   }
   pl.npad = npad; pl.k = k; pl.d = d; pl.x_base = X; pl.x_rows = rows;
-  KM_TRY(make_map(&pl.tmX, X, rows, d, kBM));
-  KM_TRY(make_map(&pl.tmBhi, pl.bhi, npad, d, npad));
-  KM_TRY(make_map(&pl.tmBlo, pl.blo, npad, d, npad));
+  KM_TRY(make_map(&pl.tmX, X, rows, d, kBM, 4));
+  KM_TRY(make_map(&pl.tmBhi, pl.bhi, npad, 64, npad, 2));
+  KM_TRY(make_map(&pl.tmBlo, pl.blo, npad, 64, npad, 2));
   if (d == 32)
     KM_CUDA(cudaFuncSetAttribute(assign_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem_bytes(d, npad)));
@@ -83,15 +122,15 @@ inline int setup(Plan& pl, const float* X, size_t rows, int k, int d) {
 
 inline int prep(Plan& pl, const float* C, const float* cnorm, cudaStream_t stream) {
   KM_CUDA(cudaMemsetAsync(pl.cn + pl.npad, 0, sizeof(float), stream));
-  prep_kernel<<<pl.npad, 64, 0, stream>>>(C, cnorm, pl.k, pl.d, pl.npad, pl.bhi, pl.blo, pl.cn);
+  prep_kernel<<<pl.npad, 64, 0, stream>>>(C, cnorm, pl.k, pl.d, pl.npad, pl.sb, pl.sx * pl.sb, pl.bhi, pl.blo, pl.cn);
   KM_CUDA(cudaGetLastError());
   return KM_OK;
 }
 
 // tol_rel: a row goes to the exact pass when second - best <= tol_rel * (|x|^2 + max|c|^2).
-// Error of the 3xTF32 product: xh truncated (exact residual), xl and both halves of
-// -2c rounded to TF32 (2^-12 relative each), xl.bl dropped (2^-21 |x||b|): about
-// 2^-20.4 (|x|^2 + |c|^2) per score, twice that for a difference -> 2^-19.
+// Error of the split product: the low halves of x and of -2c are rounded to 11 bits
+// (2^-23 relative each), xl.bl is dropped (2^-22 |x||b|), fp32 accumulation of 3 d / 16
+// partial sums: below 2^-20.4 (|x|^2 + |c|^2) per score, twice that for a difference.
 constexpr float kTolRel = 1.9073486328125e-06f;
 
 inline int launch(Plan& pl, int* labels, IterState* st, bool count_changes, unsigned int* amb_rows, float tol_rel,
@@ -101,12 +140,12 @@ inline int launch(Plan& pl, int* labels, IterState* st, bool count_changes, unsi
   const int grid = (int)std::min<size_t>(tiles, (size_t)num_sms);
   if (pl.d == 32)
     assign_tc_kernel<32><<<grid, kThreads, smem_bytes(pl.d, pl.npad), stream>>>(
-        pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, labels, pl.x_rows, (int)tiles, pl.npad, st, count_changes ? 1 : 0,
-        amb_rows, tol_rel, mask_hi);
+        pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, pl.xnorm, labels, pl.x_rows, (int)tiles, pl.npad, st,
+        count_changes ? 1 : 0, amb_rows, tol_rel, pl.sx, pl.sx * pl.sb, mask_hi);
   else
     assign_tc_kernel<64><<<grid, kThreads, smem_bytes(pl.d, pl.npad), stream>>>(
-        pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, labels, pl.x_rows, (int)tiles, pl.npad, st, count_changes ? 1 : 0,
-        amb_rows, tol_rel, mask_hi);
+        pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, pl.xnorm, labels, pl.x_rows, (int)tiles, pl.npad, st,
+        count_changes ? 1 : 0, amb_rows, tol_rel, pl.sx, pl.sx * pl.sb, mask_hi);
   KM_CUDA(cudaGetLastError());
   return KM_OK;
 }
