@@ -53,6 +53,7 @@ struct Shard {
   int num_sms = 0;
   int cc_major = 0;
   tc::Plan tcp;  // tensor-core path (float only)
+  tcb::BigPlan tcbp;  // tensor-core path for large centroid tables
   unsigned int* amb_rows = nullptr;  // rows handed to the exact re-evaluation pass
   size_t amb_cap = 0;
   unsigned int* amb_log = nullptr;
@@ -207,6 +208,7 @@ void Engine<T>::destroy() {
       if (api) api->CommDestroy(s.comm);
     }
     s.tcp.release();
+    s.tcbp.release();
     cudaFree(s.amb_rows); cudaFree(s.amb_log);
     cudaFree(s.X_owned); cudaFree(s.labels); cudaFree(s.dist); cudaFree(s.gacc);
     cudaFree(s.C[0]); cudaFree(s.C[1]); cudaFree(s.cnorm); cudaFree(s.shift_k); cudaFree(s.empties);
@@ -589,7 +591,7 @@ int Engine<T>::launch_accumulate(Shard<T>& s, T scale) {
 template <typename T>
 bool Engine<T>::tc_ok(int flags) const {
   if (!std::is_same<T, float>::value || (flags & KM_FIT_FORCE_SIMT)) return false;
-  if (!tc::shape_ok(k, d)) return false;
+  if (!tc::shape_ok(k, d) && !tcb::big_shape_ok(k, d)) return false;
   for (const auto& s : shards)
     if (s.cc_major != 10 || (reinterpret_cast<uintptr_t>(s.X) & 15) != 0 || !s.x_checked) return false;
   double xmax = 0;
@@ -612,10 +614,18 @@ int Engine<T>::tc_refresh(Shard<T>& s) {
       KM_CUDA(cudaMalloc(&s.amb_rows, s.rows * sizeof(unsigned int)));
       s.amb_cap = s.rows;
     }
-    KM_TRY(tc::setup(s.tcp, s.X, s.rows, k, d, s.num_sms, s.stream));
-    s.tcp.sx = tc_sx;
-    s.tcp.sb = tc_sb;
-    KM_TRY(tc::prep(s.tcp, s.C[cur], s.cnorm, s.stream));
+    if (tc::shape_ok(k, d)) {
+      KM_TRY(tc::setup(s.tcp, s.X, s.rows, k, d, s.num_sms, s.stream));
+      s.tcp.sx = tc_sx;
+      s.tcp.sb = tc_sb;
+      KM_TRY(tc::prep(s.tcp, s.C[cur], s.cnorm, s.stream));
+    } else {
+      KM_TRY(tc::ensure_xnorm(s.tcp, s.X, s.rows, d, s.num_sms, s.stream));
+      KM_TRY(tcb::big_setup(s.tcbp, s.X, s.rows, k, d));
+      s.tcbp.sx = tc_sx;
+      s.tcbp.sb = tc_sb;
+      KM_TRY(tcb::big_prep(s.tcbp, s.C[cur], s.cnorm, s.stream));
+    }
     ++launches;
   }
   return KM_OK;
@@ -624,6 +634,15 @@ int Engine<T>::tc_refresh(Shard<T>& s) {
 template <typename T>
 int Engine<T>::launch_assign(Shard<T>& s, bool use_tc, bool count_changes) {
   if constexpr (std::is_same<T, float>::value) {
+    if (use_tc && !tc::shape_ok(k, d)) {
+      launches += 2;
+      KM_TRY(tcb::big_launch(s.tcbp, s.tcp.xnorm, s.labels, s.st, count_changes, s.amb_rows, tc_tol_rel, s.num_sms,
+                             s.stream));
+      tcb::refine_big_kernel<float><<<s.num_sms * 2, 256, 0, s.stream>>>(s.X, d, s.C[cur], k, s.amb_rows, s.st,
+                                                                        s.labels, count_changes ? 1 : 0);
+      KM_CUDA(cudaGetLastError());
+      return KM_OK;
+    }
     if (use_tc) {
       launches += 2;
       KM_TRY(tc::launch(s.tcp, s.labels, s.st, count_changes, s.amb_rows, tc_tol_rel, s.num_sms, tc_mask_hi,

@@ -82,9 +82,8 @@ inline bool pick_scales(double xmax, double cbound, float* sx, float* sb) {
 
 inline bool shape_ok(int k, int d) { return (d == 32 || d == 64) && k > 16 && k <= kMaxNPad; }
 
-inline int setup(Plan& pl, const float* X, size_t rows, int k, int d, int num_sms, cudaStream_t stream) {
-  const int npad = (k + 15) / 16 * 16;
-  // |x|^2 per row, once per attached matrix
+// |x|^2 per row, once per attached matrix
+inline int ensure_xnorm(Plan& pl, const float* X, size_t rows, int d, int num_sms, cudaStream_t stream) {
   if (pl.xnorm_of != X || pl.xnorm_rows != rows) {
     if (pl.xnorm_cap < rows) {
       cudaFree(pl.xnorm);
@@ -97,6 +96,12 @@ inline int setup(Plan& pl, const float* X, size_t rows, int k, int d, int num_sm
     pl.xnorm_of = X;
     pl.xnorm_rows = rows;
   }
+  return KM_OK;
+}
+
+inline int setup(Plan& pl, const float* X, size_t rows, int k, int d, int num_sms, cudaStream_t stream) {
+  const int npad = (k + 15) / 16 * 16;
+  KM_TRY(ensure_xnorm(pl, X, rows, d, num_sms, stream));
   if (pl.ready && pl.k == k && pl.d == d && pl.x_base == X && pl.x_rows == rows) return KM_OK;
   if (!(pl.bhi && pl.k == k && pl.d == d)) {
     cudaFree(pl.bhi); cudaFree(pl.blo); cudaFree(pl.cn);
@@ -151,4 +156,94 @@ inline int launch(Plan& pl, int* labels, IterState* st, bool count_changes, unsi
 }
 
 }  // namespace tc
+}  // namespace km
+
+#include "km_assign_tc_big.cuh"
+
+namespace km {
+namespace tcb {
+
+struct BigPlan {
+  __half* bhi = nullptr;
+  __half* blo = nullptr;
+  float* cn = nullptr;
+  int kpad = 0, k = 0, d = 0, dp = 0;
+  const float* x_base = nullptr;
+  size_t x_rows = 0;
+  float sx = 1.f, sb = 1.f;
+  CUtensorMap tmX, tmBhi, tmBlo;
+  bool ready = false;
+  void release() {
+    cudaFree(bhi); cudaFree(blo); cudaFree(cn);
+    bhi = blo = nullptr;
+    cn = nullptr;
+    ready = false;
+  }
+};
+
+// float32, d in {32, 64, 128, 256}; the |c|^2 table of all centroids must fit shared memory
+inline bool big_shape_ok(int k, int d) {
+  return (d == 32 || d == 64 || d == 128 || d == 256) && k > 16 && k <= 6144;
+}
+
+template <int D>
+inline int big_set_attr(int kpad) {
+  KM_CUDA(cudaFuncSetAttribute(assign_tc_big_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)big_smem_bytes<D>(kpad)));
+  return KM_OK;
+}
+
+inline int big_setup(BigPlan& pl, const float* X, size_t rows, int k, int d) {
+  const int kpad = (k + kNT - 1) / kNT * kNT;
+  const int dp = d < 64 ? 64 : d;
+  if (pl.ready && pl.k == k && pl.d == d && pl.x_base == X && pl.x_rows == rows) return KM_OK;
+  if (!(pl.bhi && pl.k == k && pl.d == d)) {
+    pl.release();
+    KM_CUDA(cudaMalloc(&pl.bhi, (size_t)kpad * dp * sizeof(__half)));
+    KM_CUDA(cudaMalloc(&pl.blo, (size_t)kpad * dp * sizeof(__half)));
+    KM_CUDA(cudaMalloc(&pl.cn, (size_t)(kpad + 1) * sizeof(float)));
+  }
+  pl.kpad = kpad; pl.k = k; pl.d = d; pl.dp = dp; pl.x_base = X; pl.x_rows = rows;
+  KM_TRY(tc::make_map(&pl.tmX, X, rows, d, kBM, 4));
+  KM_TRY(tc::make_map(&pl.tmBhi, pl.bhi, kpad, dp, kNT, 2));
+  KM_TRY(tc::make_map(&pl.tmBlo, pl.blo, kpad, dp, kNT, 2));
+  if (d == 32) KM_TRY(big_set_attr<32>(kpad));
+  else if (d == 64) KM_TRY(big_set_attr<64>(kpad));
+  else if (d == 128) KM_TRY(big_set_attr<128>(kpad));
+  else KM_TRY(big_set_attr<256>(kpad));
+  pl.ready = true;
+  return KM_OK;
+}
+
+inline int big_prep(BigPlan& pl, const float* C, const float* cnorm, cudaStream_t stream) {
+  KM_CUDA(cudaMemsetAsync(pl.cn + pl.kpad, 0, sizeof(float), stream));
+  big_prep_kernel<<<pl.kpad, 256, 0, stream>>>(C, cnorm, pl.k, pl.d, pl.dp, pl.kpad, pl.sb, pl.sx * pl.sb, pl.bhi,
+                                               pl.blo, pl.cn);
+  KM_CUDA(cudaGetLastError());
+  return KM_OK;
+}
+
+template <int D>
+inline void big_launch_d(BigPlan& pl, const float* xnorm, int* labels, IterState* st, int count_changes,
+                         unsigned int* amb_rows, float tol_rel, int grid, int tiles, cudaStream_t stream) {
+  assign_tc_big_kernel<D><<<grid, kBigThreads, big_smem_bytes<D>(pl.kpad), stream>>>(
+      pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, xnorm, labels, pl.x_rows, tiles, pl.kpad, st, count_changes, amb_rows,
+      tol_rel, pl.sx, pl.sx * pl.sb);
+}
+
+inline int big_launch(BigPlan& pl, const float* xnorm, int* labels, IterState* st, bool count_changes,
+                      unsigned int* amb_rows, float tol_rel, int num_sms, cudaStream_t stream) {
+  const size_t tiles = (pl.x_rows + kBM - 1) / kBM;
+  if (tiles > 0x7fffffffULL / kBM) KM_FAIL(KM_EINVAL, "shard too large for the tensor-core kernel");
+  const int grid = (int)std::min<size_t>(tiles, (size_t)num_sms);
+  const int cc = count_changes ? 1 : 0;
+  if (pl.d == 32) big_launch_d<32>(pl, xnorm, labels, st, cc, amb_rows, tol_rel, grid, (int)tiles, stream);
+  else if (pl.d == 64) big_launch_d<64>(pl, xnorm, labels, st, cc, amb_rows, tol_rel, grid, (int)tiles, stream);
+  else if (pl.d == 128) big_launch_d<128>(pl, xnorm, labels, st, cc, amb_rows, tol_rel, grid, (int)tiles, stream);
+  else big_launch_d<256>(pl, xnorm, labels, st, cc, amb_rows, tol_rel, grid, (int)tiles, stream);
+  KM_CUDA(cudaGetLastError());
+  return KM_OK;
+}
+
+}  // namespace tcb
 }  // namespace km
