@@ -11,7 +11,9 @@
 #include <chrono>
 #include <cmath>
 #include <cstring>
+#include <map>
 #include <memory>
+#include <mutex>
 #include <vector>
 
 #include "km_accumulate.cuh"
@@ -102,6 +104,7 @@ template <typename T>
 struct Engine : EngineBase {
   std::vector<Shard<T>> shards;
   int world_rank0 = 0, world_size = 1;
+  bool comm_cached = false;
   size_t n_total = 0;
   int d = 0, k = 0;
   int cur = 0;  // index of the current centroid buffer
@@ -178,10 +181,21 @@ int Engine<T>::init(int n_local, const int* devs, int rank0, int world, const vo
     NcclApi* api = NcclApi::get();
     if (!api) KM_FAIL(KM_ENCCL, "more than one GPU requested but libnccl.so.2 could not be loaded");
     if (world == n_local) {
-      std::vector<ncclComm_t> comms(n_local);
+      // Communicators of a one-process device set are kept for the life of the process:
+      // creating them costs far more than a whole fit, and the reference's entry points
+      // are called once per fit / predict.
+      static std::mutex cache_mutex;
+      static std::map<std::vector<int>, std::vector<ncclComm_t>> cache;
+      std::lock_guard<std::mutex> lock(cache_mutex);
       std::vector<int> dl(devs, devs + n_local);
-      KM_NCCL(api, api->CommInitAll(comms.data(), n_local, dl.data()));
-      for (int i = 0; i < n_local; ++i) shards[i].comm = comms[i];
+      auto it = cache.find(dl);
+      if (it == cache.end()) {
+        std::vector<ncclComm_t> comms(n_local);
+        KM_NCCL(api, api->CommInitAll(comms.data(), n_local, dl.data()));
+        it = cache.emplace(dl, comms).first;
+      }
+      for (int i = 0; i < n_local; ++i) shards[i].comm = it->second[i];
+      comm_cached = true;
     } else {
       if (!nccl_id) KM_FAIL(KM_EINVAL, "kmeans_create: nccl_id required when world_size > n_local");
       ncclUniqueId id;
@@ -203,7 +217,7 @@ void Engine<T>::destroy() {
     if (s.dev < 0) continue;
     DevGuard g(s.dev);
     if (s.stream) cudaStreamSynchronize(s.stream);
-    if (s.comm) {
+    if (s.comm && !comm_cached) {
       NcclApi* api = NcclApi::get();
       if (api) api->CommDestroy(s.comm);
     }
@@ -648,12 +662,7 @@ int Engine<T>::launch_assign(Shard<T>& s, bool use_tc, bool count_changes) {
       KM_TRY(tc::launch(s.tcp, s.labels, s.st, count_changes, s.amb_rows, tc_tol_rel, s.num_sms, tc_mask_hi,
                         s.stream));
       // (k <= 128 on this path: four centroids per lane)
-      const size_t rsm = refine_smem_bytes<float>(k, d);
-      static bool attr_set = false;
-      if (!attr_set) {
-        KM_CUDA(cudaFuncSetAttribute(refine_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-        attr_set = true;
-      }
+      const size_t rsm = refine_smem_bytes<float>(k, d);  // at most 33 KB here: below the default limit
       refine_kernel<float><<<s.num_sms * 2, kRefineThreads, rsm, s.stream>>>(s.X, d, s.C[cur], k, s.amb_rows, s.st,
                                                                             s.labels, count_changes ? 1 : 0);
       KM_CUDA(cudaGetLastError());
