@@ -33,8 +33,10 @@ __global__ void __launch_bounds__(kAccThreads)
 accumulate_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict__ labels, int k,
                   int kc, int n_slices, long long* __restrict__ gsums,
                   unsigned long long* __restrict__ gcounts, T scale, unsigned int rows_per_part,
-                  unsigned long long dv_magic) {
+                  unsigned long long dv_magic,
+                  const unsigned long long* gate_changed, unsigned long long gate_limit) {
   constexpr int NP = Fixed<T>::NP;
+  if (delta_turn(gate_changed, gate_limit)) return;   // the incremental branch has this iteration
   extern __shared__ __align__(16) unsigned char smem_raw[];
   int* acc = reinterpret_cast<int*>(smem_raw);   // [NP][kc][d]
   int* cnt = acc + (size_t)NP * kc * d;          // [kc]

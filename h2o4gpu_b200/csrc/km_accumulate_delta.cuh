@@ -1,0 +1,236 @@
+// Incremental centroid sums.
+//
+// The fixed-point sums of km_common.cuh are exact integers, so the sums of the
+// new labelling can be had from those of the previous one without rounding:
+// for every row whose label moved from a to b, subtract the row's integers from
+// cluster a and add them to cluster b.  The result is, bit for bit, what a full
+// pass over the shard produces, whatever the order of the updates.  Once Lloyd's
+// iteration has settled only a small fraction of the rows move per step, and the
+// M-step's traffic drops from the whole shard (4d + 4 bytes per row) to the two
+// label arrays (8 bytes per row) plus the rows that moved.
+//
+// The choice between the full pass and the incremental one is made on the
+// device, from the label-change counter the E-step kernels have just written:
+// every kernel of either branch is launched in every iteration and returns at
+// once when it is not its turn, so the host never waits for the counter.
+//
+// `pure` holds the sums and counts that follow from the labels alone; the
+// iteration copies (or all-reduces) it into the working array before empty
+// clusters are repaired there, so repairs never leak into the next step.
+#pragma once
+
+#include "km_common.cuh"
+#include "km_tiles.cuh"
+
+namespace km {
+
+// Full branch, first kernel: clears the pure sums and snapshots the labels.
+__global__ void __launch_bounds__(256)
+full_prologue_kernel(long long* __restrict__ pure, size_t count, const int* __restrict__ labels,
+                     int* __restrict__ prev, size_t n, const unsigned long long* changed, unsigned long long limit) {
+  if (delta_turn(changed, limit)) return;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (size_t i = t; i < count; i += stride) pure[i] = 0;
+  const size_t n4 = n / 4;
+  const int4* l4 = reinterpret_cast<const int4*>(labels);
+  int4* p4 = reinterpret_cast<int4*>(prev);
+  for (size_t i = t; i < n4; i += stride) p4[i] = l4[i];
+  for (size_t i = n4 * 4 + t; i < n; i += stride) prev[i] = labels[i];
+}
+
+// Incremental branch: one warp per block of 32 rows; rows whose label differs from
+// the snapshot are moved between clusters with 64-bit integer reductions.
+template <typename T, int V>
+__global__ void __launch_bounds__(256)
+delta_accumulate_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict__ labels,
+                        int* __restrict__ prev, int k, long long* __restrict__ psums,
+                        unsigned long long* __restrict__ pcounts, T scale,
+                        const unsigned long long* changed, unsigned long long limit) {
+  constexpr int NP = Fixed<T>::NP;
+  if (!delta_turn(changed, limit)) return;
+  const int lane = threadIdx.x & 31;
+  const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const size_t n_warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  const int dv = d / V;
+  const size_t plane = (size_t)k * d;
+  for (size_t b = warp * 32; b < n; b += n_warps * 32) {
+    const size_t r = b + lane;
+    int nw = -1, od = -1;
+    if (r < n) { nw = labels[r]; od = prev[r]; }
+    const bool moved = nw != od;
+    unsigned int mask = __ballot_sync(0xffffffffu, moved);
+    if (moved) prev[r] = nw;
+    while (mask) {
+      const int src = __ffs(mask) - 1;
+      mask &= mask - 1;
+      const int to = __shfl_sync(0xffffffffu, nw, src);
+      const int from = __shfl_sync(0xffffffffu, od, src);
+      const bool to_ok = (unsigned)to < (unsigned)k, from_ok = (unsigned)from < (unsigned)k;
+      const T* xr = X + (b + src) * (size_t)d;
+      for (int idx = lane; idx < dv; idx += 32) {
+        T x[V];
+        VecLoad<T, V>::ld(xr + (size_t)idx * V, x);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          int p[NP];
+          split_pieces<NP>(x[e], scale, p);
+          const int col = idx * V + e;
+#pragma unroll
+          for (int q = 0; q < NP / 2; ++q) {
+            const long long v = (long long)p[2 * q] * (1LL << kPieceBits) + (long long)p[2 * q + 1];
+            if (v == 0) continue;
+            if (to_ok)
+              atomicAdd(reinterpret_cast<unsigned long long*>(psums + q * plane + (size_t)to * d + col),
+                        (unsigned long long)v);
+            if (from_ok)
+              atomicAdd(reinterpret_cast<unsigned long long*>(psums + q * plane + (size_t)from * d + col),
+                        (unsigned long long)(-v));
+          }
+        }
+      }
+      if (lane == 0) {
+        if (to_ok) atomicAdd(pcounts + to, 1ULL);
+        if (from_ok) atomicAdd(pcounts + from, ~0ULL);   // minus one, modulo 2^64
+      }
+    }
+  }
+}
+
+// Incremental branch for centroid tables whose fixed-point pieces fit shared memory.
+// Moves between a few clusters hit the same few lines of the global sums, and 64-bit
+// reductions on one line serialise in the L2; here a CTA nets the moves of its rows in
+// int32 shared accumulators first (same layout and arithmetic as accumulate_kernel) and
+// sends each non-zero total to the global sums once.  Subtracting a row is adding its
+// negation: rint is odd, so the pieces of -x are minus the pieces of x.
+constexpr int kDeltaThreads = 1024;
+constexpr int kDeltaChunk = 8192;    // rows between two looks at the overflow guard: 256 per warp
+
+template <typename T>
+inline size_t delta_smem_bytes(int k, int d) {
+  return (size_t)Fixed<T>::NP * k * d * sizeof(int) + (size_t)k * sizeof(int) + 16;
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kDeltaThreads, 1)
+delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict__ labels,
+                             int* __restrict__ prev, int k, long long* __restrict__ psums,
+                             unsigned long long* __restrict__ pcounts, T scale,
+                             const unsigned long long* changed, unsigned long long limit) {
+  constexpr int NP = Fixed<T>::NP;
+  if (!delta_turn(changed, limit)) return;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  int* acc = reinterpret_cast<int*>(smem_raw);      // [NP][k][d]
+  int* cnt = acc + (size_t)NP * k * d;              // [k]
+  __shared__ int s_touched;                         // rows netted since the last drain
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  constexpr int NWARP = kDeltaThreads / 32;
+  static_assert(kDeltaChunk == NWARP * 256, "one 256-row step per warp and chunk");
+  const int dv = d / V;
+  const size_t pstride = (size_t)k * d;
+  int lpr = 1;
+  while (lpr < dv && lpr < 32) lpr <<= 1;
+  const int groups = 32 / lpr;
+  const int g = lane / lpr;
+  const int l = lane % lpr;
+
+  size_t per = (n + gridDim.x - 1) / gridDim.x;
+  per = (per + 31) / 32 * 32;
+  const size_t r_begin = min(n, (size_t)blockIdx.x * per);
+  const size_t r_end = min(n, r_begin + per);
+
+  for (int i = tid; i < NP * k * d; i += kDeltaThreads) acc[i] = 0;
+  for (int i = tid; i < k; i += kDeltaThreads) cnt[i] = 0;
+  if (tid == 0) s_touched = 0;
+  __syncthreads();
+
+  for (size_t c0 = r_begin; c0 < r_end; c0 += kDeltaChunk) {
+    const size_t c1 = min(r_end, c0 + (size_t)kDeltaChunk);
+    // one step per warp and chunk: 256 rows, eight per lane, all label loads in flight together
+    // (c0 is a multiple of 32 rows, so the 16-byte loads are aligned)
+    const size_t wb = c0 + (size_t)warp * (kDeltaChunk / NWARP);
+    int nw[8], od[8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const size_t r4 = wb + h * 128 + lane * 4;
+      if (r4 + 3 < c1) {
+        const int4 a = *reinterpret_cast<const int4*>(labels + r4);
+        const int4 b = *reinterpret_cast<const int4*>(prev + r4);
+        nw[4 * h + 0] = a.x; nw[4 * h + 1] = a.y; nw[4 * h + 2] = a.z; nw[4 * h + 3] = a.w;
+        od[4 * h + 0] = b.x; od[4 * h + 1] = b.y; od[4 * h + 2] = b.z; od[4 * h + 3] = b.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const bool in = r4 + j < c1;
+          nw[4 * h + j] = in ? labels[r4 + j] : -1;
+          od[4 * h + j] = in ? prev[r4 + j] : -1;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const bool moved = nw[j] != od[j];
+      unsigned int mask = __ballot_sync(0xffffffffu, moved);
+      if (mask == 0) continue;
+      const size_t jb = wb + (j >> 2) * 128 + (j & 3);   // row of lane 0 for this j; lane s holds jb + 4 s
+      if (moved) prev[jb + lane * 4] = nw[j];
+      if (lane == 0) atomicAdd(&s_touched, __popc(mask));
+      while (mask) {
+        const unsigned int src = __fns(mask, 0, g + 1);   // lane of this group's row
+        const bool have = (src != 0xffffffffu);
+        const int to = __shfl_sync(0xffffffffu, nw[j], have ? src : 0);
+        const int from = __shfl_sync(0xffffffffu, od[j], have ? src : 0);
+        if (have) {
+          const bool to_ok = (unsigned)to < (unsigned)k, from_ok = (unsigned)from < (unsigned)k;
+          const T* xr = X + (jb + (size_t)src * 4) * (size_t)d;
+          for (int idx = l; idx < dv; idx += lpr) {
+            T x[V], y[V];
+            VecLoad<T, V>::ld(xr + (size_t)idx * V, x);
+#pragma unroll
+            for (int e = 0; e < V; ++e) y[e] = -x[e];
+            if (to_ok) add_vec_fixed<T, V, NP>(acc + (size_t)to * d, pstride, dv, idx, g & (V - 1), x, scale);
+            if (from_ok) add_vec_fixed<T, V, NP>(acc + (size_t)from * d, pstride, dv, idx, g & (V - 1), y, scale);
+          }
+          if (l == 0) {
+            if (to_ok) atomicAdd(&cnt[to], 1);
+            if (from_ok) atomicAdd(&cnt[from], -1);
+          }
+        }
+        for (int i = 0; i < groups && mask; ++i) mask &= mask - 1;
+      }
+    }
+    __syncthreads();
+    // every piece is at most 2^15 in magnitude: drain before 2^15 rows could have piled up
+    const bool drain = (s_touched + kDeltaChunk > 32768) || (c1 >= r_end);
+    __syncthreads();
+    if (drain) {
+      if (s_touched > 0) {
+        for (int i = tid; i < k * d; i += kDeltaThreads) {
+          const int c = i / d;
+          const int col = pos_to_col(i - c * d, dv, V);
+#pragma unroll
+          for (int q = 0; q < NP / 2; ++q) {
+            const long long v = (long long)acc[(size_t)(2 * q) * pstride + i] * (1LL << kPieceBits) +
+                                (long long)acc[(size_t)(2 * q + 1) * pstride + i];
+            if (v) atomicAdd(reinterpret_cast<unsigned long long*>(psums + (size_t)q * k * d + (size_t)c * d + col),
+                             (unsigned long long)v);
+            acc[(size_t)(2 * q) * pstride + i] = 0;
+            acc[(size_t)(2 * q + 1) * pstride + i] = 0;
+          }
+        }
+        for (int i = tid; i < k; i += kDeltaThreads) {
+          if (cnt[i]) atomicAdd(pcounts + i, (unsigned long long)(long long)cnt[i]);
+          cnt[i] = 0;
+        }
+      }
+      __syncthreads();
+      if (tid == 0) s_touched = 0;
+      __syncthreads();
+    }
+  }
+}
+
+}  // namespace km
+

@@ -73,7 +73,9 @@ template <int GS>
 __global__ void __launch_bounds__(kSortThreads, 2)
 sorted_accumulate_kernel(const float* __restrict__ X, size_t n, int d, const int* __restrict__ labels, int k,
                          long long* __restrict__ gsums, unsigned long long* __restrict__ gcounts,
-                         float scale30, int tile_rows, int smem_acc) {
+                         float scale30, int tile_rows, int smem_acc,
+                         const unsigned long long* gate_changed, unsigned long long gate_limit) {
+  if (delta_turn(gate_changed, gate_limit)) return;   // the incremental branch has this iteration
   extern __shared__ __align__(16) unsigned char smem_raw[];
   int* hist = reinterpret_cast<int*>(smem_raw);        // [k]   per-tile label counts
   int* offs = hist + k;                                // [k]   scatter cursors

@@ -158,4 +158,10 @@ struct IterState {
   double inertia;               // scratch for the inertia pass
 };
 
+// Gate of the M-step's two branches (km_accumulate_delta.cuh): true when the incremental
+// branch handles this iteration.  `changed` is the E-step's label-change counter.
+__device__ __forceinline__ bool delta_turn(const unsigned long long* changed, unsigned long long limit) {
+  return changed != nullptr && *changed <= limit;
+}
+
 }  // namespace km

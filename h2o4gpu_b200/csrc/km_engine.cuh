@@ -18,6 +18,7 @@
 
 #include "km_accumulate.cuh"
 #include "km_accumulate_sorted.cuh"
+#include "km_accumulate_delta.cuh"
 #include "km_common.cuh"
 #include "km_finalize.cuh"
 #include "km_nccl.h"
@@ -70,6 +71,9 @@ struct Shard {
   // buffers that depend on (k, d)
   int k_cap = 0, d_cap = 0;
   long long* gacc = nullptr;  // [NP/2][k][d] sums followed by [k] counts: one all-reduce covers both
+  long long* pacc = nullptr;  // same layout: sums that follow from the labels alone (incremental M-step)
+  int* labels_prev = nullptr; // labelling pacc corresponds to
+  size_t labels_prev_cap = 0;
   T* C[2] = {nullptr, nullptr};
   T* cnorm = nullptr;
   double* shift_k = nullptr;
@@ -140,7 +144,12 @@ struct Engine : EngineBase {
   int launch_tiles(Shard<T>& s, const T* Xp, size_t nrows, int* labels, int mode, T* out, size_t ld_out,
                    bool count_changes);
   int launch_smallk(Shard<T>& s, bool update, T scale);
-  int launch_accumulate(Shard<T>& s, T scale);
+  // sums of the current labels into dst (default: the working array); with a gate the
+  // kernels return at once when the incremental branch has the iteration
+  int launch_accumulate(Shard<T>& s, T scale, long long* dst = nullptr, const unsigned long long* gate = nullptr,
+                        unsigned long long limit = 0);
+  int launch_delta(Shard<T>& s, T scale, const unsigned long long* gate, unsigned long long limit);
+  int allreduce_from(bool from_pure);
   bool smallk_ok(bool update) const;
   bool vec_ok(const Shard<T>& s) const {
     constexpr int V = VecOf<T>::N;
@@ -225,6 +234,7 @@ void Engine<T>::destroy() {
     s.tcbp.release();
     cudaFree(s.amb_rows); cudaFree(s.amb_log);
     cudaFree(s.X_owned); cudaFree(s.labels); cudaFree(s.dist); cudaFree(s.gacc);
+    cudaFree(s.pacc); cudaFree(s.labels_prev);
     cudaFree(s.C[0]); cudaFree(s.C[1]); cudaFree(s.cnorm); cudaFree(s.shift_k); cudaFree(s.empties);
     cudaFree(s.st); cudaFree(s.cand_val); cudaFree(s.cand_row); cudaFree(s.sum_partials);
     cudaFree(s.shift_log); cudaFree(s.changed_log); cudaFree(s.reloc_log); cudaFree(s.xstat);
@@ -330,11 +340,12 @@ int Engine<T>::ensure_buffers(int k_) {
     if (!s.X) KM_FAIL(KM_ESTATE, "no data attached to the handle");
     DevGuard g(s.dev);
     if (s.k_cap != k_ || s.d_cap != d) {
-      cudaFree(s.gacc); cudaFree(s.C[0]); cudaFree(s.C[1]); cudaFree(s.cnorm);
+      cudaFree(s.gacc); cudaFree(s.pacc); s.pacc = nullptr; cudaFree(s.C[0]); cudaFree(s.C[1]); cudaFree(s.cnorm);
       cudaFree(s.shift_k); cudaFree(s.empties);
       s.gacc = nullptr; s.C[0] = s.C[1] = nullptr; s.cnorm = nullptr; s.shift_k = nullptr; s.empties = nullptr;
       size_t kd = (size_t)k_ * d;
       KM_CUDA(cudaMalloc(&s.gacc, ((size_t)(NP / 2) * kd + k_) * sizeof(long long)));
+      KM_CUDA(cudaMalloc(&s.pacc, ((size_t)(NP / 2) * kd + k_) * sizeof(long long)));
       KM_CUDA(cudaMalloc(&s.C[0], kd * sizeof(T)));
       KM_CUDA(cudaMalloc(&s.C[1], kd * sizeof(T)));
       KM_CUDA(cudaMalloc(&s.cnorm, k_ * sizeof(T)));
@@ -522,11 +533,12 @@ int Engine<T>::launch_smallk(Shard<T>& s, bool update, T scale) {
 
 template <int GS>
 static int launch_sorted_gs(const float* X, size_t rows, int d, const int* labels, int k, long long* gs,
-                            unsigned long long* gc, float scale30, const SortPlan& p, cudaStream_t stream) {
+                            unsigned long long* gc, float scale30, const SortPlan& p, cudaStream_t stream,
+                            const unsigned long long* gate, unsigned long long limit) {
   KM_CUDA(cudaFuncSetAttribute(sorted_accumulate_kernel<GS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                (int)p.smem_bytes));
   sorted_accumulate_kernel<GS><<<p.grid, kSortThreads, p.smem_bytes, stream>>>(X, rows, d, labels, k, gs, gc, scale30,
-                                                                              p.tile_rows, p.smem_acc);
+                                                                              p.tile_rows, p.smem_acc, gate, limit);
   KM_CUDA(cudaGetLastError());
   return KM_OK;
 }
@@ -534,7 +546,8 @@ static int launch_sorted_gs(const float* X, size_t rows, int d, const int* label
 // float shards with 16-byte rows: run-length kernel.  `scale` is 2^(15-e); the
 // run-length kernel quantises with 2^(30-e) in one step, which gives the same integers.
 template <typename T>
-static int try_sorted_accumulate(Shard<T>& s, int d, int k, T scale, bool vec, bool* done) {
+static int try_sorted_accumulate(Shard<T>& s, int d, int k, T scale, bool vec, bool* done, long long* gs,
+                                 unsigned long long* gc, const unsigned long long* gate, unsigned long long limit) {
   *done = false;
   if constexpr (std::is_same<T, float>::value) {
     static const bool enabled = [] {
@@ -546,12 +559,12 @@ static int try_sorted_accumulate(Shard<T>& s, int d, int k, T scale, bool vec, b
     const float scale30 = scale * 32768.0f;
     const int dv = d / 4;
     int rc;
-    if (dv <= 8) rc = launch_sorted_gs<8>(s.X, s.rows, d, s.labels, k, s.sums(), s.counts(k, d), scale30, p, s.stream);
-    else if (dv <= 16) rc = launch_sorted_gs<16>(s.X, s.rows, d, s.labels, k, s.sums(), s.counts(k, d), scale30, p, s.stream);
-    else if (dv <= 32) rc = launch_sorted_gs<32>(s.X, s.rows, d, s.labels, k, s.sums(), s.counts(k, d), scale30, p, s.stream);
-    else if (dv <= 64) rc = launch_sorted_gs<64>(s.X, s.rows, d, s.labels, k, s.sums(), s.counts(k, d), scale30, p, s.stream);
-    else if (dv <= 128) rc = launch_sorted_gs<128>(s.X, s.rows, d, s.labels, k, s.sums(), s.counts(k, d), scale30, p, s.stream);
-    else rc = launch_sorted_gs<256>(s.X, s.rows, d, s.labels, k, s.sums(), s.counts(k, d), scale30, p, s.stream);
+    if (dv <= 8) rc = launch_sorted_gs<8>(s.X, s.rows, d, s.labels, k, gs, gc, scale30, p, s.stream, gate, limit);
+    else if (dv <= 16) rc = launch_sorted_gs<16>(s.X, s.rows, d, s.labels, k, gs, gc, scale30, p, s.stream, gate, limit);
+    else if (dv <= 32) rc = launch_sorted_gs<32>(s.X, s.rows, d, s.labels, k, gs, gc, scale30, p, s.stream, gate, limit);
+    else if (dv <= 64) rc = launch_sorted_gs<64>(s.X, s.rows, d, s.labels, k, gs, gc, scale30, p, s.stream, gate, limit);
+    else if (dv <= 128) rc = launch_sorted_gs<128>(s.X, s.rows, d, s.labels, k, gs, gc, scale30, p, s.stream, gate, limit);
+    else rc = launch_sorted_gs<256>(s.X, s.rows, d, s.labels, k, gs, gc, scale30, p, s.stream, gate, limit);
     KM_TRY(rc);
     *done = true;
   }
@@ -559,12 +572,15 @@ static int try_sorted_accumulate(Shard<T>& s, int d, int k, T scale, bool vec, b
 }
 
 template <typename T>
-int Engine<T>::launch_accumulate(Shard<T>& s, T scale) {
+int Engine<T>::launch_accumulate(Shard<T>& s, T scale, long long* dst, const unsigned long long* gate,
+                                 unsigned long long limit) {
   constexpr int V = VecOf<T>::N;
   constexpr int NP = Fixed<T>::NP;
+  long long* gs = dst ? dst : s.sums();
+  unsigned long long* gc = reinterpret_cast<unsigned long long*>(gs + (size_t)(NP / 2) * k * d);
   {
     bool done = false;
-    KM_TRY(try_sorted_accumulate<T>(s, d, k, scale, vec_ok(s), &done));
+    KM_TRY(try_sorted_accumulate<T>(s, d, k, scale, vec_ok(s), &done, gs, gc, gate, limit));
     if (done) { ++launches; return KM_OK; }
   }
   const size_t per_cluster = (size_t)NP * d * sizeof(int) + sizeof(int);
@@ -589,11 +605,11 @@ int Engine<T>::launch_accumulate(Shard<T>& s, T scale) {
   if (vec) {
     KM_CUDA(cudaFuncSetAttribute(accumulate_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     accumulate_kernel<T, V><<<(unsigned)grid, kAccThreads, smem, s.stream>>>(
-        s.X, s.rows, d, s.labels, k, kc, n_slices, s.sums(), s.counts(k, d), scale, (unsigned)rpp, magic);
+        s.X, s.rows, d, s.labels, k, kc, n_slices, gs, gc, scale, (unsigned)rpp, magic, gate, limit);
   } else {
     KM_CUDA(cudaFuncSetAttribute(accumulate_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     accumulate_kernel<T, 1><<<(unsigned)grid, kAccThreads, smem, s.stream>>>(
-        s.X, s.rows, d, s.labels, k, kc, n_slices, s.sums(), s.counts(k, d), scale, (unsigned)rpp, magic);
+        s.X, s.rows, d, s.labels, k, kc, n_slices, gs, gc, scale, (unsigned)rpp, magic, gate, limit);
   }
   KM_CUDA(cudaGetLastError());
   ++launches;
@@ -663,7 +679,7 @@ int Engine<T>::launch_assign(Shard<T>& s, bool use_tc, bool count_changes) {
                         s.stream));
       // (k <= 128 on this path: four centroids per lane)
       const size_t rsm = refine_smem_bytes<float>(k, d);  // at most 33 KB here: below the default limit
-      refine_kernel<float><<<s.num_sms * 2, kRefineThreads, rsm, s.stream>>>(s.X, d, s.C[cur], k, s.amb_rows, s.st,
+      refine_kernel<float, 2><<<s.num_sms * 2, kRefineThreads, rsm, s.stream>>>(s.X, d, s.C[cur], k, s.amb_rows, s.st,
                                                                             s.labels, count_changes ? 1 : 0);
       KM_CUDA(cudaGetLastError());
       return KM_OK;
@@ -673,13 +689,55 @@ int Engine<T>::launch_assign(Shard<T>& s, bool use_tc, bool count_changes) {
 }
 
 template <typename T>
-int Engine<T>::allreduce_acc() {
+int Engine<T>::allreduce_acc() { return allreduce_from(false); }
+
+// Sums and counts of all ranks into the working array, read from the working array itself
+// or from the label-only sums of the incremental M-step.
+template <typename T>
+int Engine<T>::allreduce_from(bool from_pure) {
   if (world_size <= 1) return KM_OK;
   NcclApi* api = NcclApi::get();
   KM_NCCL(api, api->GroupStart());
   for (auto& s : shards)
-    KM_NCCL(api, api->AllReduce(s.gacc, s.gacc, s.gacc_count(k, d), ncclInt64, ncclSum, s.comm, s.stream));
+    KM_NCCL(api, api->AllReduce(from_pure ? s.pacc : s.gacc, s.gacc, s.gacc_count(k, d), ncclInt64, ncclSum, s.comm,
+                                s.stream));
   KM_NCCL(api, api->GroupEnd());
+  return KM_OK;
+}
+
+template <typename T>
+int Engine<T>::launch_delta(Shard<T>& s, T scale, const unsigned long long* gate, unsigned long long limit) {
+  constexpr int V = VecOf<T>::N;
+  constexpr int NP = Fixed<T>::NP;
+  long long* ps = s.pacc;
+  unsigned long long* pc = reinterpret_cast<unsigned long long*>(ps + (size_t)(NP / 2) * k * d);
+  const size_t smem = delta_smem_bytes<T>(k, d);
+  if (smem <= 200 * 1024) {
+    // centroid table small enough for shared accumulators: one CTA per SM nets its rows' moves
+    if (vec_ok(s)) {
+      KM_CUDA(cudaFuncSetAttribute(delta_accumulate_smem_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)smem));
+      delta_accumulate_smem_kernel<T, V><<<s.num_sms, kDeltaThreads, smem, s.stream>>>(
+          s.X, s.rows, d, s.labels, s.labels_prev, k, ps, pc, scale, gate, limit);
+    } else {
+      KM_CUDA(cudaFuncSetAttribute(delta_accumulate_smem_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)smem));
+      delta_accumulate_smem_kernel<T, 1><<<s.num_sms, kDeltaThreads, smem, s.stream>>>(
+          s.X, s.rows, d, s.labels, s.labels_prev, k, ps, pc, scale, gate, limit);
+    }
+    KM_CUDA(cudaGetLastError());
+    ++launches;
+    return KM_OK;
+  }
+  const int grid = s.num_sms * 8;
+  if (vec_ok(s))
+    delta_accumulate_kernel<T, V><<<grid, 256, 0, s.stream>>>(s.X, s.rows, d, s.labels, s.labels_prev, k, ps, pc,
+                                                              scale, gate, limit);
+  else
+    delta_accumulate_kernel<T, 1><<<grid, 256, 0, s.stream>>>(s.X, s.rows, d, s.labels, s.labels_prev, k, ps, pc,
+                                                              scale, gate, limit);
+  KM_CUDA(cudaGetLastError());
+  ++launches;
   return KM_OK;
 }
 

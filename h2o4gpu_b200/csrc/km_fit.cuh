@@ -137,6 +137,14 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
   const bool use_tc = !fused && tc_ok(flags);
   if (const char* e = std::getenv("H2O4GPU_KM_TC_MASK_HI")) tc_mask_hi = std::atoi(e);
   if (const char* e = std::getenv("H2O4GPU_KM_TC_TOL")) tc_tol_rel = (float)std::atof(e);
+  // incremental M-step (km_accumulate_delta.cuh): on unless the caller or the environment asks
+  // for a full recomputation every iteration; a shard switches to it, on the device, in the
+  // iterations where at most 1/16 of its labels moved
+  static const bool delta_env = [] {
+    const char* e = std::getenv("H2O4GPU_KM_DELTA_SUMS");
+    return !(e && e[0] == '0');
+  }();
+  const bool delta = !fused && delta_env && !(flags & KM_FIT_FULL_SUMS);
   const bool multi = world_size > 1;
   const bool check = (threshold > 0) || (flags & KM_FIT_CHECK_EVERY_ITER);
   stats = kmeans_stats{};
@@ -149,6 +157,12 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
     if (!multi) KM_TRY(ensure_dist(s));
     KM_CUDA(cudaMemsetAsync(s.st, 0, sizeof(IterState), s.stream));
     KM_CUDA(cudaMemsetAsync(s.labels, 0xff, s.rows * sizeof(int), s.stream));
+    if (delta && s.labels_prev_cap < s.rows) {
+      cudaFree(s.labels_prev);
+      s.labels_prev = nullptr;
+      KM_CUDA(cudaMalloc(&s.labels_prev, s.rows * sizeof(int)));
+      s.labels_prev_cap = s.rows;
+    }
     if (use_tc) KM_TRY(tc_refresh(s));
   }
 
@@ -171,10 +185,26 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
       Shard<T>& s = shards[i];
       DevGuard g(s.dev);
       if (i == 0) cudaEventRecord(ev[4 * it + 0], s.stream);
-      cudaMemsetAsync(s.gacc, 0, s.gacc_count(k, d) * sizeof(long long), s.stream);
+      if (!delta) cudaMemsetAsync(s.gacc, 0, s.gacc_count(k, d) * sizeof(long long), s.stream);
       if (fused) {
         rc = launch_smallk(s, true, scale);
         if (i == 0) { cudaEventRecord(ev[4 * it + 1], s.stream); cudaEventRecord(ev[4 * it + 2], s.stream); }
+      } else if (delta) {
+        rc = launch_assign(s, use_tc, true);
+        if (i == 0) cudaEventRecord(ev[4 * it + 1], s.stream);
+        // both branches are launched; the label-change counter decides on the device which one works
+        const unsigned long long* gate = (it == 0) ? nullptr : &s.st->changed;
+        const unsigned long long limit = s.rows / 16;
+        if (rc == KM_OK) {
+          full_prologue_kernel<<<s.num_sms * 4, 256, 0, s.stream>>>(s.pacc, s.gacc_count(k, d), s.labels,
+                                                                     s.labels_prev, s.rows, gate, limit);
+          ++launches;
+          rc = launch_accumulate(s, scale, s.pacc, gate, limit);
+        }
+        if (rc == KM_OK && it > 0) rc = launch_delta(s, scale, gate, limit);
+        if (rc == KM_OK && !multi)
+          cudaMemcpyAsync(s.gacc, s.pacc, s.gacc_count(k, d) * sizeof(long long), cudaMemcpyDeviceToDevice, s.stream);
+        if (i == 0) cudaEventRecord(ev[4 * it + 2], s.stream);
       } else {
         rc = launch_assign(s, use_tc, true);
         if (i == 0) cudaEventRecord(ev[4 * it + 1], s.stream);
@@ -183,7 +213,7 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
       }
     }
     if (rc != KM_OK) break;
-    if (multi && (rc = allreduce_acc()) != KM_OK) break;
+    if (multi && (rc = allreduce_from(delta)) != KM_OK) break;
     for (size_t i = 0; i < shards.size() && rc == KM_OK; ++i) {
       Shard<T>& s = shards[i];
       DevGuard g(s.dev);
@@ -297,12 +327,19 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
           if (ch[i] == 0) { stats.n_iter_converged = i + 1; break; }
       }
       for (int i = 0; i < done; ++i) stats.relocations += rl[i];
+      if (delta)
+        for (int i = 1; i < done; ++i) stats.incremental_iterations += (ch[i] <= s0.rows / 16);
       float a = 0, u = 0, ms = 0;
+      static const bool trace = std::getenv("H2O4GPU_KM_TRACE") != nullptr;
       for (int i = 0; i < done; ++i) {
-        cudaEventElapsedTime(&ms, ev[4 * i + 0], ev[4 * i + 1]);
-        a += ms;
-        cudaEventElapsedTime(&ms, ev[4 * i + 1], ev[4 * i + 3]);
-        u += ms;
+        float ma = 0, mu = 0;
+        cudaEventElapsedTime(&ma, ev[4 * i + 0], ev[4 * i + 1]);
+        a += ma;
+        cudaEventElapsedTime(&mu, ev[4 * i + 1], ev[4 * i + 3]);
+        u += mu;
+        if (trace)
+          std::fprintf(stderr, "[kmeans] iteration %d: %llu labels changed, %u rows re-evaluated, %d relocated, "
+                       "E-step %.3f ms, M-step %.3f ms\n", i, ch[i], am[i], rl[i], ma, mu);
       }
       stats.ms_assign = a;
       stats.ms_update = u;

@@ -129,6 +129,7 @@ FIT_NO_FINAL_ASSIGN = 1
 FIT_FORCE_SIMT = 2
 FIT_FORCE_SPLIT = 4
 FIT_CHECK_EVERY_ITER = 8
+FIT_FULL_SUMS = 16
 
 
 def centroid_sums(X, labels, k, gpu_id=0):

@@ -31,7 +31,7 @@ class KMeansLibError(RuntimeError):
 
 class Stats(ctypes.Structure):
     _fields_ = [("iterations", _c.c_int), ("n_iter_converged", _c.c_int), ("relocations", _c.c_int),
-                ("path", _c.c_int), ("gpu_launches", _c.c_int), ("reserved", _c.c_int),
+                ("path", _c.c_int), ("gpu_launches", _c.c_int), ("incremental_iterations", _c.c_int),
                 ("last_shift_sq", _c.c_double), ("inertia", _c.c_double),
                 ("seconds_upload", _c.c_double), ("seconds_fit", _c.c_double),
                 ("ms_assign", _c.c_float), ("ms_update", _c.c_float), ("ms_loop", _c.c_float),

@@ -116,6 +116,9 @@ int kmeans_upload_host(kmeans_handle_t h, const void* X, size_t rows, size_t col
 #define KM_FIT_FORCE_SIMT 2      /* never take the tcgen05 distance kernel           */
 #define KM_FIT_FORCE_SPLIT 4     /* never take the fused small-k kernel              */
 #define KM_FIT_CHECK_EVERY_ITER 8 /* host reads shift/label changes each iteration   */
+#define KM_FIT_FULL_SUMS 16       /* recompute the centroid sums from every row in every
+                                  * iteration (default: exact incremental update once few
+                                  * labels change; same bits either way)              */
 
 /* Lloyd iterations on the resident shards from k x cols host centroids.
  * Stops after max_iter, or earlier when threshold > 0 and the summed squared
@@ -139,7 +142,8 @@ typedef struct kmeans_stats {
   int relocations;         /* empty-cluster relocations over the whole fit           */
   int path;                /* 1 fused small-k, 2 SIMT tiles, 3 tcgen05               */
   int gpu_launches;        /* kernels launched by the last fit (all local devices)   */
-  int reserved;
+  int incremental_iterations; /* iterations (device 0) whose centroid sums were updated from
+                               * the rows that changed label instead of recomputed       */
   double last_shift_sq;    /* summed squared centroid shift of the last iteration    */
   double inertia;          /* sum of squared distances after the closing E-step, or -1 */
   double seconds_upload;   /* host-side wall time of the last upload                 */

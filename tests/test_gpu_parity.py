@@ -301,6 +301,30 @@ def test_deterministic_across_runs(eng):
     assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
 
 
+@pytest.mark.parametrize("dtype,cfg,kw,iters", [(np.float32, "c2", dict(n=60000), 12),
+                                                (np.float64, "c2", dict(n=30000), 10),
+                                                (np.float32, "c3", dict(n=30000, k=300), 8),
+                                                (np.float32, "c5", dict(n=8000, k=512), 6)])
+def test_incremental_sums_equal_full_recompute_bitwise(eng, dtype, cfg, kw, iters):
+    """The M-step that moves only the rows whose label changed gives the same integers as a
+    full pass: centroids and labels of every iteration count agree bit for bit."""
+    from h2o4gpu_b200 import synth
+    X, init, _ = getattr(synth, cfg)(**kw)
+    X = X.astype(dtype)
+    init = init.astype(dtype)
+    outs = []
+    for flags in (0, eng.FIT_FULL_SUMS):
+        h = eng.ResidentKMeans(dtype=dtype)
+        h.upload(X)
+        h.fit(init, iters, flags=flags)
+        outs.append((h.centroids(), h.labels(), h.stats()))
+        h.close()
+    assert outs[0][2]["incremental_iterations"] > 0 and outs[1][2]["incremental_iterations"] == 0
+    assert outs[0][2]["relocations"] == outs[1][2]["relocations"]
+    assert np.array_equal(outs[0][0], outs[1][0])
+    assert np.array_equal(outs[0][1], outs[1][1])
+
+
 # ---- edge cases ------------------------------------------------------------------------
 @pytest.mark.parametrize("n,d,k", [(1, 1, 1), (3, 2, 2), (5, 3, 5), (129, 7, 3), (257, 33, 17), (1000, 130, 20),
                                    (300, 4, 16), (300, 4, 18), (2049, 64, 100), (700, 1030, 6)])
