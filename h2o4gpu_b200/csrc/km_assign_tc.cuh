@@ -12,9 +12,9 @@
 // the comparison because |c|^2 is scaled by the same Sx*Sb.  Using kind::f16
 // (K = 16 per instruction) instead of kind::tf32 (K = 8) halves the number of
 // MMA instructions per tile (3 * d/16), which matters because for N = 112 the
-// tensor pipe is bound by a per-instruction cost, not by N.  The epilogue adds
-// |c|^2 and takes the running argmin, so the rows x k distance matrix never
-// exists.  Replaces calculate_distances + relabel
+// tensor pipe is bound by a per-instruction cost, not by N.  Every accumulator is
+// handed to the MMAs already holding |c_j|^2 in column j, so the finished score is
+// what the epilogue reads, and the rows x k distance matrix never exists.  Replaces calculate_distances + relabel
 // (src/gpu/kmeans/kmeans_labels.cu:115-244, kmeans_labels.h:360-392) for
 // float32, d in {32, 64}, 16 < k <= 128.
 //
@@ -32,10 +32,13 @@
 //               (M=128, N=kpad, K=16) per tile into one of three TMEM
 //               accumulators; tcgen05.commit releases the A buffer and publishes
 //               the accumulator.
-//   warps 12-23 epilogue (three groups of four, one per accumulator): tcgen05.ld,
-//               + |c|^2, four interleaved (min, second-min, argmin) chains, label
-//               store, changed-label count; rows whose two best scores are within
-//               the error bound go to the exact re-evaluation list.
+//   warps 12-23 epilogue (three groups of four, one per accumulator), two passes of
+//               tcgen05.ld over the row: the minimum (three-input min, half an
+//               instruction per column), then one bit per column whose score lies
+//               within the error bound of it (compare + predicated OR).  One bit:
+//               that column is the label; more: the row goes to the exact
+//               re-evaluation list.  The group then refills the accumulator with
+//               the norms (tcgen05.st) and releases it.
 // Every mbarrier wait is bounded; on a timeout the CTA sets an error word, drains
 // its copies, frees its TMEM and returns.
 #pragma once
@@ -109,13 +112,24 @@ __device__ __forceinline__ bool mbar_try_hint(uint32_t bar, uint32_t parity, uin
 }
 // Bounded wait.  Returns false when the CTA is aborting (this wait or another one
 // gave up); the caller leaves its loop.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+// Where the waits of an aborting CTA stood, one record per wait site (code): CTA, the
+// caller's tile counter, the parity waited for, 1 = this wait gave up / 2 = it saw the abort.
+// Read back by the host only to word the error message.
+__device__ int g_wait_diag[16][4];
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
+                                          int info = -1) {
   // 150000 parked waits of at most 20 us each: gives up after about 3 s
+  int why = 1;
   for (unsigned int it = 0; it < 150000u; ++it) {
     if (mbar_try_hint(bar, parity, 20000u)) return true;
-    if (*abort_flag) return false;
+    if (*abort_flag) { why = 2; break; }
   }
-  *abort_flag = code;
+  if (why == 1) *abort_flag = code;
+  g_wait_diag[code & 15][0] = (int)blockIdx.x;
+  g_wait_diag[code & 15][1] = info;
+  g_wait_diag[code & 15][2] = (int)parity;
+  g_wait_diag[code & 15][3] = why;
   return false;
 }
 
@@ -179,6 +193,12 @@ __device__ __forceinline__ void tmem_wait_ld(uint32_t (&v)[32]) {
                  "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
                :
                : "memory");
+}
+// three-input minimum (one instruction on sm_100)
+__device__ __forceinline__ float fmin3(float a, float b, float c) {
+  float d;
+  asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -244,6 +264,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   float* cn_s = reinterpret_cast<float*>(sm + off_cn);
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(sm + off_misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + off_misc + 4);
+  volatile int* issued_upto = reinterpret_cast<volatile int*>(sm + off_misc + 8);  // [2]: last tile counter issued by each issuer
   auto bar = [&](int i) { return base + off_bar + (uint32_t)i * 8u; };
 
   const int tid = threadIdx.x;
@@ -256,6 +277,8 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     for (int a = 0; a < kAcc; ++a) { mbar_init(bar(ACC_FULL + a), 1); mbar_init(bar(ACC_EMPTY + a), 128); }
     mbar_init(bar(B_FULL), 1);
     *abort_flag = 0;
+    issued_upto[0] = -1;
+    issued_upto[1] = -1;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   for (int i = tid; i < npad; i += kThreads) cn_s[i] = cn_pad[i];
@@ -287,7 +310,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++i) {
         const int s = i % kStages;
         const uint32_t ph = (uint32_t)(i / kStages) & 1u;
-        if (i >= kStages) ok = mbar_wait(bar(EMPTY + s), ph ^ 1u, abort_flag, 1);
+        if (i >= kStages) ok = mbar_wait(bar(EMPTY + s), ph ^ 1u, abort_flag, 1, i);
         if (!ok) break;
         mbar_expect_tx(bar(FULL + s), stage_bytes);
 #pragma unroll
@@ -328,8 +351,19 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         const uint32_t phb = (uint32_t)(i >> 1) & 1u;
         const int a = i % kAcc;
         const uint32_t pha = (uint32_t)(i / kAcc) & 1u;
-        ok = mbar_wait(bar(A_READY + grp), phb, abort_flag, 3);
-        if (ok && i >= kAcc) ok = mbar_wait(bar(ACC_EMPTY + a), pha ^ 1u, abort_flag, 4);
+        ok = mbar_wait(bar(A_READY + grp), phb, abort_flag, 3, i);
+        // Consecutive uses of an accumulator (tile counters i - 3 and i) belong to different
+        // issuers, and a parity wait cannot tell "two phases behind" from "done": an issuer
+        // that ran ahead of the other (a slow epilogue group is enough) could take the
+        // accumulator one use early.  So the previous use must have been issued first.
+        for (unsigned int spins = 0; ok && issued_upto[grp ^ 1] < i - 3; ++spins) {
+          if (*abort_flag) ok = false;
+          else if (spins > 40000000u) { *abort_flag = 8; ok = false; }
+          else __nanosleep(32);
+        }
+        // phase u of ACC_EMPTY completes when the accumulator holds |c|^2 again: after the
+        // epilogue's initial fill (u = 0) or after it has consumed use u - 1
+        if (ok) ok = mbar_wait(bar(ACC_EMPTY + a), pha, abort_flag, 4, i);
         if (!ok) break;
         tc_fence_after();
         const uint32_t acc = tmem_base + (uint32_t)a * 128u;
@@ -339,11 +373,13 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           for (int kk = 0; kk < KS; ++kk) {
             const uint32_t a_col = a_hi + (term == 1 ? 32u : 0u) + kk * 8u;
             const uint64_t bd = (term == 2) ? bdesc_lo[kk] : bdesc_hi[kk];
-            if (!(dbg & 2)) tc_mma_ts(acc, a_col, bd, idesc, (term | kk) ? 1u : 0u);
+            if (!(dbg & 2)) tc_mma_ts(acc, a_col, bd, idesc, 1u);
           }
         }
         tc_commit(bar(A_EMPTY + grp));
         tc_commit(bar(ACC_FULL + a));
+        __threadfence_block();
+        issued_upto[grp] = i;
         last_acc = a;
         last_ph = pha;
       }
@@ -370,8 +406,8 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       const int s = i % kStages;
       const uint32_t ph = (uint32_t)(i / kStages) & 1u;
       const uint32_t phb = (uint32_t)(i >> 1) & 1u;
-      ok = mbar_wait(bar(FULL + s), ph, abort_flag, 5);
-      if (ok && i >= 2) ok = mbar_wait(bar(A_EMPTY + grp), phb ^ 1u, abort_flag, 6);
+      ok = mbar_wait(bar(FULL + s), ph, abort_flag, 5, i);
+      if (ok && i >= 2) ok = mbar_wait(bar(A_EMPTY + grp), phb ^ 1u, abort_flag, 6, i);
       ok = __all_sync(0xffffffffu, ok);  // the tcgen05.st below needs the whole warp
       if (!ok) break;
       tc_fence_after();
@@ -417,9 +453,28 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     const int q = warp & 3;
     const int row_in_tile = q * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    const float kInf = __int_as_float(0x7f800000);
     unsigned int changed = 0;
     bool ok = true;
+    // The accumulator starts every tile holding |c_j|^2 (scaled) in column j of every row, so
+    // the MMAs leave the finished score there and the epilogue never adds the norms itself.
+    auto fill_norms = [&](uint32_t acc) {
+#pragma unroll
+      for (int c0 = 0; c0 < kMaxNPad; c0 += 16) {
+        if (c0 < npad) {
+          uint32_t c[16];
+#pragma unroll
+          for (int j4 = 0; j4 < 4; ++j4) {
+            const uint4 q4 = *reinterpret_cast<const uint4*>(cn_s + c0 + j4 * 4);
+            c[j4 * 4 + 0] = q4.x; c[j4 * 4 + 1] = q4.y; c[j4 * 4 + 2] = q4.z; c[j4 * 4 + 3] = q4.w;
+          }
+          tmem_st16(acc + c0, c);
+        }
+      }
+      tmem_wait_st();
+    };
+    fill_norms(tmem_base + lane_addr + (uint32_t)grp * 128u);
+    tc_fence_before();
+    mbar_arrive(bar(ACC_EMPTY + grp));
     int i = grp;
     for (int tile = blockIdx.x + grp * gridDim.x; tile < n_tiles && ok; tile += kAcc * gridDim.x, i += kAcc) {
       const int a = grp;
@@ -433,18 +488,44 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         xn = xnorm[row];
         if (count_changes) old_label = labels[row];
       }
-      ok = mbar_wait(bar(ACC_FULL + a), pha, abort_flag, 7);
+      ok = mbar_wait(bar(ACC_FULL + a), pha, abort_flag, 7, i);
       ok = __all_sync(0xffffffffu, ok);  // the tcgen05.ld below needs the whole warp
       if (!ok) break;
       tc_fence_after();
       const uint32_t acc = tmem_base + lane_addr + (uint32_t)a * 128u;
-      // four interleaved (best, second, index) chains keep the compare/select
-      // dependency short; chain q sees columns j with j % 4 == q in ascending order
-      float bst[4] = {kInf, kInf, kInf, kInf}, sec[4] = {kInf, kInf, kInf, kInf};
-      int bix[4] = {0, 0, 0, 0};
+      // pass 1: the smallest score of the row, two three-input minima per four columns
+      float m0 = __int_as_float(0x7f800000), m1 = m0;
+      if (!(dbg & 4)) {
+#pragma unroll
+        for (int ch = 0; ch < kMaxNPad / 32; ++ch) {
+          const int c0 = ch * 32;
+          if (c0 < npad) {
+            uint32_t v[32];
+            const bool two = (c0 + 16 < npad);
+            tmem_ld16(acc + c0, v, 0);
+            if (two) tmem_ld16(acc + c0 + 16, v, 16);
+            tmem_wait_ld(v);
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (j < 16 || two) {
+                m0 = fmin3(m0, __uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                m1 = fmin3(m1, __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+              }
+            }
+          }
+        }
+      }
+      const float best = fminf(m0, m1);
+      // rows with a second score within the error bound of the split product (scores carry the
+      // factor sx*sb) go to the exact re-evaluation pass; without that pass only exact ties count
+      const float tol = (amb_rows != nullptr) ? tol_rel * (xn + cn_max) * sxsb : 0.f;
+      const float thr = best + tol;
+      // pass 2: one bit per column whose score is within the bound of the best
+      uint32_t near[kMaxNPad / 32];
 #pragma unroll
       for (int ch = 0; ch < kMaxNPad / 32; ++ch) {
-        const int c0 = ch * 32;  // compile-time after unrolling: column indices are immediates
+        const int c0 = ch * 32;
+        uint32_t mk = 0;
         if (c0 < npad && !(dbg & 4)) {
           uint32_t v[32];
           const bool two = (c0 + 16 < npad);
@@ -452,43 +533,24 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           if (two) tmem_ld16(acc + c0 + 16, v, 16);
           tmem_wait_ld(v);
 #pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
-            if (j4 < 4 || two) {
-              const float4 cn4 = *reinterpret_cast<const float4*>(cn_s + c0 + j4 * 4);
-              const float cn[4] = {cn4.x, cn4.y, cn4.z, cn4.w};
-#pragma unroll
-              for (int qq = 0; qq < 4; ++qq) {
-                const float sc = __uint_as_float(v[j4 * 4 + qq]) + cn[qq];
-                sec[qq] = fminf(sec[qq], fmaxf(sc, bst[qq]));
-                const bool lt = sc < bst[qq];
-                bst[qq] = lt ? sc : bst[qq];
-                bix[qq] = lt ? (c0 + j4 * 4 + qq) : bix[qq];
-              }
-            }
-          }
+          for (int j = 0; j < 32; ++j)
+            if ((j < 16 || two) && __uint_as_float(v[j]) <= thr) mk |= (1u << j);
         }
+        near[ch] = mk;
       }
+      // hand the accumulator back with the norms in place
+      fill_norms(acc);
       tc_fence_before();
       mbar_arrive(bar(ACC_EMPTY + a));
-      float best = bst[0], second = sec[0];
-      int bidx = bix[0];
+      int n_near = 0, bidx = 0;
 #pragma unroll
-      for (int qq = 1; qq < 4; ++qq) {
-        if (bst[qq] < best || (bst[qq] == best && bix[qq] < bidx)) {
-          second = fminf(second, best);
-          best = bst[qq];
-          bidx = bix[qq];
-        } else {
-          second = fminf(second, bst[qq]);
-        }
-        second = fminf(second, sec[qq]);
+      for (int ch = kMaxNPad / 32 - 1; ch >= 0; --ch) {
+        n_near += __popc(near[ch]);
+        if (near[ch]) bidx = ch * 32 + __ffs(near[ch]) - 1;   // lowest column wins
       }
-      if (dbg & 4) { best = 0.f; second = 3.0e38f; }  // timing experiments: nothing is ambiguous
+      if (dbg & 4) { n_near = 1; bidx = 0; }  // timing experiments: nothing is ambiguous
       if (row < n) {
-        // rows whose two best scores are closer than the error bound of the split
-        // product are left to the exact re-evaluation pass (scores carry the factor sx*sb)
-        const float tol = tol_rel * (xn + cn_max) * sxsb;
-        if (amb_rows != nullptr && !(second - best > tol)) {
+        if (amb_rows != nullptr && n_near != 1) {
           const unsigned int pos = atomicAdd(&st->amb_count, 1u);
           amb_rows[pos] = (unsigned int)row;
         } else {

@@ -302,7 +302,16 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
     cudaError_t ce = cudaMemcpy(&hs, s.st, sizeof(hs), cudaMemcpyDeviceToHost);
     if (ce != cudaSuccess) { set_error(std::string("fit state: ") + cudaGetErrorString(ce)); free_events(); return KM_ECUDA; }
     if (hs.error != 0) {
-      set_error("a bounded device-side wait gave up (code " + std::to_string(hs.error) + ")");
+      std::string msg = "a bounded device-side wait gave up (code " + std::to_string(hs.error) + ")";
+      int diag[16][4];
+      if (cudaMemcpyFromSymbol(diag, tc::g_wait_diag, sizeof(diag)) == cudaSuccess) {
+        msg += "; waits [site: cta, tile counter, parity, 1 gave up / 2 saw abort]:";
+        for (int c = 1; c < 16; ++c)
+          if (diag[c][3] != 0)
+            msg += " [" + std::to_string(c) + ": " + std::to_string(diag[c][0]) + ", " + std::to_string(diag[c][1]) +
+                   ", " + std::to_string(diag[c][2]) + ", " + std::to_string(diag[c][3]) + "]";
+      }
+      set_error(msg);
       free_events();
       return KM_ETIMEOUT;
     }

@@ -97,13 +97,17 @@ int fit_impl(int verbose, int seed, int gpu_id, int n_gpu, size_t rows, size_t c
     k = (int)rows;  // src/gpu/kmeans/kmeans_h2o4gpu.cu:629-635
   }
   if (init_from_data == 2 && !centroids) KM_FAIL(KM_EINVAL, "init_from_data == 2 needs initial centroids");
+  static const bool trace = std::getenv("H2O4GPU_KM_TRACE") != nullptr;
+  const double t_begin = km::now_s();
   std::vector<int> devs;
   KM_TRY(device_list(gpu_id, n_gpu, rows, &devs));
   std::unique_ptr<km::Engine<T>> e;
   KM_TRY(make_engine<T>(devs, &e));
   e->verbose = verbose;
   km::log_msg(verbose, 500, "rows %zu cols %zu k %d max_iter %d devices %zu", rows, cols, k, max_iter, devs.size());
+  const double t_engine = km::now_s();
   KM_TRY(e->upload_host(X, rows, cols, 'r'));
+  const double t_upload = km::now_s();
   std::vector<T> init;
   const T* init_ptr = centroids;
   if (init_from_data != 2) {
@@ -113,6 +117,8 @@ int fit_impl(int verbose, int seed, int gpu_id, int n_gpu, size_t rows, size_t c
   }
   int flags = (threshold > 0) ? KM_FIT_CHECK_EVERY_ITER : 0;
   KM_TRY(e->fit(k, max_iter, (double)threshold, init_ptr, flags));
+  const double e_fit_s = e->stats.seconds_fit;
+  const float e_loop_ms = e->stats.ms_loop;
   bool a1 = false, a2 = false;
   KM_TRY(out_buffer(pred_centroids, (size_t)k * cols, &a1));
   int rc = out_buffer(pred_labels, rows, &a2);
@@ -130,6 +136,13 @@ int fit_impl(int verbose, int seed, int gpu_id, int n_gpu, size_t rows, size_t c
   }
   km::log_msg(verbose, 300, "fit: %d iterations, %.3f s upload, %.3f s fit", e->stats.iterations,
               e->stats.seconds_upload, e->stats.seconds_fit);
+  if (trace) {
+    const double t_out = km::now_s();
+    e.reset();
+    std::fprintf(stderr, "[kmeans] call: set-up %.2f ms, upload %.2f ms, fit %.2f ms (device loop %.2f ms), "
+                 "results to host %.2f ms, release %.2f ms\n", 1e3 * (t_engine - t_begin), 1e3 * (t_upload - t_engine),
+                 1e3 * e_fit_s, e_loop_ms, 1e3 * (t_out - t_upload - e_fit_s), 1e3 * (km::now_s() - t_out));
+  }
   return KM_OK;
 }
 
