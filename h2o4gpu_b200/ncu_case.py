@@ -1,5 +1,6 @@
-"""Small resident fit of the C2-shaped workload (d=64, k=100) for profiler captures:
-    python h2o4gpu_b200/ncu_case.py [rows] [iterations]"""
+"""Small resident fit of a bench-shaped workload for profiler captures (Gaussian mixture with
+as many components as clusters, seeded init rows; defaults: the C2 shape d=64, k=100):
+    python h2o4gpu_b200/ncu_case.py [rows] [iterations] [d] [k]"""
 import sys
 import numpy as np
 sys.path.insert(0, __import__('os').path.dirname(__import__('os').path.dirname(__import__('os').path.abspath(__file__))))
@@ -7,11 +8,12 @@ import torch
 from h2o4gpu_b200 import engine
 n = int(sys.argv[1]) if len(sys.argv) > 1 else 2_000_000
 iters = int(sys.argv[2]) if len(sys.argv) > 2 else 3
-d, k = 64, 100
+d = int(sys.argv[3]) if len(sys.argv) > 3 else 64
+k = int(sys.argv[4]) if len(sys.argv) > 4 else 100
 dev = torch.device("cuda", 0)
 rng = np.random.default_rng(0)
-centers = rng.uniform(-10, 10, (100, d)).astype(np.float32)
-w = rng.dirichlet(np.ones(100)).astype(np.float32)
+centers = rng.uniform(-10, 10, (k, d)).astype(np.float32)
+w = rng.dirichlet(np.ones(k)).astype(np.float32)
 X = torch.empty((n, d), dtype=torch.float32, device=dev)
 engine.synth_device(X.data_ptr(), n, d, np.float32, centers=centers, weights=w, sigma=1.0, seed=1)
 init = X[torch.from_numpy(np.sort(rng.choice(n, k, replace=False))).to(dev)].cpu().numpy()
