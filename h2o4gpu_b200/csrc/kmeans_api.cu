@@ -8,11 +8,15 @@
 #include <random>
 
 #include "km_fit.cuh"
+#include "km_init.cuh"
 #include "km_synth.cuh"
 
 namespace km {
 
 static thread_local std::string g_err;
+// iterations and inertia of this thread's last fit through the host-pointer entry points
+static thread_local int g_last_iterations = 0;
+static thread_local double g_last_inertia = -1.0;
 void set_error(const std::string& msg) { g_err = msg; }
 
 // Levelled stderr logger with the reference's convention: a message of level L
@@ -110,15 +114,26 @@ int fit_impl(int verbose, int seed, int gpu_id, int n_gpu, size_t rows, size_t c
   const double t_upload = km::now_s();
   std::vector<T> init;
   const T* init_ptr = centroids;
-  if (init_from_data != 2) {
-    // 0 = seeded random rows; 1 (k-means||) currently starts from the same rows
-    shuffled_rows_init(X, rows, cols, k, seed, &init);
+  if (init_from_data == 1) {
+    // k-means|| on the device (src/gpu/kmeans/kmeans_h2o4gpu.cu:331-563)
+    KM_TRY(km::init_centroids<T>(*e, k, seed, 1, &init));
+    init_ptr = init.data();
+  } else if (init_from_data != 2) {
+    shuffled_rows_init(X, rows, cols, k, seed, &init);   // 0 = seeded random rows
     init_ptr = init.data();
   }
   int flags = (threshold > 0) ? KM_FIT_CHECK_EVERY_ITER : 0;
   KM_TRY(e->fit(k, max_iter, (double)threshold, init_ptr, flags));
   const double e_fit_s = e->stats.seconds_fit;
   const float e_loop_ms = e->stats.ms_loop;
+  {
+    // what sklearn reports as n_iter_ and inertia_ (the reference leaves inertia_ unset,
+    // src/interface_py/h2o4gpu/solvers/kmeans.py:187): one more pass over X
+    double inertia = -1.0;
+    KM_TRY(e->inertia(&inertia));
+    km::g_last_iterations = e->stats.n_iter_converged > 0 ? e->stats.n_iter_converged : e->stats.iterations;
+    km::g_last_inertia = inertia;
+  }
   bool a1 = false, a2 = false;
   KM_TRY(out_buffer(pred_centroids, (size_t)k * cols, &a1));
   int rc = out_buffer(pred_labels, rows, &a2);
@@ -286,6 +301,17 @@ static int get_centroids(km::Engine<T>* e, void* out) {
 }
 
 template <typename T>
+static int init_resident(km::Engine<T>* e, int k, int seed, int method, void* out, long long* rows_out) {
+  if (!out) KM_FAIL(KM_EINVAL, "kmeans_init_resident: out is NULL");
+  std::vector<T> c;
+  std::vector<size_t> rows;
+  KM_TRY(km::init_centroids<T>(*e, k, seed, method, &c, &rows));
+  std::memcpy(out, c.data(), c.size() * sizeof(T));
+  if (rows_out)
+    for (size_t i = 0; i < rows.size(); ++i) rows_out[i] = (long long)rows[i];
+  return KM_OK;
+}
+template <typename T>
 static int get_labels(km::Engine<T>* e, int local, int32_t* out) {
   if (!out || local < 0 || local >= (int)e->shards.size()) KM_FAIL(KM_EINVAL, "kmeans_get_labels: bad argument");
   km::Shard<T>& s = e->shards[local];
@@ -318,6 +344,11 @@ static int get_stats(km::Engine<T>* e, kmeans_stats* out, int want_inertia) {
 extern "C" {
 
 const char* kmeans_last_error(void) { return km::g_err.c_str(); }
+int kmeans_last_fit_info(int* iterations, double* inertia) {
+  if (iterations) *iterations = km::g_last_iterations;
+  if (inertia) *inertia = km::g_last_inertia;
+  return KM_OK;
+}
 
 int kmeans_device_count(void) {
   int n = 0;
@@ -408,6 +439,11 @@ int kmeans_fit_resident(kmeans_handle_t h, int k, int max_iter, double threshold
   KM_DISPATCH(h, h->f32->fit(k, max_iter, threshold, static_cast<const float*>(init), flags),
               h->f64->fit(k, max_iter, threshold, static_cast<const double*>(init), flags));
 }
+int kmeans_init_resident(kmeans_handle_t h, int k, int seed, int method, void* out, long long* rows_out) {
+  KM_DISPATCH(h, init_resident(h->f32, k, seed, method, out, rows_out),
+              init_resident(h->f64, k, seed, method, out, rows_out));
+}
+
 int kmeans_set_centroids(kmeans_handle_t h, int k, const void* c) {
   KM_DISPATCH(h, h->f32->set_centroids(k, static_cast<const float*>(c)),
               h->f64->set_centroids(k, static_cast<const double*>(c)));

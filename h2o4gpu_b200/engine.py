@@ -81,6 +81,16 @@ class ResidentKMeans(object):
                                                 init.ctypes.data_as(ctypes.c_void_p), flags))
         return self
 
+    def init_centroids(self, k, seed=0, method="k-means||", return_rows=False):
+        """Initial centroids from the attached data, on the device: "k-means||" (k-means|| rounds, then
+        weighted k-means++ over the candidates) or "random" (first k rows of a seeded shuffle)."""
+        m = {"random": 0, "k-means||": 1, "k-means++": 1}[method]
+        out = np.empty((int(k), self.cols), dtype=self.dtype)
+        rows = np.empty(int(k), dtype=np.int64)
+        _lk.check(self._lib.kmeans_init_resident(self._h, int(k), int(seed), m, out.ctypes.data_as(ctypes.c_void_p),
+                                                 rows.ctypes.data_as(ctypes.c_void_p)))
+        return (out, rows) if return_rows else out
+
     def set_centroids(self, C):
         C = np.ascontiguousarray(C, dtype=self.dtype)
         self.k = C.shape[0]

@@ -44,6 +44,7 @@ class Stats(ctypes.Structure):
 # name -> (restype, argtypes); every symbol include/h2o4gpu_kmeans.h declares extern "C"
 SIGNATURES = {
     "kmeans_last_error": (_c.c_char_p, []),
+    "kmeans_last_fit_info": (_c.c_int, [_c.POINTER(_c.c_int), _c.POINTER(_c.c_double)]),
     "kmeans_fit_f32": (_c.c_int, [_c.c_int] * 4 + [_sz, _sz, _c.c_int, _c.c_int, _c.c_int, _c.c_float, _vp, _vp, _vp, _vp]),
     "kmeans_fit_f64": (_c.c_int, [_c.c_int] * 4 + [_sz, _sz, _c.c_int, _c.c_int, _c.c_int, _c.c_double, _vp, _vp, _vp, _vp]),
     "kmeans_predict_f32": (_c.c_int, [_c.c_int] * 3 + [_sz, _sz, _c.c_int, _vp, _vp, _vp]),
@@ -60,6 +61,7 @@ SIGNATURES = {
     "kmeans_fit_resident": (_c.c_int, [_vp, _c.c_int, _c.c_int, _c.c_double, _vp, _c.c_int]),
     "kmeans_assign_resident": (_c.c_int, [_vp]),
     "kmeans_set_centroids": (_c.c_int, [_vp, _c.c_int, _vp]),
+    "kmeans_init_resident": (_c.c_int, [_vp, _c.c_int, _c.c_int, _c.c_int, _vp, _vp]),
     "kmeans_get_centroids": (_c.c_int, [_vp, _vp]),
     "kmeans_get_labels": (_c.c_int, [_vp, _c.c_int, _vp]),
     "kmeans_labels_device": (_c.c_int, [_vp, _c.c_int, _c.POINTER(_vp)]),
@@ -133,6 +135,13 @@ class _Module:
         fn = getattr(self._lib, "kmeans_predict_" + suffix)
         return check(fn(verbose, gpu_id, n_gpu, rows, cols, k, _ptr(X), _ptr(C) if C is not None else None,
                         ctypes.byref(pl)))
+
+    def last_fit_info(self):
+        """(iterations, inertia) of this thread's last fit through make_ptr_*_kmeans."""
+        it = _c.c_int(0)
+        inertia = _c.c_double(-1.0)
+        check(self._lib.kmeans_last_fit_info(ctypes.byref(it), ctypes.byref(inertia)))
+        return it.value, inertia.value
 
     def make_ptr_float_kmeans(self, *a):
         return self._fit_predict("f32", np.float32, *a)

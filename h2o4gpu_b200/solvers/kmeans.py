@@ -9,7 +9,9 @@ Differences, all deliberate:
   routes it to scikit-learn because its fit ABI drops the centroids argument
   (kmeans.py:713-721, src/gpu/kmeans/kmeans_h2o4gpu.cu:983-986);
 * ``inertia_`` and ``n_iter_`` are set by the GPU path (the reference leaves
-  ``inertia_`` None, kmeans.py:187);
+  ``inertia_`` None, kmeans.py:187), ``n_init > 1`` keeps the run with the
+  lowest inertia (the reference ignores ``n_init`` on the GPU, kmeans.py:722-725)
+  and ``score`` is computed on the GPU; ``sample_weight`` is not supported;
 * when the native library or a GPU is missing and the caller did not ask for
   CPU (``n_gpus=0`` / ``backend='sklearn'``), construction raises instead of
   silently falling back (kmeans.py:768-770 falls back);
@@ -202,13 +204,21 @@ class KMeansH2O(object):
         else:
             c_init = 1 if self.init == "k-means++" else 0
             centroids = np.empty([], dtype=dtype)
-        pred_centers = np.zeros(cols * k, dtype=dtype)
-        pred_labels = np.zeros(rows, dtype=np.int32)
         fn = lib.make_ptr_double_kmeans if self.double_precision else lib.make_ptr_float_kmeans
-        fn(0, self.verbose, self.random_state, self._gpu_id, self.n_gpus, rows, cols, self._n_clusters,
-           self._max_iter, c_init, self.tol, c_data, centroids, pred_centers, pred_labels)
-        self.cluster_centers_ = np.reshape(pred_centers, (k, cols))
-        self.labels_ = np.reshape(pred_labels, rows)
+        # n_init runs from different seeds (one when the start is given), lowest inertia wins
+        runs = 1 if c_init == 2 else max(1, int(self.n_init or 1))
+        best = None
+        for r in range(runs):
+            pred_centers = np.zeros(cols * k, dtype=dtype)
+            pred_labels = np.zeros(rows, dtype=np.int32)
+            fn(0, self.verbose, self.random_state + r, self._gpu_id, self.n_gpus, rows, cols, self._n_clusters,
+               self._max_iter, c_init, self.tol, c_data, centroids, pred_centers, pred_labels)
+            n_iter, inertia = lib.last_fit_info()
+            if best is None or inertia < best[0]:
+                best = (inertia, n_iter, pred_centers, pred_labels)
+        self.inertia_, self.n_iter_ = best[0], best[1]
+        self.cluster_centers_ = np.reshape(best[2], (k, cols))
+        self.labels_ = np.reshape(best[3], rows)
         return self.cluster_centers_, self.labels_
 
     def _validate_centroids(self, X):
@@ -253,6 +263,23 @@ class KMeansH2O(object):
 
     def fit_transform(self, X, y=None):
         return self.fit(X, y).transform(X)
+
+    def score(self, X, y=None):
+        """Opposite of the k-means objective on X (sklearn's convention): minus the sum of squared
+        distances of the rows to their nearest centre, computed on the GPU."""
+        from .. import engine
+        self._load_lib()
+        X_np = _get_data(X)
+        self._validate_centroids(X_np)
+        dtype = np.float64 if self.double_precision else np.float32
+        h = engine.ResidentKMeans(dtype=dtype, devices=(self._gpu_id,))
+        try:
+            h.upload(np.ascontiguousarray(X_np, dtype=dtype))
+            h.set_centroids(np.ascontiguousarray(self.cluster_centers_, dtype=dtype))
+            h.assign()
+            return -h.inertia()
+        finally:
+            h.close()
 
     def fit_predict(self, X, y=None):
         return self.fit(X, y).labels_

@@ -36,6 +36,11 @@ extern "C" {
 #define KM_ESTATE (-8)   /* call out of order on a handle (no data, no centroids)    */
 
 const char* kmeans_last_error(void);
+/* Of the calling thread's last kmeans_fit_* / make_ptr_*_kmeans fit: Lloyd iterations run
+ * (sklearn's n_iter_: up to and including the first one that changed no label) and the sum of
+ * squared distances of the rows to their centres (sklearn's inertia_, which the reference's
+ * wrapper leaves None, src/interface_py/h2o4gpu/solvers/kmeans.py:187). */
+int kmeans_last_fit_info(int* iterations, double* inertia);
 
 /* ---- 1. the reference's entry points ------------------------------------ */
 
@@ -128,6 +133,15 @@ int kmeans_fit_resident(kmeans_handle_t h, int k, int max_iter, double threshold
 /* One E-step on the resident shards with the handle's current centroids. */
 int kmeans_assign_resident(kmeans_handle_t h);
 int kmeans_set_centroids(kmeans_handle_t h, int k, const void* centroids);
+/* Initial centroids from the attached data, computed on the device(s) of a one-process
+ * handle: method 0 = the first k rows of a seeded shuffle (copy_centroids_shuffled,
+ * src/gpu/kmeans/kmeans_h2o4gpu.cu:662-669, 687-693), method 1 = k-means|| followed by a
+ * weighted k-means++ over the candidates (kmeans_parallel / kmeans_plus_plus,
+ * kmeans_h2o4gpu.cu:154-279, 331-563), what init_from_data = 1 runs.  out: k x cols
+ * row-major host buffer of the handle's dtype; rows_out (may be NULL): the k global row
+ * indices the centroids were taken from.  seed < 0 draws a seed.  Leaves the handle's
+ * centroid table in an unspecified state; follow with kmeans_fit_resident. */
+int kmeans_init_resident(kmeans_handle_t h, int k, int seed, int method, void* out_host, long long* rows_out);
 int kmeans_get_centroids(kmeans_handle_t h, void* out_host);
 /* labels of local shard `local`, rows int32, to host / as a device pointer */
 int kmeans_get_labels(kmeans_handle_t h, int local, int32_t* out_host);

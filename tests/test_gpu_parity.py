@@ -388,6 +388,24 @@ def test_estimator_matches_cpu_backend(built_lib):
     assert m.cluster_centers_.shape == (2, 2) and m.predict(Xs).shape == (3,) and m.transform(Xs).shape == (3, 2)
 
 
+def test_estimator_sklearn_surface(built_lib):
+    """inertia_, n_iter_, score and n_init of the GPU estimator against scikit-learn on the same start."""
+    import h2o4gpu_b200
+    g = load_golden("blobs_n2000_d32_k8")
+    X, init = g["X"], g["init"]
+    gpu = h2o4gpu_b200.KMeans(n_clusters=8, init=init, max_iter=50, tol=0.0, n_gpus=1).fit(X)
+    cpu = h2o4gpu_b200.KMeans(n_clusters=8, init=init, max_iter=50, tol=0.0, n_gpus=0).fit(X)
+    assert abs(gpu.inertia_ - cpu.inertia_) <= 1e-4 * cpu.inertia_
+    assert gpu.n_iter_ == cpu.n_iter_
+    assert abs(gpu.score(X) + gpu.inertia_) <= 1e-6 * gpu.inertia_
+    assert abs(gpu.score(X[:500]) - cpu.score(X[:500])) <= 1e-4 * abs(cpu.score(X[:500]))
+    # default start (k-means|| on the device), three runs: the best of them is kept
+    one = h2o4gpu_b200.KMeans(n_clusters=8, n_init=1, max_iter=20, tol=0.0, random_state=5, n_gpus=1).fit(X)
+    three = h2o4gpu_b200.KMeans(n_clusters=8, n_init=3, max_iter=20, tol=0.0, random_state=5, n_gpus=1).fit(X)
+    assert three.inertia_ <= one.inertia_ * (1 + 1e-12)
+    assert three.cluster_centers_.shape == (8, 32) and np.isfinite(three.cluster_centers_).all()
+
+
 # ---- several GPUs in one process ------------------------------------------------------
 def test_multi_gpu_equals_single_gpu(eng):
     from h2o4gpu_b200.libs import lib_kmeans

@@ -1,0 +1,130 @@
+"""k-means|| initialisation: the numpy restatement (CPU) and the CUDA path against it (GPU)."""
+import numpy as np
+import pytest
+
+from oracle import kmeans_parallel as kp
+
+
+# ---- the oracle's random source: published known-answer vectors of Philox4x32-10
+# (Random123 kat_vectors: counter, key -> output) ---------------------------------
+@pytest.mark.parametrize("ctr,key,want", [
+    ((0, 0, 0, 0), (0, 0), (0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8)),
+    ((0xffffffff,) * 4, (0xffffffff, 0xffffffff), (0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd)),
+    ((0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344), (0xa4093822, 0x299f31d0),
+     (0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1)),
+])
+def test_philox_known_answers(ctr, key, want):
+    got = kp.philox4x32_10(*ctr, *key)
+    assert tuple(int(g[0]) for g in got) == want
+
+
+def test_uniform_is_open_interval():
+    a = np.array([0, 0xffffffff], dtype=np.uint64)
+    u = kp.u01_53(a, a)
+    assert 0.0 < u[0] < 1e-15 and 1.0 - 1e-15 < u[1] < 1.0 and u[1] == 1.0 - 2.0 ** -53
+
+
+def test_oracle_init_properties():
+    from h2o4gpu_b200 import synth
+    X, _, _ = synth.c1(n=20000)
+    C, rows, cand = kp.kmeans_parallel(X, 8, 1)
+    C2, rows2, _ = kp.kmeans_parallel(X, 8, 1)
+    assert np.array_equal(rows, rows2) and np.array_equal(C, C2)          # seeded
+    assert len(set(rows.tolist())) == 8 and np.array_equal(C, X[rows])    # k distinct rows of X
+    assert len(cand) > 8 and len(set(cand.tolist())) == len(cand)
+    rng = np.random.default_rng(1)
+    assert kp.potential(X, C) < 0.5 * kp.potential(X, X[rng.choice(20000, 8, replace=False)])
+    # fewer candidates than clusters: all kept, seeded rows fill the rest
+    Xs = np.repeat(np.arange(3, dtype=np.float32)[:, None], 4, 1)
+    C3, rows3, _ = kp.kmeans_parallel(Xs, 3, 0)
+    assert sorted(rows3.tolist()) == [0, 1, 2]
+
+
+def test_tree_sum_matches_plain_sum():
+    v = np.random.default_rng(0).random(300001)
+    assert abs(kp.tree_sum(v) - v.sum()) < 1e-9 * v.sum()
+
+
+# ---- CUDA path ---------------------------------------------------------------------
+@pytest.fixture(scope="module")
+def eng(built_lib):
+    import h2o4gpu_b200.engine as e
+    return e
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("cfg,kw,k,dtype,seed", [
+    ("c2", dict(n=30000), 20, np.float32, 3),      # rounds on the tensor-core kernels (d = 64)
+    ("c1", dict(n=20000), 8, np.float32, 1),       # small tables: fused / SIMT kernels
+    ("c1", dict(n=8000), 8, np.float64, 5),
+    ("c3", dict(n=6000, k=40, d=128), 40, np.float32, 2),
+])
+def test_kmeans_parallel_matches_oracle(eng, cfg, kw, k, dtype, seed):
+    from h2o4gpu_b200 import synth
+    X, _, _ = getattr(synth, cfg)(**kw)
+    X = X.astype(dtype)
+    want_C, want_rows, _ = kp.kmeans_parallel(X, k, seed)
+    h = eng.ResidentKMeans(dtype=dtype)
+    h.upload(X)
+    C, rows = h.init_centroids(k, seed=seed, return_rows=True)
+    # the handle is usable for a fit afterwards
+    h.fit(C, 2)
+    assert h.stats()["iterations"] == 2
+    h.close()
+    assert np.array_equal(rows, want_rows)
+    assert np.array_equal(C, want_C) and np.array_equal(C, X[rows])
+
+
+@pytest.mark.gpu
+def test_init_random_rows_matches_host_shuffle(eng, built_lib):
+    from h2o4gpu_b200 import synth
+    X, _, _ = synth.c1(n=5000)
+    h = eng.ResidentKMeans()
+    h.upload(X)
+    C, rows = h.init_centroids(6, seed=11, method="random", return_rows=True)
+    C2 = h.init_centroids(6, seed=11, method="random")
+    h.close()
+    assert np.array_equal(C, X[rows]) and np.array_equal(C, C2) and len(set(rows.tolist())) == 6
+
+
+@pytest.mark.gpu
+def test_init_is_independent_of_device_count_in_distribution(eng):
+    """Draws are keyed by the global row, so two devices sample the same rows whenever the summed
+    cost agrees to the last bit; always: k distinct rows of X and a potential like one device's."""
+    from h2o4gpu_b200.libs import lib_kmeans
+    ndev = lib_kmeans.cdll().kmeans_device_count()
+    if ndev < 2:
+        pytest.skip("one GPU visible")
+    from h2o4gpu_b200 import synth
+    X, _, _ = synth.c1(n=20001)
+    h1 = eng.ResidentKMeans(); h1.upload(X)
+    C1 = h1.init_centroids(8, seed=4)
+    h1.close()
+    h2 = eng.ResidentKMeans(devices=[0, 1]); h2.upload(X)
+    C2, rows2 = h2.init_centroids(8, seed=4, return_rows=True)
+    h2.close()
+    assert np.array_equal(C2, X[rows2]) and len(set(rows2.tolist())) == 8
+    assert kp.potential(X, C2) < 2.0 * kp.potential(X, C1)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_abi_fit_with_kmeans_parallel_init(built_lib, dtype):
+    """init_from_data = 1 through the reference's entry point: k-means|| start, Lloyd from there."""
+    from h2o4gpu_b200.libs import lib_kmeans
+    from h2o4gpu_b200 import synth
+    from oracle import lloyd
+    lib = lib_kmeans.get()
+    X, _, _ = synth.c1(n=20000)
+    X = X.astype(dtype)
+    k = 8
+    cen = np.zeros(k * X.shape[1], dtype)
+    lab = np.zeros(X.shape[0], np.int32)
+    fn = lib.make_ptr_float_kmeans if dtype == np.float32 else lib.make_ptr_double_kmeans
+    fn(0, 0, 7, 0, 1, X.shape[0], X.shape[1], k, 10, 1, 0.0, X.reshape(-1), np.zeros(1, dtype), cen, lab)
+    C = cen.reshape(k, -1)
+    # same start from the oracle, Lloyd in float64: the fit ends at the same centres
+    init, _, _ = kp.kmeans_parallel(X, k, 7)
+    want = lloyd.fit(X, init.astype(np.float64), 10)["centers"]
+    tol = 1e-4 if dtype == np.float32 else 1e-10
+    assert np.abs(C - want).max() <= tol * np.abs(want).max()
