@@ -13,7 +13,9 @@
 #include <cstring>
 #include <map>
 #include <memory>
+#include <atomic>
 #include <mutex>
+#include <thread>
 #include <vector>
 
 #include "km_accumulate.cuh"
@@ -122,7 +124,15 @@ struct Engine : EngineBase {
   int init(int n_local, const int* devs, int rank0, int world, const void* nccl_id);
   void destroy();
   int attach_device(int local, const T* dX, size_t rows, size_t cols, size_t ntot);
-  int upload_host(const T* X, size_t rows, size_t cols, char order);
+  // wait = false: the copies may still be in flight on return (host threads staging a pageable
+  // matrix, or DMA from a pinned one); upload_wait() completes them
+  int upload_host(const T* X, size_t rows, size_t cols, char order, bool wait = true);
+  int upload_wait();
+  int preallocate(int k_, int max_iter);
+  std::vector<std::thread> upload_threads;
+  std::atomic<int> upload_error{0};
+  double upload_t0 = 0;
+  bool upload_pool_locked = false;
   int ensure_buffers(int k_);
   int check_data();
   int set_centroids(int k_, const T* host_c);
@@ -173,10 +183,8 @@ int Engine<T>::init(int n_local, const int* devs, int rank0, int world, const vo
     s.dev = devs[i];
     if (s.dev < 0 || s.dev >= visible) KM_FAIL(KM_ENODEV, "kmeans_create: device id out of range");
     DevGuard g(s.dev);
-    cudaDeviceProp prop;
-    KM_CUDA(cudaGetDeviceProperties(&prop, s.dev));
-    s.num_sms = prop.multiProcessorCount;
-    s.cc_major = prop.major;
+    KM_CUDA(cudaDeviceGetAttribute(&s.num_sms, cudaDevAttrMultiProcessorCount, s.dev));
+    KM_CUDA(cudaDeviceGetAttribute(&s.cc_major, cudaDevAttrComputeCapabilityMajor, s.dev));
     KM_CUDA(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
     KM_CUDA(cudaMalloc(&s.st, sizeof(IterState)));
     KM_CUDA(cudaMemset(s.st, 0, sizeof(IterState)));
@@ -222,6 +230,7 @@ int Engine<T>::init(int n_local, const int* devs, int rank0, int world, const vo
 
 template <typename T>
 void Engine<T>::destroy() {
+  upload_wait();
   for (auto& s : shards) {
     if (s.dev < 0) continue;
     DevGuard g(s.dev);
@@ -288,25 +297,125 @@ __global__ void transpose_cm_kernel(const T* __restrict__ src, T* __restrict__ d
   }
 }
 
+// ---- host -> device ingest -----------------------------------------------------
+// A pinned (or registered) host matrix goes down in one asynchronous copy per shard.  A pageable
+// one - what numpy hands over - would be staged by the driver through a single thread; instead
+// worker threads copy 4 MB pieces into pinned buffers (two per worker, so a worker refills
+// one while the other is on the bus) and queue them on their own streams.  The buffers live in
+// a process-wide pool, created on first use and kept: pinning memory costs more than the copy.
+// Replaces the pageable thrust::host_vector staging of copy_data (src/gpu/kmeans/kmeans_h2o4gpu.h:24-42).
+struct StagePool {
+  static constexpr size_t kPiece = (size_t)4 << 20;
+  std::mutex busy;                 // one staged upload at a time
+  std::vector<void*> bufs;
+  static StagePool& get() {
+    static StagePool* p = new StagePool();   // never destroyed: the CUDA runtime may be gone at exit
+    return *p;
+  }
+  int ensure(size_t count) {
+    while (bufs.size() < count) {
+      void* b = nullptr;
+      if (cudaHostAlloc(&b, kPiece, cudaHostAllocPortable) != cudaSuccess) {
+        cudaGetLastError();
+        return KM_ENOMEM;
+      }
+      bufs.push_back(b);
+    }
+    return KM_OK;
+  }
+};
+
+inline bool host_pointer_is_pageable(const void* p) {
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+    cudaGetLastError();
+    return true;
+  }
+  return a.type == cudaMemoryTypeUnregistered;
+}
+
+// one worker: pieces first, first + stride, ... of the byte range [src, src + bytes) of one shard
+inline void stage_worker(int dev, const unsigned char* src, unsigned char* dst, size_t bytes, size_t first,
+                         size_t stride, void* buf0, void* buf1, std::atomic<int>* err) {
+  cudaStream_t st = nullptr;
+  cudaEvent_t ev[2] = {nullptr, nullptr};
+  void* buf[2] = {buf0, buf1};
+  bool ok = cudaSetDevice(dev) == cudaSuccess && cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) == cudaSuccess &&
+            cudaEventCreateWithFlags(&ev[0], cudaEventDisableTiming) == cudaSuccess &&
+            cudaEventCreateWithFlags(&ev[1], cudaEventDisableTiming) == cudaSuccess;
+  const size_t piece = StagePool::kPiece;
+  const size_t n_pieces = (bytes + piece - 1) / piece;
+  size_t q = 0;
+  for (size_t j = first; ok && j < n_pieces && err->load() == 0; j += stride, ++q) {
+    const size_t off = j * piece, len = std::min(piece, bytes - off);
+    const int b = (int)(q & 1);
+    if (q >= 2) ok = cudaEventSynchronize(ev[b]) == cudaSuccess;   // the copy that used this buffer is done
+    if (!ok) break;
+    std::memcpy(buf[b], src + off, len);
+    ok = cudaMemcpyAsync(dst + off, buf[b], len, cudaMemcpyHostToDevice, st) == cudaSuccess &&
+         cudaEventRecord(ev[b], st) == cudaSuccess;
+  }
+  if (st && cudaStreamSynchronize(st) != cudaSuccess) ok = false;
+  if (ev[0]) cudaEventDestroy(ev[0]);
+  if (ev[1]) cudaEventDestroy(ev[1]);
+  if (st) cudaStreamDestroy(st);
+  if (!ok) err->store(1);
+}
+
 template <typename T>
-int Engine<T>::upload_host(const T* X, size_t rows, size_t cols, char order) {
+int Engine<T>::upload_host(const T* X, size_t rows, size_t cols, char order, bool wait) {
   if (!X || rows == 0 || cols == 0 || cols > (1u << 20)) KM_FAIL(KM_EINVAL, "kmeans_upload_host: bad argument");
   if (order != 'r' && order != 'c') KM_FAIL(KM_EINVAL, "kmeans_upload_host: order must be 'r' or 'c'");
   if (world_size != (int)shards.size())
     KM_FAIL(KM_ESTATE, "kmeans_upload_host: one process must own all ranks; use kmeans_attach_device");
-  double t0 = now_s();
+  KM_TRY(upload_wait());
+  upload_t0 = now_s();
   const size_t g = shards.size();
   const size_t per = (rows + g - 1) / g;
+  static const bool stage_enabled = [] {
+    const char* e = std::getenv("H2O4GPU_KM_STAGED_UPLOAD");
+    return !(e && e[0] == '0');
+  }();
+  const bool staged = stage_enabled && order == 'r' && rows * cols * sizeof(T) >= ((size_t)64 << 20) &&
+                      host_pointer_is_pageable(X);
+  int workers_per_shard = 0;
+  if (staged) {
+    // a single core copies far less than the bus carries (about 4 GB/s against 55 GB/s on the
+    // hosts measured), so nearly all of them are put to work
+    const unsigned hw = std::max(3u, std::thread::hardware_concurrency());
+    workers_per_shard = (int)std::max<size_t>(1, std::min<size_t>(14, hw - 2) / g);
+    StagePool& pool = StagePool::get();
+    pool.busy.lock();
+    upload_pool_locked = true;
+    if (pool.ensure(2 * workers_per_shard * g) != KM_OK) {
+      pool.busy.unlock();
+      upload_pool_locked = false;
+      workers_per_shard = 0;          // no pinned memory to be had: let the driver stage the copy
+    }
+  }
+  upload_error.store(0);
   size_t off = 0;
   for (size_t i = 0; i < g; ++i) {
     Shard<T>& s = shards[i];
     size_t r = (off < rows) ? std::min(per, rows - off) : 0;
-    if (r == 0) KM_FAIL(KM_EINVAL, "kmeans_upload_host: fewer rows than devices");
+    if (r == 0) { upload_wait(); KM_FAIL(KM_EINVAL, "kmeans_upload_host: fewer rows than devices"); }
     DevGuard gd(s.dev);
     cudaFree(s.X_owned);
     s.X_owned = nullptr;
-    KM_CUDA(cudaMalloc(&s.X_owned, r * cols * sizeof(T)));
-    if (order == 'r') {
+    if (cudaMalloc(&s.X_owned, r * cols * sizeof(T)) != cudaSuccess) {
+      cudaGetLastError();
+      upload_wait();
+      KM_FAIL(KM_ENOMEM, "kmeans_upload_host: device allocation failed");
+    }
+    if (order == 'r' && workers_per_shard > 0) {
+      StagePool& pool = StagePool::get();
+      for (int w = 0; w < workers_per_shard; ++w) {
+        const size_t b = 2 * (i * workers_per_shard + w);
+        upload_threads.emplace_back(stage_worker, s.dev, reinterpret_cast<const unsigned char*>(X + off * cols),
+                                    reinterpret_cast<unsigned char*>(s.X_owned), r * cols * sizeof(T), (size_t)w,
+                                    (size_t)workers_per_shard, pool.bufs[b], pool.bufs[b + 1], &upload_error);
+      }
+    } else if (order == 'r') {
       KM_CUDA(cudaMemcpyAsync(s.X_owned, X + off * cols, r * cols * sizeof(T), cudaMemcpyHostToDevice, s.stream));
     } else {
       // column-major host matrix (leading dimension = total rows): strided copy of the
@@ -325,11 +434,57 @@ int Engine<T>::upload_host(const T* X, size_t rows, size_t cols, char order) {
     s.row0 = off;
     off += r;
   }
+  if (wait) return upload_wait();
+  return KM_OK;
+}
+
+template <typename T>
+int Engine<T>::upload_wait() {
+  for (auto& t : upload_threads)
+    if (t.joinable()) t.join();
+  upload_threads.clear();
+  if (upload_pool_locked) {
+    StagePool::get().busy.unlock();
+    upload_pool_locked = false;
+  }
   for (auto& s : shards) {
+    if (!s.stream) continue;
     DevGuard gd(s.dev);
     KM_CUDA(cudaStreamSynchronize(s.stream));
   }
-  stats.seconds_upload = now_s() - t0;
+  if (upload_t0 > 0) { stats.seconds_upload = now_s() - upload_t0; upload_t0 = 0; }
+  if (upload_error.exchange(0) != 0) KM_FAIL(KM_ECUDA, "kmeans_upload_host: a staged copy failed");
+  return KM_OK;
+}
+
+// Buffers a fit of k clusters will ask for, allocated ahead of time (e.g. while an upload is
+// still on the bus); fit() finds them in place.
+template <typename T>
+int Engine<T>::preallocate(int k_, int max_iter) {
+  if (k_ < 1 || d == 0) return KM_OK;
+  KM_TRY(ensure_buffers(k_));
+  for (auto& s : shards) {
+    DevGuard g(s.dev);
+    if (s.dist_cap < s.rows && world_size == 1) {
+      cudaFree(s.dist);
+      s.dist = nullptr;
+      KM_CUDA(cudaMalloc(&s.dist, s.rows * sizeof(double)));
+      s.dist_cap = s.rows;
+    }
+    if (s.labels_prev_cap < s.rows) {
+      cudaFree(s.labels_prev);
+      s.labels_prev = nullptr;
+      KM_CUDA(cudaMalloc(&s.labels_prev, s.rows * sizeof(int)));
+      s.labels_prev_cap = s.rows;
+    }
+    if (std::is_same<T, float>::value && s.amb_cap < s.rows) {
+      cudaFree(s.amb_rows);
+      s.amb_rows = nullptr;
+      KM_CUDA(cudaMalloc(&s.amb_rows, s.rows * sizeof(unsigned int)));
+      s.amb_cap = s.rows;
+    }
+  }
+  (void)max_iter;
   return KM_OK;
 }
 

@@ -110,7 +110,11 @@ int fit_impl(int verbose, int seed, int gpu_id, int n_gpu, size_t rows, size_t c
   e->verbose = verbose;
   km::log_msg(verbose, 500, "rows %zu cols %zu k %d max_iter %d devices %zu", rows, cols, k, max_iter, devs.size());
   const double t_engine = km::now_s();
-  KM_TRY(e->upload_host(X, rows, cols, 'r'));
+  // the copy goes down while the host allocates what the fit needs
+  KM_TRY(e->upload_host(X, rows, cols, 'r', false));
+  int prc = e->preallocate(k, max_iter);
+  KM_TRY(e->upload_wait());
+  KM_TRY(prc);
   const double t_upload = km::now_s();
   std::vector<T> init;
   const T* init_ptr = centroids;

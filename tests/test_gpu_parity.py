@@ -406,6 +406,25 @@ def test_estimator_sklearn_surface(built_lib):
     assert three.cluster_centers_.shape == (8, 32) and np.isfinite(three.cluster_centers_).all()
 
 
+def test_staged_upload_of_a_pageable_matrix(eng):
+    """A pageable matrix above 64 MB goes down through the pinned staging pool (worker threads,
+    4 MB pieces): every row must land where it belongs."""
+    from h2o4gpu_b200 import synth
+    from oracle import lloyd
+    X, init, _ = synth.c2(n=300001)            # 76.8 MB, not a multiple of the piece size
+    h = eng.ResidentKMeans()
+    h.upload(X)
+    h.fit(init, 1, flags=eng.FIT_NO_FINAL_ASSIGN)
+    lab = h.labels()
+    h.set_centroids(np.zeros((1, X.shape[1]), np.float32))
+    h.assign()
+    total = h.inertia()
+    h.close()
+    want = lloyd.assign(X, init.astype(np.float64))
+    check_labels(X, init.astype(np.float64), lab, want)
+    assert abs(total - (X.astype(np.float64) ** 2).sum()) <= 1e-12 * total
+
+
 # ---- several GPUs in one process ------------------------------------------------------
 def test_multi_gpu_equals_single_gpu(eng):
     from h2o4gpu_b200.libs import lib_kmeans
