@@ -303,9 +303,12 @@ def main():
             # the same call on a pageable copy of the matrix (what numpy hands over): the library
             # stages it through its pinned pool
             Xp = np.array(Xn)
-            t0 = time.perf_counter()
-            lib.make_ptr_float_kmeans(0, 0, 0, local_rank, 1, n, d, k, K, 2, 0.0, Xp, init.reshape(-1), cen, lab)
-            pageable = time.perf_counter() - t0
+            pageable = None
+            for rep in range(2):   # best of two, as above: the first pass over a fresh array pays page faults
+                t0 = time.perf_counter()
+                lib.make_ptr_float_kmeans(0, 0, 0, local_rank, 1, n, d, k, K, 2, 0.0, Xp, init.reshape(-1), cen, lab)
+                dt = time.perf_counter() - t0
+                pageable = dt if pageable is None else min(pageable, dt)
             del Xp
             e2e = {"value": n * K / best, "unit": "points*iters/s", "pageable_seconds_per_call": pageable,
                    "h2d_bytes_per_step": (n * d * 4 + k * d * 4) / K, "d2h_bytes_per_step": (n * 4 + k * d * 4) / K,

@@ -104,7 +104,7 @@ delta_accumulate_kernel(const T* __restrict__ X, size_t n, int d, const int* __r
 // sends each non-zero total to the global sums once.  Subtracting a row is adding its
 // negation: rint is odd, so the pieces of -x are minus the pieces of x.
 constexpr int kDeltaThreads = 1024;
-constexpr int kDeltaChunk = 8192;    // rows between two looks at the overflow guard: 256 per warp
+constexpr int kDeltaChunk = 32768;   // rows between two drains: the int32 accumulators hold 2^15 rows of 2^15-sized pieces
 
 template <typename T>
 inline size_t delta_smem_bytes(int k, int d) {
@@ -127,7 +127,7 @@ delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int
   const int lane = tid & 31;
   const int warp = tid >> 5;
   constexpr int NWARP = kDeltaThreads / 32;
-  static_assert(kDeltaChunk == NWARP * 256, "one 256-row step per warp and chunk");
+  static_assert(kDeltaChunk % (NWARP * 256) == 0, "whole 256-row steps per warp and chunk");
   const int dv = d / V;
   const size_t pstride = (size_t)k * d;
   int lpr = 1;
@@ -148,9 +148,10 @@ delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int
 
   for (size_t c0 = r_begin; c0 < r_end; c0 += kDeltaChunk) {
     const size_t c1 = min(r_end, c0 + (size_t)kDeltaChunk);
-    // one step per warp and chunk: 256 rows, eight per lane, all label loads in flight together
-    // (c0 is a multiple of 32 rows, so the 16-byte loads are aligned)
-    const size_t wb = c0 + (size_t)warp * (kDeltaChunk / NWARP);
+    // a warp takes 256 rows per step, eight per lane, all label loads in flight together
+    // (c0 is a multiple of 32 rows, so the 16-byte loads are aligned); between two drains the
+    // warps run free of one another
+    for (size_t wb = c0 + (size_t)warp * 256; wb < c1; wb += (size_t)NWARP * 256) {
     int nw[8], od[8];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -201,11 +202,10 @@ delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int
         for (int i = 0; i < groups && mask; ++i) mask &= mask - 1;
       }
     }
+    }
     __syncthreads();
-    // every piece is at most 2^15 in magnitude: drain before 2^15 rows could have piled up
-    const bool drain = (s_touched + kDeltaChunk > 32768) || (c1 >= r_end);
-    __syncthreads();
-    if (drain) {
+    // every piece is at most 2^15 in magnitude and a chunk has 2^15 rows: drain after each
+    {
       if (s_touched > 0) {
         for (int i = tid; i < k * d; i += kDeltaThreads) {
           const int c = i / d;

@@ -202,19 +202,41 @@ __device__ __forceinline__ float fmin3(float a, float b, float c) {
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// |x|^2 of every row (float), once per upload: the error bound of a row's scores.
+// |x|^2 of every row (float), once per upload: the error bound of a row's scores.  The
+// tensor-core paths have d % 4 == 0 and 16-byte aligned rows: a row is shared by lpr lanes
+// loading a float4 each, four sets of rows per loop trip.
 __global__ void __launch_bounds__(256)
 rownorm_kernel(const float* __restrict__ X, size_t n, int d, float* __restrict__ xn) {
+  constexpr int U = 4;
   const int lane = threadIdx.x & 31;
   const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const size_t nwarp = ((size_t)gridDim.x * blockDim.x) >> 5;
-  for (size_t row = warp; row < n; row += nwarp) {
-    const float* x = X + row * (size_t)d;
-    float s = 0.f;
-    for (int t = lane; t < d; t += 32) s = fmaf(x[t], x[t], s);
+  const int dv = d >> 2;
+  int lpr = 1;
+  while (lpr < dv && lpr < 32) lpr <<= 1;
+  const int gpw = 32 / lpr;
+  const int g = lane / lpr, l = lane % lpr;
+  const size_t stride = nwarp * gpw;
+  for (size_t base = warp * gpw; base < n; base += stride * U) {
+    float s[U];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (lane == 0) xn[row] = s;
+    for (int u = 0; u < U; ++u) {
+      s[u] = 0.f;
+      const size_t row = base + g + (size_t)u * stride;
+      if (row < n) {
+        const float4* x = reinterpret_cast<const float4*>(X + row * (size_t)d);
+        for (int idx = l; idx < dv; idx += lpr) {
+          const float4 v = x[idx];
+          s[u] = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, s[u]))));
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      for (int o = lpr >> 1; o > 0; o >>= 1) s[u] += __shfl_xor_sync(0xffffffffu, s[u], o);
+      const size_t row = base + g + (size_t)u * stride;
+      if (l == 0 && row < n) xn[row] = s[u];
+    }
   }
 }
 

@@ -2,6 +2,10 @@
 // representation of the centroid sums, small device utilities.
 #pragma once
 
+#include <algorithm>
+#include <cstdlib>
+#include <mutex>
+
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -42,6 +46,91 @@ struct Status {
     ::km::set_error(msg);              \
     return (code);                     \
   } while (0)
+
+// ---- device memory ------------------------------------------------------------
+// Every buffer of the library comes from one stream-ordered memory pool per device that
+// keeps what is freed (release threshold: unlimited).  A fit through the host-pointer entry
+// points creates and destroys some twenty-five buffers, one of them the whole matrix;
+// with cudaMalloc / cudaFree that costs 5-20 ms per call in mapping and unmapping alone,
+// with the pool a later call finds the memory in place.  kmeans_trim_memory() hands the
+// cached memory back to the driver; H2O4GPU_KM_POOL=0 turns the pool off.
+// km_malloc returns memory that any stream may use at once (the allocation is made on a
+// stream of its own, which is then waited for); km_free waits for the device to go idle
+// first, as cudaFree does.  Both act on the current device.
+struct DevicePools {
+  static constexpr int kMaxDev = 64;
+  cudaMemPool_t pool[kMaxDev] = {};
+  cudaStream_t stream[kMaxDev] = {};
+  int state[kMaxDev] = {};        // 0 untried, 1 pool in use, -1 plain cudaMalloc
+  std::mutex m;
+  static DevicePools& get() {
+    static DevicePools* p = new DevicePools();   // outlives the CUDA runtime's own teardown
+    return *p;
+  }
+  int mode(int dev) {
+    if (dev < 0 || dev >= kMaxDev) return -1;
+    std::lock_guard<std::mutex> lock(m);
+    if (state[dev] != 0) return state[dev];
+    state[dev] = -1;
+    const char* e = std::getenv("H2O4GPU_KM_POOL");
+    if (e && e[0] == '0') return -1;
+    int supported = 0;
+    if (cudaDeviceGetAttribute(&supported, cudaDevAttrMemoryPoolsSupported, dev) != cudaSuccess || !supported) {
+      cudaGetLastError();
+      return -1;
+    }
+    cudaMemPoolProps props = {};
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = dev;
+    if (cudaMemPoolCreate(&pool[dev], &props) != cudaSuccess) { cudaGetLastError(); return -1; }
+    unsigned long long keep = ~0ULL;
+    cudaMemPoolSetAttribute(pool[dev], cudaMemPoolAttrReleaseThreshold, &keep);
+    if (cudaStreamCreateWithFlags(&stream[dev], cudaStreamNonBlocking) != cudaSuccess) {
+      cudaGetLastError();
+      cudaMemPoolDestroy(pool[dev]);
+      return -1;
+    }
+    state[dev] = 1;
+    return 1;
+  }
+};
+
+inline cudaError_t km_malloc_bytes(void** p, size_t bytes) {
+  int dev = 0;
+  cudaError_t ce = cudaGetDevice(&dev);
+  if (ce != cudaSuccess) return ce;
+  DevicePools& dp = DevicePools::get();
+  if (dp.mode(dev) != 1) return cudaMalloc(p, bytes);
+  ce = cudaMallocFromPoolAsync(p, std::max<size_t>(bytes, 1), dp.pool[dev], dp.stream[dev]);
+  if (ce != cudaSuccess) return ce;
+  return cudaStreamSynchronize(dp.stream[dev]);
+}
+template <typename P>
+inline cudaError_t km_malloc(P** p, size_t bytes) { return km_malloc_bytes(reinterpret_cast<void**>(p), bytes); }
+
+inline cudaError_t km_free(void* p) {
+  if (!p) return cudaSuccess;
+  int dev = 0;
+  cudaError_t ce = cudaGetDevice(&dev);
+  if (ce != cudaSuccess) return ce;
+  DevicePools& dp = DevicePools::get();
+  if (dp.mode(dev) != 1) return cudaFree(p);
+  ce = cudaDeviceSynchronize();      // nothing in flight may still use the buffer
+  if (ce != cudaSuccess) return ce;
+  return cudaFreeAsync(p, dp.stream[dev]);
+}
+
+inline void km_trim_pools() {
+  DevicePools& dp = DevicePools::get();
+  std::lock_guard<std::mutex> lock(dp.m);
+  for (int dev = 0; dev < DevicePools::kMaxDev; ++dev)
+    if (dp.state[dev] == 1) {
+      cudaStreamSynchronize(dp.stream[dev]);
+      cudaMemPoolTrimTo(dp.pool[dev], 0);
+    }
+}
 
 // ---- fixed-point centroid sums ------------------------------------------------
 // A value x (|x| <= xmax < 2^e) is cut into NP signed pieces of 15 bits:

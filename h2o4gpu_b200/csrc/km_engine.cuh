@@ -159,6 +159,14 @@ struct Engine : EngineBase {
   int launch_accumulate(Shard<T>& s, T scale, long long* dst = nullptr, const unsigned long long* gate = nullptr,
                         unsigned long long limit = 0);
   int launch_delta(Shard<T>& s, T scale, const unsigned long long* gate, unsigned long long limit);
+  // exact squared distance of every row to its labelled centroid into s.dist
+  void launch_rowdist(Shard<T>& s, int force) {
+    constexpr int V = VecOf<T>::N;
+    if (vec_ok(s))
+      rowdist_kernel<T, V><<<s.num_sms * 8, 256, 0, s.stream>>>(s.X, s.rows, d, s.labels, s.C[cur], s.dist, s.st, force);
+    else
+      rowdist_kernel<T, 1><<<s.num_sms * 8, 256, 0, s.stream>>>(s.X, s.rows, d, s.labels, s.C[cur], s.dist, s.st, force);
+  }
   int allreduce_from(bool from_pure);
   bool smallk_ok(bool update) const;
   bool vec_ok(const Shard<T>& s) const {
@@ -186,13 +194,13 @@ int Engine<T>::init(int n_local, const int* devs, int rank0, int world, const vo
     KM_CUDA(cudaDeviceGetAttribute(&s.num_sms, cudaDevAttrMultiProcessorCount, s.dev));
     KM_CUDA(cudaDeviceGetAttribute(&s.cc_major, cudaDevAttrComputeCapabilityMajor, s.dev));
     KM_CUDA(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
-    KM_CUDA(cudaMalloc(&s.st, sizeof(IterState)));
+    KM_CUDA(km_malloc(&s.st, sizeof(IterState)));
     KM_CUDA(cudaMemset(s.st, 0, sizeof(IterState)));
-    KM_CUDA(cudaMalloc(&s.xstat, 2 * sizeof(double)));
+    KM_CUDA(km_malloc(&s.xstat, 2 * sizeof(double)));
     KM_CUDA(cudaMallocHost(&s.host_pin, 8 * sizeof(double)));
-    KM_CUDA(cudaMalloc(&s.cand_val, 1024 * sizeof(double)));
-    KM_CUDA(cudaMalloc(&s.cand_row, 1024 * sizeof(unsigned long long)));
-    KM_CUDA(cudaMalloc(&s.sum_partials, 1024 * sizeof(double)));
+    KM_CUDA(km_malloc(&s.cand_val, 1024 * sizeof(double)));
+    KM_CUDA(km_malloc(&s.cand_row, 1024 * sizeof(unsigned long long)));
+    KM_CUDA(km_malloc(&s.sum_partials, 1024 * sizeof(double)));
   }
   if (world > 1) {
     NcclApi* api = NcclApi::get();
@@ -241,12 +249,12 @@ void Engine<T>::destroy() {
     }
     s.tcp.release();
     s.tcbp.release();
-    cudaFree(s.amb_rows); cudaFree(s.amb_log);
-    cudaFree(s.X_owned); cudaFree(s.labels); cudaFree(s.dist); cudaFree(s.gacc);
-    cudaFree(s.pacc); cudaFree(s.labels_prev);
-    cudaFree(s.C[0]); cudaFree(s.C[1]); cudaFree(s.cnorm); cudaFree(s.shift_k); cudaFree(s.empties);
-    cudaFree(s.st); cudaFree(s.cand_val); cudaFree(s.cand_row); cudaFree(s.sum_partials);
-    cudaFree(s.shift_log); cudaFree(s.changed_log); cudaFree(s.reloc_log); cudaFree(s.xstat);
+    km_free(s.amb_rows); km_free(s.amb_log);
+    km_free(s.X_owned); km_free(s.labels); km_free(s.dist); km_free(s.gacc);
+    km_free(s.pacc); km_free(s.labels_prev);
+    km_free(s.C[0]); km_free(s.C[1]); km_free(s.cnorm); km_free(s.shift_k); km_free(s.empties);
+    km_free(s.st); km_free(s.cand_val); km_free(s.cand_row); km_free(s.sum_partials);
+    km_free(s.shift_log); km_free(s.changed_log); km_free(s.reloc_log); km_free(s.xstat);
     if (s.host_pin) cudaFreeHost(s.host_pin);
     if (s.stream) cudaStreamDestroy(s.stream);
     s.dev = -1;
@@ -261,7 +269,7 @@ int Engine<T>::attach_device(int local, const T* dX, size_t rows, size_t cols, s
   if (d != 0 && d != (int)cols && local != 0) KM_FAIL(KM_EINVAL, "kmeans_attach_device: shards disagree on cols");
   Shard<T>& s = shards[local];
   DevGuard g(s.dev);
-  if (s.X_owned && s.X_owned != dX) { cudaFree(s.X_owned); s.X_owned = nullptr; }
+  if (s.X_owned && s.X_owned != dX) { km_free(s.X_owned); s.X_owned = nullptr; }
   s.X = dX;
   s.rows = rows;
   s.x_checked = false;
@@ -269,9 +277,9 @@ int Engine<T>::attach_device(int local, const T* dX, size_t rows, size_t cols, s
   d = (int)cols;
   n_total = ntot;
   if (s.labels_cap < rows) {
-    cudaFree(s.labels);
+    km_free(s.labels);
     s.labels = nullptr;
-    KM_CUDA(cudaMalloc(&s.labels, rows * sizeof(int)));
+    KM_CUDA(km_malloc(&s.labels, rows * sizeof(int)));
     s.labels_cap = rows;
   }
   KM_CUDA(cudaMemsetAsync(s.labels, 0xff, rows * sizeof(int), s.stream));
@@ -400,9 +408,9 @@ int Engine<T>::upload_host(const T* X, size_t rows, size_t cols, char order, boo
     size_t r = (off < rows) ? std::min(per, rows - off) : 0;
     if (r == 0) { upload_wait(); KM_FAIL(KM_EINVAL, "kmeans_upload_host: fewer rows than devices"); }
     DevGuard gd(s.dev);
-    cudaFree(s.X_owned);
+    km_free(s.X_owned);
     s.X_owned = nullptr;
-    if (cudaMalloc(&s.X_owned, r * cols * sizeof(T)) != cudaSuccess) {
+    if (km_malloc(&s.X_owned, r * cols * sizeof(T)) != cudaSuccess) {
       cudaGetLastError();
       upload_wait();
       KM_FAIL(KM_ENOMEM, "kmeans_upload_host: device allocation failed");
@@ -421,14 +429,14 @@ int Engine<T>::upload_host(const T* X, size_t rows, size_t cols, char order, boo
       // column-major host matrix (leading dimension = total rows): strided copy of the
       // shard's rows of every column, then a transpose on the device
       T* tmp = nullptr;
-      KM_CUDA(cudaMalloc(&tmp, r * cols * sizeof(T)));
+      KM_CUDA(km_malloc(&tmp, r * cols * sizeof(T)));
       KM_CUDA(cudaMemcpy2DAsync(tmp, r * sizeof(T), X + off, rows * sizeof(T), r * sizeof(T), cols,
                                 cudaMemcpyHostToDevice, s.stream));
       dim3 grid((unsigned)((r + 31) / 32), (unsigned)((cols + 31) / 32));
       transpose_cm_kernel<T><<<grid, dim3(32, 8), 0, s.stream>>>(tmp, s.X_owned, r, (int)cols);
       KM_CUDA(cudaGetLastError());
       KM_CUDA(cudaStreamSynchronize(s.stream));
-      cudaFree(tmp);
+      km_free(tmp);
     }
     KM_TRY(attach_device((int)i, s.X_owned, r, cols, rows));
     s.row0 = off;
@@ -466,21 +474,21 @@ int Engine<T>::preallocate(int k_, int max_iter) {
   for (auto& s : shards) {
     DevGuard g(s.dev);
     if (s.dist_cap < s.rows && world_size == 1) {
-      cudaFree(s.dist);
+      km_free(s.dist);
       s.dist = nullptr;
-      KM_CUDA(cudaMalloc(&s.dist, s.rows * sizeof(double)));
+      KM_CUDA(km_malloc(&s.dist, s.rows * sizeof(double)));
       s.dist_cap = s.rows;
     }
     if (s.labels_prev_cap < s.rows) {
-      cudaFree(s.labels_prev);
+      km_free(s.labels_prev);
       s.labels_prev = nullptr;
-      KM_CUDA(cudaMalloc(&s.labels_prev, s.rows * sizeof(int)));
+      KM_CUDA(km_malloc(&s.labels_prev, s.rows * sizeof(int)));
       s.labels_prev_cap = s.rows;
     }
     if (std::is_same<T, float>::value && s.amb_cap < s.rows) {
-      cudaFree(s.amb_rows);
+      km_free(s.amb_rows);
       s.amb_rows = nullptr;
-      KM_CUDA(cudaMalloc(&s.amb_rows, s.rows * sizeof(unsigned int)));
+      KM_CUDA(km_malloc(&s.amb_rows, s.rows * sizeof(unsigned int)));
       s.amb_cap = s.rows;
     }
   }
@@ -495,17 +503,17 @@ int Engine<T>::ensure_buffers(int k_) {
     if (!s.X) KM_FAIL(KM_ESTATE, "no data attached to the handle");
     DevGuard g(s.dev);
     if (s.k_cap != k_ || s.d_cap != d) {
-      cudaFree(s.gacc); cudaFree(s.pacc); s.pacc = nullptr; cudaFree(s.C[0]); cudaFree(s.C[1]); cudaFree(s.cnorm);
-      cudaFree(s.shift_k); cudaFree(s.empties);
+      km_free(s.gacc); km_free(s.pacc); s.pacc = nullptr; km_free(s.C[0]); km_free(s.C[1]); km_free(s.cnorm);
+      km_free(s.shift_k); km_free(s.empties);
       s.gacc = nullptr; s.C[0] = s.C[1] = nullptr; s.cnorm = nullptr; s.shift_k = nullptr; s.empties = nullptr;
       size_t kd = (size_t)k_ * d;
-      KM_CUDA(cudaMalloc(&s.gacc, ((size_t)(NP / 2) * kd + k_) * sizeof(long long)));
-      KM_CUDA(cudaMalloc(&s.pacc, ((size_t)(NP / 2) * kd + k_) * sizeof(long long)));
-      KM_CUDA(cudaMalloc(&s.C[0], kd * sizeof(T)));
-      KM_CUDA(cudaMalloc(&s.C[1], kd * sizeof(T)));
-      KM_CUDA(cudaMalloc(&s.cnorm, k_ * sizeof(T)));
-      KM_CUDA(cudaMalloc(&s.shift_k, k_ * sizeof(double)));
-      KM_CUDA(cudaMalloc(&s.empties, k_ * sizeof(int)));
+      KM_CUDA(km_malloc(&s.gacc, ((size_t)(NP / 2) * kd + k_) * sizeof(long long)));
+      KM_CUDA(km_malloc(&s.pacc, ((size_t)(NP / 2) * kd + k_) * sizeof(long long)));
+      KM_CUDA(km_malloc(&s.C[0], kd * sizeof(T)));
+      KM_CUDA(km_malloc(&s.C[1], kd * sizeof(T)));
+      KM_CUDA(km_malloc(&s.cnorm, k_ * sizeof(T)));
+      KM_CUDA(km_malloc(&s.shift_k, k_ * sizeof(double)));
+      KM_CUDA(km_malloc(&s.empties, k_ * sizeof(int)));
       s.k_cap = k_;
       s.d_cap = d;
     }
@@ -794,9 +802,9 @@ int Engine<T>::tc_refresh(Shard<T>& s) {
       KM_FAIL(KM_EINVAL, "data magnitude outside the range of the tensor-core kernel");
     if (s.rows > 0xffffffffULL) KM_FAIL(KM_EINVAL, "shard too large for the tensor-core kernel");
     if (s.amb_cap < s.rows) {
-      cudaFree(s.amb_rows);
+      km_free(s.amb_rows);
       s.amb_rows = nullptr;
-      KM_CUDA(cudaMalloc(&s.amb_rows, s.rows * sizeof(unsigned int)));
+      KM_CUDA(km_malloc(&s.amb_rows, s.rows * sizeof(unsigned int)));
       s.amb_cap = s.rows;
     }
     if (tc::shape_ok(k, d)) {

@@ -122,26 +122,53 @@ prepare_kernel(const unsigned long long* __restrict__ gcounts, int k, IterState*
 }
 
 // ---- squared distance of every row to its assigned (old) centre ---------------
-// Direct differences in double.  Runs only when the M-step found empty clusters.
-template <typename T>
+// Direct differences in double.  Runs only when the M-step found empty clusters (and for
+// inertia).  A row is shared by lpr lanes (a power of two, at most 32) that load V elements
+// each; a warp works on 32 / lpr rows at a time and on four such sets per loop trip, so
+// that enough loads are in flight to stream X at HBM speed.
+template <typename T, int V>
 __global__ void __launch_bounds__(256)
 rowdist_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict__ labels,
                const T* __restrict__ C_old, double* __restrict__ dist, const IterState* st,
                int force) {
   if (!force && st->n_empty == 0) return;
+  constexpr int U = 4;
   const int lane = threadIdx.x & 31;
   const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const size_t nwarp = ((size_t)gridDim.x * blockDim.x) >> 5;
-  for (size_t row = warp; row < n; row += nwarp) {
-    const T* x = X + row * (size_t)d;
-    const T* c = C_old + (size_t)labels[row] * d;
-    double s = 0;
-    for (int t = lane; t < d; t += 32) {
-      double q = (double)x[t] - (double)c[t];
-      s += q * q;
+  const int dv = d / V;
+  int lpr = 1;
+  while (lpr < dv && lpr < 32) lpr <<= 1;
+  const int gpw = 32 / lpr;
+  const int g = lane / lpr, l = lane % lpr;
+  const size_t stride = nwarp * gpw;
+  for (size_t base = warp * gpw; base < n; base += stride * U) {
+    double s[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      s[u] = 0;
+      const size_t row = base + g + (size_t)u * stride;
+      if (row < n) {
+        const T* x = X + row * (size_t)d;
+        const T* c = C_old + (size_t)labels[row] * d;
+        for (int idx = l; idx < dv; idx += lpr) {
+          T xv[V], cv[V];
+          VecLoad<T, V>::ld(x + (size_t)idx * V, xv);
+          VecLoad<T, V>::ld(c + (size_t)idx * V, cv);
+#pragma unroll
+          for (int e = 0; e < V; ++e) {
+            const double q = (double)xv[e] - (double)cv[e];
+            s[u] = fma(q, q, s[u]);
+          }
+        }
+      }
     }
-    s = warp_sum(s);
-    if (lane == 0) dist[row] = s;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      for (int o = lpr >> 1; o > 0; o >>= 1) s[u] += __shfl_xor_sync(0xffffffffu, s[u], o);
+      const size_t row = base + g + (size_t)u * stride;
+      if (l == 0 && row < n) dist[row] = s[u];
+    }
   }
 }
 

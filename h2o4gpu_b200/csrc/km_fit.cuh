@@ -8,9 +8,9 @@ namespace km {
 template <typename T>
 static int ensure_dist(Shard<T>& s) {
   if (s.dist_cap < s.rows) {
-    cudaFree(s.dist);
+    km_free(s.dist);
     s.dist = nullptr;
-    KM_CUDA(cudaMalloc(&s.dist, s.rows * sizeof(double)));
+    KM_CUDA(km_malloc(&s.dist, s.rows * sizeof(double)));
     s.dist_cap = s.rows;
   }
   return KM_OK;
@@ -19,12 +19,12 @@ static int ensure_dist(Shard<T>& s) {
 template <typename T>
 static int ensure_logs(Shard<T>& s, int n) {
   if (s.log_cap < n) {
-    cudaFree(s.shift_log); cudaFree(s.changed_log); cudaFree(s.reloc_log); cudaFree(s.amb_log);
+    km_free(s.shift_log); km_free(s.changed_log); km_free(s.reloc_log); km_free(s.amb_log);
     s.shift_log = nullptr; s.changed_log = nullptr; s.reloc_log = nullptr; s.amb_log = nullptr;
-    KM_CUDA(cudaMalloc(&s.amb_log, n * sizeof(unsigned int)));
-    KM_CUDA(cudaMalloc(&s.shift_log, n * sizeof(double)));
-    KM_CUDA(cudaMalloc(&s.changed_log, n * sizeof(unsigned long long)));
-    KM_CUDA(cudaMalloc(&s.reloc_log, n * sizeof(int)));
+    KM_CUDA(km_malloc(&s.amb_log, n * sizeof(unsigned int)));
+    KM_CUDA(km_malloc(&s.shift_log, n * sizeof(double)));
+    KM_CUDA(km_malloc(&s.changed_log, n * sizeof(unsigned long long)));
+    KM_CUDA(km_malloc(&s.reloc_log, n * sizeof(int)));
     s.log_cap = n;
   }
   return KM_OK;
@@ -77,9 +77,9 @@ int Engine<T>::relocate_multi(double scale) {
     Shard<T>& s = shards[i];
     DevGuard gd(s.dev);
     KM_TRY(ensure_dist(s));
-    KM_CUDA(cudaMalloc(&rec[i], rec_bytes));
-    KM_CUDA(cudaMalloc(&all[i], rec_bytes * world_size));
-    rowdist_kernel<T><<<s.num_sms * 8, 256, 0, s.stream>>>(s.X, s.rows, d, s.labels, s.C[cur], s.dist, s.st, 1);
+    KM_CUDA(km_malloc(&rec[i], rec_bytes));
+    KM_CUDA(km_malloc(&all[i], rec_bytes * world_size));
+    launch_rowdist(s, 1);
     KM_CUDA(cudaGetLastError());
     const T* Xp = s.X;
     size_t n = s.rows;
@@ -107,8 +107,8 @@ int Engine<T>::relocate_multi(double scale) {
     KM_CUDA(cudaGetLastError());
     ++launches;
     KM_CUDA(cudaStreamSynchronize(s.stream));
-    cudaFree(rec[i]);
-    cudaFree(all[i]);
+    km_free(rec[i]);
+    km_free(all[i]);
   }
   return KM_OK;
 }
@@ -158,9 +158,9 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
     KM_CUDA(cudaMemsetAsync(s.st, 0, sizeof(IterState), s.stream));
     KM_CUDA(cudaMemsetAsync(s.labels, 0xff, s.rows * sizeof(int), s.stream));
     if (delta && s.labels_prev_cap < s.rows) {
-      cudaFree(s.labels_prev);
+      km_free(s.labels_prev);
       s.labels_prev = nullptr;
-      KM_CUDA(cudaMalloc(&s.labels_prev, s.rows * sizeof(int)));
+      KM_CUDA(km_malloc(&s.labels_prev, s.rows * sizeof(int)));
       s.labels_prev_cap = s.rows;
     }
     if (use_tc) KM_TRY(tc_refresh(s));
@@ -221,7 +221,7 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
                                              reinterpret_cast<int*>(&s.host_pin[2]));
       ++launches;
       if (!multi) {
-        rowdist_kernel<T><<<s.num_sms * 8, 256, 0, s.stream>>>(s.X, s.rows, d, s.labels, s.C[cur], s.dist, s.st, 0);
+        launch_rowdist(s, 0);
         const T* Xp = s.X;
         size_t n = s.rows;
         int dd = d, kk = k;
@@ -371,7 +371,7 @@ int Engine<T>::inertia(double* out) {
   for (auto& s : shards) {
     DevGuard g(s.dev);
     KM_TRY(ensure_dist(s));
-    rowdist_kernel<T><<<s.num_sms * 8, 256, 0, s.stream>>>(s.X, s.rows, d, s.labels, s.C[cur], s.dist, s.st, 1);
+    launch_rowdist(s, 1);
     sum_partials_kernel<<<1024, 256, 0, s.stream>>>(s.dist, s.rows, s.sum_partials);
     sum_final_kernel<<<1, 32, 0, s.stream>>>(s.sum_partials, 1024, &s.st->inertia);
     KM_CUDA(cudaGetLastError());
@@ -411,7 +411,7 @@ int Engine<T>::transform_shard(int local, T* out_host, size_t ld) {
   batch = (batch + 127) / 128 * 128;
   batch = std::min(batch, (s.rows + 127) / 128 * 128);
   T* buf = nullptr;
-  KM_CUDA(cudaMalloc(&buf, batch * (size_t)k * sizeof(T)));
+  KM_CUDA(km_malloc(&buf, batch * (size_t)k * sizeof(T)));
   int rc = KM_OK;
   for (size_t r = 0; r < s.rows && rc == KM_OK; r += batch) {
     size_t nr = std::min(batch, s.rows - r);
@@ -422,7 +422,7 @@ int Engine<T>::transform_shard(int local, T* out_host, size_t ld) {
     if (ce == cudaSuccess) ce = cudaStreamSynchronize(s.stream);
     if (ce != cudaSuccess) { set_error(std::string("transform copy: ") + cudaGetErrorString(ce)); rc = KM_ECUDA; }
   }
-  cudaFree(buf);
+  km_free(buf);
   return rc;
 }
 

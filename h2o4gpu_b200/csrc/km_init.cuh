@@ -274,7 +274,7 @@ int init_centroids(Engine<T>& e, int k, int seed, int method, std::vector<T>* ou
   auto release = [&]() {
     for (size_t i = 0; i < e.shards.size(); ++i) {
       DevGuard g(e.shards[i].dev);
-      cudaFree(d_list[i]); cudaFree(d_count[i]); cudaFree(d_rows[i]);
+      km_free(d_list[i]); km_free(d_count[i]); km_free(d_rows[i]);
     }
   };
   int rc = KM_OK;
@@ -283,9 +283,9 @@ int init_centroids(Engine<T>& e, int k, int seed, int method, std::vector<T>* ou
     DevGuard g(s.dev);
     rc = ensure_dist(s);
     if (rc != KM_OK) break;
-    if (cudaMalloc(&d_list[i], (size_t)cap * sizeof(unsigned int)) != cudaSuccess ||
-        cudaMalloc(&d_count[i], sizeof(unsigned int)) != cudaSuccess ||
-        cudaMalloc(&d_rows[i], (size_t)cap * d * sizeof(T)) != cudaSuccess) {
+    if (km_malloc(&d_list[i], (size_t)cap * sizeof(unsigned int)) != cudaSuccess ||
+        km_malloc(&d_count[i], sizeof(unsigned int)) != cudaSuccess ||
+        km_malloc(&d_rows[i], (size_t)cap * d * sizeof(T)) != cudaSuccess) {
       set_error("initialisation: device allocation failed");
       rc = KM_ENOMEM;
       break;
@@ -402,13 +402,13 @@ int init_centroids(Engine<T>& e, int k, int seed, int method, std::vector<T>* ou
     for (auto& s : e.shards) {
       DevGuard g(s.dev);
       unsigned long long* dc = nullptr;
-      KM_CUDA(cudaMalloc(&dc, (size_t)m * sizeof(unsigned long long)));
+      KM_CUDA(km_malloc(&dc, (size_t)m * sizeof(unsigned long long)));
       cudaMemsetAsync(dc, 0, (size_t)m * sizeof(unsigned long long), s.stream);
       label_histogram_kernel<<<s.num_sms * 8, 256, 0, s.stream>>>(s.labels, s.rows, m, dc);
       cudaError_t ce = cudaMemcpyAsync(cnt.data(), dc, (size_t)m * sizeof(unsigned long long), cudaMemcpyDeviceToHost,
                                        s.stream);
       if (ce == cudaSuccess) ce = cudaStreamSynchronize(s.stream);
-      cudaFree(dc);
+      km_free(dc);
       if (ce != cudaSuccess) KM_FAIL(KM_ECUDA, "initialisation: candidate weights failed");
       for (int j = 0; j < m; ++j) w[j] += (double)cnt[j];
     }
@@ -419,12 +419,12 @@ int init_centroids(Engine<T>& e, int k, int seed, int method, std::vector<T>* ou
   int *d_state = nullptr, *d_chosen = nullptr;
   unsigned char* d_taken = nullptr;
   std::vector<int> chosen(k);
-  cudaError_t ce = cudaMalloc(&d_w, (size_t)m * sizeof(double));
-  if (ce == cudaSuccess) ce = cudaMalloc(&d_mind, (size_t)m * sizeof(double));
-  if (ce == cudaSuccess) ce = cudaMalloc(&d_wm, (size_t)m * sizeof(double));
-  if (ce == cudaSuccess) ce = cudaMalloc(&d_state, sizeof(int));
-  if (ce == cudaSuccess) ce = cudaMalloc(&d_chosen, (size_t)k * sizeof(int));
-  if (ce == cudaSuccess) ce = cudaMalloc(&d_taken, (size_t)m);
+  cudaError_t ce = km_malloc(&d_w, (size_t)m * sizeof(double));
+  if (ce == cudaSuccess) ce = km_malloc(&d_mind, (size_t)m * sizeof(double));
+  if (ce == cudaSuccess) ce = km_malloc(&d_wm, (size_t)m * sizeof(double));
+  if (ce == cudaSuccess) ce = km_malloc(&d_state, sizeof(int));
+  if (ce == cudaSuccess) ce = km_malloc(&d_chosen, (size_t)k * sizeof(int));
+  if (ce == cudaSuccess) ce = km_malloc(&d_taken, (size_t)m);
   if (ce == cudaSuccess) {
     cudaMemcpyAsync(d_w, w.data(), (size_t)m * sizeof(double), cudaMemcpyHostToDevice, s0.stream);
     cudaMemcpyAsync(d_wm, w.data(), (size_t)m * sizeof(double), cudaMemcpyHostToDevice, s0.stream);
@@ -441,7 +441,7 @@ int init_centroids(Engine<T>& e, int k, int seed, int method, std::vector<T>* ou
       ce = cudaMemcpyAsync(chosen.data(), d_chosen, (size_t)k * sizeof(int), cudaMemcpyDeviceToHost, s0.stream);
     if (ce == cudaSuccess) ce = cudaStreamSynchronize(s0.stream);
   }
-  cudaFree(d_w); cudaFree(d_mind); cudaFree(d_wm); cudaFree(d_state); cudaFree(d_chosen); cudaFree(d_taken);
+  km_free(d_w); km_free(d_mind); km_free(d_wm); km_free(d_state); km_free(d_chosen); km_free(d_taken);
   if (ce != cudaSuccess) KM_FAIL(KM_ECUDA, std::string("initialisation: k-means++ stage: ") + cudaGetErrorString(ce));
   e.launches += 2 * k;
   out->resize((size_t)k * d);

@@ -57,7 +57,7 @@ struct Plan {
   bool ready = false;
 
   void release() {
-    cudaFree(bhi); cudaFree(blo); cudaFree(cn); cudaFree(xnorm);
+    km_free(bhi); km_free(blo); km_free(cn); km_free(xnorm);
     bhi = blo = nullptr;
     cn = xnorm = nullptr;
     xnorm_cap = 0;
@@ -86,9 +86,9 @@ inline bool shape_ok(int k, int d) { return (d == 32 || d == 64) && k > 16 && k 
 inline int ensure_xnorm(Plan& pl, const float* X, size_t rows, int d, int num_sms, cudaStream_t stream) {
   if (pl.xnorm_of != X || pl.xnorm_rows != rows) {
     if (pl.xnorm_cap < rows) {
-      cudaFree(pl.xnorm);
+      km_free(pl.xnorm);
       pl.xnorm = nullptr;
-      KM_CUDA(cudaMalloc(&pl.xnorm, rows * sizeof(float)));
+      KM_CUDA(km_malloc(&pl.xnorm, rows * sizeof(float)));
       pl.xnorm_cap = rows;
     }
     rownorm_kernel<<<num_sms * 8, 256, 0, stream>>>(X, rows, d, pl.xnorm);
@@ -104,12 +104,12 @@ inline int setup(Plan& pl, const float* X, size_t rows, int k, int d, int num_sm
   KM_TRY(ensure_xnorm(pl, X, rows, d, num_sms, stream));
   if (pl.ready && pl.k == k && pl.d == d && pl.x_base == X && pl.x_rows == rows) return KM_OK;
   if (!(pl.bhi && pl.k == k && pl.d == d)) {
-    cudaFree(pl.bhi); cudaFree(pl.blo); cudaFree(pl.cn);
+    km_free(pl.bhi); km_free(pl.blo); km_free(pl.cn);
     pl.bhi = pl.blo = nullptr;
     pl.cn = nullptr;
-    KM_CUDA(cudaMalloc(&pl.bhi, (size_t)npad * 64 * sizeof(__half)));
-    KM_CUDA(cudaMalloc(&pl.blo, (size_t)npad * 64 * sizeof(__half)));
-    KM_CUDA(cudaMalloc(&pl.cn, (size_t)(npad + 1) * sizeof(float)));
+    KM_CUDA(km_malloc(&pl.bhi, (size_t)npad * 64 * sizeof(__half)));
+    KM_CUDA(km_malloc(&pl.blo, (size_t)npad * 64 * sizeof(__half)));
+    KM_CUDA(km_malloc(&pl.cn, (size_t)(npad + 1) * sizeof(float)));
   }
   pl.npad = npad; pl.k = k; pl.d = d; pl.x_base = X; pl.x_rows = rows;
   KM_TRY(make_map(&pl.tmX, X, rows, d, kBM, 4));
@@ -174,7 +174,7 @@ struct BigPlan {
   CUtensorMap tmX, tmBhi, tmBlo;
   bool ready = false;
   void release() {
-    cudaFree(bhi); cudaFree(blo); cudaFree(cn);
+    km_free(bhi); km_free(blo); km_free(cn);
     bhi = blo = nullptr;
     cn = nullptr;
     ready = false;
@@ -199,9 +199,9 @@ inline int big_setup(BigPlan& pl, const float* X, size_t rows, int k, int d) {
   if (pl.ready && pl.k == k && pl.d == d && pl.x_base == X && pl.x_rows == rows) return KM_OK;
   if (!(pl.bhi && pl.k == k && pl.d == d)) {
     pl.release();
-    KM_CUDA(cudaMalloc(&pl.bhi, (size_t)kpad * dp * sizeof(__half)));
-    KM_CUDA(cudaMalloc(&pl.blo, (size_t)kpad * dp * sizeof(__half)));
-    KM_CUDA(cudaMalloc(&pl.cn, (size_t)(kpad + 1) * sizeof(float)));
+    KM_CUDA(km_malloc(&pl.bhi, (size_t)kpad * dp * sizeof(__half)));
+    KM_CUDA(km_malloc(&pl.blo, (size_t)kpad * dp * sizeof(__half)));
+    KM_CUDA(km_malloc(&pl.cn, (size_t)(kpad + 1) * sizeof(float)));
   }
   pl.kpad = kpad; pl.k = k; pl.d = d; pl.dp = dp; pl.x_base = X; pl.x_rows = rows;
   KM_TRY(tc::make_map(&pl.tmX, X, rows, d, kBM, 4));

@@ -41,6 +41,8 @@ struct km_engine {
 };
 
 using km::set_error;
+using km::km_malloc;
+using km::km_free;
 
 namespace {
 
@@ -266,16 +268,16 @@ int synth_impl(int gpu_id, T* dX, size_t rows, size_t cols, size_t row0, int kin
       cdf[i] = (float)run;
     }
     cdf[n_comp - 1] = 1.0f;
-    KM_CUDA(cudaMalloc(&dc, (size_t)n_comp * cols * sizeof(T)));
-    KM_CUDA(cudaMalloc(&dcdf, n_comp * sizeof(float)));
+    KM_CUDA(km_malloc(&dc, (size_t)n_comp * cols * sizeof(T)));
+    KM_CUDA(km_malloc(&dcdf, n_comp * sizeof(float)));
     KM_CUDA(cudaMemcpy(dc, centers_host, (size_t)n_comp * cols * sizeof(T), cudaMemcpyHostToDevice));
     KM_CUDA(cudaMemcpy(dcdf, cdf.data(), n_comp * sizeof(float), cudaMemcpyHostToDevice));
   }
   km::synth_kernel<T><<<148 * 16, 256>>>(dX, rows, (int)cols, row0, kind, dc, n_comp, dcdf, sigma, seed);
   cudaError_t ce = cudaGetLastError();
   if (ce == cudaSuccess) ce = cudaDeviceSynchronize();
-  cudaFree(dc);
-  cudaFree(dcdf);
+  km_free(dc);
+  km_free(dcdf);
   if (ce != cudaSuccess) KM_FAIL(KM_ECUDA, std::string("synth: ") + cudaGetErrorString(ce));
   return KM_OK;
 }
@@ -348,6 +350,10 @@ static int get_stats(km::Engine<T>* e, kmeans_stats* out, int want_inertia) {
 extern "C" {
 
 const char* kmeans_last_error(void) { return km::g_err.c_str(); }
+int kmeans_trim_memory(void) {
+  km::km_trim_pools();
+  return KM_OK;
+}
 int kmeans_last_fit_info(int* iterations, double* inertia) {
   if (iterations) *iterations = km::g_last_iterations;
   if (inertia) *inertia = km::g_last_inertia;

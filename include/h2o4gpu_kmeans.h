@@ -41,6 +41,12 @@ const char* kmeans_last_error(void);
  * squared distances of the rows to their centres (sklearn's inertia_, which the reference's
  * wrapper leaves None, src/interface_py/h2o4gpu/solvers/kmeans.py:187). */
 int kmeans_last_fit_info(int* iterations, double* inertia);
+/* Device buffers come from one memory pool per device that keeps freed memory for the next
+ * call (the reference allocates and frees per call through thrust::device_vector,
+ * src/gpu/kmeans/kmeans_h2o4gpu.cu:672-683, 795-812).  This returns everything the pools hold
+ * and no live handle uses to the driver.  H2O4GPU_KM_POOL=0 in the environment turns the
+ * pools off. */
+int kmeans_trim_memory(void);
 
 /* ---- 1. the reference's entry points ------------------------------------ */
 

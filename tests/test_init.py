@@ -76,6 +76,21 @@ def test_kmeans_parallel_matches_oracle(eng, cfg, kw, k, dtype, seed):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("n,d,k", [(5, 3, 5), (40, 2, 1), (300, 9, 7), (64, 4, 60)])
+def test_kmeans_parallel_edge_shapes(eng, n, d, k):
+    """k = 1, k = rows, fewer candidates than clusters: always k distinct rows of X, same as the oracle."""
+    rng = np.random.default_rng(n)
+    X = rng.standard_normal((n, d)).astype(np.float32)
+    want_C, want_rows, _ = kp.kmeans_parallel(X, k, 9)
+    h = eng.ResidentKMeans()
+    h.upload(X)
+    C, rows = h.init_centroids(k, seed=9, return_rows=True)
+    h.close()
+    assert len(set(rows.tolist())) == k and np.array_equal(C, X[rows])
+    assert np.array_equal(rows, want_rows)
+
+
+@pytest.mark.gpu
 def test_init_random_rows_matches_host_shuffle(eng, built_lib):
     from h2o4gpu_b200 import synth
     X, _, _ = synth.c1(n=5000)
