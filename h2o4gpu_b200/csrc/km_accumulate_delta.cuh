@@ -103,7 +103,7 @@ delta_accumulate_kernel(const T* __restrict__ X, size_t n, int d, const int* __r
 // int32 shared accumulators first (same layout and arithmetic as accumulate_kernel) and
 // sends each non-zero total to the global sums once.  Subtracting a row is adding its
 // negation: rint is odd, so the pieces of -x are minus the pieces of x.
-constexpr int kDeltaThreads = 1024;
+constexpr int kDeltaThreads = 512;    // two CTAs per SM: room for the registers of a prefetched step
 constexpr int kDeltaChunk = 32768;   // rows between two drains: the int32 accumulators hold 2^15 rows of 2^15-sized pieces
 
 template <typename T>
@@ -112,7 +112,7 @@ inline size_t delta_smem_bytes(int k, int d) {
 }
 
 template <typename T, int V>
-__global__ void __launch_bounds__(kDeltaThreads, 1)
+__global__ void __launch_bounds__(kDeltaThreads, 2)
 delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict__ labels,
                              int* __restrict__ prev, int k, long long* __restrict__ psums,
                              unsigned long long* __restrict__ pcounts, T scale,
@@ -151,24 +151,38 @@ delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int
     // a warp takes 256 rows per step, eight per lane, all label loads in flight together
     // (c0 is a multiple of 32 rows, so the 16-byte loads are aligned); between two drains the
     // warps run free of one another
+    auto load_step = [&](size_t wb, int (&nw)[8], int (&od)[8]) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const size_t r4 = wb + h * 128 + lane * 4;
+        if (r4 + 3 < c1) {
+          const int4 a = *reinterpret_cast<const int4*>(labels + r4);
+          const int4 b = *reinterpret_cast<const int4*>(prev + r4);
+          nw[4 * h + 0] = a.x; nw[4 * h + 1] = a.y; nw[4 * h + 2] = a.z; nw[4 * h + 3] = a.w;
+          od[4 * h + 0] = b.x; od[4 * h + 1] = b.y; od[4 * h + 2] = b.z; od[4 * h + 3] = b.w;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const bool in = r4 + j < c1;
+            nw[4 * h + j] = in ? labels[r4 + j] : -1;
+            od[4 * h + j] = in ? prev[r4 + j] : -1;
+          }
+        }
+      }
+    };
+    int nwn[8], odn[8];
+    {
+      const size_t wb0 = c0 + (size_t)warp * 256;
+      if (wb0 < c1) load_step(wb0, nwn, odn);
+    }
     for (size_t wb = c0 + (size_t)warp * 256; wb < c1; wb += (size_t)NWARP * 256) {
     int nw[8], od[8];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const size_t r4 = wb + h * 128 + lane * 4;
-      if (r4 + 3 < c1) {
-        const int4 a = *reinterpret_cast<const int4*>(labels + r4);
-        const int4 b = *reinterpret_cast<const int4*>(prev + r4);
-        nw[4 * h + 0] = a.x; nw[4 * h + 1] = a.y; nw[4 * h + 2] = a.z; nw[4 * h + 3] = a.w;
-        od[4 * h + 0] = b.x; od[4 * h + 1] = b.y; od[4 * h + 2] = b.z; od[4 * h + 3] = b.w;
-      } else {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const bool in = r4 + j < c1;
-          nw[4 * h + j] = in ? labels[r4 + j] : -1;
-          od[4 * h + j] = in ? prev[r4 + j] : -1;
-        }
-      }
+    for (int j = 0; j < 8; ++j) { nw[j] = nwn[j]; od[j] = odn[j]; }
+    {
+      // the next step's labels are requested before this step's rows are worked on
+      const size_t wbn = wb + (size_t)NWARP * 256;
+      if (wbn < c1) load_step(wbn, nwn, odn);
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {

@@ -207,7 +207,7 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 // loading a float4 each, four sets of rows per loop trip.
 __global__ void __launch_bounds__(256)
 rownorm_kernel(const float* __restrict__ X, size_t n, int d, float* __restrict__ xn) {
-  constexpr int U = 4;
+  constexpr int U = 8;
   const int lane = threadIdx.x & 31;
   const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const size_t nwarp = ((size_t)gridDim.x * blockDim.x) >> 5;
@@ -217,24 +217,37 @@ rownorm_kernel(const float* __restrict__ X, size_t n, int d, float* __restrict__
   const int gpw = 32 / lpr;
   const int g = lane / lpr, l = lane % lpr;
   const size_t stride = nwarp * gpw;
-  for (size_t base = warp * gpw; base < n; base += stride * U) {
+  for (size_t base = warp * gpw * U; base < n; base += stride * U) {
     float s[U];
+    if (dv <= 32) {
+      // one float4 per lane and row: all of them requested before any arithmetic
+      float4 v[U];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      s[u] = 0.f;
-      const size_t row = base + g + (size_t)u * stride;
-      if (row < n) {
-        const float4* x = reinterpret_cast<const float4*>(X + row * (size_t)d);
-        for (int idx = l; idx < dv; idx += lpr) {
-          const float4 v = x[idx];
-          s[u] = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, s[u]))));
+      for (int u = 0; u < U; ++u) {
+        const size_t row = base + (size_t)u * gpw + g;
+        v[u] = (row < n && l < dv) ? reinterpret_cast<const float4*>(X + row * (size_t)d)[l] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        s[u] = fmaf(v[u].x, v[u].x, fmaf(v[u].y, v[u].y, fmaf(v[u].z, v[u].z, v[u].w * v[u].w)));
+    } else {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        s[u] = 0.f;
+        const size_t row = base + (size_t)u * gpw + g;
+        if (row < n) {
+          const float4* x = reinterpret_cast<const float4*>(X + row * (size_t)d);
+          for (int idx = l; idx < dv; idx += lpr) {
+            const float4 v = x[idx];
+            s[u] = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, s[u]))));
+          }
         }
       }
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       for (int o = lpr >> 1; o > 0; o >>= 1) s[u] += __shfl_xor_sync(0xffffffffu, s[u], o);
-      const size_t row = base + g + (size_t)u * stride;
+      const size_t row = base + (size_t)u * gpw + g;
       if (l == 0 && row < n) xn[row] = s[u];
     }
   }

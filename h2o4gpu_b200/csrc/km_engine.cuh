@@ -77,6 +77,7 @@ struct Shard {
   int* labels_prev = nullptr; // labelling pacc corresponds to
   size_t labels_prev_cap = 0;
   T* C[2] = {nullptr, nullptr};
+  double* Cd[2] = {nullptr, nullptr};  // the same tables in double (float shards; the row-distance kernel reads them)
   T* cnorm = nullptr;
   double* shift_k = nullptr;
   int* empties = nullptr;
@@ -162,10 +163,11 @@ struct Engine : EngineBase {
   // exact squared distance of every row to its labelled centroid into s.dist
   void launch_rowdist(Shard<T>& s, int force) {
     constexpr int V = VecOf<T>::N;
+    const double* cd = std::is_same<T, double>::value ? reinterpret_cast<const double*>(s.C[cur]) : s.Cd[cur];
     if (vec_ok(s))
-      rowdist_kernel<T, V><<<s.num_sms * 8, 256, 0, s.stream>>>(s.X, s.rows, d, s.labels, s.C[cur], s.dist, s.st, force);
+      rowdist_kernel<T, V><<<s.num_sms * 8, 256, 0, s.stream>>>(s.X, s.rows, d, s.labels, cd, s.dist, s.st, force);
     else
-      rowdist_kernel<T, 1><<<s.num_sms * 8, 256, 0, s.stream>>>(s.X, s.rows, d, s.labels, s.C[cur], s.dist, s.st, force);
+      rowdist_kernel<T, 1><<<s.num_sms * 8, 256, 0, s.stream>>>(s.X, s.rows, d, s.labels, cd, s.dist, s.st, force);
   }
   int allreduce_from(bool from_pure);
   bool smallk_ok(bool update) const;
@@ -252,7 +254,7 @@ void Engine<T>::destroy() {
     km_free(s.amb_rows); km_free(s.amb_log);
     km_free(s.X_owned); km_free(s.labels); km_free(s.dist); km_free(s.gacc);
     km_free(s.pacc); km_free(s.labels_prev);
-    km_free(s.C[0]); km_free(s.C[1]); km_free(s.cnorm); km_free(s.shift_k); km_free(s.empties);
+    km_free(s.C[0]); km_free(s.C[1]); km_free(s.Cd[0]); km_free(s.Cd[1]); km_free(s.cnorm); km_free(s.shift_k); km_free(s.empties);
     km_free(s.st); km_free(s.cand_val); km_free(s.cand_row); km_free(s.sum_partials);
     km_free(s.shift_log); km_free(s.changed_log); km_free(s.reloc_log); km_free(s.xstat);
     if (s.host_pin) cudaFreeHost(s.host_pin);
@@ -504,6 +506,7 @@ int Engine<T>::ensure_buffers(int k_) {
     DevGuard g(s.dev);
     if (s.k_cap != k_ || s.d_cap != d) {
       km_free(s.gacc); km_free(s.pacc); s.pacc = nullptr; km_free(s.C[0]); km_free(s.C[1]); km_free(s.cnorm);
+      km_free(s.Cd[0]); km_free(s.Cd[1]); s.Cd[0] = s.Cd[1] = nullptr;
       km_free(s.shift_k); km_free(s.empties);
       s.gacc = nullptr; s.C[0] = s.C[1] = nullptr; s.cnorm = nullptr; s.shift_k = nullptr; s.empties = nullptr;
       size_t kd = (size_t)k_ * d;
@@ -511,6 +514,10 @@ int Engine<T>::ensure_buffers(int k_) {
       KM_CUDA(km_malloc(&s.pacc, ((size_t)(NP / 2) * kd + k_) * sizeof(long long)));
       KM_CUDA(km_malloc(&s.C[0], kd * sizeof(T)));
       KM_CUDA(km_malloc(&s.C[1], kd * sizeof(T)));
+      if (!std::is_same<T, double>::value) {
+        KM_CUDA(km_malloc(&s.Cd[0], kd * sizeof(double)));
+        KM_CUDA(km_malloc(&s.Cd[1], kd * sizeof(double)));
+      }
       KM_CUDA(km_malloc(&s.cnorm, k_ * sizeof(T)));
       KM_CUDA(km_malloc(&s.shift_k, k_ * sizeof(double)));
       KM_CUDA(km_malloc(&s.empties, k_ * sizeof(int)));
@@ -581,7 +588,7 @@ int Engine<T>::set_centroids(int k_, const T* host_c) {
   for (auto& s : shards) {
     DevGuard g(s.dev);
     KM_CUDA(cudaMemcpyAsync(s.C[0], host_c, (size_t)k * d * sizeof(T), cudaMemcpyHostToDevice, s.stream));
-    cnorm_kernel<T><<<k, 128, 0, s.stream>>>(s.C[0], k, d, s.cnorm);
+    cnorm_kernel<T><<<k, 128, 0, s.stream>>>(s.C[0], k, d, s.cnorm, s.Cd[0]);
     KM_CUDA(cudaGetLastError());
     ++launches;
     // host_c may be freed by the caller right after this returns
@@ -876,16 +883,16 @@ int Engine<T>::launch_delta(Shard<T>& s, T scale, const unsigned long long* gate
   unsigned long long* pc = reinterpret_cast<unsigned long long*>(ps + (size_t)(NP / 2) * k * d);
   const size_t smem = delta_smem_bytes<T>(k, d);
   if (smem <= 200 * 1024) {
-    // centroid table small enough for shared accumulators: one CTA per SM nets its rows' moves
+    // centroid table small enough for shared accumulators: one or two CTAs per SM net their rows' moves
     if (vec_ok(s)) {
       KM_CUDA(cudaFuncSetAttribute(delta_accumulate_smem_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)smem));
-      delta_accumulate_smem_kernel<T, V><<<s.num_sms, kDeltaThreads, smem, s.stream>>>(
+      delta_accumulate_smem_kernel<T, V><<<s.num_sms * (smem <= 100 * 1024 ? 2 : 1), kDeltaThreads, smem, s.stream>>>(
           s.X, s.rows, d, s.labels, s.labels_prev, k, ps, pc, scale, gate, limit);
     } else {
       KM_CUDA(cudaFuncSetAttribute(delta_accumulate_smem_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)smem));
-      delta_accumulate_smem_kernel<T, 1><<<s.num_sms, kDeltaThreads, smem, s.stream>>>(
+      delta_accumulate_smem_kernel<T, 1><<<s.num_sms * (smem <= 100 * 1024 ? 2 : 1), kDeltaThreads, smem, s.stream>>>(
           s.X, s.rows, d, s.labels, s.labels_prev, k, ps, pc, scale, gate, limit);
     }
     KM_CUDA(cudaGetLastError());

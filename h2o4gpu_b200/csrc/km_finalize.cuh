@@ -61,12 +61,13 @@ absmax_kernel(const T* __restrict__ X, size_t count, double* __restrict__ out_ma
 // ---- |c|^2 of a centroid table -------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(128)
-cnorm_kernel(const T* __restrict__ C, int k, int d, T* __restrict__ cnorm) {
+cnorm_kernel(const T* __restrict__ C, int k, int d, T* __restrict__ cnorm, double* __restrict__ C_double = nullptr) {
   __shared__ double red[4];
   int j = blockIdx.x;
   double s = 0;
   for (int t = threadIdx.x; t < d; t += blockDim.x) {
     double v = (double)C[(size_t)j * d + t];
+    if (C_double) C_double[(size_t)j * d + t] = v;
     s += v * v;
   }
   s = warp_sum(s);
@@ -124,15 +125,28 @@ prepare_kernel(const unsigned long long* __restrict__ gcounts, int k, IterState*
 // ---- squared distance of every row to its assigned (old) centre ---------------
 // Direct differences in double.  Runs only when the M-step found empty clusters (and for
 // inertia).  A row is shared by lpr lanes (a power of two, at most 32) that load V elements
-// each; a warp works on 32 / lpr rows at a time and on four such sets per loop trip, so
-// that enough loads are in flight to stream X at HBM speed.
+// each; a warp works on 32 / lpr rows at a time and on eight adjacent such sets per loop trip
+// (4 KB of contiguous rows for d = 64), so that enough loads are in flight to stream X at
+// HBM speed.
+// The centroid table arrives in double (kept beside the T table by the kernels that write
+// centroids) and x is widened with integer operations: float -> double conversions run at a
+// small fraction of the FMA rate and were the limit of this kernel.
+__device__ __forceinline__ double widen_exact(double x) { return x; }
+__device__ __forceinline__ double widen_exact(float x) {
+  // normal numbers exactly; zero and denormals (below 1.2e-38) become zero; the data has
+  // been checked for Inf / NaN
+  const unsigned int u = __float_as_uint(x);
+  const unsigned int hi = (u & 0x80000000u) | (((u & 0x7fffffffu) >> 3) + 0x38000000u);
+  return (u & 0x7f800000u) ? __hiloint2double((int)hi, (int)(u << 29)) : 0.0;
+}
+
 template <typename T, int V>
 __global__ void __launch_bounds__(256)
 rowdist_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict__ labels,
-               const T* __restrict__ C_old, double* __restrict__ dist, const IterState* st,
+               const double* __restrict__ C_old, double* __restrict__ dist, const IterState* st,
                int force) {
   if (!force && st->n_empty == 0) return;
-  constexpr int U = 4;
+  constexpr int U = 8;
   const int lane = threadIdx.x & 31;
   const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const size_t nwarp = ((size_t)gridDim.x * blockDim.x) >> 5;
@@ -142,22 +156,60 @@ rowdist_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict__
   const int gpw = 32 / lpr;
   const int g = lane / lpr, l = lane % lpr;
   const size_t stride = nwarp * gpw;
-  for (size_t base = warp * gpw; base < n; base += stride * U) {
+  if (dv <= 32) {
+    // one vector per lane and row: labels, then rows, are all requested before any arithmetic
+    for (size_t base = warp * gpw * U; base < n; base += stride * U) {
+      int lab[U];
+      T xv[U][V];
+      double s[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const size_t row = base + (size_t)u * gpw + g;
+        lab[u] = (row < n) ? labels[row] : 0;
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const size_t row = base + (size_t)u * gpw + g;
+        if (row < n && l < dv) {
+          VecLoadStream<T, V>::ld(X + row * (size_t)d + (size_t)l * V, xv[u]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < V; ++e) xv[u][e] = (T)0;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const size_t row = base + (size_t)u * gpw + g;
+        s[u] = 0;
+        if (row < n && l < dv) {
+          const double* c = C_old + (size_t)lab[u] * d + (size_t)l * V;
+#pragma unroll
+          for (int e = 0; e < V; ++e) {
+            const double q = widen_exact(xv[u][e]) - c[e];
+            s[u] = fma(q, q, s[u]);
+          }
+        }
+        for (int o = lpr >> 1; o > 0; o >>= 1) s[u] += __shfl_xor_sync(0xffffffffu, s[u], o);
+        if (l == 0 && row < n) dist[row] = s[u];
+      }
+    }
+    return;
+  }
+  for (size_t base = warp * gpw * U; base < n; base += stride * U) {
     double s[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       s[u] = 0;
-      const size_t row = base + g + (size_t)u * stride;
+      const size_t row = base + (size_t)u * gpw + g;
       if (row < n) {
         const T* x = X + row * (size_t)d;
-        const T* c = C_old + (size_t)labels[row] * d;
+        const double* c = C_old + (size_t)labels[row] * d;
         for (int idx = l; idx < dv; idx += lpr) {
-          T xv[V], cv[V];
-          VecLoad<T, V>::ld(x + (size_t)idx * V, xv);
-          VecLoad<T, V>::ld(c + (size_t)idx * V, cv);
+          T xv[V];
+          VecLoadStream<T, V>::ld(x + (size_t)idx * V, xv);
 #pragma unroll
           for (int e = 0; e < V; ++e) {
-            const double q = (double)xv[e] - (double)cv[e];
+            const double q = widen_exact(xv[e]) - c[(size_t)idx * V + e];
             s[u] = fma(q, q, s[u]);
           }
         }
@@ -166,7 +218,7 @@ rowdist_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict__
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       for (int o = lpr >> 1; o > 0; o >>= 1) s[u] += __shfl_xor_sync(0xffffffffu, s[u], o);
-      const size_t row = base + g + (size_t)u * stride;
+      const size_t row = base + (size_t)u * gpw + g;
       if (l == 0 && row < n) dist[row] = s[u];
     }
   }
@@ -187,12 +239,15 @@ sum_partials_kernel(const double* __restrict__ v, size_t n, double* __restrict__
     partials[blockIdx.x] = t;
   }
 }
+// One warp: lane l adds partials [l * per, (l + 1) * per) in order, then a butterfly over the lanes.
 __global__ void sum_final_kernel(const double* __restrict__ partials, int m, double* out) {
-  if (threadIdx.x == 0 && blockIdx.x == 0) {
-    double t = 0;
-    for (int i = 0; i < m; ++i) t += partials[i];
-    *out = t;
-  }
+  if (blockIdx.x != 0 || threadIdx.x >= 32) return;
+  const int per = (m + 31) / 32;
+  const int b = threadIdx.x * per, e = min(m, b + per);
+  double t = 0;
+  for (int i = b; i < e; ++i) t += partials[i];
+  t = warp_sum(t);
+  if (threadIdx.x == 0) *out = t;
 }
 
 // ---- relocation of empty clusters (cooperative launch, single shard) ----------
@@ -300,7 +355,8 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 average_kernel(const long long* __restrict__ gsums, const unsigned long long* __restrict__ gcounts,
                int k, int d, double inv, const T* __restrict__ C_old, T* __restrict__ C_new,
-               T* __restrict__ cnorm, double* __restrict__ shift_k, const IterState* st) {
+               T* __restrict__ cnorm, double* __restrict__ shift_k, const IterState* st,
+               double* __restrict__ C_new_double) {
   constexpr int NP = Fixed<T>::NP;
   __shared__ double red_n[4], red_s[4];
   const int j = blockIdx.x;
@@ -322,6 +378,7 @@ average_kernel(const long long* __restrict__ gsums, const unsigned long long* __
     T v = (T)(fixed_to_double<NP>(g, inv) * a);
     C_new[(size_t)j * d + t] = v;
     double dv = (double)v;
+    if (C_new_double) C_new_double[(size_t)j * d + t] = dv;
     double df = dv - (double)C_old[(size_t)j * d + t];
     sn += dv * dv;
     ss += df * df;

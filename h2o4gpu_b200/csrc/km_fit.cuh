@@ -247,7 +247,7 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
       Shard<T>& s = shards[i];
       DevGuard g(s.dev);
       average_kernel<T><<<k, 128, 0, s.stream>>>(s.sums(), s.counts(k, d), k, d, inv, s.C[cur], s.C[cur ^ 1], s.cnorm,
-                                               s.shift_k, s.st);
+                                               s.shift_k, s.st, s.Cd[cur ^ 1]);
       iter_close_kernel<<<1, 256, 0, s.stream>>>(s.shift_k, k, s.st, s.shift_log, s.changed_log, s.reloc_log,
                                                  s.amb_log, it,
                                                  &s.host_pin[0], reinterpret_cast<unsigned long long*>(&s.host_pin[1]));

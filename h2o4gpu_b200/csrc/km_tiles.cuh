@@ -39,6 +39,24 @@ template <> struct VecLoad<double, 2> {
 template <typename T> struct VecLoad<T, 1> {
   __device__ static void ld(const T* p, T (&v)[1]) { v[0] = *p; }
 };
+// The same loads marked streaming (evict first): for one-pass reads of X beside a small table
+// that should stay in L1.
+template <typename T, int N> struct VecLoadStream;
+template <> struct VecLoadStream<float, 4> {
+  __device__ static void ld(const float* p, float (&v)[4]) {
+    float4 t = __ldcs(reinterpret_cast<const float4*>(p));
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  }
+};
+template <> struct VecLoadStream<double, 2> {
+  __device__ static void ld(const double* p, double (&v)[2]) {
+    double2 t = __ldcs(reinterpret_cast<const double2*>(p));
+    v[0] = t.x; v[1] = t.y;
+  }
+};
+template <typename T> struct VecLoadStream<T, 1> {
+  __device__ static void ld(const T* p, T (&v)[1]) { v[0] = __ldcs(p); }
+};
 
 // BM x BN output tile per CTA, BK columns of d per stage, TM x TN per thread.
 // VEC: elements per global load (needs d % VEC == 0 and 16-byte aligned rows).

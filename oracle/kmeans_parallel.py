@@ -91,7 +91,8 @@ def row_cost(X, C):
 
 def tree_sum(v):
     """Sum in the order of the two-stage CUDA reduction: 1024 blocks x 256 threads grid-stride,
-    butterfly per warp, the eight warps in sequence, the 1024 blocks in sequence."""
+    butterfly per warp, the eight warps in sequence; then one warp adds 32 block sums per lane in
+    sequence and finishes with a butterfly."""
     n = v.shape[0]
     span = 1024 * 256
     reps = -(-n // span)
@@ -105,10 +106,11 @@ def tree_sum(v):
     blocks = np.zeros(1024)
     for j in range(8):
         blocks = blocks + w[:, j]
-    total = 0.0
-    for b in blocks:
-        total += float(b)
-    return total
+    lanes = np.zeros(32)
+    blocks = blocks.reshape(32, 32)
+    for j in range(32):
+        lanes = lanes + blocks[:, j]
+    return float(_warp_sum(lanes))
 
 
 def _weighted_pick(wm, u, taken):

@@ -425,6 +425,23 @@ def test_staged_upload_of_a_pageable_matrix(eng):
     assert abs(total - (X.astype(np.float64) ** 2).sum()) <= 1e-12 * total
 
 
+def test_memory_pool_trim_and_reuse(eng, built_lib):
+    """Buffers come from a per-device pool that keeps freed memory; trimming it leaves the library usable."""
+    from h2o4gpu_b200 import synth
+    from h2o4gpu_b200.libs import lib_kmeans
+    X, init, _ = synth.c2(n=40000)
+    outs = []
+    for rep in range(3):
+        h = eng.ResidentKMeans()
+        h.upload(X)
+        h.fit(init, 4)
+        outs.append((h.centroids(), h.labels()))
+        h.close()
+        if rep == 1:
+            assert lib_kmeans.cdll().kmeans_trim_memory() == 0
+    assert all(np.array_equal(outs[0][0], o[0]) and np.array_equal(outs[0][1], o[1]) for o in outs[1:])
+
+
 # ---- several GPUs in one process ------------------------------------------------------
 def test_multi_gpu_equals_single_gpu(eng):
     from h2o4gpu_b200.libs import lib_kmeans
