@@ -103,6 +103,12 @@ delta_accumulate_kernel(const T* __restrict__ X, size_t n, int d, const int* __r
 // int32 shared accumulators first (same layout and arithmetic as accumulate_kernel) and
 // sends each non-zero total to the global sums once.  Subtracting a row is adding its
 // negation: rint is odd, so the pieces of -x are minus the pieces of x.
+// The netting kernels drain into a padded copy of the sums, one int64 per 128-byte line:
+// several hundred CTAs send their totals to the same k * d addresses, and 64-bit reductions
+// on one L2 line are served one after the other (about 13 ns each measured), so with the
+// dense layout (16 sums per line) the drain alone took longer than the netting.
+// fold_flush_kernel adds the padded array into the dense sums and clears it.
+constexpr int kFlushPad = 16;
 constexpr int kDeltaThreads = 512;    // two CTAs per SM: room for the registers of a prefetched step
 constexpr int kDeltaChunk = 32768;   // rows between two drains: the int32 accumulators hold 2^15 rows of 2^15-sized pieces
 
@@ -228,14 +234,14 @@ delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int
           for (int q = 0; q < NP / 2; ++q) {
             const long long v = (long long)acc[(size_t)(2 * q) * pstride + i] * (1LL << kPieceBits) +
                                 (long long)acc[(size_t)(2 * q + 1) * pstride + i];
-            if (v) atomicAdd(reinterpret_cast<unsigned long long*>(psums + (size_t)q * k * d + (size_t)c * d + col),
+            if (v) atomicAdd(reinterpret_cast<unsigned long long*>(psums + ((size_t)q * k * d + (size_t)c * d + col) * kFlushPad),
                              (unsigned long long)v);
             acc[(size_t)(2 * q) * pstride + i] = 0;
             acc[(size_t)(2 * q + 1) * pstride + i] = 0;
           }
         }
         for (int i = tid; i < k; i += kDeltaThreads) {
-          if (cnt[i]) atomicAdd(pcounts + i, (unsigned long long)(long long)cnt[i]);
+          if (cnt[i]) atomicAdd(pcounts + (size_t)i * kFlushPad, (unsigned long long)(long long)cnt[i]);
           cnt[i] = 0;
         }
       }
@@ -246,5 +252,126 @@ delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int
   }
 }
 
-}  // namespace km
+// The same netting, fed by the moved-rows bit map the tensor-core E-step writes (one bit per
+// row, one word per 32 rows): the scan reads rows / 8 bytes instead of 8 bytes per row, and
+// the two labels are fetched only for the 32-row blocks that have a bit set.
+template <typename T, int V>
+__global__ void __launch_bounds__(kDeltaThreads, 2)
+delta_accumulate_bitmap_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict__ labels,
+                               int* __restrict__ prev, const unsigned int* __restrict__ moved_bits, int k,
+                               long long* __restrict__ psums, unsigned long long* __restrict__ pcounts, T scale,
+                               const unsigned long long* changed, unsigned long long limit) {
+  constexpr int NP = Fixed<T>::NP;
+  if (!delta_turn(changed, limit)) return;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  int* acc = reinterpret_cast<int*>(smem_raw);      // [NP][k][d]
+  int* cnt = acc + (size_t)NP * k * d;              // [k]
+  __shared__ int s_touched;
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  constexpr int NWARP = kDeltaThreads / 32;
+  const int dv = d / V;
+  const size_t pstride = (size_t)k * d;
+  int lpr = 1;
+  while (lpr < dv && lpr < 32) lpr <<= 1;
+  const int groups = 32 / lpr;
+  const int g = lane / lpr;
+  const int l = lane % lpr;
 
+  // partitions in whole chunks of 32768 rows (1024 words), so a word never straddles two CTAs
+  const size_t n_chunks = (n + kDeltaChunk - 1) / kDeltaChunk;
+  const size_t n_words = (n + 31) / 32;
+
+  for (int i = tid; i < NP * k * d; i += kDeltaThreads) acc[i] = 0;
+  for (int i = tid; i < k; i += kDeltaThreads) cnt[i] = 0;
+  if (tid == 0) s_touched = 0;
+  __syncthreads();
+
+  for (size_t chunk = blockIdx.x; chunk < n_chunks; chunk += gridDim.x) {
+    const size_t w0 = chunk * (kDeltaChunk / 32);
+    const size_t w1 = min(n_words, w0 + kDeltaChunk / 32);
+    for (size_t wb = w0 + (size_t)warp * 32; wb < w1; wb += (size_t)NWARP * 32) {
+      const size_t wi = wb + lane;
+      const unsigned int my_word = (wi < w1) ? moved_bits[wi] : 0u;
+      unsigned int nonzero = __ballot_sync(0xffffffffu, my_word != 0u);
+      while (nonzero) {
+        const int wsrc = __ffs(nonzero) - 1;
+        nonzero &= nonzero - 1;
+        unsigned int mask = __shfl_sync(0xffffffffu, my_word, wsrc);
+        const size_t b = (wb + wsrc) * 32;            // first row of this 32-row block
+        const size_t r = b + lane;
+        int nw = -1, od = -1;
+        if (r < n && ((mask >> lane) & 1u)) { nw = labels[r]; od = prev[r]; prev[r] = nw; }
+        if (lane == 0) atomicAdd(&s_touched, __popc(mask));
+        while (mask) {
+          const unsigned int src = __fns(mask, 0, g + 1);   // lane of this group's row
+          const bool have = (src != 0xffffffffu);
+          const int to = __shfl_sync(0xffffffffu, nw, have ? src : 0);
+          const int from = __shfl_sync(0xffffffffu, od, have ? src : 0);
+          if (have && to != from) {
+            const bool to_ok = (unsigned)to < (unsigned)k, from_ok = (unsigned)from < (unsigned)k;
+            const T* xr = X + (b + src) * (size_t)d;
+            for (int idx = l; idx < dv; idx += lpr) {
+              T x[V], y[V];
+              VecLoad<T, V>::ld(xr + (size_t)idx * V, x);
+#pragma unroll
+              for (int e = 0; e < V; ++e) y[e] = -x[e];
+              if (to_ok) add_vec_fixed<T, V, NP>(acc + (size_t)to * d, pstride, dv, idx, g & (V - 1), x, scale);
+              if (from_ok) add_vec_fixed<T, V, NP>(acc + (size_t)from * d, pstride, dv, idx, g & (V - 1), y, scale);
+            }
+            if (l == 0) {
+              if (to_ok) atomicAdd(&cnt[to], 1);
+              if (from_ok) atomicAdd(&cnt[from], -1);
+            }
+          }
+          for (int i = 0; i < groups && mask; ++i) mask &= mask - 1;
+        }
+      }
+    }
+    __syncthreads();
+    // a chunk has 2^15 rows and every piece is at most 2^15 in magnitude: drain after each
+    if (s_touched > 0) {
+      for (int i = tid; i < k * d; i += kDeltaThreads) {
+        const int c = i / d;
+        const int col = pos_to_col(i - c * d, dv, V);
+#pragma unroll
+        for (int q = 0; q < NP / 2; ++q) {
+          const long long v = (long long)acc[(size_t)(2 * q) * pstride + i] * (1LL << kPieceBits) +
+                              (long long)acc[(size_t)(2 * q + 1) * pstride + i];
+          if (v) atomicAdd(reinterpret_cast<unsigned long long*>(psums + ((size_t)q * k * d + (size_t)c * d + col) * kFlushPad),
+                           (unsigned long long)v);
+          acc[(size_t)(2 * q) * pstride + i] = 0;
+          acc[(size_t)(2 * q + 1) * pstride + i] = 0;
+        }
+      }
+      for (int i = tid; i < k; i += kDeltaThreads) {
+        if (cnt[i]) atomicAdd(pcounts + (size_t)i * kFlushPad, (unsigned long long)(long long)cnt[i]);
+        cnt[i] = 0;
+      }
+    }
+    __syncthreads();
+    if (tid == 0) s_touched = 0;
+    __syncthreads();
+  }
+}
+
+// pure[i] += flush[i * kFlushPad] (then cleared); work[i] = pure[i] when work is given.
+__global__ void __launch_bounds__(256)
+fold_flush_kernel(long long* __restrict__ flush, long long* __restrict__ pure, long long* __restrict__ work,
+                  size_t count) {
+  for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < count; i += (size_t)gridDim.x * 256) {
+    long long v = pure[i];
+    if (flush != nullptr) {
+      const long long f = flush[i * kFlushPad];
+      if (f != 0) {
+        v += f;
+        flush[i * kFlushPad] = 0;
+        pure[i] = v;
+      }
+    }
+    if (work != nullptr) work[i] = v;
+  }
+}
+
+}  // namespace km

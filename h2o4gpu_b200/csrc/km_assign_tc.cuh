@@ -281,7 +281,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                  const __grid_constant__ CUtensorMap tmBlo, const float* __restrict__ cn_pad,
                  const float* __restrict__ xnorm, int* __restrict__ labels, size_t n, int n_tiles, int npad,
                  IterState* st, int count_changes, unsigned int* __restrict__ amb_rows, float tol_rel, float sx,
-                 float sxsb, int dbg) {
+                 float sxsb, int dbg, unsigned int* __restrict__ moved_bits, uint4* __restrict__ amb_near) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_u32 = smem_u32(smem_raw);
   const uint32_t base = (raw_u32 + 1023u) & ~1023u;
@@ -584,14 +584,24 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         if (near[ch]) bidx = ch * 32 + __ffs(near[ch]) - 1;   // lowest column wins
       }
       if (dbg & 4) { n_near = 1; bidx = 0; }  // timing experiments: nothing is ambiguous
+      bool moved = false;
       if (row < n) {
         if (amb_rows != nullptr && n_near != 1) {
           const unsigned int pos = atomicAdd(&st->amb_count, 1u);
           amb_rows[pos] = (unsigned int)row;
+          amb_near[pos] = make_uint4(near[0], near[1], near[2], near[3]);   // the candidates of the exact pass
         } else {
-          changed += (old_label != bidx);
+          moved = (old_label != bidx);
+          changed += moved;
           labels[row] = bidx;
         }
+      }
+      // one bit per row whose label moved (the warp's 32 rows are one word): the incremental
+      // M-step reads this map instead of comparing two label arrays.  Rows left to the exact
+      // pass get their bit there.
+      if (moved_bits != nullptr) {
+        const unsigned int word = __ballot_sync(0xffffffffu, moved);
+        if (lane == 0) moved_bits[(size_t)tile * (kBM / 32) + q] = word;
       }
     }
     if (count_changes) {

@@ -61,6 +61,8 @@ struct Shard {
   tcb::BigPlan tcbp;  // tensor-core path for large centroid tables
   unsigned int* amb_rows = nullptr;  // rows handed to the exact re-evaluation pass
   size_t amb_cap = 0;
+  uint4* amb_near = nullptr;         // per listed row: bit mask of the candidate centroids (small tables)
+  size_t amb_near_cap = 0;
   unsigned int* amb_log = nullptr;
   cudaStream_t stream = nullptr;
   const T* X = nullptr;
@@ -74,7 +76,10 @@ struct Shard {
   int k_cap = 0, d_cap = 0;
   long long* gacc = nullptr;  // [NP/2][k][d] sums followed by [k] counts: one all-reduce covers both
   long long* pacc = nullptr;  // same layout: sums that follow from the labels alone (incremental M-step)
+  long long* pflush = nullptr;  // padded drain target of the netting kernels (kFlushPad int64 per entry), or null
   int* labels_prev = nullptr; // labelling pacc corresponds to
+  unsigned int* moved_bits = nullptr;  // one bit per row whose label the last E-step moved (tensor-core path)
+  bool moved_bits_valid = false;
   size_t labels_prev_cap = 0;
   T* C[2] = {nullptr, nullptr};
   double* Cd[2] = {nullptr, nullptr};  // the same tables in double (float shards; the row-distance kernel reads them)
@@ -251,9 +256,9 @@ void Engine<T>::destroy() {
     }
     s.tcp.release();
     s.tcbp.release();
-    km_free(s.amb_rows); km_free(s.amb_log);
+    km_free(s.amb_rows); km_free(s.amb_near); km_free(s.amb_log);
     km_free(s.X_owned); km_free(s.labels); km_free(s.dist); km_free(s.gacc);
-    km_free(s.pacc); km_free(s.labels_prev);
+    km_free(s.pacc); km_free(s.pflush); km_free(s.labels_prev); km_free(s.moved_bits);
     km_free(s.C[0]); km_free(s.C[1]); km_free(s.Cd[0]); km_free(s.Cd[1]); km_free(s.cnorm); km_free(s.shift_k); km_free(s.empties);
     km_free(s.st); km_free(s.cand_val); km_free(s.cand_row); km_free(s.sum_partials);
     km_free(s.shift_log); km_free(s.changed_log); km_free(s.reloc_log); km_free(s.xstat);
@@ -483,8 +488,11 @@ int Engine<T>::preallocate(int k_, int max_iter) {
     }
     if (s.labels_prev_cap < s.rows) {
       km_free(s.labels_prev);
+      km_free(s.moved_bits);
       s.labels_prev = nullptr;
+      s.moved_bits = nullptr;
       KM_CUDA(km_malloc(&s.labels_prev, s.rows * sizeof(int)));
+      KM_CUDA(km_malloc(&s.moved_bits, (s.rows / 32 + 8) * sizeof(unsigned int)));
       s.labels_prev_cap = s.rows;
     }
     if (std::is_same<T, float>::value && s.amb_cap < s.rows) {
@@ -492,6 +500,12 @@ int Engine<T>::preallocate(int k_, int max_iter) {
       s.amb_rows = nullptr;
       KM_CUDA(km_malloc(&s.amb_rows, s.rows * sizeof(unsigned int)));
       s.amb_cap = s.rows;
+    }
+    if (std::is_same<T, float>::value && tc::shape_ok(k_, d) && s.amb_near_cap < s.rows) {
+      km_free(s.amb_near);
+      s.amb_near = nullptr;
+      KM_CUDA(km_malloc(&s.amb_near, s.rows * sizeof(uint4)));
+      s.amb_near_cap = s.rows;
     }
   }
   (void)max_iter;
@@ -505,13 +519,18 @@ int Engine<T>::ensure_buffers(int k_) {
     if (!s.X) KM_FAIL(KM_ESTATE, "no data attached to the handle");
     DevGuard g(s.dev);
     if (s.k_cap != k_ || s.d_cap != d) {
-      km_free(s.gacc); km_free(s.pacc); s.pacc = nullptr; km_free(s.C[0]); km_free(s.C[1]); km_free(s.cnorm);
+      km_free(s.gacc); km_free(s.pacc); s.pacc = nullptr; km_free(s.pflush); s.pflush = nullptr; km_free(s.C[0]); km_free(s.C[1]); km_free(s.cnorm);
       km_free(s.Cd[0]); km_free(s.Cd[1]); s.Cd[0] = s.Cd[1] = nullptr;
       km_free(s.shift_k); km_free(s.empties);
       s.gacc = nullptr; s.C[0] = s.C[1] = nullptr; s.cnorm = nullptr; s.shift_k = nullptr; s.empties = nullptr;
       size_t kd = (size_t)k_ * d;
       KM_CUDA(km_malloc(&s.gacc, ((size_t)(NP / 2) * kd + k_) * sizeof(long long)));
       KM_CUDA(km_malloc(&s.pacc, ((size_t)(NP / 2) * kd + k_) * sizeof(long long)));
+      if (delta_smem_bytes<T>(k_, d) <= 200 * 1024) {
+        const size_t fb = ((size_t)(NP / 2) * kd + k_) * kFlushPad * sizeof(long long);
+        KM_CUDA(km_malloc(&s.pflush, fb));
+        KM_CUDA(cudaMemsetAsync(s.pflush, 0, fb, s.stream));
+      }
       KM_CUDA(km_malloc(&s.C[0], kd * sizeof(T)));
       KM_CUDA(km_malloc(&s.C[1], kd * sizeof(T)));
       if (!std::is_same<T, double>::value) {
@@ -814,6 +833,12 @@ int Engine<T>::tc_refresh(Shard<T>& s) {
       KM_CUDA(km_malloc(&s.amb_rows, s.rows * sizeof(unsigned int)));
       s.amb_cap = s.rows;
     }
+    if (tc::shape_ok(k, d) && s.amb_near_cap < s.rows) {
+      km_free(s.amb_near);
+      s.amb_near = nullptr;
+      KM_CUDA(km_malloc(&s.amb_near, s.rows * sizeof(uint4)));
+      s.amb_near_cap = s.rows;
+    }
     if (tc::shape_ok(k, d)) {
       KM_TRY(tc::setup(s.tcp, s.X, s.rows, k, d, s.num_sms, s.stream));
       s.tcp.sx = tc_sx;
@@ -845,12 +870,12 @@ int Engine<T>::launch_assign(Shard<T>& s, bool use_tc, bool count_changes) {
     }
     if (use_tc) {
       launches += 2;
+      unsigned int* bits = (count_changes && s.labels_prev_cap >= s.rows) ? s.moved_bits : nullptr;
       KM_TRY(tc::launch(s.tcp, s.labels, s.st, count_changes, s.amb_rows, tc_tol_rel, s.num_sms, tc_mask_hi,
-                        s.stream));
-      // (k <= 128 on this path: four centroids per lane)
-      const size_t rsm = refine_smem_bytes<float>(k, d);  // at most 33 KB here: below the default limit
-      refine_kernel<float, 2><<<s.num_sms * 2, kRefineThreads, rsm, s.stream>>>(s.X, d, s.C[cur], k, s.amb_rows, s.st,
-                                                                            s.labels, count_changes ? 1 : 0);
+                        s.stream, bits, s.amb_near));
+      s.moved_bits_valid = bits != nullptr;
+      refine_near_kernel<float><<<s.num_sms * 4, kRefineThreads, 0, s.stream>>>(
+          s.X, d, s.C[cur], k, s.amb_rows, s.amb_near, s.st, s.labels, count_changes ? 1 : 0, bits);
       KM_CUDA(cudaGetLastError());
       return KM_OK;
     }
@@ -881,19 +906,36 @@ int Engine<T>::launch_delta(Shard<T>& s, T scale, const unsigned long long* gate
   constexpr int NP = Fixed<T>::NP;
   long long* ps = s.pacc;
   unsigned long long* pc = reinterpret_cast<unsigned long long*>(ps + (size_t)(NP / 2) * k * d);
+  // the shared-memory netting kernels drain into the padded array (counts behind the sums)
+  long long* fs = s.pflush;
+  unsigned long long* fc = reinterpret_cast<unsigned long long*>(fs + (size_t)(NP / 2) * k * d * kFlushPad);
   const size_t smem = delta_smem_bytes<T>(k, d);
-  if (smem <= 200 * 1024) {
+  static const bool bitmap_env = [] {
+    const char* e = std::getenv("H2O4GPU_KM_DELTA_BITMAP");
+    return e && e[0] == '1';
+  }();
+  if (bitmap_env && s.pflush && smem <= 100 * 1024 && s.moved_bits_valid && vec_ok(s)) {
+    // the E-step left a map of the rows that moved: no label scan
+    KM_CUDA(cudaFuncSetAttribute(delta_accumulate_bitmap_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem));
+    delta_accumulate_bitmap_kernel<T, V><<<s.num_sms * 2, kDeltaThreads, smem, s.stream>>>(
+        s.X, s.rows, d, s.labels, s.labels_prev, s.moved_bits, k, fs, fc, scale, gate, limit);
+    KM_CUDA(cudaGetLastError());
+    ++launches;
+    return KM_OK;
+  }
+  if (smem <= 200 * 1024 && s.pflush) {
     // centroid table small enough for shared accumulators: one or two CTAs per SM net their rows' moves
     if (vec_ok(s)) {
       KM_CUDA(cudaFuncSetAttribute(delta_accumulate_smem_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)smem));
       delta_accumulate_smem_kernel<T, V><<<s.num_sms * (smem <= 100 * 1024 ? 2 : 1), kDeltaThreads, smem, s.stream>>>(
-          s.X, s.rows, d, s.labels, s.labels_prev, k, ps, pc, scale, gate, limit);
+          s.X, s.rows, d, s.labels, s.labels_prev, k, fs, fc, scale, gate, limit);
     } else {
       KM_CUDA(cudaFuncSetAttribute(delta_accumulate_smem_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)smem));
       delta_accumulate_smem_kernel<T, 1><<<s.num_sms * (smem <= 100 * 1024 ? 2 : 1), kDeltaThreads, smem, s.stream>>>(
-          s.X, s.rows, d, s.labels, s.labels_prev, k, ps, pc, scale, gate, limit);
+          s.X, s.rows, d, s.labels, s.labels_prev, k, fs, fc, scale, gate, limit);
     }
     KM_CUDA(cudaGetLastError());
     ++launches;

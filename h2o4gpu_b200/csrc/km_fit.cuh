@@ -159,10 +159,16 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
     KM_CUDA(cudaMemsetAsync(s.labels, 0xff, s.rows * sizeof(int), s.stream));
     if (delta && s.labels_prev_cap < s.rows) {
       km_free(s.labels_prev);
+      km_free(s.moved_bits);
       s.labels_prev = nullptr;
+      s.moved_bits = nullptr;
       KM_CUDA(km_malloc(&s.labels_prev, s.rows * sizeof(int)));
+      KM_CUDA(km_malloc(&s.moved_bits, (s.rows / 32 + 8) * sizeof(unsigned int)));
       s.labels_prev_cap = s.rows;
     }
+    s.moved_bits_valid = false;
+    if (s.pflush)   // all zero between iterations; cleared here in case an earlier fit stopped half-way
+      KM_CUDA(cudaMemsetAsync(s.pflush, 0, s.gacc_count(k, d) * kFlushPad * sizeof(long long), s.stream));
     if (use_tc) KM_TRY(tc_refresh(s));
   }
 
@@ -202,8 +208,15 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
           rc = launch_accumulate(s, scale, s.pacc, gate, limit);
         }
         if (rc == KM_OK && it > 0) rc = launch_delta(s, scale, gate, limit);
-        if (rc == KM_OK && !multi)
-          cudaMemcpyAsync(s.gacc, s.pacc, s.gacc_count(k, d) * sizeof(long long), cudaMemcpyDeviceToDevice, s.stream);
+        if (rc == KM_OK) {
+          // fold the padded drain array into the label-only sums; one shard: also the working copy
+          const size_t cnt = s.gacc_count(k, d);
+          if (!multi || s.pflush) {
+            fold_flush_kernel<<<(unsigned)std::min<size_t>((cnt + 255) / 256, (size_t)s.num_sms * 4), 256, 0, s.stream>>>(
+                s.pflush, s.pacc, multi ? nullptr : s.gacc, cnt);
+            ++launches;
+          }
+        }
         if (i == 0) cudaEventRecord(ev[4 * it + 2], s.stream);
       } else {
         rc = launch_assign(s, use_tc, true);

@@ -139,18 +139,20 @@ inline int prep(Plan& pl, const float* C, const float* cnorm, cudaStream_t strea
 constexpr float kTolRel = 1.9073486328125e-06f;
 
 inline int launch(Plan& pl, int* labels, IterState* st, bool count_changes, unsigned int* amb_rows, float tol_rel,
-                  int num_sms, int mask_hi, cudaStream_t stream) {
+                  int num_sms, int mask_hi, cudaStream_t stream, unsigned int* moved_bits, uint4* amb_near) {
   const size_t tiles = (pl.x_rows + kBM - 1) / kBM;
   if (tiles > 0x7fffffffULL / kBM) KM_FAIL(KM_EINVAL, "shard too large for the tensor-core kernel");
   const int grid = (int)std::min<size_t>(tiles, (size_t)num_sms);
   if (pl.d == 32)
     assign_tc_kernel<32><<<grid, kThreads, smem_bytes(pl.d, pl.npad), stream>>>(
         pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, pl.xnorm, labels, pl.x_rows, (int)tiles, pl.npad, st,
-        count_changes ? 1 : 0, amb_rows, tol_rel, pl.sx, pl.sx * pl.sb, mask_hi);
+        count_changes ? 1 : 0, amb_rows, tol_rel, pl.sx, pl.sx * pl.sb, mask_hi, count_changes ? moved_bits : nullptr,
+        amb_near);
   else
     assign_tc_kernel<64><<<grid, kThreads, smem_bytes(pl.d, pl.npad), stream>>>(
         pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, pl.xnorm, labels, pl.x_rows, (int)tiles, pl.npad, st,
-        count_changes ? 1 : 0, amb_rows, tol_rel, pl.sx, pl.sx * pl.sb, mask_hi);
+        count_changes ? 1 : 0, amb_rows, tol_rel, pl.sx, pl.sx * pl.sb, mask_hi, count_changes ? moved_bits : nullptr,
+        amb_near);
   KM_CUDA(cudaGetLastError());
   return KM_OK;
 }
