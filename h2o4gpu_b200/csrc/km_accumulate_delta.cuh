@@ -190,37 +190,54 @@ delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int
       const size_t wbn = wb + (size_t)NWARP * 256;
       if (wbn < c1) load_step(wbn, nwn, odn);
     }
+    // which of the eight label pairs of every lane moved: lane j keeps the ballot of pair j, so
+    // that the loop over the pairs below need not be unrolled (its body is long, and eight copies
+    // of it made the kernel wait for instruction fetches more than for memory)
+    unsigned int my_ballot = 0;
+    bool any = false;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const bool moved = nw[j] != od[j];
-      unsigned int mask = __ballot_sync(0xffffffffu, moved);
-      if (mask == 0) continue;
-      const size_t jb = wb + (j >> 2) * 128 + (j & 3);   // row of lane 0 for this j; lane s holds jb + 4 s
-      if (moved) prev[jb + lane * 4] = nw[j];
-      if (lane == 0) atomicAdd(&s_touched, __popc(mask));
-      while (mask) {
-        const unsigned int src = __fns(mask, 0, g + 1);   // lane of this group's row
-        const bool have = (src != 0xffffffffu);
-        const int to = __shfl_sync(0xffffffffu, nw[j], have ? src : 0);
-        const int from = __shfl_sync(0xffffffffu, od[j], have ? src : 0);
-        if (have) {
-          const bool to_ok = (unsigned)to < (unsigned)k, from_ok = (unsigned)from < (unsigned)k;
-          const T* xr = X + (jb + (size_t)src * 4) * (size_t)d;
-          for (int idx = l; idx < dv; idx += lpr) {
-            T x[V], y[V];
-            VecLoad<T, V>::ld(xr + (size_t)idx * V, x);
+      const unsigned int m = __ballot_sync(0xffffffffu, nw[j] != od[j]);
+      if (lane == j) my_ballot = m;
+      any |= (m != 0);
+    }
+    if (any) {
+#pragma unroll 1
+      for (int j = 0; j < 8; ++j) {
+        unsigned int mask = __shfl_sync(0xffffffffu, my_ballot, j);
+        if (mask == 0) continue;
+        const size_t jb = wb + (j >> 2) * 128 + (j & 3);   // row of lane 0 for this pair; lane s holds jb + 4 s
+        if (lane == 0) atomicAdd(&s_touched, __popc(mask));
+        while (mask) {
+          const unsigned int src = __fns(mask, 0, g + 1);   // lane of this group's row
+          const bool have = (src != 0xffffffffu);
+          if (have) {
+            // the two labels are read again (they are in L1) rather than indexed out of registers
+            const size_t row = jb + (size_t)src * 4;
+            const int to = labels[row], from = prev[row];
+            const bool to_ok = (unsigned)to < (unsigned)k, from_ok = (unsigned)from < (unsigned)k;
+            const T* xr = X + row * (size_t)d;
+            for (int idx = l; idx < dv; idx += lpr) {
+              T x[V], y[V];
+              VecLoad<T, V>::ld(xr + (size_t)idx * V, x);
 #pragma unroll
-            for (int e = 0; e < V; ++e) y[e] = -x[e];
-            if (to_ok) add_vec_fixed<T, V, NP>(acc + (size_t)to * d, pstride, dv, idx, g & (V - 1), x, scale);
-            if (from_ok) add_vec_fixed<T, V, NP>(acc + (size_t)from * d, pstride, dv, idx, g & (V - 1), y, scale);
+              for (int e = 0; e < V; ++e) y[e] = -x[e];
+              if (to_ok) add_vec_fixed<T, V, NP>(acc + (size_t)to * d, pstride, dv, idx, g & (V - 1), x, scale);
+              if (from_ok) add_vec_fixed<T, V, NP>(acc + (size_t)from * d, pstride, dv, idx, g & (V - 1), y, scale);
+            }
+            if (l == 0) {
+              if (to_ok) atomicAdd(&cnt[to], 1);
+              if (from_ok) atomicAdd(&cnt[from], -1);
+            }
           }
-          if (l == 0) {
-            if (to_ok) atomicAdd(&cnt[to], 1);
-            if (from_ok) atomicAdd(&cnt[from], -1);
-          }
+          for (int i = 0; i < groups && mask; ++i) mask &= mask - 1;
         }
-        for (int i = 0; i < groups && mask; ++i) mask &= mask - 1;
       }
+      // the snapshot follows once every group has read the old labels
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (nw[j] != od[j]) prev[wb + (j >> 2) * 128 + lane * 4 + (j & 3)] = nw[j];
     }
     }
     __syncthreads();
