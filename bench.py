@@ -38,6 +38,8 @@ WORKLOADS = {
     # contraction-bound shape (rows per GPU of the 8-GPU split of n = 4e7); offset centres N(0, 4I)
     # are approximated by U(-3.5, 3.5) centres of the same variance
     "c5": dict(n=5_000_000, d=256, k=4096, comp=4096, sigma=1.0, half=3.5, dirichlet=False, T=10),
+    # image-like rows (0 with probability 0.8, else an integer in 1..255): bandwidth-bound, fused small-k kernel
+    "c4": dict(n=2_000_000, d=784, k=10, comp=0, sigma=0.0, half=0.0, dirichlet=False, T=100, kind=1),
 }
 
 
@@ -109,6 +111,8 @@ class ClockSampler(object):
 
 
 def mixture_params(w, seed=0):
+    if w.get("kind", 0) == 1:
+        return None, None
     rng = np.random.default_rng(seed)
     centers = rng.uniform(-w["half"], w["half"], (w["comp"], w["d"])).astype(np.float32)
     weights = rng.dirichlet(np.ones(w["comp"])).astype(np.float32) if w["dirichlet"] else None
@@ -118,6 +122,9 @@ def mixture_params(w, seed=0):
 def host_sample(w, n, seed=0):
     """The same distribution on the host (numpy), for the CPU arm."""
     rng = np.random.default_rng(seed)
+    if w.get("kind", 0) == 1:
+        X = np.where(rng.random((n, w["d"])) < 0.8, 0, rng.integers(1, 256, (n, w["d"]))).astype(np.float32)
+        return X, X[:w["k"]].copy()
     centers = rng.uniform(-w["half"], w["half"], (w["comp"], w["d"]))
     weights = rng.dirichlet(np.ones(w["comp"])) if w["dirichlet"] else None
     comp = rng.choice(w["comp"], n, p=weights) if weights is not None else rng.integers(0, w["comp"], n)
@@ -166,8 +173,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     K, W = args.steps, max(args.warmup, 0)
-    config = {"workload": "%s: n=%d rows/GPU x d=%d fp32, k=%d, %d-component Gaussian mixture, seeded init rows"
-                          % (args.workload, w["n"], w["d"], w["k"], w["comp"]),
+    dist_name = ("image-like rows (0 w.p. 0.8, else 1..255)" if w.get("kind", 0) == 1
+                 else "%d-component Gaussian mixture" % w["comp"])
+    config = {"workload": "%s: n=%d rows/GPU x d=%d fp32, k=%d, %s, seeded init rows"
+                          % (args.workload, w["n"], w["d"], w["k"], dist_name),
               "rows_per_gpu": w["n"], "d": w["d"], "k": w["k"], "sharding": "rows, dp%d" % world,
               "l2": "inputs (%.2f GB/GPU) exceed L2; no flush needed" % (w["n"] * w["d"] * 4 / 1e9)}
 
@@ -203,7 +212,7 @@ def main():
     n, d, k = w["n"], w["d"], w["k"]
     centers, weights = mixture_params(w)
     X = torch.empty((n, d), dtype=torch.float32, device=dev)
-    engine.synth_device(X.data_ptr(), n, d, np.float32, row0=rank * n, kind=0, centers=centers, weights=weights,
+    engine.synth_device(X.data_ptr(), n, d, np.float32, row0=rank * n, kind=w.get("kind", 0), centers=centers, weights=weights,
                         sigma=w["sigma"], seed=1234, gpu_id=local_rank)
     # seeded initial rows, taken from rank 0's shard and shared
     rows0 = np.sort(np.random.default_rng(7).choice(n, k, replace=False))
@@ -322,7 +331,7 @@ def main():
                 lib = lib_kmeans.get()
                 Xh = torch.empty((world * n, d), dtype=torch.float32, pin_memory=True)
                 for r in range(world):
-                    engine.synth_device(X.data_ptr(), n, d, np.float32, row0=r * n, kind=0, centers=centers,
+                    engine.synth_device(X.data_ptr(), n, d, np.float32, row0=r * n, kind=w.get("kind", 0), centers=centers,
                                         weights=weights, sigma=w["sigma"], seed=1234, gpu_id=local_rank)
                     Xh[r * n:(r + 1) * n].copy_(X)
                 torch.cuda.synchronize()

@@ -26,6 +26,7 @@
 #include "km_nccl.h"
 #include "km_refine.cuh"
 #include "km_smallk.cuh"
+#include "km_smallk_stream.cuh"
 #include "km_tc_host.cuh"
 #include "km_tiles.cuh"
 
@@ -664,13 +665,14 @@ template <typename T, int V>
 using SmallKFn = void (*)(const T*, size_t, int, const T*, int, const T*, int*, IterState*, long long*,
                           unsigned long long*, T, int, unsigned int);
 
-template <typename T, int V>
+template <typename T, int V, int RPW>
 static SmallKFn<T, V> smallk_pick(int k, int* K) {
-#define KM_PICK(KK) if (k <= KK) { *K = KK; return smallk_kernel<T, KK, V>; }
+  // more rows per group only while the K x RPW dot products fit the register budget
+#define KM_PICK(KK) if (k <= KK) { *K = KK; return smallk_kernel<T, KK, V, (KK <= 10 ? RPW : kSmallKRpw)>; }
   KM_PICK(1) KM_PICK(2) KM_PICK(3) KM_PICK(4) KM_PICK(5) KM_PICK(6) KM_PICK(8) KM_PICK(10) KM_PICK(12)
 #undef KM_PICK
   *K = 16;
-  return smallk_kernel<T, 16, V>;
+  return smallk_kernel<T, 16, V, kSmallKRpw>;
 }
 inline int smallk_bound(int k) {
   const int ks[] = {1, 2, 3, 4, 5, 6, 8, 10, 12, 16};
@@ -681,7 +683,12 @@ inline int smallk_bound(int k) {
 template <typename T>
 bool Engine<T>::smallk_ok(bool update) const {
   if (k > 16) return false;
-  return smallk_smem_bytes<T>(smallk_bound(k), d, update) <= kMaxDynSmem;
+  const size_t smem = smallk_smem_bytes<T>(smallk_bound(k), d, update);
+  // The fused step keeps fixed-point accumulators of the whole table in shared memory: good
+  // while they are small (several CTAs per SM stay resident); for wide rows the E-step runs
+  // alone and the sums come from the run-length / incremental kernels.
+  if (update) return smem <= 48 * 1024;
+  return smem <= kMaxDynSmem;
 }
 
 template <typename T>
@@ -699,18 +706,21 @@ int Engine<T>::launch_smallk(Shard<T>& s, bool update, T scale) {
   size_t grid = (s.rows + rpc - 1) / rpc;
   cudaError_t e;
   if (vec) {
-    auto fn = smallk_pick<T, V>(k, &K);
+    auto fn = update ? smallk_pick<T, V, kSmallKRpw>(k, &K) : smallk_pick<T, V, kSmallKRpwAssign>(k, &K);
     smem = smallk_smem_bytes<T>(K, d, update);
     e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) KM_CUDA(e);
+    // without this the driver sizes the shared-memory carve-out for one CTA and only one is resident
+    cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     fn<<<(unsigned)grid, kSmallKThreads, smem, s.stream>>>(s.X, s.rows, d, s.C[cur], k, s.cnorm, s.labels, s.st,
                                                           s.sums(), s.counts(k, d), scale, update ? 1 : 0,
                                                           (unsigned)rpc);
   } else {
-    auto fn = smallk_pick<T, 1>(k, &K);
+    auto fn = update ? smallk_pick<T, 1, kSmallKRpw>(k, &K) : smallk_pick<T, 1, kSmallKRpwAssign>(k, &K);
     smem = smallk_smem_bytes<T>(K, d, update);
     e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) KM_CUDA(e);
+    cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     fn<<<(unsigned)grid, kSmallKThreads, smem, s.stream>>>(s.X, s.rows, d, s.C[cur], k, s.cnorm, s.labels, s.st,
                                                           s.sums(), s.counts(k, d), scale, update ? 1 : 0,
                                                           (unsigned)rpc);
@@ -879,6 +889,34 @@ int Engine<T>::launch_assign(Shard<T>& s, bool use_tc, bool count_changes) {
       KM_CUDA(cudaGetLastError());
       return KM_OK;
     }
+  }
+  if constexpr (std::is_same<T, float>::value) {
+    // few centroids, wide rows: the streaming small-k kernel
+    const int K = (k + 3) / 4 * 4;
+    if (k <= 16 && d >= 128 && vec_ok(s) && sks::smem_bytes(K, d) <= kMaxDynSmem) {
+      const size_t smem = sks::smem_bytes(K, d);
+      const size_t tiles = (s.rows + sks::kRows - 1) / sks::kRows;
+      const int grid = (int)std::min<size_t>(tiles, (size_t)s.num_sms);
+      IterState* stp = count_changes ? s.st : nullptr;
+      auto go = [&](auto fn) -> int {
+        KM_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        fn<<<grid, sks::kThreads, smem, s.stream>>>(s.X, s.rows, d, s.C[cur], k, s.cnorm, s.labels, stp);
+        KM_CUDA(cudaGetLastError());
+        ++launches;
+        return KM_OK;
+      };
+      if (K == 4) return go(sks::assign_stream_kernel<4>);
+      if (K == 8) return go(sks::assign_stream_kernel<8>);
+      if (K == 12) return go(sks::assign_stream_kernel<12>);
+      return go(sks::assign_stream_kernel<16>);
+    }
+  }
+  if (smallk_ok(false)) {
+    IterState* keep = s.st;
+    if (!count_changes) s.st = nullptr;
+    const int rc = launch_smallk(s, false, (T)1);
+    s.st = keep;
+    return rc;
   }
   return launch_tiles(s, s.X, s.rows, s.labels, MODE_ASSIGN, nullptr, 0, count_changes);
 }

@@ -15,7 +15,8 @@
 namespace km {
 
 constexpr int kSmallKThreads = 256;
-constexpr int kSmallKRpw = 2;  // rows per lane group processed together (shares centroid loads)
+constexpr int kSmallKRpw = 2;        // rows per lane group processed together (shares centroid loads): fused step
+constexpr int kSmallKRpwAssign = 4;  // the same for the E-step alone, which has the registers for it
 
 template <typename T>
 inline size_t smallk_smem_bytes(int K, int d, bool update) {
@@ -26,14 +27,13 @@ inline size_t smallk_smem_bytes(int K, int d, bool update) {
 
 // K: compile-time bound on the number of centroids (k <= K).  V: elements per
 // global load.  rows [blockIdx.x * rows_per_cta, ...) belong to this CTA.
-template <typename T, int K, int V>
-__global__ void __launch_bounds__(kSmallKThreads)
+template <typename T, int K, int V, int RPW>
+__global__ void __launch_bounds__(kSmallKThreads, 2)
 smallk_kernel(const T* __restrict__ X, size_t n, int d, const T* __restrict__ C, int k,
               const T* __restrict__ cnorm, int* __restrict__ labels, IterState* st,
               long long* __restrict__ gsums, unsigned long long* __restrict__ gcounts, T scale,
               int update, unsigned int rows_per_cta) {
   constexpr int NP = Fixed<T>::NP;
-  constexpr int RPW = kSmallKRpw;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* Cs = reinterpret_cast<T*>(smem_raw);                 // [K][d]
   T* cns = Cs + (size_t)K * d;                            // [K]
