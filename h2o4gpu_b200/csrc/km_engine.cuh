@@ -148,7 +148,8 @@ struct Engine : EngineBase {
   int transform_shard(int local, T* out_host, size_t ld);
   int inertia(double* out);
   int allreduce_acc();
-  int relocate_multi(double scale);
+  int relocate_multi(double scale, int seq, int* n_empty);
+  int poll_seq = 0;   // sequence number the finalize kernels publish to pinned memory
   bool tc_ok(int flags) const;
   int tc_refresh(Shard<T>& s);  // split the current centroids for the tensor-core kernel
   int launch_assign(Shard<T>& s, bool use_tc, bool count_changes);
@@ -206,6 +207,7 @@ int Engine<T>::init(int n_local, const int* devs, int rank0, int world, const vo
     KM_CUDA(cudaMemset(s.st, 0, sizeof(IterState)));
     KM_CUDA(km_malloc(&s.xstat, 2 * sizeof(double)));
     KM_CUDA(cudaMallocHost(&s.host_pin, 8 * sizeof(double)));
+    std::memset(s.host_pin, 0, 8 * sizeof(double));
     KM_CUDA(km_malloc(&s.cand_val, 1024 * sizeof(double)));
     KM_CUDA(km_malloc(&s.cand_row, 1024 * sizeof(unsigned long long)));
     KM_CUDA(km_malloc(&s.sum_partials, 1024 * sizeof(double)));

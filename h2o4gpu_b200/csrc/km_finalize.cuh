@@ -80,7 +80,7 @@ cnorm_kernel(const T* __restrict__ C, int k, int d, T* __restrict__ cnorm, doubl
 // `empties` receives the ids of the empty clusters in ascending order.
 __global__ void __launch_bounds__(256)
 prepare_kernel(const unsigned long long* __restrict__ gcounts, int k, IterState* st,
-               int* __restrict__ empties, int* __restrict__ host_n_empty) {
+               int* __restrict__ empties, int* __restrict__ host_n_empty, int* __restrict__ host_seq, int seq) {
   __shared__ int s_n;
   __shared__ unsigned long long s_best[256];
   __shared__ int s_idx[256];
@@ -113,11 +113,16 @@ prepare_kernel(const unsigned long long* __restrict__ gcounts, int k, IterState*
     st->argmax_count = s_idx[0];
     st->n_empty = s_n;
     st->relocated = 0;
-    if (host_n_empty) *host_n_empty = s_n;
     if (s_n) {
       int e = 0;
       for (int j = 0; j < k; ++j)
         if (gcounts[j] == 0) empties[e++] = j;
+    }
+    if (host_n_empty) *host_n_empty = s_n;
+    if (host_seq) {
+      // the host polls this word (pinned memory) instead of synchronising the stream
+      __threadfence_system();
+      *reinterpret_cast<volatile int*>(host_seq) = seq;
     }
   }
 }
@@ -356,8 +361,11 @@ __global__ void __launch_bounds__(128)
 average_kernel(const long long* __restrict__ gsums, const unsigned long long* __restrict__ gcounts,
                int k, int d, double inv, const T* __restrict__ C_old, T* __restrict__ C_new,
                T* __restrict__ cnorm, double* __restrict__ shift_k, const IterState* st,
-               double* __restrict__ C_new_double) {
+               double* __restrict__ C_new_double, int only_if_no_empty) {
   constexpr int NP = Fixed<T>::NP;
+  // launched ahead of the host's look at n_empty when several ranks work together: it must
+  // not average sums that still wait for their empty clusters to be repaired
+  if (only_if_no_empty && st->n_empty != 0) return;
   __shared__ double red_n[4], red_s[4];
   const int j = blockIdx.x;
   unsigned long long cnt = gcounts[j];
@@ -399,7 +407,9 @@ __global__ void __launch_bounds__(256)
 iter_close_kernel(const double* __restrict__ shift_k, int k, IterState* st, double* __restrict__ shift_log,
                   unsigned long long* __restrict__ changed_log, int* __restrict__ reloc_log,
                   unsigned int* __restrict__ amb_log, int it,
-                  double* __restrict__ host_shift, unsigned long long* __restrict__ host_changed) {
+                  double* __restrict__ host_shift, unsigned long long* __restrict__ host_changed,
+                  int only_if_no_empty) {
+  if (only_if_no_empty && st->n_empty != 0) return;
   __shared__ double red[256];
   double s = 0;
   for (int j = threadIdx.x; j < k; j += 256) s += shift_k[j];

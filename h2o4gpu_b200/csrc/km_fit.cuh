@@ -57,19 +57,32 @@ int Engine<T>::assign_all(int flags) {
 }
 
 template <typename T>
-int Engine<T>::relocate_multi(double scale) {
+int Engine<T>::relocate_multi(double scale, int seq, int* n_empty) {
   NcclApi* api = NcclApi::get();
   const size_t g = shards.size();
   std::vector<int> E(g, 0);
   for (size_t i = 0; i < g; ++i) {
     Shard<T>& s = shards[i];
     DevGuard gd(s.dev);
-    KM_CUDA(cudaStreamSynchronize(s.stream));
+    // wait for this iteration's prepare kernel by polling the word it writes to pinned memory:
+    // cheaper than a stream synchronisation, and the kernels queued behind it keep the GPU busy
+    volatile int* seqp = reinterpret_cast<volatile int*>(&s.host_pin[3]);
+    const double t0 = now_s();
+    unsigned int spins = 0;
+    while (*seqp != seq) {
+      if ((++spins & 0xfff) == 0) {
+        cudaError_t q = cudaStreamQuery(s.stream);
+        if (q != cudaSuccess && q != cudaErrorNotReady) KM_CUDA(q);
+        if (q == cudaSuccess && *seqp != seq) KM_FAIL(KM_ESTATE, "finalize kernel did not publish its sequence number");
+        if (now_s() - t0 > 30.0) KM_FAIL(KM_ETIMEOUT, "timed out waiting for the iteration's cluster counts");
+      }
+    }
     E[i] = *reinterpret_cast<volatile int*>(&s.host_pin[2]);
   }
   for (size_t i = 1; i < g; ++i)
     if (E[i] != E[0]) KM_FAIL(KM_ESTATE, "shards disagree on the number of empty clusters");
   const int ne = E[0];
+  *n_empty = ne;
   if (ne == 0) return KM_OK;
   const size_t rec_bytes = (size_t)ne * 24 + (size_t)ne * d * sizeof(T);
   std::vector<unsigned char*> rec(g, nullptr), all(g, nullptr);
@@ -226,12 +239,14 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
       }
     }
     if (rc != KM_OK) break;
+    const int seq = ++poll_seq;
     if (multi && (rc = allreduce_from(delta)) != KM_OK) break;
     for (size_t i = 0; i < shards.size() && rc == KM_OK; ++i) {
       Shard<T>& s = shards[i];
       DevGuard g(s.dev);
       prepare_kernel<<<1, 256, 0, s.stream>>>(s.counts(k, d), k, s.st, s.empties,
-                                             reinterpret_cast<int*>(&s.host_pin[2]));
+                                             reinterpret_cast<int*>(&s.host_pin[2]),
+                                             reinterpret_cast<int*>(&s.host_pin[3]), seq);
       ++launches;
       if (!multi) {
         launch_rowdist(s, 0);
@@ -255,21 +270,39 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
       }
     }
     if (rc != KM_OK) break;
-    if (multi && (rc = relocate_multi((double)scale)) != KM_OK) break;
-    for (size_t i = 0; i < shards.size() && rc == KM_OK; ++i) {
-      Shard<T>& s = shards[i];
-      DevGuard g(s.dev);
-      average_kernel<T><<<k, 128, 0, s.stream>>>(s.sums(), s.counts(k, d), k, d, inv, s.C[cur], s.C[cur ^ 1], s.cnorm,
-                                               s.shift_k, s.st, s.Cd[cur ^ 1]);
-      iter_close_kernel<<<1, 256, 0, s.stream>>>(s.shift_k, k, s.st, s.shift_log, s.changed_log, s.reloc_log,
-                                                 s.amb_log, it,
-                                                 &s.host_pin[0], reinterpret_cast<unsigned long long*>(&s.host_pin[1]));
-      launches += 2;
-      if (i == 0) cudaEventRecord(ev[4 * it + 3], s.stream);
-      cudaError_t ce = cudaGetLastError();
-      if (ce != cudaSuccess) { set_error(std::string("iteration launch: ") + cudaGetErrorString(ce)); rc = KM_ECUDA; }
+    // Several ranks: whether an empty cluster must be repaired is known on the host only (the
+    // repair needs a collective).  The averaging kernels are queued first, told to do nothing if
+    // a cluster is empty; then the host reads the count, and only in that rare case repairs and
+    // queues them again.  One rank: the repair kernels ran in the stream already.
+    auto close_iteration = [&](int only_if_no_empty) {
+      for (size_t i = 0; i < shards.size() && rc == KM_OK; ++i) {
+        Shard<T>& s = shards[i];
+        DevGuard g(s.dev);
+        average_kernel<T><<<k, 128, 0, s.stream>>>(s.sums(), s.counts(k, d), k, d, inv, s.C[cur], s.C[cur ^ 1],
+                                                 s.cnorm, s.shift_k, s.st, s.Cd[cur ^ 1], only_if_no_empty);
+        iter_close_kernel<<<1, 256, 0, s.stream>>>(s.shift_k, k, s.st, s.shift_log, s.changed_log, s.reloc_log,
+                                                   s.amb_log, it, &s.host_pin[0],
+                                                   reinterpret_cast<unsigned long long*>(&s.host_pin[1]),
+                                                   only_if_no_empty);
+        launches += 2;
+        cudaError_t ce = cudaGetLastError();
+        if (ce != cudaSuccess) { set_error(std::string("iteration launch: ") + cudaGetErrorString(ce)); rc = KM_ECUDA; }
+      }
+    };
+    if (multi) {
+      close_iteration(1);
+      if (rc != KM_OK) break;
+      int ne = 0;
+      if ((rc = relocate_multi((double)scale, seq, &ne)) != KM_OK) break;
+      if (ne > 0) close_iteration(0);
+    } else {
+      close_iteration(0);
     }
     if (rc != KM_OK) break;
+    {
+      DevGuard g(s0.dev);
+      cudaEventRecord(ev[4 * it + 3], s0.stream);
+    }
     cur ^= 1;
     if (use_tc) {
       for (size_t i = 0; i < shards.size() && rc == KM_OK; ++i) {
