@@ -425,6 +425,29 @@ def test_staged_upload_of_a_pageable_matrix(eng):
     assert abs(total - (X.astype(np.float64) ** 2).sum()) <= 1e-12 * total
 
 
+def test_bitmap_fed_incremental_sums_in_a_child_process(built_lib):
+    """The optional variant that feeds the incremental M-step from the E-step's moved-rows bit map
+    (environment switch, read once per process) gives the same bits as the full pass."""
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import numpy as np\n"
+        "from h2o4gpu_b200 import engine, synth\n"
+        "X, init, _ = synth.c2(n=60000)\n"
+        "outs = []\n"
+        "for flags in (0, engine.FIT_FULL_SUMS):\n"
+        "    h = engine.ResidentKMeans(); h.upload(X); h.fit(init, 12, flags=flags)\n"
+        "    outs.append((h.centroids(), h.labels(), h.stats()['incremental_iterations'])); h.close()\n"
+        "assert outs[0][2] > 0 and outs[1][2] == 0\n"
+        "assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])\n"
+        "print('bitmap ok')\n")
+    env = dict(os.environ, H2O4GPU_KM_DELTA_BITMAP="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "bitmap ok" in r.stdout, r.stdout + r.stderr
+
+
 def test_memory_pool_trim_and_reuse(eng, built_lib):
     """Buffers come from a per-device pool that keeps freed memory; trimming it leaves the library usable."""
     from h2o4gpu_b200 import synth
