@@ -148,7 +148,6 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
 
   const bool fused = smallk_ok(true) && !(flags & KM_FIT_FORCE_SPLIT);
   const bool use_tc = !fused && tc_ok(flags);
-  if (const char* e = std::getenv("H2O4GPU_KM_TC_MASK_HI")) tc_mask_hi = std::atoi(e);
   if (const char* e = std::getenv("H2O4GPU_KM_TC_TOL")) tc_tol_rel = (float)std::atof(e);
   // incremental M-step (km_accumulate_delta.cuh): on unless the caller or the environment asks
   // for a full recomputation every iteration; a shard switches to it, on the device, in the
