@@ -24,6 +24,7 @@
 #include "km_common.cuh"
 #include "km_finalize.cuh"
 #include "km_nccl.h"
+#include "km_push.cuh"
 #include "km_refine.cuh"
 #include "km_smallk.cuh"
 #include "km_smallk_stream.cuh"
@@ -98,6 +99,7 @@ struct Shard {
   double* xstat = nullptr;  // device: [0] max|x| ; int flag behind it
   double* host_pin = nullptr;  // pinned: [0] shift, [1] changed (as u64), [2] n_empty etc.
   ncclComm_t comm = nullptr;
+  PushState push;   // one-shot push all-reduce over peer memory (several ranks, small tables)
   bool x_checked = false;
   double xmax = 0;
 
@@ -177,6 +179,9 @@ struct Engine : EngineBase {
       rowdist_kernel<T, 1><<<s.num_sms * 8, 256, 0, s.stream>>>(s.X, s.rows, d, s.labels, cd, s.dist, s.st, force);
   }
   int allreduce_from(bool from_pure);
+  int push_setup(size_t count);
+  void push_release();
+  bool push_failed = false;   // set-up was tried and is not available: stay with NCCL
   bool smallk_ok(bool update) const;
   bool vec_ok(const Shard<T>& s) const {
     constexpr int V = VecOf<T>::N;
@@ -249,6 +254,7 @@ int Engine<T>::init(int n_local, const int* devs, int rank0, int world, const vo
 template <typename T>
 void Engine<T>::destroy() {
   upload_wait();
+  push_release();
   for (auto& s : shards) {
     if (s.dev < 0) continue;
     DevGuard g(s.dev);
@@ -931,6 +937,31 @@ int Engine<T>::allreduce_acc() { return allreduce_from(false); }
 template <typename T>
 int Engine<T>::allreduce_from(bool from_pure) {
   if (world_size <= 1) return KM_OK;
+  {
+    const size_t count = shards[0].gacc_count(k, d);
+    static const bool push_env = [] {
+      const char* e = std::getenv("H2O4GPU_KM_PUSH_ALLREDUCE");
+      return !(e && e[0] == '0');
+    }();
+    if (push_env && !push_failed && count * sizeof(long long) <= kPushMaxBytes) {
+      if (!shards[0].push.ready || shards[0].push.count != count) {
+        if (push_setup(count) != KM_OK) { push_release(); push_failed = true; }
+      }
+      if (!push_failed) {
+        const unsigned int seq = (unsigned int)poll_seq;   // one value per iteration, the same on every rank
+        for (size_t i = 0; i < shards.size(); ++i) {
+          Shard<T>& s = shards[i];
+          DevGuard g(s.dev);
+          push_allreduce_kernel<<<kPushCtas, kPushThreads, 0, s.stream>>>(
+              from_pure ? s.pacc : s.gacc, s.gacc, count, world_rank0 + (int)i, world_size, s.push.d_peer_mailbox,
+              s.push.d_peer_flags, s.push.mailbox, s.push.flags, s.push.done, seq, s.st);
+          KM_CUDA(cudaGetLastError());
+          ++launches;
+        }
+        return KM_OK;
+      }
+    }
+  }
   NcclApi* api = NcclApi::get();
   KM_NCCL(api, api->GroupStart());
   for (auto& s : shards)
@@ -993,4 +1024,180 @@ int Engine<T>::launch_delta(Shard<T>& s, T scale, const unsigned long long* gate
   return KM_OK;
 }
 
+// Mailboxes of all ranks mapped into every local device.  Ranks of this process are reached
+// through peer access, ranks of other processes through CUDA IPC handles gathered with NCCL.
+// The mailboxes come from cudaMalloc, not from the pool: pool memory cannot be exported.
+template <typename T>
+int Engine<T>::push_setup(size_t count) {
+  push_release();
+  NcclApi* api = NcclApi::get();
+  if (!api || !api->AllGather) return KM_ENCCL;
+  const int W = world_size;
+  const size_t g = shards.size();
+  struct Handles { cudaIpcMemHandle_t mailbox, flags; };
+  std::vector<Handles> all((size_t)W);
+  // A rank that fails locally still walks through the collectives below, and the last one
+  // tells everybody: either all ranks push or all stay with NCCL.
+  bool ok = true;
+  // 1. allocate, clear, export
+  for (size_t i = 0; i < g; ++i) {
+    Shard<T>& s = shards[i];
+    DevGuard gd(s.dev);
+    PushState& ps = s.push;
+    ps.count = count;
+    ps.world = W;
+    ps.peers.assign((size_t)W, PushPeer());
+    const size_t mb = (size_t)2 * W * count * sizeof(long long), fb = (size_t)2 * W * sizeof(unsigned int);
+    if (cudaMalloc(&ps.done, sizeof(unsigned int)) != cudaSuccess) { cudaGetLastError(); return KM_ENOMEM; }
+    if (cudaMalloc(&ps.mailbox, mb) != cudaSuccess || cudaMalloc(&ps.flags, fb) != cudaSuccess ||
+        cudaMalloc(&ps.d_peer_mailbox, W * sizeof(long long*)) != cudaSuccess ||
+        cudaMalloc(&ps.d_peer_flags, W * sizeof(unsigned int*)) != cudaSuccess) {
+      cudaGetLastError();
+      ok = false;
+      continue;
+    }
+    cudaMemsetAsync(ps.mailbox, 0, mb, s.stream);
+    cudaMemsetAsync(ps.flags, 0, fb, s.stream);
+    Handles& h = all[(size_t)world_rank0 + i];
+    if (cudaIpcGetMemHandle(&h.mailbox, ps.mailbox) != cudaSuccess ||
+        cudaIpcGetMemHandle(&h.flags, ps.flags) != cudaSuccess) {
+      cudaGetLastError();
+      ok = false;
+    }
+  }
+  // 2. every rank's handles to every process (device buffers, one all-gather per local shard)
+  if ((int)g != W) {
+    std::vector<unsigned char*> d_send(g, nullptr), d_recv(g, nullptr);
+    bool bufs = true;
+    for (size_t i = 0; i < g; ++i) {
+      DevGuard gd(shards[i].dev);
+      if (cudaMalloc(&d_send[i], sizeof(Handles)) != cudaSuccess ||
+          cudaMalloc(&d_recv[i], sizeof(Handles) * W) != cudaSuccess) { cudaGetLastError(); bufs = false; break; }
+      cudaMemcpyAsync(d_send[i], &all[(size_t)world_rank0 + i], sizeof(Handles), cudaMemcpyHostToDevice,
+                      shards[i].stream);
+    }
+    if (!bufs) return KM_ENOMEM;   // cannot even take part in the exchange: a collective failure
+    ncclResult_t nr = api->GroupStart();
+    for (size_t i = 0; i < g && nr == ncclSuccess; ++i)
+      nr = api->AllGather(d_send[i], d_recv[i], sizeof(Handles), ncclChar, shards[i].comm, shards[i].stream);
+    if (nr == ncclSuccess) nr = api->GroupEnd();
+    int rc = (nr == ncclSuccess) ? KM_OK : KM_ENCCL;
+    if (rc == KM_OK) {
+      DevGuard gd(shards[0].dev);
+      if (cudaMemcpyAsync(all.data(), d_recv[0], sizeof(Handles) * W, cudaMemcpyDeviceToHost, shards[0].stream) !=
+              cudaSuccess ||
+          cudaStreamSynchronize(shards[0].stream) != cudaSuccess) rc = KM_ECUDA;
+    }
+    for (size_t i = 0; i < g; ++i) {
+      DevGuard gd(shards[i].dev);
+      cudaStreamSynchronize(shards[i].stream);
+      cudaFree(d_send[i]);
+      cudaFree(d_recv[i]);
+    }
+    if (rc != KM_OK) return rc;
+  }
+  // 3. map every rank's mailbox into every local device
+  for (size_t i = 0; i < g && ok; ++i) {
+    Shard<T>& s = shards[i];
+    DevGuard gd(s.dev);
+    PushState& ps = s.push;
+    std::vector<long long*> pm((size_t)W);
+    std::vector<unsigned int*> pf((size_t)W);
+    for (int r = 0; r < W && ok; ++r) {
+      const int local = r - world_rank0;
+      PushPeer& pp = ps.peers[(size_t)r];
+      if (local >= 0 && local < (int)g) {
+        Shard<T>& o = shards[(size_t)local];
+        if (o.dev != s.dev) {
+          int can = 0;
+          if (cudaDeviceCanAccessPeer(&can, s.dev, o.dev) != cudaSuccess || !can) { cudaGetLastError(); ok = false; break; }
+          cudaError_t pe = cudaDeviceEnablePeerAccess(o.dev, 0);
+          cudaGetLastError();
+          if (pe != cudaSuccess && pe != cudaErrorPeerAccessAlreadyEnabled) { ok = false; break; }
+        }
+        pp.mailbox = o.push.mailbox;
+        pp.flags = o.push.flags;
+      } else {
+        void* a = nullptr;
+        void* b = nullptr;
+        if (cudaIpcOpenMemHandle(&a, all[(size_t)r].mailbox, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+          cudaGetLastError();
+          ok = false;
+          break;
+        }
+        pp.mailbox = static_cast<long long*>(a);
+        pp.ipc_mailbox = true;
+        if (cudaIpcOpenMemHandle(&b, all[(size_t)r].flags, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+          cudaGetLastError();
+          ok = false;
+          break;
+        }
+        pp.flags = static_cast<unsigned int*>(b);
+        pp.ipc_flags = true;
+      }
+      pm[(size_t)r] = pp.mailbox;
+      pf[(size_t)r] = pp.flags;
+    }
+    if (!ok) break;
+    if (cudaMemcpyAsync(ps.d_peer_mailbox, pm.data(), W * sizeof(long long*), cudaMemcpyHostToDevice, s.stream) !=
+            cudaSuccess ||
+        cudaMemcpyAsync(ps.d_peer_flags, pf.data(), W * sizeof(unsigned int*), cudaMemcpyHostToDevice, s.stream) !=
+            cudaSuccess ||
+        cudaStreamSynchronize(s.stream) != cudaSuccess) {
+      cudaGetLastError();
+      ok = false;
+    }
+  }
+  // 4. agreement and barrier in one collective: the sum of the ranks' failure words.  Nobody
+  // pushes before every mailbox is cleared and mapped, and nobody pushes unless everybody can.
+  unsigned int failures = 0;
+  {
+    for (size_t i = 0; i < g; ++i) {
+      DevGuard gd(shards[i].dev);
+      const unsigned int mine = ok ? 0u : 1u;
+      KM_CUDA(cudaMemcpyAsync(shards[i].push.done, &mine, sizeof(mine), cudaMemcpyHostToDevice, shards[i].stream));
+      KM_CUDA(cudaStreamSynchronize(shards[i].stream));
+    }
+    ncclResult_t nr = api->GroupStart();
+    for (size_t i = 0; i < g && nr == ncclSuccess; ++i)
+      nr = api->AllReduce(shards[i].push.done, shards[i].push.done, 1, ncclUint32, ncclSum, shards[i].comm,
+                          shards[i].stream);
+    if (nr == ncclSuccess) nr = api->GroupEnd();
+    if (nr != ncclSuccess) return KM_ENCCL;
+    for (size_t i = 0; i < g; ++i) {
+      DevGuard gd(shards[i].dev);
+      unsigned int f = 0;
+      KM_CUDA(cudaMemcpyAsync(&f, shards[i].push.done, sizeof(f), cudaMemcpyDeviceToHost, shards[i].stream));
+      KM_CUDA(cudaMemsetAsync(shards[i].push.done, 0, sizeof(unsigned int), shards[i].stream));
+      KM_CUDA(cudaStreamSynchronize(shards[i].stream));
+      failures += f;
+    }
+  }
+  if (failures != 0) {
+    log_msg(verbose, 300, "push all-reduce not available on %u rank(s): staying with NCCL", failures);
+    return KM_ESTATE;
+  }
+  for (auto& s : shards) s.push.ready = true;
+  return KM_OK;
+}
+
+template <typename T>
+void Engine<T>::push_release() {
+  for (auto& s : shards) {
+    if (s.dev < 0) continue;
+    DevGuard gd(s.dev);
+    PushState& ps = s.push;
+    if (s.stream) cudaStreamSynchronize(s.stream);
+    for (auto& pp : ps.peers) {
+      if (pp.ipc_mailbox && pp.mailbox) cudaIpcCloseMemHandle(pp.mailbox);
+      if (pp.ipc_flags && pp.flags) cudaIpcCloseMemHandle(pp.flags);
+    }
+    ps.peers.clear();
+    cudaFree(ps.mailbox); cudaFree(ps.flags); cudaFree(ps.done); cudaFree(ps.d_peer_mailbox); cudaFree(ps.d_peer_flags);
+    cudaGetLastError();
+    ps = PushState();
+  }
+}
+
 }  // namespace km
+
