@@ -11,6 +11,12 @@
 // independent of the order of additions, so it is deterministic without sorting.
 // With one slice (k*d small) the CTA streams its partition as a flat array; with
 // several slices each warp compacts the in-slice rows of 32-row blocks first.
+//
+// Sample weights (W != null; the sklearn-style fit(X, sample_weight=w) of the wrapper,
+// src/interface_py/h2o4gpu/solvers/kmeans.py:800-804, which the reference hands to the CPU):
+// a row adds w * x to the sums and its weight to the count.  The weight enters the count as a
+// two-piece fixed-point number (30 bits below the largest weight), so weighted counts are
+// integers too and stay order-independent; `scale` then covers |w * x|.
 #pragma once
 
 #include "km_common.cuh"
@@ -22,7 +28,7 @@ constexpr int kAccThreads = 512;
 
 template <typename T>
 inline size_t accumulate_smem_bytes(int kc, int d) {
-  return (size_t)Fixed<T>::NP * kc * d * sizeof(int) + (size_t)kc * sizeof(int) + 16;
+  return (size_t)Fixed<T>::NP * kc * d * sizeof(int) + (size_t)2 * kc * sizeof(int) + 16;
 }
 
 // divisor for idx / dv with idx * dv < 2^40: q = (idx * magic) >> 40
@@ -34,12 +40,13 @@ accumulate_kernel(const T* __restrict__ X, size_t n, int d, const int* __restric
                   int kc, int n_slices, long long* __restrict__ gsums,
                   unsigned long long* __restrict__ gcounts, T scale, unsigned int rows_per_part,
                   unsigned long long dv_magic,
-                  const unsigned long long* gate_changed, unsigned long long gate_limit) {
+                  const unsigned long long* gate_changed, unsigned long long gate_limit,
+                  const T* __restrict__ W, T wscale) {
   constexpr int NP = Fixed<T>::NP;
   if (delta_turn(gate_changed, gate_limit)) return;   // the incremental branch has this iteration
   extern __shared__ __align__(16) unsigned char smem_raw[];
   int* acc = reinterpret_cast<int*>(smem_raw);   // [NP][kc][d]
-  int* cnt = acc + (size_t)NP * kc * d;          // [kc]
+  int* cnt = acc + (size_t)NP * kc * d;          // [2][kc]: units, then units * 2^15
 
   const int tid = threadIdx.x;
   const int slice = blockIdx.x % n_slices;
@@ -55,11 +62,22 @@ accumulate_kernel(const T* __restrict__ X, size_t n, int d, const int* __restric
   const size_t pstride = (size_t)kc * d;
 
   for (int i = tid; i < NP * kc * d; i += kAccThreads) acc[i] = 0;
-  for (int i = tid; i < kc; i += kAccThreads) cnt[i] = 0;
+  for (int i = tid; i < 2 * kc; i += kAccThreads) cnt[i] = 0;
   __syncthreads();
 
   const T* Xp = X + r0 * (size_t)d;
   const int* Lp = labels + r0;
+  const T* Wp = W ? W + r0 : nullptr;
+  auto count_row = [&](int c, T w) {
+    if (Wp) {
+      int p[2];
+      split_pieces<2>(w, wscale, p);
+      if (p[1]) atomicAdd(&cnt[c], p[1]);
+      if (p[0]) atomicAdd(&cnt[kc + c], p[0]);
+    } else {
+      atomicAdd(&cnt[c], 1);
+    }
+  };
 
   if (n_slices == 1) {
     // flat stream over the partition: item = one vector of V elements
@@ -79,8 +97,13 @@ accumulate_kernel(const T* __restrict__ X, size_t n, int d, const int* __restric
           rowu[u] = row;
           VecLoad<T, V>::ld(Xp + (size_t)idx * V, x[u]);
           lab[u] = Lp[row];
+          const T w = Wp ? Wp[row] : (T)1;
           if ((unsigned)lab[u] >= (unsigned)k) lab[u] = -1;  // cannot come from the E-step kernels; skipped
-          else if (col[u] == 0) atomicAdd(&cnt[lab[u]], 1);
+          else if (col[u] == 0) count_row(lab[u], w);
+          if (Wp) {
+#pragma unroll
+            for (int e = 0; e < V; ++e) x[u][e] *= w;
+          }
         }
       }
 #pragma unroll
@@ -103,17 +126,23 @@ accumulate_kernel(const T* __restrict__ X, size_t n, int d, const int* __restric
       int my = (r < nrows) ? Lp[r] : -1;
       bool in = (my >= c0 && my < c1);
       unsigned int mask = __ballot_sync(0xffffffffu, in);
-      if (in) atomicAdd(&cnt[my - c0], 1);
+      const T myw = (Wp && r < nrows) ? Wp[r] : (T)1;
+      if (in) count_row(my - c0, myw);
       while (mask) {
         unsigned int src = __fns(mask, 0, g + 1);  // lane of the (g+1)-th in-slice row
         bool have = (src != 0xffffffffu);
         int lab = __shfl_sync(0xffffffffu, my, have ? src : 0);
+        const T w = __shfl_sync(0xffffffffu, myw, have ? src : 0);
         if (have) {
           const T* xr = Xp + (size_t)(b + src) * d;
           int* a = acc + (size_t)(lab - c0) * d;
           for (int idx = l; idx < dv; idx += lpr) {
             T x[V];
             VecLoad<T, V>::ld(xr + (size_t)idx * V, x);
+            if (Wp) {
+#pragma unroll
+              for (int e = 0; e < V; ++e) x[e] *= w;
+            }
             add_vec_fixed<T, V, NP>(a, pstride, dv, idx, g & (V - 1), x, scale);
           }
         }
@@ -135,8 +164,10 @@ accumulate_kernel(const T* __restrict__ X, size_t n, int d, const int* __restric
                        (unsigned long long)v);
     }
   }
-  for (int i = tid; i < kloc; i += kAccThreads)
-    if (cnt[i]) atomicAdd(gcounts + c0 + i, (unsigned long long)cnt[i]);
+  for (int i = tid; i < kloc; i += kAccThreads) {
+    const long long v = (long long)cnt[kc + i] * (1LL << kPieceBits) + (long long)cnt[i];
+    if (v) atomicAdd(gcounts + c0 + i, (unsigned long long)v);
+  }
 }
 
 }  // namespace km

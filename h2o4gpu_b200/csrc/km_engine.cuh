@@ -18,6 +18,8 @@
 #include <thread>
 #include <vector>
 
+#include <cuda_fp16.h>
+
 #include "km_accumulate.cuh"
 #include "km_accumulate_sorted.cuh"
 #include "km_accumulate_delta.cuh"
@@ -69,6 +71,10 @@ struct Shard {
   cudaStream_t stream = nullptr;
   const T* X = nullptr;
   T* X_owned = nullptr;
+  T* w = nullptr;             // sample weights of the shard's rows (weighted fits), or null
+  size_t w_cap = 0;
+  void* raw = nullptr;        // bytes of an upload in another element type, until they are converted
+  int raw_dtype = -1;
   size_t rows = 0, row0 = 0;
   int* labels = nullptr;
   size_t labels_cap = 0;
@@ -135,8 +141,20 @@ struct Engine : EngineBase {
   int attach_device(int local, const T* dX, size_t rows, size_t cols, size_t ntot);
   // wait = false: the copies may still be in flight on return (host threads staging a pageable
   // matrix, or DMA from a pinned one); upload_wait() completes them
-  int upload_host(const T* X, size_t rows, size_t cols, char order, bool wait = true);
+  int upload_host(const T* X, size_t rows, size_t cols, char order, bool wait = true) {
+    return upload_host_typed(X, sizeof(T) == 8 ? KM_DTYPE_F64 : KM_DTYPE_F32, rows, cols, order, wait);
+  }
+  // the same for a host matrix of any supported element type: the bytes go down as they are
+  // and a kernel converts them into T
+  int upload_host_typed(const void* X, int src_dtype, size_t rows, size_t cols, char order, bool wait = true);
   int upload_wait();
+  // Sample weights of all local rows, shard after shard (null: back to unit weights).  They must
+  // be finite and non-negative with a positive maximum.  Attaching other data drops them.
+  int set_sample_weight(const T* host_w, size_t count);
+  bool weighted = false;
+  double wmax = 0;          // largest weight over all ranks
+  double w_scale = 1;       // 2^(15 - e), wmax < 2^e: a weight counts as rint(w * w_scale * 2^15) units
+  double count_unit = 1;    // weight of one unit of the counts (1 without weights)
   int preallocate(int k_, int max_iter);
   std::vector<std::thread> upload_threads;
   std::atomic<int> upload_error{0};
@@ -266,7 +284,7 @@ void Engine<T>::destroy() {
     s.tcp.release();
     s.tcbp.release();
     km_free(s.amb_rows); km_free(s.amb_near); km_free(s.amb_log);
-    km_free(s.X_owned); km_free(s.labels); km_free(s.dist); km_free(s.gacc);
+    km_free(s.X_owned); km_free(s.raw); km_free(s.w); km_free(s.labels); km_free(s.dist); km_free(s.gacc);
     km_free(s.pacc); km_free(s.pflush); km_free(s.labels_prev); km_free(s.moved_bits);
     km_free(s.C[0]); km_free(s.C[1]); km_free(s.Cd[0]); km_free(s.Cd[1]); km_free(s.cnorm); km_free(s.shift_k); km_free(s.empties);
     km_free(s.st); km_free(s.cand_val); km_free(s.cand_row); km_free(s.sum_partials);
@@ -289,6 +307,7 @@ int Engine<T>::attach_device(int local, const T* dX, size_t rows, size_t cols, s
   s.X = dX;
   s.rows = rows;
   s.x_checked = false;
+  weighted = false;
   if ((int)cols != d) have_centroids = false;
   d = (int)cols;
   n_total = ntot;
@@ -302,22 +321,79 @@ int Engine<T>::attach_device(int local, const T* dX, size_t rows, size_t cols, s
   return KM_OK;
 }
 
-template <typename T>
-__global__ void transpose_cm_kernel(const T* __restrict__ src, T* __restrict__ dst, size_t rows, int cols) {
-  // src: column-major rows x cols (leading dimension rows) -> dst row-major
+// ---- element types a host matrix may arrive in -----------------------------------
+inline size_t dtype_size(int dt) {
+  switch (dt) {
+    case KM_DTYPE_F32: case KM_DTYPE_I32: case KM_DTYPE_U32: return 4;
+    case KM_DTYPE_F64: case KM_DTYPE_I64: case KM_DTYPE_U64: return 8;
+    case KM_DTYPE_F16: case KM_DTYPE_I16: case KM_DTYPE_U16: return 2;
+    case KM_DTYPE_I8: case KM_DTYPE_U8: return 1;
+    default: return 0;
+  }
+}
+// value conversion as numpy's astype does it (round to nearest even where the target is narrower)
+template <typename T, typename S> __device__ __forceinline__ T convert_value(S v) { return (T)v; }
+template <> __device__ __forceinline__ float convert_value<float, __half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ double convert_value<double, __half>(__half v) { return (double)__half2float(v); }
+
+// src: column-major rows x cols (leading dimension rows) of S -> dst row-major of T
+template <typename S, typename T>
+__global__ void transpose_cm_kernel(const S* __restrict__ src, T* __restrict__ dst, size_t rows, int cols) {
   __shared__ T tile[32][33];
   size_t r0 = (size_t)blockIdx.x * 32;
   int c0 = blockIdx.y * 32;
   for (int j = threadIdx.y; j < 32; j += 8) {
     size_t r = r0 + threadIdx.x;
     int c = c0 + j;
-    if (r < rows && c < cols) tile[j][threadIdx.x] = src[(size_t)c * rows + r];
+    if (r < rows && c < cols) tile[j][threadIdx.x] = convert_value<T, S>(src[(size_t)c * rows + r]);
   }
   __syncthreads();
   for (int j = threadIdx.y; j < 32; j += 8) {
     size_t r = r0 + j;
     int c = c0 + threadIdx.x;
     if (r < rows && c < cols) dst[r * (size_t)cols + c] = tile[threadIdx.x][j];
+  }
+}
+
+// Row-major matrix of S -> T, element by element: replaces the host-side astype copy of the
+// wrapper (src/interface_py/h2o4gpu/solvers/utils.py:46-96), which for 8-bit data quadruples the
+// bytes that cross the bus.  A thread converts 16 bytes of the source per step.
+template <typename S, typename T>
+__global__ void __launch_bounds__(256)
+convert_rm_kernel(const S* __restrict__ src, T* __restrict__ dst, size_t count) {
+  constexpr int E = 16 / sizeof(S);
+  const size_t nvec = count / E;
+  const bool aligned = (reinterpret_cast<uintptr_t>(src) & 15) == 0;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (aligned) {
+    for (size_t i = tid; i < nvec; i += stride) {
+      union { uint4 q; S e[E]; } u;
+      u.q = __ldcs(reinterpret_cast<const uint4*>(src) + i);
+#pragma unroll
+      for (int e = 0; e < E; ++e) dst[i * E + e] = convert_value<T, S>(u.e[e]);
+    }
+    for (size_t i = nvec * E + tid; i < count; i += stride) dst[i] = convert_value<T, S>(src[i]);
+  } else {
+    for (size_t i = tid; i < count; i += stride) dst[i] = convert_value<T, S>(src[i]);
+  }
+}
+
+template <typename T, typename F>
+inline bool dispatch_dtype(int dt, F&& f) {
+  switch (dt) {
+    case KM_DTYPE_F32: f((const float*)nullptr); return true;
+    case KM_DTYPE_F64: f((const double*)nullptr); return true;
+    case KM_DTYPE_F16: f((const __half*)nullptr); return true;
+    case KM_DTYPE_I8: f((const signed char*)nullptr); return true;
+    case KM_DTYPE_U8: f((const unsigned char*)nullptr); return true;
+    case KM_DTYPE_I16: f((const short*)nullptr); return true;
+    case KM_DTYPE_U16: f((const unsigned short*)nullptr); return true;
+    case KM_DTYPE_I32: f((const int*)nullptr); return true;
+    case KM_DTYPE_U32: f((const unsigned int*)nullptr); return true;
+    case KM_DTYPE_I64: f((const long long*)nullptr); return true;
+    case KM_DTYPE_U64: f((const unsigned long long*)nullptr); return true;
+    default: return false;
   }
 }
 
@@ -387,12 +463,16 @@ inline void stage_worker(int dev, const unsigned char* src, unsigned char* dst, 
 }
 
 template <typename T>
-int Engine<T>::upload_host(const T* X, size_t rows, size_t cols, char order, bool wait) {
-  if (!X || rows == 0 || cols == 0 || cols > (1u << 20)) KM_FAIL(KM_EINVAL, "kmeans_upload_host: bad argument");
+int Engine<T>::upload_host_typed(const void* Xv, int src_dtype, size_t rows, size_t cols, char order, bool wait) {
+  const size_t esz = dtype_size(src_dtype);
+  if (!Xv || rows == 0 || cols == 0 || cols > (1u << 20)) KM_FAIL(KM_EINVAL, "kmeans_upload_host: bad argument");
+  if (esz == 0) KM_FAIL(KM_EINVAL, "kmeans_upload_host_typed: unknown element type");
   if (order != 'r' && order != 'c') KM_FAIL(KM_EINVAL, "kmeans_upload_host: order must be 'r' or 'c'");
   if (world_size != (int)shards.size())
     KM_FAIL(KM_ESTATE, "kmeans_upload_host: one process must own all ranks; use kmeans_attach_device");
   KM_TRY(upload_wait());
+  const bool native = src_dtype == (sizeof(T) == 8 ? KM_DTYPE_F64 : KM_DTYPE_F32);
+  const unsigned char* X = static_cast<const unsigned char*>(Xv);
   upload_t0 = now_s();
   const size_t g = shards.size();
   const size_t per = (rows + g - 1) / g;
@@ -400,7 +480,7 @@ int Engine<T>::upload_host(const T* X, size_t rows, size_t cols, char order, boo
     const char* e = std::getenv("H2O4GPU_KM_STAGED_UPLOAD");
     return !(e && e[0] == '0');
   }();
-  const bool staged = stage_enabled && order == 'r' && rows * cols * sizeof(T) >= ((size_t)64 << 20) &&
+  const bool staged = stage_enabled && order == 'r' && rows * cols * esz >= ((size_t)64 << 20) &&
                       host_pointer_is_pageable(X);
   int workers_per_shard = 0;
   if (staged) {
@@ -426,39 +506,53 @@ int Engine<T>::upload_host(const T* X, size_t rows, size_t cols, char order, boo
     DevGuard gd(s.dev);
     km_free(s.X_owned);
     s.X_owned = nullptr;
-    if (km_malloc(&s.X_owned, r * cols * sizeof(T)) != cudaSuccess) {
+    km_free(s.raw);
+    s.raw = nullptr;
+    // bytes land in the matrix itself when they are T already and row-major, else in a raw
+    // buffer that a kernel converts (and transposes) from
+    const bool direct = native && order == 'r';
+    if (km_malloc(&s.X_owned, r * cols * sizeof(T)) != cudaSuccess ||
+        (!direct && km_malloc(&s.raw, r * cols * esz) != cudaSuccess)) {
       cudaGetLastError();
       upload_wait();
       KM_FAIL(KM_ENOMEM, "kmeans_upload_host: device allocation failed");
     }
+    s.raw_dtype = src_dtype;
+    unsigned char* dst = direct ? reinterpret_cast<unsigned char*>(s.X_owned) : static_cast<unsigned char*>(s.raw);
     if (order == 'r' && workers_per_shard > 0) {
       StagePool& pool = StagePool::get();
       for (int w = 0; w < workers_per_shard; ++w) {
         const size_t b = 2 * (i * workers_per_shard + w);
-        upload_threads.emplace_back(stage_worker, s.dev, reinterpret_cast<const unsigned char*>(X + off * cols),
-                                    reinterpret_cast<unsigned char*>(s.X_owned), r * cols * sizeof(T), (size_t)w,
+        upload_threads.emplace_back(stage_worker, s.dev, X + off * cols * esz, dst, r * cols * esz, (size_t)w,
                                     (size_t)workers_per_shard, pool.bufs[b], pool.bufs[b + 1], &upload_error);
       }
     } else if (order == 'r') {
-      KM_CUDA(cudaMemcpyAsync(s.X_owned, X + off * cols, r * cols * sizeof(T), cudaMemcpyHostToDevice, s.stream));
+      KM_CUDA(cudaMemcpyAsync(dst, X + off * cols * esz, r * cols * esz, cudaMemcpyHostToDevice, s.stream));
     } else {
       // column-major host matrix (leading dimension = total rows): strided copy of the
-      // shard's rows of every column, then a transpose on the device
-      T* tmp = nullptr;
-      KM_CUDA(km_malloc(&tmp, r * cols * sizeof(T)));
-      KM_CUDA(cudaMemcpy2DAsync(tmp, r * sizeof(T), X + off, rows * sizeof(T), r * sizeof(T), cols,
-                                cudaMemcpyHostToDevice, s.stream));
+      // shard's rows of every column, then a converting transpose on the device
+      KM_CUDA(cudaMemcpy2DAsync(dst, r * esz, X + off * esz, rows * esz, r * esz, cols, cudaMemcpyHostToDevice,
+                                s.stream));
       dim3 grid((unsigned)((r + 31) / 32), (unsigned)((cols + 31) / 32));
-      transpose_cm_kernel<T><<<grid, dim3(32, 8), 0, s.stream>>>(tmp, s.X_owned, r, (int)cols);
+      T* out = s.X_owned;
+      cudaStream_t st = s.stream;
+      dispatch_dtype<T>(src_dtype, [&](auto* tag) {
+        using S = std::remove_cv_t<std::remove_pointer_t<decltype(tag)>>;
+        transpose_cm_kernel<S, T><<<grid, dim3(32, 8), 0, st>>>(reinterpret_cast<const S*>(dst), out, r, (int)cols);
+      });
       KM_CUDA(cudaGetLastError());
       KM_CUDA(cudaStreamSynchronize(s.stream));
-      km_free(tmp);
+      km_free(s.raw);
+      s.raw = nullptr;
     }
     KM_TRY(attach_device((int)i, s.X_owned, r, cols, rows));
     s.row0 = off;
     off += r;
   }
-  if (wait) return upload_wait();
+  // a raw row-major buffer is converted once its bytes are down: upload_wait() does that
+  bool pending_raw = false;
+  for (auto& s : shards) pending_raw = pending_raw || s.raw != nullptr;
+  if (wait || pending_raw) return upload_wait();
   return KM_OK;
 }
 
@@ -471,10 +565,24 @@ int Engine<T>::upload_wait() {
     StagePool::get().busy.unlock();
     upload_pool_locked = false;
   }
+  const bool copy_failed = upload_error.load() != 0;
   for (auto& s : shards) {
     if (!s.stream) continue;
     DevGuard gd(s.dev);
+    if (s.raw && !copy_failed && s.X_owned) {
+      const size_t count = s.rows * (size_t)d;
+      T* out = s.X_owned;
+      const void* raw = s.raw;
+      cudaStream_t st = s.stream;
+      const int grid = s.num_sms * 8;
+      dispatch_dtype<T>(s.raw_dtype, [&](auto* tag) {
+        using S = std::remove_cv_t<std::remove_pointer_t<decltype(tag)>>;
+        convert_rm_kernel<S, T><<<grid, 256, 0, st>>>(static_cast<const S*>(raw), out, count);
+      });
+      KM_CUDA(cudaGetLastError());
+    }
     KM_CUDA(cudaStreamSynchronize(s.stream));
+    if (s.raw) { km_free(s.raw); s.raw = nullptr; }
   }
   if (upload_t0 > 0) { stats.seconds_upload = now_s() - upload_t0; upload_t0 = 0; }
   if (upload_error.exchange(0) != 0) KM_FAIL(KM_ECUDA, "kmeans_upload_host: a staged copy failed");
@@ -553,6 +661,79 @@ int Engine<T>::ensure_buffers(int k_) {
       s.d_cap = d;
     }
   }
+  return KM_OK;
+}
+
+// max of the weights and a flag for a negative or non-finite one
+template <typename T>
+__global__ void __launch_bounds__(256)
+weight_stat_kernel(const T* __restrict__ w, size_t n, double* __restrict__ out_max, int* __restrict__ out_bad) {
+  double m = 0;
+  int bad = 0;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const double a = (double)w[i];
+    bad |= !(a >= 0.0 && a <= 1.7976931348623157e308);
+    m = fmax(m, a);
+  }
+  m = warp_max(m);
+  bad = __any_sync(0xffffffffu, bad);
+  if ((threadIdx.x & 31) == 0) {
+    if (m > 0) atomicMax(reinterpret_cast<unsigned long long*>(out_max), (unsigned long long)__double_as_longlong(m));
+    if (bad) atomicOr(out_bad, 1);
+  }
+}
+
+template <typename T>
+int Engine<T>::set_sample_weight(const T* host_w, size_t count) {
+  if (!host_w) { weighted = false; return KM_OK; }
+  size_t local = 0;
+  for (auto& s : shards) {
+    if (!s.X) KM_FAIL(KM_ESTATE, "kmeans_set_sample_weight: attach the data first");
+    local += s.rows;
+  }
+  if (count != local) KM_FAIL(KM_EINVAL, "kmeans_set_sample_weight: one weight per local row expected");
+  weighted = false;   // a refused set of weights leaves unit weights behind
+  KM_TRY(upload_wait());
+  size_t off = 0;
+  for (auto& s : shards) {
+    DevGuard g(s.dev);
+    if (s.w_cap < s.rows) {
+      km_free(s.w);
+      s.w = nullptr;
+      KM_CUDA(km_malloc(&s.w, s.rows * sizeof(T)));
+      s.w_cap = s.rows;
+    }
+    KM_CUDA(cudaMemcpyAsync(s.w, host_w + off, s.rows * sizeof(T), cudaMemcpyHostToDevice, s.stream));
+    KM_CUDA(cudaMemsetAsync(s.xstat, 0, 2 * sizeof(double), s.stream));
+    weight_stat_kernel<T><<<s.num_sms * 4, 256, 0, s.stream>>>(s.w, s.rows, s.xstat, reinterpret_cast<int*>(s.xstat + 1));
+    KM_CUDA(cudaGetLastError());
+    off += s.rows;
+  }
+  if (world_size > 1) {
+    NcclApi* api = NcclApi::get();
+    KM_NCCL(api, api->GroupStart());
+    for (auto& s : shards) KM_NCCL(api, api->AllReduce(s.xstat, s.xstat, 2, ncclDouble, ncclMax, s.comm, s.stream));
+    KM_NCCL(api, api->GroupEnd());
+  }
+  double m = 0;
+  for (auto& s : shards) {
+    DevGuard g(s.dev);
+    double h[2];
+    KM_CUDA(cudaMemcpyAsync(h, s.xstat, sizeof(h), cudaMemcpyDeviceToHost, s.stream));
+    KM_CUDA(cudaStreamSynchronize(s.stream));
+    long long flag;
+    std::memcpy(&flag, &h[1], sizeof(flag));
+    if (flag != 0) KM_FAIL(KM_EINVAL, "sample weights must be finite and non-negative");
+    m = std::max(m, h[0]);
+  }
+  if (!(m > 0)) KM_FAIL(KM_EINVAL, "sample weights are all zero");
+  int e = 0;
+  std::frexp(m, &e);
+  if (sizeof(T) == 4 && (e > 100 || e < -100)) KM_FAIL(KM_EINVAL, "sample weights outside the supported range");
+  wmax = m;
+  w_scale = std::ldexp(1.0, kPieceBits - e);
+  count_unit = std::ldexp(1.0, -(2 * kPieceBits - e));
+  weighted = true;
   return KM_OK;
 }
 
@@ -785,12 +966,13 @@ int Engine<T>::launch_accumulate(Shard<T>& s, T scale, long long* dst, const uns
   constexpr int NP = Fixed<T>::NP;
   long long* gs = dst ? dst : s.sums();
   unsigned long long* gc = reinterpret_cast<unsigned long long*>(gs + (size_t)(NP / 2) * k * d);
-  {
+  const T* W = weighted ? s.w : nullptr;
+  if (!W) {
     bool done = false;
     KM_TRY(try_sorted_accumulate<T>(s, d, k, scale, vec_ok(s), &done, gs, gc, gate, limit));
     if (done) { ++launches; return KM_OK; }
   }
-  const size_t per_cluster = (size_t)NP * d * sizeof(int) + sizeof(int);
+  const size_t per_cluster = (size_t)NP * d * sizeof(int) + 2 * sizeof(int);
   const size_t budget = 200 * 1024;
   if (per_cluster + 16 > budget) KM_FAIL(KM_EINVAL, "cols too large for the centroid-sum kernel");
   int kc_max = (int)((budget - 16) / per_cluster);
@@ -812,11 +994,11 @@ int Engine<T>::launch_accumulate(Shard<T>& s, T scale, long long* dst, const uns
   if (vec) {
     KM_CUDA(cudaFuncSetAttribute(accumulate_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     accumulate_kernel<T, V><<<(unsigned)grid, kAccThreads, smem, s.stream>>>(
-        s.X, s.rows, d, s.labels, k, kc, n_slices, gs, gc, scale, (unsigned)rpp, magic, gate, limit);
+        s.X, s.rows, d, s.labels, k, kc, n_slices, gs, gc, scale, (unsigned)rpp, magic, gate, limit, W, (T)w_scale);
   } else {
     KM_CUDA(cudaFuncSetAttribute(accumulate_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     accumulate_kernel<T, 1><<<(unsigned)grid, kAccThreads, smem, s.stream>>>(
-        s.X, s.rows, d, s.labels, k, kc, n_slices, gs, gc, scale, (unsigned)rpp, magic, gate, limit);
+        s.X, s.rows, d, s.labels, k, kc, n_slices, gs, gc, scale, (unsigned)rpp, magic, gate, limit, W, (T)w_scale);
   }
   KM_CUDA(cudaGetLastError());
   ++launches;

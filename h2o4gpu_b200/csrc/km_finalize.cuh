@@ -229,12 +229,16 @@ rowdist_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict__
   }
 }
 
-// Sum of dist (inertia), deterministic two-stage tree: per-CTA partials then CTA 0.
+// Sum of dist (inertia; weighted by W when given), deterministic two-stage tree: per-CTA partials
+// then CTA 0.
+template <typename T>
 __global__ void __launch_bounds__(256)
-sum_partials_kernel(const double* __restrict__ v, size_t n, double* __restrict__ partials) {
+sum_partials_kernel(const double* __restrict__ v, size_t n, double* __restrict__ partials,
+                    const T* __restrict__ W = nullptr) {
   __shared__ double red[8];
   double s = 0;
-  for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) s += v[i];
+  for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256)
+    s += W ? v[i] * (double)W[i] : v[i];
   s = warp_sum(s);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
   __syncthreads();
@@ -266,7 +270,7 @@ relocate_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict_
                 double* __restrict__ dist, long long* __restrict__ gsums,
                 unsigned long long* __restrict__ gcounts, const int* __restrict__ empties,
                 IterState* st, double* __restrict__ cand_val, unsigned long long* __restrict__ cand_row,
-                T scale) {
+                T scale, const T* __restrict__ W, T wscale) {
   constexpr int NP = Fixed<T>::NP;
   const int E = st->n_empty;
   if (E == 0) return;
@@ -331,9 +335,17 @@ relocate_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict_
       const int cid = empties[e];
       const int old = labels[br];
       const T* x = X + (size_t)br * d;
+      // with sample weights the row carries w * x in the sums and its fixed-point weight in the counts
+      const T w = W ? W[br] : (T)1;
+      long long units = 1;
+      if (W) {
+        int pw[2];
+        split_pieces<2>(w, wscale, pw);
+        units = (long long)pw[0] * (1LL << kPieceBits) + (long long)pw[1];
+      }
       for (int t = threadIdx.x; t < d; t += 256) {
         int p[NP];
-        split_pieces<NP>(x[t], scale, p);
+        split_pieces<NP>(W ? x[t] * w : x[t], scale, p);
 #pragma unroll
         for (int q = 0; q < NP / 2; ++q) {
           long long v = (long long)p[2 * q] * (1LL << kPieceBits) + (long long)p[2 * q + 1];
@@ -342,8 +354,8 @@ relocate_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict_
         }
       }
       if (threadIdx.x == 0) {
-        gcounts[cid] = 1;
-        gcounts[old] -= 1;
+        gcounts[cid] = (unsigned long long)units;
+        gcounts[old] -= (unsigned long long)units;
         dist[br] = -2.0;
         st->relocated += 1;
       }
@@ -361,22 +373,36 @@ __global__ void __launch_bounds__(128)
 average_kernel(const long long* __restrict__ gsums, const unsigned long long* __restrict__ gcounts,
                int k, int d, double inv, const T* __restrict__ C_old, T* __restrict__ C_new,
                T* __restrict__ cnorm, double* __restrict__ shift_k, const IterState* st,
-               double* __restrict__ C_new_double, int only_if_no_empty) {
+               double* __restrict__ C_new_double, int only_if_no_empty, double count_unit) {
   constexpr int NP = Fixed<T>::NP;
+  // count_unit: weight of one unit of gcounts (1 for plain counts, a power of two for sample weights)
   // launched ahead of the host's look at n_empty when several ranks work together: it must
   // not average sums that still wait for their empty clusters to be repaired
   if (only_if_no_empty && st->n_empty != 0) return;
   __shared__ double red_n[4], red_s[4];
+  __shared__ int s_src;
   const int j = blockIdx.x;
   unsigned long long cnt = gcounts[j];
   int src = j;
   double a;
   if (cnt > 0) {
-    a = 1.0 / (double)cnt;
+    a = 1.0 / ((double)cnt * count_unit);
   } else {
-    src = st->argmax_count;
+    // still empty after the relocation (no row left to take, or a row of weight zero): the
+    // largest cluster as the counts stand now, lowest id on ties
+    if (threadIdx.x == 0) {
+      unsigned long long best = 0;
+      int bi = 0;
+      for (int c = 0; c < k; ++c) {
+        const unsigned long long v = gcounts[c];
+        if (v > best) { best = v; bi = c; }
+      }
+      s_src = bi;
+    }
+    __syncthreads();
+    src = s_src;
     unsigned long long cb = gcounts[src];
-    a = (src < j && cb > 0) ? 1.0 / (double)cb : 1.0;
+    a = (src < j && cb > 0) ? 1.0 / ((double)cb * count_unit) : 1.0;
   }
   double sn = 0, ss = 0;
   for (int t = threadIdx.x; t < d; t += blockDim.x) {
@@ -437,7 +463,7 @@ namespace km {
 
 // ---- relocation across several shards / ranks ----------------------------------
 // Each shard lists its E farthest rows (descending distance, ties lowest row) as
-// one packed record: [E double val][E u64 id][E i64 label][E*d T row].  The
+// one packed record: [E double val][E u64 id][E i64 label][E double weight][E*d T row].  The
 // records of all ranks are all-gathered and every rank applies the same E-way
 // choice to its (already all-reduced, hence identical) sums.
 template <typename T>
@@ -445,14 +471,15 @@ __global__ void __launch_bounds__(256)
 select_far_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict__ labels,
                   double* __restrict__ dist, int E, unsigned long long id_base,
                   double* __restrict__ cand_val, unsigned long long* __restrict__ cand_row,
-                  unsigned char* __restrict__ rec) {
+                  unsigned char* __restrict__ rec, const T* __restrict__ W) {
   cg::grid_group grid = cg::this_grid();
   __shared__ double s_v[256];
   __shared__ unsigned long long s_r[256];
   double* r_val = reinterpret_cast<double*>(rec);
   unsigned long long* r_id = reinterpret_cast<unsigned long long*>(rec + (size_t)E * 8);
   long long* r_lab = reinterpret_cast<long long*>(rec + (size_t)E * 16);
-  T* r_vec = reinterpret_cast<T*>(rec + (size_t)E * 24);
+  double* r_w = reinterpret_cast<double*>(rec + (size_t)E * 24);
+  T* r_vec = reinterpret_cast<T*>(rec + (size_t)E * 32);
   const size_t per = (n + gridDim.x - 1) / gridDim.x;
   const size_t b0 = (size_t)blockIdx.x * per;
   const size_t b1 = (b0 + per < n) ? b0 + per : n;
@@ -509,6 +536,7 @@ select_far_kernel(const T* __restrict__ X, size_t n, int d, const int* __restric
         r_val[e] = have ? bv : -1.0;
         r_id[e] = have ? (id_base + br) : ~0ULL;
         r_lab[e] = have ? (long long)labels[br] : -1;
+        r_w[e] = (have && W) ? (double)W[br] : 1.0;
         if (have) dist[br] = -2.0;
       }
       for (int t = threadIdx.x; t < d; t += 256) r_vec[(size_t)e * d + t] = have ? X[(size_t)br * d + t] : (T)0;
@@ -521,7 +549,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 apply_far_kernel(const unsigned char* __restrict__ rec_all, int world, int E, size_t rec_bytes, int k, int d,
                  long long* __restrict__ gsums, unsigned long long* __restrict__ gcounts,
-                 const int* __restrict__ empties, IterState* st, T scale) {
+                 const int* __restrict__ empties, IterState* st, T scale, int weighted, T wscale) {
   constexpr int NP = Fixed<T>::NP;
   __shared__ int head[64];
   __shared__ int s_w;
@@ -549,11 +577,18 @@ apply_far_kernel(const unsigned char* __restrict__ rec_all, int world, int E, si
     const unsigned char* rec = rec_all + (size_t)w * rec_bytes;
     const int h = head[w];
     const int old = (int)reinterpret_cast<const long long*>(rec + (size_t)E * 16)[h];
-    const T* x = reinterpret_cast<const T*>(rec + (size_t)E * 24) + (size_t)h * d;
+    const T* x = reinterpret_cast<const T*>(rec + (size_t)E * 32) + (size_t)h * d;
+    const T wt = (T)reinterpret_cast<const double*>(rec + (size_t)E * 24)[h];
+    long long units = 1;
+    if (weighted) {
+      int pw[2];
+      split_pieces<2>(wt, wscale, pw);
+      units = (long long)pw[0] * (1LL << kPieceBits) + (long long)pw[1];
+    }
     const int cid = empties[e];
     for (int t = threadIdx.x; t < d; t += 256) {
       int p[NP];
-      split_pieces<NP>(x[t], scale, p);
+      split_pieces<NP>(weighted ? x[t] * wt : x[t], scale, p);
 #pragma unroll
       for (int q = 0; q < NP / 2; ++q) {
         long long v = (long long)p[2 * q] * (1LL << kPieceBits) + (long long)p[2 * q + 1];
@@ -563,8 +598,8 @@ apply_far_kernel(const unsigned char* __restrict__ rec_all, int world, int E, si
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-      gcounts[cid] = 1;
-      gcounts[old] -= 1;
+      gcounts[cid] = (unsigned long long)units;
+      gcounts[old] -= (unsigned long long)units;
       st->relocated += 1;
       head[w] = h + 1;
     }

@@ -84,7 +84,7 @@ int Engine<T>::relocate_multi(double scale, int seq, int* n_empty) {
   const int ne = E[0];
   *n_empty = ne;
   if (ne == 0) return KM_OK;
-  const size_t rec_bytes = (size_t)ne * 24 + (size_t)ne * d * sizeof(T);
+  const size_t rec_bytes = (size_t)ne * 32 + (size_t)ne * d * sizeof(T);
   std::vector<unsigned char*> rec(g, nullptr), all(g, nullptr);
   for (size_t i = 0; i < g; ++i) {
     Shard<T>& s = shards[i];
@@ -104,7 +104,8 @@ int Engine<T>::relocate_multi(double scale, int seq, int* n_empty) {
     double* cv = s.cand_val;
     unsigned long long* cr = s.cand_row;
     unsigned char* rp = rec[i];
-    void* args[] = {&Xp, &n, &dd, &lab, &dist, &ee, &id_base, &cv, &cr, &rp};
+    const T* Wp = weighted ? s.w : nullptr;
+    void* args[] = {&Xp, &n, &dd, &lab, &dist, &ee, &id_base, &cv, &cr, &rp, &Wp};
     KM_CUDA(cudaLaunchCooperativeKernel((void*)select_far_kernel<T>, dim3(s.num_sms), dim3(256), args, 0, s.stream));
     launches += 2;
   }
@@ -116,7 +117,7 @@ int Engine<T>::relocate_multi(double scale, int seq, int* n_empty) {
     Shard<T>& s = shards[i];
     DevGuard gd(s.dev);
     apply_far_kernel<T><<<1, 256, 0, s.stream>>>(all[i], world_size, ne, rec_bytes, k, d, s.sums(), s.counts(k, d),
-                                                 s.empties, s.st, (T)scale);
+                                                 s.empties, s.st, (T)scale, weighted ? 1 : 0, (T)w_scale);
     KM_CUDA(cudaGetLastError());
     ++launches;
     KM_CUDA(cudaStreamSynchronize(s.stream));
@@ -136,9 +137,11 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
   KM_TRY(check_data());
   KM_TRY(set_centroids(k_, init));
 
-  // fixed-point scale from the global max |x|: xmax < 2^e, first piece <= 2^15
+  // fixed-point scale from the global max |x|: xmax < 2^e, first piece <= 2^15 (with sample
+  // weights the sums hold w * x, bounded by the product of the two maxima)
   double xmax = 0;
   for (auto& s : shards) xmax = std::max(xmax, s.xmax);
+  if (weighted) xmax *= wmax;
   int e = 0;
   if (xmax > 0) std::frexp(xmax, &e);
   const int sa = kPieceBits - e;
@@ -146,7 +149,9 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
   const double inv = std::ldexp(1.0, -(sa + kPieceBits));
   if (!std::isfinite((double)scale) || scale == (T)0) KM_FAIL(KM_EINVAL, "data magnitude outside the supported range");
 
-  const bool fused = smallk_ok(true) && !(flags & KM_FIT_FORCE_SPLIT);
+  // weighted fits take the general M-step kernel: neither the fused small-k update nor the
+  // incremental sums carry weights
+  const bool fused = smallk_ok(true) && !(flags & KM_FIT_FORCE_SPLIT) && !weighted;
   const bool use_tc = !fused && tc_ok(flags);
   if (const char* e = std::getenv("H2O4GPU_KM_TC_TOL")) tc_tol_rel = (float)std::atof(e);
   // incremental M-step (km_accumulate_delta.cuh): on unless the caller or the environment asks
@@ -156,7 +161,7 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
     const char* e = std::getenv("H2O4GPU_KM_DELTA_SUMS");
     return !(e && e[0] == '0');
   }();
-  const bool delta = !fused && delta_env && !(flags & KM_FIT_FULL_SUMS);
+  const bool delta = !fused && delta_env && !(flags & KM_FIT_FULL_SUMS) && !weighted;
   const bool multi = world_size > 1;
   const bool check = (threshold > 0) || (flags & KM_FIT_CHECK_EVERY_ITER);
   stats = kmeans_stats{};
@@ -261,7 +266,9 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
         double* cv = s.cand_val;
         unsigned long long* cr = s.cand_row;
         T sc = scale;
-        void* args[] = {&Xp, &n, &dd, &lab, &kk, &dist, &gs, &gc, &em, &st, &cv, &cr, &sc};
+        const T* Wp = weighted ? s.w : nullptr;
+        T wsc = (T)w_scale;
+        void* args[] = {&Xp, &n, &dd, &lab, &kk, &dist, &gs, &gc, &em, &st, &cv, &cr, &sc, &Wp, &wsc};
         cudaError_t ce = cudaLaunchCooperativeKernel((void*)relocate_kernel<T>, dim3(s.num_sms), dim3(256), args, 0,
                                                      s.stream);
         if (ce != cudaSuccess) { set_error(std::string("relocate launch: ") + cudaGetErrorString(ce)); rc = KM_ECUDA; }
@@ -278,7 +285,8 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
         Shard<T>& s = shards[i];
         DevGuard g(s.dev);
         average_kernel<T><<<k, 128, 0, s.stream>>>(s.sums(), s.counts(k, d), k, d, inv, s.C[cur], s.C[cur ^ 1],
-                                                 s.cnorm, s.shift_k, s.st, s.Cd[cur ^ 1], only_if_no_empty);
+                                                 s.cnorm, s.shift_k, s.st, s.Cd[cur ^ 1], only_if_no_empty,
+                                                 weighted ? count_unit : 1.0);
         iter_close_kernel<<<1, 256, 0, s.stream>>>(s.shift_k, k, s.st, s.shift_log, s.changed_log, s.reloc_log,
                                                    s.amb_log, it, &s.host_pin[0],
                                                    reinterpret_cast<unsigned long long*>(&s.host_pin[1]),
@@ -417,7 +425,7 @@ int Engine<T>::inertia(double* out) {
     DevGuard g(s.dev);
     KM_TRY(ensure_dist(s));
     launch_rowdist(s, 1);
-    sum_partials_kernel<<<1024, 256, 0, s.stream>>>(s.dist, s.rows, s.sum_partials);
+    sum_partials_kernel<T><<<1024, 256, 0, s.stream>>>(s.dist, s.rows, s.sum_partials, weighted ? s.w : nullptr);
     sum_final_kernel<<<1, 32, 0, s.stream>>>(s.sum_partials, 1024, &s.st->inertia);
     KM_CUDA(cudaGetLastError());
     launches += 3;

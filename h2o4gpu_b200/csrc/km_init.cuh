@@ -310,7 +310,7 @@ int init_centroids(Engine<T>& e, int k, int seed, int method, std::vector<T>* ou
     double phi = 0;
     for (auto& s : e.shards) {
       DevGuard g(s.dev);
-      sum_partials_kernel<<<1024, 256, 0, s.stream>>>(s.dist, s.rows, s.sum_partials);
+      sum_partials_kernel<T><<<1024, 256, 0, s.stream>>>(s.dist, s.rows, s.sum_partials);
       sum_final_kernel<<<1, 32, 0, s.stream>>>(s.sum_partials, 1024, &s.st->inertia);
       double part = 0;
       if (cudaMemcpyAsync(&part, &s.st->inertia, sizeof(double), cudaMemcpyDeviceToHost, s.stream) != cudaSuccess ||

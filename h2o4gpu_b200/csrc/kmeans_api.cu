@@ -445,6 +445,14 @@ int kmeans_upload_host(kmeans_handle_t h, const void* X, size_t rows, size_t col
   KM_DISPATCH(h, h->f32->upload_host(static_cast<const float*>(X), rows, cols, order),
               h->f64->upload_host(static_cast<const double*>(X), rows, cols, order));
 }
+int kmeans_upload_host_typed(kmeans_handle_t h, const void* X, int src_dtype, size_t rows, size_t cols, char order) {
+  KM_DISPATCH(h, h->f32->upload_host_typed(X, src_dtype, rows, cols, order),
+              h->f64->upload_host_typed(X, src_dtype, rows, cols, order));
+}
+int kmeans_set_sample_weight(kmeans_handle_t h, const void* weights, size_t count) {
+  KM_DISPATCH(h, h->f32->set_sample_weight(static_cast<const float*>(weights), count),
+              h->f64->set_sample_weight(static_cast<const double*>(weights), count));
+}
 int kmeans_fit_resident(kmeans_handle_t h, int k, int max_iter, double threshold, const void* init, int flags) {
   KM_DISPATCH(h, h->f32->fit(k, max_iter, threshold, static_cast<const float*>(init), flags),
               h->f64->fit(k, max_iter, threshold, static_cast<const double*>(init), flags));

@@ -65,14 +65,35 @@ class ResidentKMeans(object):
         self._rows[local] = rows
         self.cols = cols
 
-    def upload(self, X, order='r'):
-        X = np.ascontiguousarray(X, dtype=self.dtype) if order == 'r' else np.asfortranarray(X, dtype=self.dtype)
+    def upload(self, X, order=None):
+        """Copy a host matrix to the device(s).  Any dtype of ``DTYPE_CODES`` goes down as it is and is
+        converted to the handle's dtype on the device; ``order`` 'r' / 'c' forces a layout, None keeps the
+        array's own when it is C- or Fortran-contiguous."""
+        X = np.asarray(X)
+        if X.ndim != 2:
+            raise ValueError("X must be two-dimensional")
+        if X.dtype == np.bool_:
+            X = X.view(np.uint8)
+        if X.dtype not in DTYPE_CODES:   # also: non-native byte order
+            X = X.astype(self.dtype)
+        if order is None:
+            order = 'c' if (X.flags.f_contiguous and not X.flags.c_contiguous) else 'r'
+        X = np.ascontiguousarray(X) if order == 'r' else np.asfortranarray(X)
         rows, cols = X.shape
-        _lk.check(self._lib.kmeans_upload_host(self._h, X.ctypes.data_as(ctypes.c_void_p), rows, cols,
-                                               order.encode()))
+        _lk.check(self._lib.kmeans_upload_host_typed(self._h, X.ctypes.data_as(ctypes.c_void_p),
+                                                     DTYPE_CODES[X.dtype], rows, cols, order.encode()))
         per = -(-rows // self.n_local)
         self._rows = [min(per, rows - i * per) for i in range(self.n_local)]
         self.cols = cols
+
+    def set_sample_weight(self, w):
+        """Per-row weights (all local rows, shard after shard) for the next fits and ``inertia()``; None
+        restores unit weights."""
+        if w is None:
+            _lk.check(self._lib.kmeans_set_sample_weight(self._h, None, 0))
+            return
+        w = np.ascontiguousarray(w, dtype=self.dtype).reshape(-1)
+        _lk.check(self._lib.kmeans_set_sample_weight(self._h, w.ctypes.data_as(ctypes.c_void_p), w.shape[0]))
 
     def fit(self, init, max_iter, threshold=0.0, flags=0):
         init = np.ascontiguousarray(init, dtype=self.dtype)
@@ -134,6 +155,10 @@ class ResidentKMeans(object):
         _lk.check(self._lib.kmeans_inertia(self._h, ctypes.byref(v)))
         return v.value
 
+
+DTYPE_CODES = {np.dtype(np.float32): 0, np.dtype(np.float64): 1, np.dtype(np.float16): 2, np.dtype(np.int8): 3,
+               np.dtype(np.uint8): 4, np.dtype(np.int16): 5, np.dtype(np.uint16): 6, np.dtype(np.int32): 7,
+               np.dtype(np.uint32): 8, np.dtype(np.int64): 9, np.dtype(np.uint64): 10}
 
 FIT_NO_FINAL_ASSIGN = 1
 FIT_FORCE_SIMT = 2

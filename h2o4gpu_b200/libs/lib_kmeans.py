@@ -59,6 +59,8 @@ SIGNATURES = {
     "kmeans_nccl_unique_id": (_c.c_int, [_vp]),
     "kmeans_attach_device": (_c.c_int, [_vp, _c.c_int, _vp, _sz, _sz, _sz]),
     "kmeans_upload_host": (_c.c_int, [_vp, _vp, _sz, _sz, _c.c_char]),
+    "kmeans_set_sample_weight": (_c.c_int, [_vp, _vp, _sz]),
+    "kmeans_upload_host_typed": (_c.c_int, [_vp, _vp, _c.c_int, _sz, _sz, _c.c_char]),
     "kmeans_fit_resident": (_c.c_int, [_vp, _c.c_int, _c.c_int, _c.c_double, _vp, _c.c_int]),
     "kmeans_assign_resident": (_c.c_int, [_vp]),
     "kmeans_set_centroids": (_c.c_int, [_vp, _c.c_int, _vp]),

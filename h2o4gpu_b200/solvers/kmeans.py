@@ -182,12 +182,60 @@ class KMeansH2O(object):
             print(msg)
             sys.stdout.flush()
 
-    def fit(self, X, y=None):
+    def fit(self, X, y=None, sample_weight=None):
+        """Fit on the GPU.  float32 / float64 input goes through the reference's entry points
+        (``make_ptr_*_kmeans``); other numeric dtypes and weighted fits - which the reference converts on
+        the host or sends to scikit-learn (kmeans.py:508-521, 800-804) - go through the resident engine,
+        which converts on the device and carries the weights."""
         X_np = _get_data(X)
         _check_data_content(self.do_checks, "X", X_np)
-        self._fit(X_np)
+        if sample_weight is not None or X_np.dtype not in (np.float32, np.float64):
+            self._fit_resident(X_np, sample_weight)
+        else:
+            self._fit(X_np)
         self._did_sklearn_fit = 0
         return self
+
+    def _fit_resident(self, data, sample_weight):
+        from .. import engine
+        self._load_lib()
+        dtype = np.float64 if data.dtype == np.float64 else np.float32
+        self.double_precision = int(dtype == np.float64)
+        rows, cols = data.shape
+        k = min(self._n_clusters, rows)
+        ndev = max(1, min(device_count(self.n_gpus)[0], rows))
+        total = device_count(-1)[1]
+        devices = [(self._gpu_id + i) % total for i in range(ndev)]
+        given = isinstance(self.init, np.ndarray) or (not isinstance(self.init, str) and hasattr(self.init, '__array__'))
+        if given:
+            init = np.ascontiguousarray(np.asarray(self.init), dtype=dtype)
+            if init.shape != (self._n_clusters, cols):
+                raise ValueError("init has shape %s, expected %s" % (init.shape, (self._n_clusters, cols)))
+        h = engine.ResidentKMeans(dtype=dtype, devices=devices)
+        try:
+            h.upload(data)
+            if sample_weight is not None:
+                w = np.asarray(sample_weight, dtype=dtype).reshape(-1)
+                if w.shape[0] != rows:
+                    raise ValueError("sample_weight has %d entries for %d rows" % (w.shape[0], rows))
+                h.set_sample_weight(w)
+            runs = 1 if given else max(1, int(self.n_init or 1))
+            best = None
+            for r in range(runs):
+                start = init if given else h.init_centroids(
+                    k, seed=self.random_state + r, method="k-means||" if self.init == "k-means++" else "random")
+                h.fit(start, self._max_iter, threshold=self.tol,
+                      flags=engine.FIT_CHECK_EVERY_ITER if self.tol > 0 else 0)
+                st = h.stats()
+                inertia = h.inertia()
+                if best is None or inertia < best[0]:
+                    n_iter = st["n_iter_converged"] if st["n_iter_converged"] > 0 else st["iterations"]
+                    best = (inertia, n_iter, h.centroids(), h.all_labels())
+        finally:
+            h.close()
+        self.inertia_, self.n_iter_ = best[0], best[1]
+        self.cluster_centers_, self.labels_ = best[2], best[3]
+        return self.cluster_centers_, self.labels_
 
     def _fit(self, data):
         lib = self._load_lib()
@@ -261,12 +309,12 @@ class KMeansH2O(object):
         fn(self.verbose, self._gpu_id, self.n_gpus, rows, cols, k, c_X, centers, c_res)
         return np.reshape(c_res, (rows, k), order='F')
 
-    def fit_transform(self, X, y=None):
-        return self.fit(X, y).transform(X)
+    def fit_transform(self, X, y=None, sample_weight=None):
+        return self.fit(X, y, sample_weight).transform(X)
 
-    def score(self, X, y=None):
-        """Opposite of the k-means objective on X (sklearn's convention): minus the sum of squared
-        distances of the rows to their nearest centre, computed on the GPU."""
+    def score(self, X, y=None, sample_weight=None):
+        """Opposite of the k-means objective on X (sklearn's convention): minus the (weighted) sum of
+        squared distances of the rows to their nearest centre, computed on the GPU."""
         from .. import engine
         self._load_lib()
         X_np = _get_data(X)
@@ -274,15 +322,17 @@ class KMeansH2O(object):
         dtype = np.float64 if self.double_precision else np.float32
         h = engine.ResidentKMeans(dtype=dtype, devices=(self._gpu_id,))
         try:
-            h.upload(np.ascontiguousarray(X_np, dtype=dtype))
+            h.upload(X_np)
+            if sample_weight is not None:
+                h.set_sample_weight(sample_weight)
             h.set_centroids(np.ascontiguousarray(self.cluster_centers_, dtype=dtype))
             h.assign()
             return -h.inertia()
         finally:
             h.close()
 
-    def fit_predict(self, X, y=None):
-        return self.fit(X, y).labels_
+    def fit_predict(self, X, y=None, sample_weight=None):
+        return self.fit(X, y, sample_weight).labels_
 
     # -- CPU re-seeding helpers of the reference (kmeans.py:321-343, 376-387, 424-436)
     def sklearn_fit(self, X, y=None):
@@ -344,26 +394,17 @@ class KMeans(object):
             print("Using %s backend" % ("sklearn" if self.do_sklearn else "h2o4gpu"))
 
     def fit(self, X, y=None, sample_weight=None):
-        if self.do_sklearn:
-            res = self.model.fit(X, y, sample_weight)
-        else:
-            res = self.model.fit(X, y)
+        res = self.model.fit(X, y, sample_weight)
         self.set_attributes()
         return res
 
     def fit_predict(self, X, y=None, sample_weight=None):
-        if self.do_sklearn:
-            res = self.model.fit_predict(X, y, sample_weight)
-        else:
-            res = self.model.fit_predict(X, y)
+        res = self.model.fit_predict(X, y, sample_weight)
         self.set_attributes()
         return res
 
     def fit_transform(self, X, y=None, sample_weight=None):
-        if self.do_sklearn:
-            res = self.model.fit_transform(X, y, sample_weight)
-        else:
-            res = self.model.fit_transform(X, y)
+        res = self.model.fit_transform(X, y, sample_weight)
         self.set_attributes()
         return res
 
@@ -384,8 +425,6 @@ class KMeans(object):
         return res
 
     def score(self, X, y=None, sample_weight=None):
-        if not self.do_sklearn:
-            raise NotImplementedError("score() runs on the sklearn backend only")
         return self.model.score(X, y, sample_weight)
 
     def set_attributes(self):

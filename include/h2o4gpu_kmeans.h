@@ -121,6 +121,33 @@ int kmeans_attach_device(kmeans_handle_t h, int local, const void* dX, size_t ro
  * (ceil split, every row covered).  order 'r' = row-major, 'c' = column-major
  * (the two layouts of copy_data, src/gpu/kmeans/kmeans_h2o4gpu.h:24-42). */
 int kmeans_upload_host(kmeans_handle_t h, const void* X, size_t rows, size_t cols, char order);
+/* The same for a host matrix of another element type.  The reference's wrapper converts every
+ * input to float32 / float64 on the host before the call (`_to_np`,
+ * src/interface_py/h2o4gpu/solvers/utils.py:46-96; kmeans.py:508-521); here the bytes cross the
+ * bus as they are (a quarter of them for 8-bit data) and a kernel converts them into the
+ * handle's dtype with the rounding of numpy's astype. */
+#define KM_DTYPE_F32 0
+#define KM_DTYPE_F64 1
+#define KM_DTYPE_F16 2
+#define KM_DTYPE_I8 3
+#define KM_DTYPE_U8 4   /* also numpy bool */
+#define KM_DTYPE_I16 5
+#define KM_DTYPE_U16 6
+#define KM_DTYPE_I32 7
+#define KM_DTYPE_U32 8
+#define KM_DTYPE_I64 9
+#define KM_DTYPE_U64 10
+int kmeans_upload_host_typed(kmeans_handle_t h, const void* X, int src_dtype, size_t rows, size_t cols,
+                             char order);
+
+/* Sample weights for the next fits / inertia on this handle: `count` values of the handle's dtype,
+ * one per local row, shard after shard (NULL: back to unit weights).  A row then adds w * x to its
+ * centroid's sum and w to its count, and inertia is the weighted sum - the meaning of
+ * fit(X, sample_weight=w) in the wrapper (src/interface_py/h2o4gpu/solvers/kmeans.py:800-804), which
+ * the reference can only serve on the CPU.  Weights must be finite and >= 0, not all zero; they enter
+ * as 30-bit fixed-point numbers relative to the largest one.  Attaching or uploading other data drops
+ * them. */
+int kmeans_set_sample_weight(kmeans_handle_t h, const void* weights, size_t count);
 
 /* flags for kmeans_fit_resident */
 #define KM_FIT_NO_FINAL_ASSIGN 1 /* skip the closing E-step (benchmark loops)        */

@@ -23,6 +23,9 @@ rule comes from in scikit-learn's published algorithm:
   centres (``_kmeans_single_lloyd``; the GPU reference does the same final
   pass, src/gpu/kmeans/kmeans_impl.h:217-231).
 * fit() subtracts the column mean of X from X and init and adds it back.
+* Sample weights (``fit(X, sample_weight=w)``): sums of w * x, counts of w, inertia of
+  w * distance; the farthest points of the empty-cluster rule are chosen by the unweighted
+  distance and move with their weight (``_relocate_empty_clusters_dense``).
 
 The GPU reference's output conventions restated here: transform returns
 |(|x|^2 + |c|^2 - 2 x.c)| (squared, no sqrt) as one column-major n x k block
@@ -75,13 +78,19 @@ def near_tie_mask(X, C, rel=1e-5, dtype=np.float64):
     return (second - best) < rel * np.maximum(np.abs(second), np.finfo(dtype).tiny)
 
 
-def sums_counts(X, labels, k, dtype=np.float64):
-    """Un-normalised per-cluster sums (k x d) and integer counts (k)."""
+def sums_counts(X, labels, k, dtype=np.float64, sample_weight=None):
+    """Un-normalised per-cluster sums (k x d) and integer counts (k); with sample weights the sums of
+    w * x and the per-cluster sums of w (float)."""
     d = X.shape[1]
     sums = np.zeros((k, d), dtype=dtype)
-    counts = np.bincount(labels, minlength=k).astype(np.int64)
+    if sample_weight is None:
+        counts = np.bincount(labels, minlength=k).astype(np.int64)
+    else:
+        counts = np.bincount(labels, weights=_as(sample_weight, dtype), minlength=k).astype(dtype)
     for s in range(0, X.shape[0], _CHUNK * 8):
         Xc = _as(X[s:s + _CHUNK * 8], dtype)
+        if sample_weight is not None:
+            Xc = Xc * _as(sample_weight[s:s + _CHUNK * 8], dtype)[:, None]
         lc = labels[s:s + _CHUNK * 8]
         order = np.argsort(lc, kind="stable")
         ls = lc[order]
@@ -90,7 +99,7 @@ def sums_counts(X, labels, k, dtype=np.float64):
     return sums, counts
 
 
-def relocate_empty(X, labels, C_old, sums, counts, order="sklearn", dtype=np.float64):
+def relocate_empty(X, labels, C_old, sums, counts, order="sklearn", dtype=np.float64, sample_weight=None):
     """Empty-cluster rule.  ``order='sklearn'`` picks the far points exactly as
     scikit-learn does (``np.argpartition`` tail, reversed: not a sorted order when
     two or more clusters are empty); ``order='descending'`` hands the farthest
@@ -112,10 +121,11 @@ def relocate_empty(X, labels, C_old, sums, counts, order="sklearn", dtype=np.flo
         far = np.lexsort((np.arange(dist.size), -dist))[:ne]
     for cid, row in zip(empty, far):
         old = labels[row]
-        sums[old] -= Xd[row]
-        sums[cid] = Xd[row]
-        counts[cid] = 1
-        counts[old] -= 1
+        w = 1 if sample_weight is None else dtype(sample_weight[row])
+        sums[old] -= w * Xd[row]
+        sums[cid] = w * Xd[row]
+        counts[cid] = w
+        counts[old] -= w
         moved.append((int(cid), int(row)))
     return moved
 
@@ -133,18 +143,18 @@ def average(sums, counts):
     return C
 
 
-def step(X, C, dtype=np.float64, order="sklearn"):
+def step(X, C, dtype=np.float64, order="sklearn", sample_weight=None):
     """One Lloyd iteration from centres C.  Returns (C_new, labels, counts, moved);
     counts are the ones after relocation."""
     k = C.shape[0]
     labels = assign(X, C, dtype=dtype)
-    sums, counts = sums_counts(X, labels, k, dtype=dtype)
-    moved = relocate_empty(X, labels, C, sums, counts, order=order, dtype=dtype)
+    sums, counts = sums_counts(X, labels, k, dtype=dtype, sample_weight=sample_weight)
+    moved = relocate_empty(X, labels, C, sums, counts, order=order, dtype=dtype, sample_weight=sample_weight)
     return average(sums, counts), labels, counts, moved
 
 
 def fit(X, init, max_iter, tol=0.0, dtype=np.float64, center=True, order="sklearn",
-        stop_on_repeat=True, keep_trajectory=False):
+        stop_on_repeat=True, keep_trajectory=False, sample_weight=None):
     """Whole fit.  Returns dict(centers, labels, n_iter, trajectory?)."""
     Xw = _as(X, dtype)
     C = _as(init, dtype).copy()
@@ -157,7 +167,7 @@ def fit(X, init, max_iter, tol=0.0, dtype=np.float64, center=True, order="sklear
     strict = False
     it = 0
     for it in range(max_iter):
-        C_new, labels, _, moved = step(Xw, C, dtype=dtype, order=order)
+        C_new, labels, _, moved = step(Xw, C, dtype=dtype, order=order, sample_weight=sample_weight)
         shift = float(((C_new - C) ** 2).sum())
         C = C_new
         if keep_trajectory:
@@ -178,9 +188,12 @@ def fit(X, init, max_iter, tol=0.0, dtype=np.float64, center=True, order="sklear
     return out
 
 
-def inertia(X, C, labels, dtype=np.float64):
+def inertia(X, C, labels, dtype=np.float64, sample_weight=None):
     Xd = _as(X, dtype)
-    return float(((Xd - _as(C, dtype)[labels]) ** 2).sum())
+    dist = ((Xd - _as(C, dtype)[labels]) ** 2).sum(axis=1)
+    if sample_weight is not None:
+        dist = dist * _as(sample_weight, dtype)
+    return float(dist.sum())
 
 
 def transform_sq_colmajor(X, C, dtype=np.float64):

@@ -22,8 +22,9 @@ def _make(n_clusters, init, max_iter, tol, random_state=0):
                   algorithm="lloyd")
 
 
-def fit(X, init, max_iter, tol=0.0):
-    """Run the reference CPU path from explicit initial centroids.
+def fit(X, init, max_iter, tol=0.0, sample_weight=None):
+    """Run the reference CPU path from explicit initial centroids (optionally with the
+    ``sample_weight`` the wrapper forwards, kmeans.py:800-804).
 
     Returns a dict with ``centers`` (k x d, dtype of X), ``labels`` (int32),
     ``n_iter`` and ``inertia``.
@@ -33,7 +34,7 @@ def fit(X, init, max_iter, tol=0.0):
     km = _make(init.shape[0], init, max_iter, tol)
     with warnings.catch_warnings():
         warnings.simplefilter("ignore")
-        km.fit(X)
+        km.fit(X, sample_weight=sample_weight)
     return {"centers": km.cluster_centers_, "labels": km.labels_.astype(np.int32),
             "n_iter": int(km.n_iter_), "inertia": float(km.inertia_), "model": km}
 

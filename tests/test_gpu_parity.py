@@ -484,3 +484,182 @@ def test_multi_gpu_equals_single_gpu(eng):
     assert np.array_equal(h1.labels(), h2.all_labels())
     h1.close()
     h2.close()
+
+
+# ---- ingest of other element types: converted on the device ------------------------
+_TYPED = [np.float16, np.int8, np.uint8, np.int16, np.uint16, np.int32, np.uint32, np.int64, np.uint64, np.bool_,
+          np.float64, np.float32]
+
+
+def _typed_matrix(rng, dt, rows, cols):
+    dt = np.dtype(dt)
+    if dt == np.bool_:
+        return rng.integers(0, 2, (rows, cols)).astype(np.bool_)
+    if dt.kind == 'f':
+        return (rng.standard_normal((rows, cols)) * 8).astype(dt)
+    info = np.iinfo(dt)
+    # wide integers carry more bits than the float mantissa: conversion must round like astype
+    lo, hi = max(info.min, -(1 << 40)), min(info.max, 1 << 40)
+    return rng.integers(lo, hi, (rows, cols), dtype=np.int64 if dt.kind == 'i' else np.uint64).astype(dt)
+
+
+@pytest.mark.parametrize("handle_dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("order", ["r", "c"])
+def test_typed_upload_matches_astype(eng, handle_dtype, order):
+    """kmeans_upload_host_typed gives the shard that a host-side astype + native upload gives, bit for bit
+    (seen through the transform of every row, which reads every element)."""
+    rng = np.random.default_rng(5)
+    rows, cols, k = 1003, 19, 5
+    for dt in _TYPED:
+        X = _typed_matrix(rng, dt, rows, cols)
+        Xn = X.astype(handle_dtype)
+        scale = max(float(np.abs(Xn).max()), 1.0)
+        C = (rng.standard_normal((k, cols)) * scale).astype(handle_dtype)
+        outs = []
+        for src in (X if order == "r" else np.asfortranarray(X), Xn):
+            h = eng.ResidentKMeans(dtype=handle_dtype)
+            h.upload(src, order=order)
+            h.set_centroids(C)
+            h.assign()
+            outs.append((h.transform().copy(), h.labels().copy()))
+            h.close()
+        assert np.array_equal(outs[0][0], outs[1][0]), np.dtype(dt).name
+        assert np.array_equal(outs[0][1], outs[1][1]), np.dtype(dt).name
+
+
+def test_typed_upload_staged_u8_fit(eng):
+    """An 8-bit matrix large enough for the pinned staging pool: a fit on it equals, bit for bit, the fit on
+    its float32 copy (image-like data, a quarter of the bytes on the bus)."""
+    rng = np.random.default_rng(9)
+    rows, cols, k = 600_000, 128, 10
+    X = (rng.integers(1, 256, (rows, cols)) * (rng.random((rows, cols)) < 0.2)).astype(np.uint8)
+    init = X[:k].astype(np.float32)
+    res = []
+    for src in (X, X.astype(np.float32)):
+        h = eng.ResidentKMeans()
+        h.upload(src)
+        h.fit(init, 5)
+        res.append((h.centroids(), h.labels()))
+        h.close()
+    assert np.array_equal(res[0][0], res[1][0])
+    assert np.array_equal(res[0][1], res[1][1])
+
+
+# ---- sample weights ------------------------------------------------------------------
+def _weighted_case(rng, n, d, k, dtype):
+    centers = rng.uniform(-8, 8, (k, d))
+    noise = rng.standard_normal((n, d))
+    X = (centers[rng.integers(0, k, n)] + noise).astype(dtype)
+    w = rng.gamma(2.0, 1.5, n).astype(dtype)
+    # some rows of weight zero, taken among those nearest to their centre: a row of weight zero that is
+    # relocated into an empty cluster leaves it empty, and scikit-learn then copies un-averaged sums of
+    # centred data into it, which no other implementation can be compared with
+    w[np.argsort((noise ** 2).sum(1))[:max(1, n // 60)]] = 0
+    init = X[rng.choice(n, k, replace=False)].copy()
+    return X, w, init
+
+
+@pytest.mark.parametrize("dtype,n,d,k", [(np.float64, 3000, 6, 7), (np.float32, 20000, 64, 100),
+                                         (np.float32, 4000, 33, 5), (np.float32, 30000, 256, 300)])
+def test_weighted_fit_matches_oracle(eng, dtype, n, d, k):
+    """fit with sample weights against the restatement (itself pinned to scikit-learn's
+    fit(X, sample_weight=w)): teacher-forced steps, then a whole fit, inertia included.  Weights enter
+    the counts as 30-bit fixed-point numbers, so the float64 bound here is 1e-8, not 1e-10."""
+    rng = np.random.default_rng(33)
+    X, w, init = _weighted_case(rng, n, d, k, dtype)
+    tol = F32_TOL if dtype == np.float32 else 1e-8
+    T = 6
+    ref = lloyd.fit(X, init, T, dtype=np.float64, sample_weight=w, keep_trajectory=True, stop_on_repeat=False,
+                    order="descending")
+    h = eng.ResidentKMeans(dtype=dtype)
+    h.upload(X)
+    h.set_sample_weight(w)
+    C = init.astype(np.float64)
+    for Cn, labels, _ in ref["trajectory"]:
+        h.fit(C.astype(dtype), 1, flags=eng.FIT_NO_FINAL_ASSIGN)
+        check_labels(X, C, h.labels(), labels)
+        assert rel_err(h.centroids(), Cn) < tol
+        C = Cn
+    h.fit(init, T)
+    assert rel_err(h.centroids(), ref["centers"]) < tol
+    check_labels(X, ref["centers"], h.labels(), ref["labels"])
+    want = lloyd.inertia(X, ref["centers"], ref["labels"], sample_weight=w)
+    assert abs(h.inertia() / want - 1) < (1e-4 if dtype == np.float32 else 1e-8)
+    # unit weights again: the plain fit, bit for bit
+    h.set_sample_weight(None)
+    h.fit(init, T)
+    plain = h.centroids()
+    h.set_sample_weight(np.ones(n, dtype))
+    h.fit(init, T)
+    assert np.array_equal(h.centroids(), plain)
+    h.close()
+
+
+def test_weighted_fit_equals_repeated_rows(eng):
+    """Integer weights mean repeated rows: the weighted fit of X equals the plain fit of X with row i
+    written w_i times (same partition, hence the same centres up to the fixed-point quantum)."""
+    rng = np.random.default_rng(34)
+    n, d, k = 5000, 32, 20
+    X, _, init = _weighted_case(rng, n, d, k, np.float32)
+    w = rng.integers(0, 4, n)
+    h = eng.ResidentKMeans()
+    h.upload(X)
+    h.set_sample_weight(w)
+    h.fit(init, 8)
+    Cw, lw = h.centroids(), h.labels()
+    h.close()
+    rep = np.repeat(np.arange(n), w)
+    h = eng.ResidentKMeans()
+    h.upload(X[rep])
+    h.fit(init, 8)
+    Cr, lr = h.centroids(), h.labels()
+    h.close()
+    assert rel_err(Cw, Cr.astype(np.float64)) < 1e-6
+    assert np.array_equal(lw[rep], lr)
+
+
+def test_weighted_relocation_and_errors(eng):
+    """An empty cluster in a weighted fit takes the farthest row with that row's weight; bad weights are
+    refused."""
+    rng = np.random.default_rng(35)
+    X, w, init = _weighted_case(rng, 3000, 6, 7, np.float64)
+    init[3] = 1e3
+    ref = lloyd.fit(X, init, 10, dtype=np.float64, sample_weight=w, order="descending")
+    h = eng.ResidentKMeans(dtype=np.float64)
+    h.upload(X)
+    h.set_sample_weight(w)
+    h.fit(init, 10)
+    assert h.stats()["relocations"] >= 1
+    assert rel_err(h.centroids(), ref["centers"]) < 1e-8
+    assert np.array_equal(h.labels(), ref["labels"])
+    from h2o4gpu_b200.libs import lib_kmeans
+    for bad in (np.full(3000, -1.0), np.zeros(3000), np.r_[np.ones(2999), np.nan], np.ones(17)):
+        with pytest.raises(lib_kmeans.KMeansLibError):
+            h.set_sample_weight(bad)
+    h.close()
+
+
+def test_estimator_weights_and_other_dtypes(built_lib):
+    """fit(X, sample_weight=w) and 8-bit input stay on the GPU backend and agree with scikit-learn (the
+    reference's CPU backend) on the same start."""
+    import h2o4gpu_b200
+    rng = np.random.default_rng(41)
+    X, w, init = _weighted_case(rng, 4000, 16, 6, np.float32)
+    gpu = h2o4gpu_b200.KMeans(n_clusters=6, init=init, max_iter=15, tol=0.0, n_gpus=1)
+    gpu.fit(X, sample_weight=w)
+    cpu = h2o4gpu_b200.KMeans(n_clusters=6, init=init, max_iter=15, tol=0.0, n_gpus=0)
+    cpu.fit(X, sample_weight=w)
+    assert rel_err(gpu.cluster_centers_, cpu.cluster_centers_.astype(np.float64)) < F32_TOL
+    check_labels(X, cpu.cluster_centers_.astype(np.float64), gpu.labels_, cpu.labels_)
+    assert abs(gpu.inertia_ - cpu.inertia_) <= 1e-4 * cpu.inertia_
+    assert abs(gpu.score(X, sample_weight=w) - cpu.score(X, sample_weight=w)) <= 1e-4 * cpu.inertia_
+    assert np.array_equal(gpu.fit_predict(X, sample_weight=w), gpu.labels_)
+    # 8-bit pixels: converted on the device, same result as their float32 copy
+    P = rng.integers(0, 256, (3000, 24)).astype(np.uint8)
+    pinit = P[:5].astype(np.float32)
+    a = h2o4gpu_b200.KMeans(n_clusters=5, init=pinit, max_iter=10, tol=0.0, n_gpus=1).fit(P)
+    b = h2o4gpu_b200.KMeans(n_clusters=5, init=pinit, max_iter=10, tol=0.0, n_gpus=1).fit(P.astype(np.float32))
+    assert a.cluster_centers_.dtype == np.float32
+    assert np.array_equal(a.cluster_centers_, b.cluster_centers_)
+    assert np.array_equal(a.labels_, b.labels_)
+    assert abs(a.inertia_ - b.inertia_) <= 1e-9 * b.inertia_

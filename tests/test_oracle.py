@@ -115,3 +115,25 @@ def test_ref_readme_example():
     r = lloyd.fit(X, X[[0, 1]], 10)
     assert np.allclose(sorted(map(tuple, r["centers"])), [(1.0, 0.5), (1.0, 4.0)])
     assert r["labels"].tolist() == [0, 1, 0]
+
+
+@pytest.mark.parametrize("empty", [False, True])
+def test_weighted_restatement_matches_sklearn(empty):
+    """fit(X, sample_weight=w): the restatement against scikit-learn itself (installed on every box this
+    suite runs on), float64, with and without an empty cluster to relocate."""
+    from oracle import sklearn_oracle
+    rng = np.random.default_rng(21)
+    n, d, k, T = 3000, 6, 7, 12
+    centers = rng.uniform(-8, 8, (k, d))
+    X = centers[rng.integers(0, k, n)] + rng.standard_normal((n, d))
+    w = rng.gamma(2.0, 1.5, n)
+    w[rng.integers(0, n, 50)] = 0.0
+    init = X[rng.choice(n, k, replace=False)].copy()
+    if empty:
+        init[3] = 1e3      # no row is nearest to it: relocation in the first M-step
+    ref = sklearn_oracle.fit(X, init, T, sample_weight=w)
+    r = lloyd.fit(X, init, T, dtype=np.float64, sample_weight=w)
+    assert np.abs(r["centers"] - ref["centers"]).max() / np.abs(ref["centers"]).max() < 1e-12
+    assert np.array_equal(r["labels"], ref["labels"])
+    assert r["n_iter"] == ref["n_iter"]
+    assert abs(lloyd.inertia(X, r["centers"], r["labels"], sample_weight=w) / ref["inertia"] - 1) < 1e-10
