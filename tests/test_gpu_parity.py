@@ -663,3 +663,32 @@ def test_estimator_weights_and_other_dtypes(built_lib):
     assert np.array_equal(a.cluster_centers_, b.cluster_centers_)
     assert np.array_equal(a.labels_, b.labels_)
     assert abs(a.inertia_ - b.inertia_) <= 1e-9 * b.inertia_
+
+
+def test_multi_gpu_weighted_and_typed_equal_single_gpu(eng):
+    """Weighted fit with an empty cluster, and an 8-bit upload, sharded over several GPUs of one process:
+    integer sums make the result identical, bit for bit, to the one-GPU run."""
+    from h2o4gpu_b200.libs import lib_kmeans
+    ndev = lib_kmeans.cdll().kmeans_device_count()
+    if ndev < 2:
+        pytest.skip("one GPU visible")
+    rng = np.random.default_rng(51)
+    X, w, init = _weighted_case(rng, 40001, 32, 24, np.float32)
+    init[5] = 1e3                                            # empty in the first M-step: relocation
+    P = rng.integers(0, 256, (30001, 48)).astype(np.uint8)
+    res = []
+    for devs in ([0], list(range(min(ndev, 4)))):
+        h = eng.ResidentKMeans(devices=devs)
+        h.upload(X)
+        h.set_sample_weight(w)
+        h.fit(init, 6)
+        out = [h.centroids(), h.all_labels(), h.stats()["relocations"], h.inertia()]
+        h.upload(P)
+        h.fit(P[:7].astype(np.float32), 4)
+        out += [h.centroids(), h.all_labels()]
+        h.close()
+        res.append(out)
+    assert res[0][2] == res[1][2] >= 1
+    assert np.array_equal(res[0][0], res[1][0]) and np.array_equal(res[0][1], res[1][1])
+    assert abs(res[0][3] - res[1][3]) <= 1e-9 * res[0][3]
+    assert np.array_equal(res[0][4], res[1][4]) and np.array_equal(res[0][5], res[1][5])
