@@ -46,7 +46,8 @@ __global__ void __launch_bounds__(256)
 delta_accumulate_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict__ labels,
                         int* __restrict__ prev, int k, long long* __restrict__ psums,
                         unsigned long long* __restrict__ pcounts, T scale,
-                        const unsigned long long* changed, unsigned long long limit) {
+                        const unsigned long long* changed, unsigned long long limit,
+                        const T* __restrict__ W, T wscale) {
   constexpr int NP = Fixed<T>::NP;
   if (!delta_turn(changed, limit)) return;
   const int lane = threadIdx.x & 31;
@@ -68,13 +69,21 @@ delta_accumulate_kernel(const T* __restrict__ X, size_t n, int d, const int* __r
       const int from = __shfl_sync(0xffffffffu, od, src);
       const bool to_ok = (unsigned)to < (unsigned)k, from_ok = (unsigned)from < (unsigned)k;
       const T* xr = X + (b + src) * (size_t)d;
+      // sample weights: the row moves w * x and its fixed-point weight (see accumulate_kernel)
+      const T w = W ? W[b + src] : (T)1;
+      unsigned long long units = 1;
+      if (W) {
+        int pw[2];
+        split_pieces<2>(w, wscale, pw);
+        units = (unsigned long long)((long long)pw[0] * (1LL << kPieceBits) + (long long)pw[1]);
+      }
       for (int idx = lane; idx < dv; idx += 32) {
         T x[V];
         VecLoad<T, V>::ld(xr + (size_t)idx * V, x);
 #pragma unroll
         for (int e = 0; e < V; ++e) {
           int p[NP];
-          split_pieces<NP>(x[e], scale, p);
+          split_pieces<NP>(W ? x[e] * w : x[e], scale, p);
           const int col = idx * V + e;
 #pragma unroll
           for (int q = 0; q < NP / 2; ++q) {
@@ -90,8 +99,8 @@ delta_accumulate_kernel(const T* __restrict__ X, size_t n, int d, const int* __r
         }
       }
       if (lane == 0) {
-        if (to_ok) atomicAdd(pcounts + to, 1ULL);
-        if (from_ok) atomicAdd(pcounts + from, ~0ULL);   // minus one, modulo 2^64
+        if (to_ok) atomicAdd(pcounts + to, units);
+        if (from_ok) atomicAdd(pcounts + from, 0ULL - units);   // minus, modulo 2^64
       }
     }
   }
@@ -114,7 +123,7 @@ constexpr int kDeltaChunk = 32768;   // rows between two drains: the int32 accum
 
 template <typename T>
 inline size_t delta_smem_bytes(int k, int d) {
-  return (size_t)Fixed<T>::NP * k * d * sizeof(int) + (size_t)k * sizeof(int) + 16;
+  return (size_t)Fixed<T>::NP * k * d * sizeof(int) + (size_t)2 * k * sizeof(int) + 16;
 }
 
 template <typename T, int V>
@@ -122,12 +131,13 @@ __global__ void __launch_bounds__(kDeltaThreads, 2)
 delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict__ labels,
                              int* __restrict__ prev, int k, long long* __restrict__ psums,
                              unsigned long long* __restrict__ pcounts, T scale,
-                             const unsigned long long* changed, unsigned long long limit) {
+                             const unsigned long long* changed, unsigned long long limit,
+                             const T* __restrict__ W, T wscale) {
   constexpr int NP = Fixed<T>::NP;
   if (!delta_turn(changed, limit)) return;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   int* acc = reinterpret_cast<int*>(smem_raw);      // [NP][k][d]
-  int* cnt = acc + (size_t)NP * k * d;              // [k]
+  int* cnt = acc + (size_t)NP * k * d;              // [2][k]: units, then units * 2^15 (sample weights)
   __shared__ int s_touched;                         // rows netted since the last drain
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -148,7 +158,7 @@ delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int
   const size_t r_end = min(n, r_begin + per);
 
   for (int i = tid; i < NP * k * d; i += kDeltaThreads) acc[i] = 0;
-  for (int i = tid; i < k; i += kDeltaThreads) cnt[i] = 0;
+  for (int i = tid; i < 2 * k; i += kDeltaThreads) cnt[i] = 0;
   if (tid == 0) s_touched = 0;
   __syncthreads();
 
@@ -217,17 +227,24 @@ delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int
             const int to = labels[row], from = prev[row];
             const bool to_ok = (unsigned)to < (unsigned)k, from_ok = (unsigned)from < (unsigned)k;
             const T* xr = X + row * (size_t)d;
+            const T w = W ? W[row] : (T)1;
             for (int idx = l; idx < dv; idx += lpr) {
               T x[V], y[V];
               VecLoad<T, V>::ld(xr + (size_t)idx * V, x);
+              if (W) {
+#pragma unroll
+                for (int e = 0; e < V; ++e) x[e] *= w;
+              }
 #pragma unroll
               for (int e = 0; e < V; ++e) y[e] = -x[e];
               if (to_ok) add_vec_fixed<T, V, NP>(acc + (size_t)to * d, pstride, dv, idx, g & (V - 1), x, scale);
               if (from_ok) add_vec_fixed<T, V, NP>(acc + (size_t)from * d, pstride, dv, idx, g & (V - 1), y, scale);
             }
             if (l == 0) {
-              if (to_ok) atomicAdd(&cnt[to], 1);
-              if (from_ok) atomicAdd(&cnt[from], -1);
+              int pw[2] = {0, 1};
+              if (W) split_pieces<2>(w, wscale, pw);
+              if (to_ok) { atomicAdd(&cnt[to], pw[1]); if (pw[0]) atomicAdd(&cnt[k + to], pw[0]); }
+              if (from_ok) { atomicAdd(&cnt[from], -pw[1]); if (pw[0]) atomicAdd(&cnt[k + from], -pw[0]); }
             }
           }
           for (int i = 0; i < groups && mask; ++i) mask &= mask - 1;
@@ -258,8 +275,10 @@ delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int
           }
         }
         for (int i = tid; i < k; i += kDeltaThreads) {
-          if (cnt[i]) atomicAdd(pcounts + (size_t)i * kFlushPad, (unsigned long long)(long long)cnt[i]);
+          const long long v = (long long)cnt[k + i] * (1LL << kPieceBits) + (long long)cnt[i];
+          if (v) atomicAdd(pcounts + (size_t)i * kFlushPad, (unsigned long long)v);
           cnt[i] = 0;
+          cnt[k + i] = 0;
         }
       }
       __syncthreads();

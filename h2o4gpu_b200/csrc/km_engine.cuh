@@ -1167,7 +1167,9 @@ int Engine<T>::launch_delta(Shard<T>& s, T scale, const unsigned long long* gate
     const char* e = std::getenv("H2O4GPU_KM_DELTA_BITMAP");
     return e && e[0] == '1';
   }();
-  if (bitmap_env && s.pflush && smem <= 100 * 1024 && s.moved_bits_valid && vec_ok(s)) {
+  const T* W = weighted ? s.w : nullptr;
+  const T wsc = (T)w_scale;
+  if (bitmap_env && !W && s.pflush && smem <= 100 * 1024 && s.moved_bits_valid && vec_ok(s)) {
     // the E-step left a map of the rows that moved: no label scan
     KM_CUDA(cudaFuncSetAttribute(delta_accumulate_bitmap_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem));
@@ -1183,12 +1185,12 @@ int Engine<T>::launch_delta(Shard<T>& s, T scale, const unsigned long long* gate
       KM_CUDA(cudaFuncSetAttribute(delta_accumulate_smem_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)smem));
       delta_accumulate_smem_kernel<T, V><<<s.num_sms * (smem <= 100 * 1024 ? 2 : 1), kDeltaThreads, smem, s.stream>>>(
-          s.X, s.rows, d, s.labels, s.labels_prev, k, fs, fc, scale, gate, limit);
+          s.X, s.rows, d, s.labels, s.labels_prev, k, fs, fc, scale, gate, limit, W, wsc);
     } else {
       KM_CUDA(cudaFuncSetAttribute(delta_accumulate_smem_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)smem));
       delta_accumulate_smem_kernel<T, 1><<<s.num_sms * (smem <= 100 * 1024 ? 2 : 1), kDeltaThreads, smem, s.stream>>>(
-          s.X, s.rows, d, s.labels, s.labels_prev, k, fs, fc, scale, gate, limit);
+          s.X, s.rows, d, s.labels, s.labels_prev, k, fs, fc, scale, gate, limit, W, wsc);
     }
     KM_CUDA(cudaGetLastError());
     ++launches;
@@ -1197,10 +1199,10 @@ int Engine<T>::launch_delta(Shard<T>& s, T scale, const unsigned long long* gate
   const int grid = s.num_sms * 8;
   if (vec_ok(s))
     delta_accumulate_kernel<T, V><<<grid, 256, 0, s.stream>>>(s.X, s.rows, d, s.labels, s.labels_prev, k, ps, pc,
-                                                              scale, gate, limit);
+                                                              scale, gate, limit, W, wsc);
   else
     delta_accumulate_kernel<T, 1><<<grid, 256, 0, s.stream>>>(s.X, s.rows, d, s.labels, s.labels_prev, k, ps, pc,
-                                                              scale, gate, limit);
+                                                              scale, gate, limit, W, wsc);
   KM_CUDA(cudaGetLastError());
   ++launches;
   return KM_OK;

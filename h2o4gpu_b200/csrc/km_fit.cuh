@@ -149,8 +149,8 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
   const double inv = std::ldexp(1.0, -(sa + kPieceBits));
   if (!std::isfinite((double)scale) || scale == (T)0) KM_FAIL(KM_EINVAL, "data magnitude outside the supported range");
 
-  // weighted fits take the general M-step kernel: neither the fused small-k update nor the
-  // incremental sums carry weights
+  // weighted fits take the general M-step kernel for full passes (the fused small-k update and
+  // the sorted pass do not carry weights); the incremental sums do
   const bool fused = smallk_ok(true) && !(flags & KM_FIT_FORCE_SPLIT) && !weighted;
   const bool use_tc = !fused && tc_ok(flags);
   if (const char* e = std::getenv("H2O4GPU_KM_TC_TOL")) tc_tol_rel = (float)std::atof(e);
@@ -161,7 +161,7 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
     const char* e = std::getenv("H2O4GPU_KM_DELTA_SUMS");
     return !(e && e[0] == '0');
   }();
-  const bool delta = !fused && delta_env && !(flags & KM_FIT_FULL_SUMS) && !weighted;
+  const bool delta = !fused && delta_env && !(flags & KM_FIT_FULL_SUMS);
   const bool multi = world_size > 1;
   const bool check = (threshold > 0) || (flags & KM_FIT_CHECK_EVERY_ITER);
   stats = kmeans_stats{};

@@ -585,6 +585,13 @@ def test_weighted_fit_matches_oracle(eng, dtype, n, d, k):
     check_labels(X, ref["centers"], h.labels(), ref["labels"])
     want = lloyd.inertia(X, ref["centers"], ref["labels"], sample_weight=w)
     assert abs(h.inertia() / want - 1) < (1e-4 if dtype == np.float32 else 1e-8)
+    # incremental weighted sums (rows that moved leave and join with w * x) against a full weighted
+    # pass in every iteration: the same integers
+    h.fit(init, 12)
+    inc = (h.centroids(), h.labels(), h.stats()["incremental_iterations"])
+    h.fit(init, 12, flags=eng.FIT_FULL_SUMS)
+    assert np.array_equal(inc[0], h.centroids()) and np.array_equal(inc[1], h.labels())
+    assert inc[2] > 0 and h.stats()["incremental_iterations"] == 0
     # unit weights again: the plain fit, bit for bit
     h.set_sample_weight(None)
     h.fit(init, T)
