@@ -78,17 +78,20 @@ mincost_update_kernel(const T* __restrict__ X, size_t n, int d, const int* __res
   }
 }
 
-// Bernoulli draw per row: selected when 2 k cost / phi exceeds the row's uniform number.
+// Bernoulli draw per row: selected when 2 k cost / phi exceeds the row's uniform number
+// (cost = weight * squared distance when sample weights are set).
+template <typename T>
 __global__ void __launch_bounds__(256)
 sample_rows_kernel(const double* __restrict__ cost, size_t n, size_t row0, double phi, double two_k,
                    unsigned long long seed, unsigned int round, unsigned int* __restrict__ list,
-                   unsigned int cap, unsigned int* __restrict__ count) {
+                   unsigned int cap, unsigned int* __restrict__ count, const T* __restrict__ W) {
   const uint2 key = make_uint2((unsigned int)seed, (unsigned int)(seed >> 32));
   for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) {
     const size_t gr = row0 + i;
     const uint4 r = Philox::run(make_uint4((unsigned int)gr, (unsigned int)(gr >> 32), round, kStreamSample), key);
     const double u = u01_53(r.x, r.y);
-    const double p = (two_k * cost[i]) / phi;
+    const double cw = W ? cost[i] * (double)W[i] : cost[i];
+    const double p = (two_k * cw) / phi;
     if (p > u) {
       const unsigned int pos = atomicAdd(count, 1u);
       if (pos < cap) list[pos] = (unsigned int)i;
@@ -107,11 +110,21 @@ gather_rows_kernel(const T* __restrict__ X, int d, const unsigned int* __restric
   }
 }
 
+// rows (or, with sample weights, fixed-point weight units: integers, so the totals do not depend on
+// the order of the additions) nearest to each candidate
+template <typename T>
 __global__ void __launch_bounds__(256)
-label_histogram_kernel(const int* __restrict__ labels, size_t n, int m, unsigned long long* __restrict__ counts) {
+label_histogram_kernel(const int* __restrict__ labels, size_t n, int m, unsigned long long* __restrict__ counts,
+                       const T* __restrict__ W, T wscale) {
   for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) {
     const int l = labels[i];
-    if ((unsigned)l < (unsigned)m) atomicAdd(counts + l, 1ULL);
+    unsigned long long units = 1;
+    if (W) {
+      int pw[2];
+      split_pieces<2>(W[i], wscale, pw);
+      units = (unsigned long long)((long long)pw[0] * (1LL << kPieceBits) + (long long)pw[1]);
+    }
+    if ((unsigned)l < (unsigned)m && units) atomicAdd(counts + l, units);
   }
 }
 
@@ -310,7 +323,7 @@ int init_centroids(Engine<T>& e, int k, int seed, int method, std::vector<T>* ou
     double phi = 0;
     for (auto& s : e.shards) {
       DevGuard g(s.dev);
-      sum_partials_kernel<T><<<1024, 256, 0, s.stream>>>(s.dist, s.rows, s.sum_partials);
+      sum_partials_kernel<T><<<1024, 256, 0, s.stream>>>(s.dist, s.rows, s.sum_partials, e.weighted ? s.w : nullptr);
       sum_final_kernel<<<1, 32, 0, s.stream>>>(s.sum_partials, 1024, &s.st->inertia);
       double part = 0;
       if (cudaMemcpyAsync(&part, &s.st->inertia, sizeof(double), cudaMemcpyDeviceToHost, s.stream) != cudaSuccess ||
@@ -330,8 +343,9 @@ int init_centroids(Engine<T>& e, int k, int seed, int method, std::vector<T>* ou
       Shard<T>& s = e.shards[i];
       DevGuard g(s.dev);
       cudaMemsetAsync(d_count[i], 0, sizeof(unsigned int), s.stream);
-      sample_rows_kernel<<<s.num_sms * 8, 256, 0, s.stream>>>(s.dist, s.rows, s.row0, phi, 2.0 * k, useed,
-                                                             (unsigned int)round, d_list[i], cap, d_count[i]);
+      sample_rows_kernel<T><<<s.num_sms * 8, 256, 0, s.stream>>>(s.dist, s.rows, s.row0, phi, 2.0 * k, useed,
+                                                                (unsigned int)round, d_list[i], cap, d_count[i],
+                                                                e.weighted ? s.w : nullptr);
       unsigned int cnt = 0;
       if (cudaMemcpyAsync(&cnt, d_count[i], sizeof(cnt), cudaMemcpyDeviceToHost, s.stream) != cudaSuccess ||
           cudaStreamSynchronize(s.stream) != cudaSuccess) {
@@ -393,7 +407,7 @@ int init_centroids(Engine<T>& e, int k, int seed, int method, std::vector<T>* ou
     return KM_OK;
   }
 
-  // 3. weights = rows nearest to each candidate, then weighted k-means++ on the device
+  // 3. weights = rows (sample weight) nearest to each candidate, then weighted k-means++ on the device
   KM_TRY(e.set_centroids(m, all.data()));
   KM_TRY(e.assign_all(0));
   std::vector<double> w(m, 0.0);
@@ -404,13 +418,14 @@ int init_centroids(Engine<T>& e, int k, int seed, int method, std::vector<T>* ou
       unsigned long long* dc = nullptr;
       KM_CUDA(km_malloc(&dc, (size_t)m * sizeof(unsigned long long)));
       cudaMemsetAsync(dc, 0, (size_t)m * sizeof(unsigned long long), s.stream);
-      label_histogram_kernel<<<s.num_sms * 8, 256, 0, s.stream>>>(s.labels, s.rows, m, dc);
+      label_histogram_kernel<T><<<s.num_sms * 8, 256, 0, s.stream>>>(s.labels, s.rows, m, dc,
+                                                                    e.weighted ? s.w : nullptr, (T)e.w_scale);
       cudaError_t ce = cudaMemcpyAsync(cnt.data(), dc, (size_t)m * sizeof(unsigned long long), cudaMemcpyDeviceToHost,
                                        s.stream);
       if (ce == cudaSuccess) ce = cudaStreamSynchronize(s.stream);
       km_free(dc);
       if (ce != cudaSuccess) KM_FAIL(KM_ECUDA, "initialisation: candidate weights failed");
-      for (int j = 0; j < m; ++j) w[j] += (double)cnt[j];
+      for (int j = 0; j < m; ++j) w[j] += (double)cnt[j] * (e.weighted ? e.count_unit : 1.0);
     }
   }
   Shard<T>& s0 = e.shards[0];

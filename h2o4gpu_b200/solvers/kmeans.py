@@ -278,11 +278,33 @@ class KMeansH2O(object):
             "The dimension of X [%d] and centroids [%d] is not equal." % (cols, centroids_dim)
         return cols, rows
 
+    def _resident_apply(self, X_np, what):
+        """predict / transform for input that is not float32 / float64: the matrix goes down in its own
+        dtype (converted on the device) through a resident handle."""
+        from .. import engine
+        self._load_lib()
+        dtype = np.float64 if self.double_precision else np.float32
+        rows = X_np.shape[0]
+        ndev = max(1, min(device_count(self.n_gpus)[0], rows))
+        total = device_count(-1)[1]
+        h = engine.ResidentKMeans(dtype=dtype, devices=[(self._gpu_id + i) % total for i in range(ndev)])
+        try:
+            h.upload(X_np)
+            h.set_centroids(np.ascontiguousarray(self.cluster_centers_, dtype=dtype))
+            if what == "predict":
+                h.assign()
+                return h.all_labels()
+            return np.concatenate([h.transform(i) for i in range(ndev)], axis=0)
+        finally:
+            h.close()
+
     def predict(self, X):
         lib = self._load_lib()
         X_np = _get_data(X)
         cols, rows = self._validate_centroids(X_np)
         _check_data_content(self.do_checks, "X", X_np)
+        if X_np.dtype not in (np.float32, np.float64):
+            return self._resident_apply(X_np, "predict")
         c_X = self._toc(X_np)
         dtype = np.float64 if self.double_precision else np.float32
         centers = np.ascontiguousarray(self.cluster_centers_, dtype=dtype).reshape(-1)
@@ -300,6 +322,8 @@ class KMeansH2O(object):
         lib = self._load_lib()
         X_np = _get_data(X)
         cols, rows = self._validate_centroids(X_np)
+        if X_np.dtype not in (np.float32, np.float64):
+            return self._resident_apply(X_np, "transform")
         c_X = self._toc(X_np)
         dtype = np.float64 if self.double_precision else np.float32
         k = self.cluster_centers_.shape[0]

@@ -159,9 +159,23 @@ def _weighted_pick(wm, u, taken):
     return pick
 
 
-def kmeans_parallel(X, k, seed):
-    """Returns (centres k x d, global row index of every centre, rows of all candidates)."""
+def weight_units(w):
+    """Sample weights as the fixed-point integers of the CUDA path: wmax < 2^e,
+    units = rint(w 2^(15-e)) 2^15 + rint(remainder 2^15); returns (units, weight of one unit)."""
+    w = np.asarray(w, dtype=np.float64)
+    _, e = math.frexp(float(w.max()))
+    v = w * 2.0 ** (15 - e)
+    p0 = np.rint(v)
+    p1 = np.rint((v - p0) * 32768.0)
+    return p0 * 32768.0 + p1, 2.0 ** -(30 - e)
+
+
+def kmeans_parallel(X, k, seed, sample_weight=None):
+    """Returns (centres k x d, global row index of every centre, rows of all candidates).  With sample
+    weights a row's cost is weight x squared distance and a candidate's weight the sum of the weights
+    of the rows nearest to it (the first candidate stays a uniform draw)."""
     n, d = X.shape
+    w64 = None if sample_weight is None else np.asarray(sample_weight).astype(np.float64)
     k0, k1 = seed & 0xFFFFFFFF, 0
     r = philox4x32_10(0, 0, 0, STREAM_FIRST, k0, k1)
     first = ((int(r[0][0]) << 32) | int(r[1][0])) % n
@@ -174,13 +188,14 @@ def kmeans_parallel(X, k, seed):
         if fresh:
             c, _ = row_cost(X, X[np.asarray(fresh)])
             cost = np.minimum(cost, c)
-        phi = tree_sum(cost)
+        cw = cost if w64 is None else cost * w64
+        phi = tree_sum(cw)
         fresh = []
         if not phi > 0:
             continue
         rr = philox4x32_10(rows & _MASK, rows >> np.uint64(32), rnd, STREAM_SAMPLE, k0, k1)
         u = u01_53(rr[0], rr[1])
-        p = (2.0 * k * cost) / phi
+        p = (2.0 * k * cw) / phi
         fresh = [int(i) for i in np.flatnonzero(p > u)]
         picked.extend(fresh)
     m = len(picked)
@@ -196,7 +211,11 @@ def kmeans_parallel(X, k, seed):
         return X[np.asarray(out)].copy(), np.asarray(out), np.asarray(picked)
     cand = X[np.asarray(picked)]
     _, lab = row_cost(X, cand)
-    w = np.bincount(lab, minlength=m).astype(np.float64)
+    if w64 is None:
+        w = np.bincount(lab, minlength=m).astype(np.float64)
+    else:
+        units, unit = weight_units(np.asarray(sample_weight))
+        w = np.bincount(lab, weights=units, minlength=m) * unit
     cand64 = cand.astype(np.float64)
     mind = np.full(m, np.finfo(np.float64).max)
     wm = w.copy()

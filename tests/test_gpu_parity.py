@@ -670,6 +670,9 @@ def test_estimator_weights_and_other_dtypes(built_lib):
     assert np.array_equal(a.cluster_centers_, b.cluster_centers_)
     assert np.array_equal(a.labels_, b.labels_)
     assert abs(a.inertia_ - b.inertia_) <= 1e-9 * b.inertia_
+    assert np.array_equal(a.predict(P), b.predict(P.astype(np.float32)))
+    assert np.array_equal(a.transform(P), b.transform(P.astype(np.float32)))
+    assert abs(a.score(P) - b.score(P.astype(np.float32))) <= 1e-9 * abs(b.inertia_)
 
 
 def test_multi_gpu_weighted_and_typed_equal_single_gpu(eng):

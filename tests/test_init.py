@@ -143,3 +143,29 @@ def test_abi_fit_with_kmeans_parallel_init(built_lib, dtype):
     want = lloyd.fit(X, init.astype(np.float64), 10)["centers"]
     tol = 1e-4 if dtype == np.float32 else 1e-10
     assert np.abs(C - want).max() <= tol * np.abs(want).max()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,seed", [(np.float32, 3), (np.float64, 6)])
+def test_kmeans_parallel_with_sample_weights_matches_oracle(eng, dtype, seed):
+    """Sample weights in the initialisation: cost = weight x squared distance in the sampling rounds,
+    candidate weights = summed sample weights; draw for draw the numpy restatement.  Rows of weight zero
+    are never drawn in a sampling round."""
+    from h2o4gpu_b200 import synth
+    X, _, _ = synth.c2(n=20000)
+    X = X.astype(dtype)
+    rng = np.random.default_rng(seed)
+    w = rng.gamma(2.0, 1.5, X.shape[0]).astype(dtype)
+    w[rng.random(X.shape[0]) < 0.3] = 0
+    want_C, want_rows, cand = kp.kmeans_parallel(X, 20, seed, sample_weight=w)
+    plain_rows = kp.kmeans_parallel(X, 20, seed)[1]
+    h = eng.ResidentKMeans(dtype=dtype)
+    h.upload(X)
+    h.set_sample_weight(w)
+    C, rows = h.init_centroids(20, seed=seed, return_rows=True)
+    h.set_sample_weight(None)
+    C0, rows0 = h.init_centroids(20, seed=seed, return_rows=True)
+    h.close()
+    assert np.array_equal(rows, want_rows) and np.array_equal(C, want_C)
+    assert np.array_equal(rows0, plain_rows) and not np.array_equal(rows, rows0)
+    assert (w[cand[1:]] > 0).all()
