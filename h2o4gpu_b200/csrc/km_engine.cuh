@@ -357,26 +357,45 @@ __global__ void transpose_cm_kernel(const S* __restrict__ src, T* __restrict__ d
 
 // Row-major matrix of S -> T, element by element: replaces the host-side astype copy of the
 // wrapper (src/interface_py/h2o4gpu/solvers/utils.py:46-96), which for 8-bit data quadruples the
-// bytes that cross the bus.  A thread converts 16 bytes of the source per step.
+// bytes that cross the bus.  A thread converts E consecutive elements with one vector load and one
+// vector store, so a warp reads and writes contiguous runs (bound by HBM: sizeof(S) + sizeof(T) bytes
+// per element); four such groups are in flight per thread.
+template <typename X, int E>
+struct alignas(E * sizeof(X) > 16 ? 16 : E * sizeof(X)) ElemPack { X e[E]; };
+
 template <typename S, typename T>
 __global__ void __launch_bounds__(256)
 convert_rm_kernel(const S* __restrict__ src, T* __restrict__ dst, size_t count) {
-  constexpr int E = 16 / sizeof(S);
-  const size_t nvec = count / E;
-  const bool aligned = (reinterpret_cast<uintptr_t>(src) & 15) == 0;
+  constexpr int E = (sizeof(S) >= 8 || sizeof(T) >= 8) ? 2 : 4;
+  constexpr int U = 4;
+  using PS = ElemPack<S, E>;
+  using PT = ElemPack<T, E>;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (aligned) {
-    for (size_t i = tid; i < nvec; i += stride) {
-      union { uint4 q; S e[E]; } u;
-      u.q = __ldcs(reinterpret_cast<const uint4*>(src) + i);
+  const bool aligned = (reinterpret_cast<uintptr_t>(src) % sizeof(PS)) == 0 &&
+                       (reinterpret_cast<uintptr_t>(dst) % sizeof(PT)) == 0;
+  const size_t nvec = aligned ? count / E : 0;
+  const PS* vs = reinterpret_cast<const PS*>(src);
+  PT* vd = reinterpret_cast<PT*>(dst);
+  for (size_t i0 = tid; i0 < nvec; i0 += stride * U) {
+    PS in[U];
 #pragma unroll
-      for (int e = 0; e < E; ++e) dst[i * E + e] = convert_value<T, S>(u.e[e]);
+    for (int u = 0; u < U; ++u) {
+      const size_t i = i0 + (size_t)u * stride;
+      if (i < nvec) in[u] = vs[i];
     }
-    for (size_t i = nvec * E + tid; i < count; i += stride) dst[i] = convert_value<T, S>(src[i]);
-  } else {
-    for (size_t i = tid; i < count; i += stride) dst[i] = convert_value<T, S>(src[i]);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t i = i0 + (size_t)u * stride;
+      if (i < nvec) {
+        PT out;
+#pragma unroll
+        for (int e = 0; e < E; ++e) out.e[e] = convert_value<T, S>(in[u].e[e]);
+        vd[i] = out;
+      }
+    }
   }
+  for (size_t i = nvec * E + tid; i < count; i += stride) dst[i] = convert_value<T, S>(src[i]);
 }
 
 template <typename T, typename F>

@@ -1,6 +1,8 @@
 """Small resident fit of a bench-shaped workload for profiler captures (Gaussian mixture with
 as many components as clusters, seeded init rows; defaults: the C2 shape d=64, k=100):
-    python h2o4gpu_b200/ncu_case.py [rows] [iterations] [d] [k]"""
+    python h2o4gpu_b200/ncu_case.py [rows] [iterations] [d] [k] [mode]
+mode "weighted": the same fit with gamma-distributed sample weights; mode "u8": an 8-bit pixel matrix
+(80 % zeros) uploaded from the host in its own dtype and converted on the device, then fitted."""
 import sys
 import numpy as np
 sys.path.insert(0, __import__('os').path.dirname(__import__('os').path.dirname(__import__('os').path.abspath(__file__))))
@@ -10,8 +12,17 @@ n = int(sys.argv[1]) if len(sys.argv) > 1 else 2_000_000
 iters = int(sys.argv[2]) if len(sys.argv) > 2 else 3
 d = int(sys.argv[3]) if len(sys.argv) > 3 else 64
 k = int(sys.argv[4]) if len(sys.argv) > 4 else 100
+mode = sys.argv[5] if len(sys.argv) > 5 else ""
 dev = torch.device("cuda", 0)
 rng = np.random.default_rng(0)
+if mode == "u8":
+    P = (rng.integers(1, 256, (n, d), dtype=np.uint8) * (rng.random((n, d), dtype=np.float32) < 0.2)).astype(np.uint8)
+    h = engine.ResidentKMeans()
+    h.upload(P)
+    h.fit(P[:k].astype(np.float32), iters, flags=engine.FIT_NO_FINAL_ASSIGN)
+    print(h.stats())
+    h.close()
+    sys.exit(0)
 centers = rng.uniform(-10, 10, (k, d)).astype(np.float32)
 w = rng.dirichlet(np.ones(k)).astype(np.float32)
 X = torch.empty((n, d), dtype=torch.float32, device=dev)
@@ -19,6 +30,8 @@ engine.synth_device(X.data_ptr(), n, d, np.float32, centers=centers, weights=w, 
 init = X[torch.from_numpy(np.sort(rng.choice(n, k, replace=False))).to(dev)].cpu().numpy()
 h = engine.ResidentKMeans()
 h.attach_device(0, X.data_ptr(), n, d)
+if mode == "weighted":
+    h.set_sample_weight(rng.gamma(2.0, 1.5, n).astype(np.float32))
 h.fit(init, iters, flags=engine.FIT_NO_FINAL_ASSIGN)
 print(h.stats())
 h.close()
