@@ -702,3 +702,90 @@ def test_multi_gpu_weighted_and_typed_equal_single_gpu(eng):
     assert np.array_equal(res[0][0], res[1][0]) and np.array_equal(res[0][1], res[1][1])
     assert abs(res[0][3] - res[1][3]) <= 1e-9 * res[0][3]
     assert np.array_equal(res[0][4], res[1][4]) and np.array_equal(res[0][5], res[1][5])
+
+
+# ---- one process per GPU (the layout of the bench under torchrun) ---------------------------
+_RANK_CODE = r'''
+import os, sys, time
+import numpy as np
+import torch
+from h2o4gpu_b200 import engine, synth
+rank, world, tmp = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
+idf = os.path.join(tmp, "nccl_id")
+if rank == 0:
+    nid = engine.ResidentKMeans.nccl_unique_id()
+    with open(idf + ".part", "wb") as f:
+        f.write(nid)
+    os.replace(idf + ".part", idf)
+else:
+    t0 = time.time()
+    while not os.path.exists(idf):
+        if time.time() - t0 > 120:
+            sys.exit("no NCCL id from rank 0")
+        time.sleep(0.05)
+    nid = open(idf, "rb").read()
+X, init, _ = synth.c2(n=50001)
+w = np.random.default_rng(3).gamma(2.0, 1.5, X.shape[0]).astype(np.float32)
+per = -(-X.shape[0] // world)
+lo, hi = rank * per, min(X.shape[0], (rank + 1) * per)
+dev = torch.device("cuda", rank)
+Xd = torch.from_numpy(X[lo:hi]).to(dev)
+h = engine.ResidentKMeans(devices=[rank], rank0=rank, world_size=world, nccl_id=nid)
+h.attach_device(0, Xd.data_ptr(), hi - lo, X.shape[1], n_total=X.shape[0])
+out = {}
+h.fit(init, 5)
+out["C"], out["lab"], out["reloc"] = h.centroids(), h.labels(), h.stats()["relocations"]
+out["inertia"] = h.inertia()
+h.set_sample_weight(w[lo:hi])
+h.fit(init, 5)
+out["Cw"], out["labw"], out["inertia_w"] = h.centroids(), h.labels(), h.inertia()
+h.close()
+np.savez(os.path.join(tmp, "rank%d.npz" % rank), **out)
+print("rank ok")
+'''
+
+
+@pytest.mark.parametrize("push", ["1", "0"])
+def test_one_process_per_gpu_equals_single_gpu(eng, tmp_path, push):
+    """Two processes, one GPU each, exchanging the centroid sums by the push all-reduce over peer memory
+    (push = 1) or by NCCL (push = 0): the same bits as one GPU, with an empty cluster repaired across ranks,
+    without and with sample weights."""
+    import os
+    import subprocess
+    import sys
+    from h2o4gpu_b200.libs import lib_kmeans
+    if lib_kmeans.cdll().kmeans_device_count() < 2:
+        pytest.skip("one GPU visible")
+    from h2o4gpu_b200 import synth
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, H2O4GPU_KM_PUSH_ALLREDUCE=push, NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, "-c", _RANK_CODE, str(r), "2", str(tmp_path)], cwd=root, env=env,
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=300)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            o, _ = p.communicate()
+        outs.append(o)
+    assert all(p.returncode == 0 for p in procs) and all("rank ok" in o for o in outs), "\n".join(outs)
+    X, init, _ = synth.c2(n=50001)
+    w = np.random.default_rng(3).gamma(2.0, 1.5, X.shape[0]).astype(np.float32)
+    h = eng.ResidentKMeans()
+    h.upload(X)
+    h.fit(init, 5)
+    C, lab, reloc, inertia = h.centroids(), h.labels(), h.stats()["relocations"], h.inertia()
+    h.set_sample_weight(w)
+    h.fit(init, 5)
+    Cw, labw, inertia_w = h.centroids(), h.labels(), h.inertia()
+    h.close()
+    r = [np.load(tmp_path / ("rank%d.npz" % i)) for i in range(2)]
+    assert reloc > 0
+    for i in range(2):
+        assert int(r[i]["reloc"]) == reloc
+        assert np.array_equal(r[i]["C"], C) and np.array_equal(r[i]["Cw"], Cw)
+        assert abs(float(r[i]["inertia"]) - inertia) <= 1e-9 * inertia
+        assert abs(float(r[i]["inertia_w"]) - inertia_w) <= 1e-9 * inertia_w
+    assert np.array_equal(np.concatenate([r[0]["lab"], r[1]["lab"]]), lab)
+    assert np.array_equal(np.concatenate([r[0]["labw"], r[1]["labw"]]), labw)
