@@ -23,6 +23,7 @@
 #include "km_accumulate.cuh"
 #include "km_accumulate_sorted.cuh"
 #include "km_accumulate_delta.cuh"
+#include "km_assign_dmma.cuh"
 #include "km_common.cuh"
 #include "km_finalize.cuh"
 #include "km_nccl.h"
@@ -856,6 +857,13 @@ template <> struct TileCfg<float> {
 template <> struct TileCfg<double> {
   static int go(const double* X, size_t n, int d, const double* C, int k, const double* cn, int* lab, IterState* st,
                 double* out, size_t ld, int mode, bool vec, cudaStream_t s) {
+    // labels for more than a few centroids: the float64 matrix unit (km_assign_dmma.cuh)
+    static const bool dmma_env = [] {
+      const char* e = std::getenv("H2O4GPU_KM_DMMA");
+      return !(e && e[0] == '0');
+    }();
+    if (dmma_env && mode == MODE_ASSIGN && vec && dmma::shape_ok(k, d) && (reinterpret_cast<uintptr_t>(C) & 15) == 0)
+      return dmma::launch(X, n, d, C, k, cn, lab, st, s);
     return launch_tile_cfg<double, 64, 64, 16, 4, 4>(X, n, d, C, k, cn, lab, st, out, ld, mode, vec, s);
   }
 };
