@@ -789,3 +789,57 @@ def test_one_process_per_gpu_equals_single_gpu(eng, tmp_path, push):
         assert abs(float(r[i]["inertia_w"]) - inertia_w) <= 1e-9 * inertia_w
     assert np.array_equal(np.concatenate([r[0]["lab"], r[1]["lab"]]), lab)
     assert np.array_equal(np.concatenate([r[0]["labw"], r[1]["labw"]]), labw)
+
+
+# ---- float64 E-step on the matrix unit -----------------------------------------------------
+_DMMA_SHAPES = [(30011, 50, 777), (5003, 6, 40), (20000, 256, 300), (777, 34, 33)]
+_DMMA_CODE = r'''
+import sys
+import numpy as np
+from h2o4gpu_b200 import engine
+shapes = %r
+out = {}
+for i, (n, d, k) in enumerate(shapes):
+    rng = np.random.default_rng(100 + i)
+    centers = rng.uniform(-6, 6, (k, d))
+    X = centers[rng.integers(0, k, n)] + rng.standard_normal((n, d))
+    init = X[rng.choice(n, k, replace=False)].copy()
+    h = engine.ResidentKMeans(dtype=np.float64)
+    h.upload(X)
+    h.fit(init, 3)
+    out["C%%d" %% i], out["lab%%d" %% i] = h.centroids(), h.labels()
+    h.close()
+np.savez(sys.argv[1], **out)
+print("simt ok")
+'''
+
+
+def test_f64_matrix_unit_kernel_matches_simt_kernel_and_oracle(eng, tmp_path):
+    """The float64 E-step on the double-precision matrix unit (default for k > 32) against the register-tiled
+    kernel (environment switch, child process) - same labels and centroids, ragged n, d and k - and its
+    labels against the numpy E-step from the same centres."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = str(tmp_path / "simt.npz")
+    r = subprocess.run([sys.executable, "-c", _DMMA_CODE % (_DMMA_SHAPES,), path], cwd=root,
+                       env=dict(os.environ, H2O4GPU_KM_DMMA="0"), capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "simt ok" in r.stdout, r.stdout + r.stderr
+    simt = np.load(path)
+    for i, (n, d, k) in enumerate(_DMMA_SHAPES):
+        rng = np.random.default_rng(100 + i)
+        centers = rng.uniform(-6, 6, (k, d))
+        X = centers[rng.integers(0, k, n)] + rng.standard_normal((n, d))
+        init = X[rng.choice(n, k, replace=False)].copy()
+        h = eng.ResidentKMeans(dtype=np.float64)
+        h.upload(X)
+        h.fit(init, 3)
+        C, lab = h.centroids(), h.labels()
+        h.set_centroids(init)
+        h.assign()
+        lab0 = h.labels()
+        h.close()
+        assert np.array_equal(lab, simt["lab%d" % i]), (n, d, k)
+        assert rel_err(C, simt["C%d" % i]) < 1e-13
+        check_labels(X, init, lab0, lloyd.assign(X, init))
