@@ -8,9 +8,11 @@
 // The products are exact and every accumulation rounds once, like an FMA chain, so the scores
 // are float64-accurate; they are |c|^2 - 2 x.c, first minimum wins, as in the other kernels.
 //
-//   CTA: 128 rows x 128 centroids, 16 warps as 4 (rows) x 4 (centroids), warp tile 32 x 32
-//        = 4 x 4 fragments of 8 x 8, 32 accumulator doubles per lane;
-//   d in chunks of 16 columns: X chunk (128 x 16) and centroid chunk (128 x 16) through a
+//   CTA: 128 rows x 64 centroids, 8 warps as 4 (rows) x 2 (centroids), warp tile 32 x 32
+//        = 4 x 4 fragments of 8 x 8, 32 accumulator doubles per lane; two CTAs per SM, so that
+//        one computes while the other sits at its barrier (one CTA of 16 warps and a 128 x 128
+//        tile left the unit idle a quarter of the time);
+//   d in chunks of 16 columns: X chunk (128 x 16) and centroid chunk (64 x 16) through a
 //        three-stage cp.async pipeline; rows of 16 doubles are padded to 20 in shared memory,
 //        which makes the fragment loads (lane = (row in 0..7, column in 0..3)) conflict-free;
 //   the pipeline runs over the flattened (centroid tile, chunk) pairs, the running
@@ -24,10 +26,13 @@
 namespace km {
 namespace dmma {
 
-constexpr int BM = 128, BN = 128, BK = 16;
+constexpr int BM = 128, BN = 64, BK = 16;
 constexpr int kPitch = BK + 4;          // doubles per padded row
-constexpr int kThreads = 512;
+constexpr int kWarpsN = BN / 32;        // warps side by side over the centroids
+constexpr int kThreads = (BM / 32) * kWarpsN * 32;
 constexpr int kStages = 3;
+constexpr int kVecPerThread = (BM + BN) * (BK / 2) / kThreads;
+static_assert((BM + BN) * (BK / 2) % kThreads == 0, "whole vectors per thread");
 constexpr size_t kStageDoubles = (size_t)(BM + BN) * kPitch;
 constexpr size_t kSmemBytes = kStages * kStageDoubles * sizeof(double);
 
@@ -49,17 +54,17 @@ __device__ __forceinline__ void mma884(double (&c)[2], double a, double b) {
                : "d"(a), "d"(b));
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 assign_kernel(const double* __restrict__ X, size_t n, int d, const double* __restrict__ C, int k,
               const double* __restrict__ cnorm, int* __restrict__ labels, IterState* st) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   double* stage = reinterpret_cast<double*>(smem_raw);   // [kStages][(BM + BN)][kPitch]
-  __shared__ double s_best[4][BM];
-  __shared__ int s_idx[4][BM];
+  __shared__ double s_best[kWarpsN][BM];
+  __shared__ int s_idx[kWarpsN][BM];
   __shared__ unsigned int s_changed;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int wm = warp >> 2, wn = warp & 3;       // warp's place in the 4 x 4 grid
+  const int wm = warp / kWarpsN, wn = warp % kWarpsN;   // warp's place in the grid of warp tiles
   const int g = lane >> 2, t = lane & 3;
   const size_t row0 = (size_t)blockIdx.x * BM;
   const int n_chunks = (d + BK - 1) / BK;
@@ -67,14 +72,14 @@ assign_kernel(const double* __restrict__ X, size_t n, int d, const double* __res
   const int total = n_ctiles * n_chunks;
   if (tid == 0) s_changed = 0;
 
-  // one pair = X chunk + centroid chunk: (128 + 128) rows x 8 vectors of 16 bytes, four per thread
+  // one pair = X chunk + centroid chunk: (BM + BN) rows x 8 vectors of 16 bytes
   auto issue = [&](int pair) {
     if (pair < total) {
       const int ct = pair / n_chunks, kc = pair - ct * n_chunks;
       double* dst = stage + (size_t)(pair % kStages) * kStageDoubles;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int v = tid + j * kThreads;          // 0 .. 2047
+      for (int j = 0; j < kVecPerThread; ++j) {
+        const int v = tid + j * kThreads;
         const int r = v >> 3, q = v & 7;           // row of the stage (X rows first), vector of the row
         const int col = kc * BK + q * 2;
         const bool is_x = r < BM;
@@ -159,7 +164,7 @@ assign_kernel(const double* __restrict__ X, size_t n, int d, const double* __res
     double m = s_best[0][tid];
     int mi = s_idx[0][tid];
 #pragma unroll
-    for (int w = 1; w < 4; ++w) {
+    for (int w = 1; w < kWarpsN; ++w) {
       const double om = s_best[w][tid];
       const int oi = s_idx[w][tid];
       if (om < m || (om == m && oi < mi)) { m = om; mi = oi; }
@@ -182,6 +187,8 @@ inline int launch(const double* X, size_t n, int d, const double* C, int k, cons
                   IterState* st, cudaStream_t stream) {
   // per device, so set on every launch (cheap)
   KM_CUDA(cudaFuncSetAttribute(assign_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+  // without this the driver sizes the shared-memory carve-out for one CTA and only one is resident
+  cudaFuncSetAttribute(assign_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   const size_t grid = (n + BM - 1) / BM;
   if (grid == 0) return KM_OK;
   if (grid > 0x7fffffffULL) KM_FAIL(KM_EINVAL, "shard too large for one launch");
