@@ -222,7 +222,8 @@ def main():
 
     h = engine.ResidentKMeans(np.float32, devices=(local_rank,), rank0=rank, world_size=world, nccl_id=nccl_id)
     h.attach_device(0, X.data_ptr(), n, d, n_total=n * world)
-    flags = engine.FIT_NO_FINAL_ASSIGN | args.flags
+    # per-upload preparation (row norms, fp16-split copy of the rows for the d = 64 kernel) happens in the warm-up
+    flags = engine.FIT_NO_FINAL_ASSIGN | engine.FIT_PRESPLIT | args.flags
 
     def barrier():
         torch.cuda.synchronize()

@@ -158,6 +158,17 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
       : "memory");
 }
 
+// the same with A from shared memory (descriptor)
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // K-major, 128-byte swizzle, dense 8-row groups (1024 B apart)
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
   uint64_t desc = (uint64_t)((addr & 0x3FFFFu) >> 4);
@@ -275,9 +286,36 @@ prep_kernel(const float* __restrict__ C, const float* __restrict__ cnorm, int k,
 // dbg: bit 1 (2) = do not issue the MMAs, bit 2 (4) = skip the epilogue arithmetic,
 // bit 3 (8) = skip the TMEM stores (timing experiments only; labels stay valid;
 // 0 or 1 in production).
-template <int D>
+// The rows of X split once into the two fp16 operands of the product (the arithmetic of the
+// converter warps below: y = x * sx, upper half = fp16(y), lower half = fp16(y - upper)), so that
+// the E-step can read them with TMA straight into the layout the MMA consumes and needs no
+// conversion per iteration.  Same bytes per element as the float32 matrix (2 + 2).
+__global__ void __launch_bounds__(256)
+split_rows_kernel(const float* __restrict__ X, size_t count, float sx, __half* __restrict__ xh,
+                  __half* __restrict__ xl) {
+  const size_t nvec = count / 8;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+    const float4 a = __ldcs(reinterpret_cast<const float4*>(X) + 2 * i);
+    const float4 b = __ldcs(reinterpret_cast<const float4*>(X) + 2 * i + 1);
+    const float y[8] = {a.x * sx, a.y * sx, a.z * sx, a.w * sx, b.x * sx, b.y * sx, b.z * sx, b.w * sx};
+    uint32_t hi[4], lo[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const __half2 h = __floats2half2_rn(y[2 * c], y[2 * c + 1]);
+      const float2 f = __half22float2(h);
+      const __half2 l = __floats2half2_rn(y[2 * c] - f.x, y[2 * c + 1] - f.y);
+      hi[c] = *reinterpret_cast<const uint32_t*>(&h);
+      lo[c] = *reinterpret_cast<const uint32_t*>(&l);
+    }
+    reinterpret_cast<uint4*>(xh)[i] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    reinterpret_cast<uint4*>(xl)[i] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+  }
+}
+
+template <int D, bool PRE>
 __global__ void __launch_bounds__(kThreads, 1)
-assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmBhi,
+assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmXl,
+                 const __grid_constant__ CUtensorMap tmBhi,
                  const __grid_constant__ CUtensorMap tmBlo, const float* __restrict__ cn_pad,
                  const float* __restrict__ xnorm, int* __restrict__ labels, size_t n, int n_tiles, int npad,
                  IterState* st, int count_changes, unsigned int* __restrict__ amb_rows, float tol_rel, float sx,
@@ -307,7 +345,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   const int lane = tid & 31;
 
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(bar(FULL + s), 1); mbar_init(bar(EMPTY + s), 128); }
+    for (int s = 0; s < kStages; ++s) { mbar_init(bar(FULL + s), 1); mbar_init(bar(EMPTY + s), PRE ? 1 : 128); }
     for (int b = 0; b < 2; ++b) { mbar_init(bar(A_READY + b), 128); mbar_init(bar(A_EMPTY + b), 1); }
     for (int a = 0; a < kAcc; ++a) { mbar_init(bar(ACC_FULL + a), 1); mbar_init(bar(ACC_EMPTY + a), 128); }
     mbar_init(bar(B_FULL), 1);
@@ -348,9 +386,16 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         if (i >= kStages) ok = mbar_wait(bar(EMPTY + s), ph ^ 1u, abort_flag, 1, i);
         if (!ok) break;
         mbar_expect_tx(bar(FULL + s), stage_bytes);
+        if (PRE) {
+          // the row tile arrives split already: upper halves, then lower halves, each 128 rows x 64 halves in
+          // the layout the MMA reads
+          tma_load_2d(base + off_stage + s * stage_bytes, &tmX, 0, tile * kBM, bar(FULL + s));
+          tma_load_2d(base + off_stage + s * stage_bytes + 16384u, &tmXl, 0, tile * kBM, bar(FULL + s));
+        } else {
 #pragma unroll
-        for (int p = 0; p < P; ++p)
-          tma_load_2d(base + off_stage + s * stage_bytes + p * 16384u, &tmX, p * 32, tile * kBM, bar(FULL + s));
+          for (int p = 0; p < P; ++p)
+            tma_load_2d(base + off_stage + s * stage_bytes + p * 16384u, &tmX, p * 32, tile * kBM, bar(FULL + s));
+        }
       }
       if (!ok) {
         // aborting: let the copies already issued land before the CTA exits
@@ -386,7 +431,9 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         const uint32_t phb = (uint32_t)(i >> 1) & 1u;
         const int a = i % kAcc;
         const uint32_t pha = (uint32_t)(i / kAcc) & 1u;
-        ok = mbar_wait(bar(A_READY + grp), phb, abort_flag, 3, i);
+        const int s = i % kStages;
+        if (PRE) ok = mbar_wait(bar(FULL + s), (uint32_t)(i / kStages) & 1u, abort_flag, 3, i);
+        else ok = mbar_wait(bar(A_READY + grp), phb, abort_flag, 3, i);
         // Consecutive uses of an accumulator (tile counters i - 3 and i) belong to different
         // issuers, and a parity wait cannot tell "two phases behind" from "done": an issuer
         // that ran ahead of the other (a slow epilogue group is enough) could take the
@@ -408,10 +455,15 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           for (int kk = 0; kk < KS; ++kk) {
             const uint32_t a_col = a_hi + (term == 1 ? 32u : 0u) + kk * 8u;
             const uint64_t bd = (term == 2) ? bdesc_lo[kk] : bdesc_hi[kk];
-            if (!(dbg & 2)) tc_mma_ts(acc, a_col, bd, idesc, 1u);
+            if (PRE) {
+              const uint32_t a_smem = base + off_stage + (uint32_t)s * stage_bytes + (term == 1 ? 16384u : 0u) + kk * 32u;
+              tc_mma_ss(acc, smem_desc_sw128(a_smem), bd, idesc, 1u);
+            } else if (!(dbg & 2)) {
+              tc_mma_ts(acc, a_col, bd, idesc, 1u);
+            }
           }
         }
-        tc_commit(bar(A_EMPTY + grp));
+        tc_commit(bar(PRE ? EMPTY + s : A_EMPTY + grp));
         tc_commit(bar(ACC_FULL + a));
         __threadfence_block();
         issued_upto[grp] = i;
@@ -437,7 +489,8 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     const uint32_t a_hi = tmem_base + lane_addr + kACol + (uint32_t)grp * 64u;
     bool ok = true;
     int i = grp;
-    for (int tile = blockIdx.x + grp * gridDim.x; tile < n_tiles && ok; tile += 2 * gridDim.x, i += 2) {
+    // (nothing to convert when the rows arrive split)
+    for (int tile = blockIdx.x + grp * gridDim.x; !PRE && tile < n_tiles && ok; tile += 2 * gridDim.x, i += 2) {
       const int s = i % kStages;
       const uint32_t ph = (uint32_t)(i / kStages) & 1u;
       const uint32_t phb = (uint32_t)(i >> 1) & 1u;

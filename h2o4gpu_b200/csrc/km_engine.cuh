@@ -175,6 +175,7 @@ struct Engine : EngineBase {
   int tc_refresh(Shard<T>& s);  // split the current centroids for the tensor-core kernel
   int launch_assign(Shard<T>& s, bool use_tc, bool count_changes);
   int tc_mask_hi = 1;
+  bool tc_split_build = false;   // the running fit has enough iterations to pay for the split copy of X
   float tc_tol_rel = tc::kTolRel;
   float tc_sx = 1.f, tc_sb = 1.f;   // operand scales of the tensor-core kernel
   double cbound = 0;                // bound on |centroid coordinate|: max(|x|, |initial centroids|)
@@ -309,6 +310,12 @@ int Engine<T>::attach_device(int local, const T* dX, size_t rows, size_t cols, s
   s.rows = rows;
   s.x_checked = false;
   weighted = false;
+  // what the tensor-core path keeps per matrix (row norms, split copy, tensor maps) belongs to the old one,
+  // even when the new one has the same address and shape
+  s.tcp.xnorm_of = nullptr;
+  s.tcp.xsplit_of = nullptr;
+  s.tcp.ready = false;
+  s.tcbp.ready = false;
   if ((int)cols != d) have_centroids = false;
   d = (int)cols;
   n_total = ntot;
@@ -1099,7 +1106,7 @@ int Engine<T>::launch_assign(Shard<T>& s, bool use_tc, bool count_changes) {
       launches += 2;
       unsigned int* bits = (count_changes && s.labels_prev_cap >= s.rows) ? s.moved_bits : nullptr;
       KM_TRY(tc::launch(s.tcp, s.labels, s.st, count_changes, s.amb_rows, tc_tol_rel, s.num_sms, tc_mask_hi,
-                        s.stream, bits, s.amb_near));
+                        s.stream, bits, s.amb_near, tc_split_build));
       s.moved_bits_valid = bits != nullptr;
       refine_near_kernel<float><<<s.num_sms * 4, kRefineThreads, 0, s.stream>>>(
           s.X, d, s.C[cur], k, s.amb_rows, s.amb_near, s.st, s.labels, count_changes ? 1 : 0, bits);

@@ -153,6 +153,10 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
   // the sorted pass do not carry weights); the incremental sums do
   const bool fused = smallk_ok(true) && !(flags & KM_FIT_FORCE_SPLIT) && !weighted;
   const bool use_tc = !fused && tc_ok(flags);
+  // the split copy of X (d = 64 tensor-core kernel without converter warps) costs about as much as
+  // sixteen iterations save
+  tc_split_build = max_iter >= 16 || (flags & KM_FIT_PRESPLIT);
+  struct SplitBuildGuard { bool& f; ~SplitBuildGuard() { f = false; } } split_build_guard{tc_split_build};
   if (const char* e = std::getenv("H2O4GPU_KM_TC_TOL")) tc_tol_rel = (float)std::atof(e);
   // incremental M-step (km_accumulate_delta.cuh): on unless the caller or the environment asks
   // for a full recomputation every iteration; a shard switches to it, on the device, in the

@@ -55,13 +55,22 @@ struct Plan {
   float sx = 1.f, sb = 1.f;
   CUtensorMap tmX, tmBhi, tmBlo;
   bool ready = false;
+  // the rows split once into fp16 halves (d = 64): [rows][64] upper, then [rows][64] lower
+  __half* xsplit = nullptr;
+  size_t xsplit_cap = 0;
+  const float* xsplit_of = nullptr;
+  size_t xsplit_rows = 0;
+  float xsplit_sx = 0.f;
+  bool xsplit_failed = false;   // no memory for it: stay with the converting kernel
+  CUtensorMap tmXh, tmXl;
 
   void release() {
-    km_free(bhi); km_free(blo); km_free(cn); km_free(xnorm);
+    km_free(bhi); km_free(blo); km_free(cn); km_free(xnorm); km_free(xsplit);
     bhi = blo = nullptr;
     cn = xnorm = nullptr;
-    xnorm_cap = 0;
-    xnorm_of = nullptr;
+    xsplit = nullptr;
+    xnorm_cap = xsplit_cap = 0;
+    xnorm_of = xsplit_of = nullptr;
     ready = false;
   }
 };
@@ -99,6 +108,45 @@ inline int ensure_xnorm(Plan& pl, const float* X, size_t rows, int d, int num_sm
   return KM_OK;
 }
 
+// The split copy of X for the kernel variant without converter warps (d = 64): made when the
+// matrix, its size or the scale changed; costs one pass over X and as much memory again.
+inline bool presplit_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("H2O4GPU_KM_TC_PRESPLIT");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+inline bool ensure_xsplit(Plan& pl, const float* X, size_t rows, int d, float sx, int num_sms, cudaStream_t stream,
+                          bool allow_build) {
+  if (d != 64 || !presplit_enabled() || pl.xsplit_failed) return false;
+  if (pl.xsplit && pl.xsplit_of == X && pl.xsplit_rows == rows && pl.xsplit_sx == sx) return true;
+  if (!allow_build) return false;   // a single pass (predict) does not pay for the split
+  if (pl.xsplit_cap < rows) {
+    km_free(pl.xsplit);
+    pl.xsplit = nullptr;
+    pl.xsplit_cap = 0;
+    if (km_malloc(&pl.xsplit, rows * 64 * 2 * sizeof(__half)) != cudaSuccess) {
+      cudaGetLastError();
+      pl.xsplit_failed = true;
+      return false;
+    }
+    pl.xsplit_cap = rows;
+  }
+  __half* xh = pl.xsplit;
+  __half* xl = pl.xsplit + rows * 64;
+  split_rows_kernel<<<num_sms * 8, 256, 0, stream>>>(X, rows * 64, sx, xh, xl);
+  if (cudaGetLastError() != cudaSuccess || make_map(&pl.tmXh, xh, rows, 64, kBM, 2) != KM_OK ||
+      make_map(&pl.tmXl, xl, rows, 64, kBM, 2) != KM_OK) {
+    pl.xsplit_failed = true;
+    return false;
+  }
+  pl.xsplit_of = X;
+  pl.xsplit_rows = rows;
+  pl.xsplit_sx = sx;
+  return true;
+}
+
 inline int setup(Plan& pl, const float* X, size_t rows, int k, int d, int num_sms, cudaStream_t stream) {
   const int npad = (k + 15) / 16 * 16;
   KM_TRY(ensure_xnorm(pl, X, rows, d, num_sms, stream));
@@ -115,12 +163,15 @@ inline int setup(Plan& pl, const float* X, size_t rows, int k, int d, int num_sm
   KM_TRY(make_map(&pl.tmX, X, rows, d, kBM, 4));
   KM_TRY(make_map(&pl.tmBhi, pl.bhi, npad, 64, npad, 2));
   KM_TRY(make_map(&pl.tmBlo, pl.blo, npad, 64, npad, 2));
-  if (d == 32)
-    KM_CUDA(cudaFuncSetAttribute(assign_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  if (d == 32) {
+    KM_CUDA(cudaFuncSetAttribute(assign_tc_kernel<32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem_bytes(d, npad)));
-  else
-    KM_CUDA(cudaFuncSetAttribute(assign_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  } else {
+    KM_CUDA(cudaFuncSetAttribute(assign_tc_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem_bytes(d, npad)));
+    KM_CUDA(cudaFuncSetAttribute(assign_tc_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem_bytes(d, npad)));
+  }
   pl.ready = true;
   return KM_OK;
 }
@@ -139,18 +190,25 @@ inline int prep(Plan& pl, const float* C, const float* cnorm, cudaStream_t strea
 constexpr float kTolRel = 1.9073486328125e-06f;
 
 inline int launch(Plan& pl, int* labels, IterState* st, bool count_changes, unsigned int* amb_rows, float tol_rel,
-                  int num_sms, int mask_hi, cudaStream_t stream, unsigned int* moved_bits, uint4* amb_near) {
+                  int num_sms, int mask_hi, cudaStream_t stream, unsigned int* moved_bits, uint4* amb_near,
+                  bool allow_split_build) {
   const size_t tiles = (pl.x_rows + kBM - 1) / kBM;
   if (tiles > 0x7fffffffULL / kBM) KM_FAIL(KM_EINVAL, "shard too large for the tensor-core kernel");
   const int grid = (int)std::min<size_t>(tiles, (size_t)num_sms);
+  const bool pre = ensure_xsplit(pl, pl.x_base, pl.x_rows, pl.d, pl.sx, num_sms, stream, allow_split_build);
   if (pl.d == 32)
-    assign_tc_kernel<32><<<grid, kThreads, smem_bytes(pl.d, pl.npad), stream>>>(
-        pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, pl.xnorm, labels, pl.x_rows, (int)tiles, pl.npad, st,
+    assign_tc_kernel<32, false><<<grid, kThreads, smem_bytes(pl.d, pl.npad), stream>>>(
+        pl.tmX, pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, pl.xnorm, labels, pl.x_rows, (int)tiles, pl.npad, st,
+        count_changes ? 1 : 0, amb_rows, tol_rel, pl.sx, pl.sx * pl.sb, mask_hi, count_changes ? moved_bits : nullptr,
+        amb_near);
+  else if (pre)
+    assign_tc_kernel<64, true><<<grid, kThreads, smem_bytes(pl.d, pl.npad), stream>>>(
+        pl.tmXh, pl.tmXl, pl.tmBhi, pl.tmBlo, pl.cn, pl.xnorm, labels, pl.x_rows, (int)tiles, pl.npad, st,
         count_changes ? 1 : 0, amb_rows, tol_rel, pl.sx, pl.sx * pl.sb, mask_hi, count_changes ? moved_bits : nullptr,
         amb_near);
   else
-    assign_tc_kernel<64><<<grid, kThreads, smem_bytes(pl.d, pl.npad), stream>>>(
-        pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, pl.xnorm, labels, pl.x_rows, (int)tiles, pl.npad, st,
+    assign_tc_kernel<64, false><<<grid, kThreads, smem_bytes(pl.d, pl.npad), stream>>>(
+        pl.tmX, pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, pl.xnorm, labels, pl.x_rows, (int)tiles, pl.npad, st,
         count_changes ? 1 : 0, amb_rows, tol_rel, pl.sx, pl.sx * pl.sb, mask_hi, count_changes ? moved_bits : nullptr,
         amb_near);
   KM_CUDA(cudaGetLastError());

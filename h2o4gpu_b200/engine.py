@@ -165,6 +165,7 @@ FIT_FORCE_SIMT = 2
 FIT_FORCE_SPLIT = 4
 FIT_CHECK_EVERY_ITER = 8
 FIT_FULL_SUMS = 16
+FIT_PRESPLIT = 32
 
 
 def centroid_sums(X, labels, k, gpu_id=0):

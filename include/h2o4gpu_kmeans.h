@@ -157,6 +157,8 @@ int kmeans_set_sample_weight(kmeans_handle_t h, const void* weights, size_t coun
 #define KM_FIT_FULL_SUMS 16       /* recompute the centroid sums from every row in every
                                   * iteration (default: exact incremental update once few
                                   * labels change; same bits either way)              */
+#define KM_FIT_PRESPLIT 32        /* d = 64 tensor-core path: build the fp16-split copy of the rows now, whatever
+                                    the iteration count (by default only fits of 16 iterations or more pay for it) */
 
 /* Lloyd iterations on the resident shards from k x cols host centroids.
  * Stops after max_iter, or earlier when threshold > 0 and the summed squared

@@ -843,3 +843,51 @@ def test_f64_matrix_unit_kernel_matches_simt_kernel_and_oracle(eng, tmp_path):
         assert np.array_equal(lab, simt["lab%d" % i]), (n, d, k)
         assert rel_err(C, simt["C%d" % i]) < 1e-13
         check_labels(X, init, lab0, lloyd.assign(X, init))
+
+
+def test_presplit_tensor_core_kernel_matches_converting_kernel(eng, tmp_path):
+    """d = 64, 16 iterations or more: the E-step that reads rows split once into fp16 halves against the kernel that
+    converts every tile (environment switch, child process): the same labels and centroids, bit for bit;
+    and new data at the same address and shape on one handle is not mistaken for the old."""
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import sys, numpy as np\n"
+        "from h2o4gpu_b200 import engine, synth\n"
+        "X, init, _ = synth.c2(n=300001)\n"
+        "h = engine.ResidentKMeans(); h.upload(X); h.fit(init, 16)\n"
+        "np.savez(sys.argv[1], C=h.centroids(), lab=h.labels()); h.close(); print('conv ok')\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = str(tmp_path / "conv.npz")
+    r = subprocess.run([sys.executable, "-c", code, path], cwd=root, env=dict(os.environ, H2O4GPU_KM_TC_PRESPLIT="0"),
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "conv ok" in r.stdout, r.stdout + r.stderr
+    conv = np.load(path)
+    from h2o4gpu_b200 import synth
+    X, init, _ = synth.c2(n=300001)
+    h = eng.ResidentKMeans()
+    h.upload(X)
+    h.fit(init, 16)
+    assert h.stats()["path"] == 3
+    assert np.array_equal(h.centroids(), conv["C"]) and np.array_equal(h.labels(), conv["lab"])
+    # a short fit takes the converting kernel unless told otherwise: both give the same bits
+    outs = []
+    for flags in (0, eng.FIT_PRESPLIT):
+        h2 = eng.ResidentKMeans()
+        h2.upload(X)
+        h2.fit(init, 2, flags=flags)
+        outs.append((h2.centroids(), h2.labels()))
+        h2.close()
+    assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
+    # other rows, same shape, same handle (the pool hands back the same address)
+    X2 = np.ascontiguousarray(X[::-1])
+    h.upload(X2)
+    h.fit(init, 16)
+    C2, lab2 = h.centroids(), h.labels()
+    h.close()
+    h = eng.ResidentKMeans()
+    h.upload(X2)
+    h.fit(init, 16)
+    assert np.array_equal(C2, h.centroids()) and np.array_equal(lab2, h.labels())
+    h.close()
