@@ -34,6 +34,6 @@ h = engine.ResidentKMeans(dtype=npdt)
 h.attach_device(0, X.data_ptr(), n, d)
 if mode == "weighted":
     h.set_sample_weight(rng.gamma(2.0, 1.5, n).astype(np.float32))
-h.fit(init, iters, flags=engine.FIT_NO_FINAL_ASSIGN)
+h.fit(init, iters, flags=engine.FIT_NO_FINAL_ASSIGN | engine.FIT_PRESPLIT)
 print(h.stats())
 h.close()
