@@ -213,6 +213,24 @@ __device__ __forceinline__ float fmin3(float a, float b, float c) {
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// Bound on the error of the difference of two scores of one row, in the scaled units of the
+// accumulator (scores carry the factor sx * sb).  Two parts:
+//  * relative: tol_rel * (|x|^2 + max|c|^2) covers the dropped xl.bl term, the 11-bit rounding of
+//    the low halves and the fp32 accumulation;
+//  * absolute: a low half whose magnitude falls below fp16's smallest normal number (2^-14) is a
+//    subnormal with a fixed quantum of 2^-24, so an element of x * sx (or of -2c * sb) is only
+//    known to 2^-25 whatever its size; the product error is then at most
+//    2^-25 * (|y|_1 + |b|_1) per score with y = x * sx, b = -2c * sb, and
+//    |y|_1 <= sqrt(d) * sx * |x|, |b|_1 <= sqrt(d) * 2 sb * max|c|.  tol_floor = 2^-23 sqrt(d)
+//    (two scores, and a factor two of margin).  This term matters only when the data spans many
+//    orders of magnitude (an element 1e5 times the typical one); it then widens the band of rows
+//    handed to the exact pass instead of letting a wrong label through.
+__device__ __forceinline__ float split_tolerance(float tol_rel, float tol_floor, float xn, float cn_max, float sx,
+                                                 float sxsb) {
+  const float sb2 = 2.0f * sxsb / sx;
+  return tol_rel * (xn + cn_max) * sxsb + tol_floor * (sx * sqrtf(xn) + sb2 * sqrtf(cn_max));
+}
+
 // |x|^2 of every row (float), once per upload: the error bound of a row's scores.  The
 // tensor-core paths have d % 4 == 0 and 16-byte aligned rows: a row is shared by lpr lanes
 // loading a float4 each, four sets of rows per loop trip.
@@ -283,9 +301,6 @@ prep_kernel(const float* __restrict__ C, const float* __restrict__ cnorm, int k,
   }
 }
 
-// dbg: bit 1 (2) = do not issue the MMAs, bit 2 (4) = skip the epilogue arithmetic,
-// bit 3 (8) = skip the TMEM stores (timing experiments only; labels stay valid;
-// 0 or 1 in production).
 // The rows of X split once into the two fp16 operands of the product (the arithmetic of the
 // converter warps below: y = x * sx, upper half = fp16(y), lower half = fp16(y - upper)), so that
 // the E-step can read them with TMA straight into the layout the MMA consumes and needs no
@@ -318,8 +333,8 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                  const __grid_constant__ CUtensorMap tmBhi,
                  const __grid_constant__ CUtensorMap tmBlo, const float* __restrict__ cn_pad,
                  const float* __restrict__ xnorm, int* __restrict__ labels, size_t n, int n_tiles, int npad,
-                 IterState* st, int count_changes, unsigned int* __restrict__ amb_rows, float tol_rel, float sx,
-                 float sxsb, int dbg, unsigned int* __restrict__ moved_bits, uint4* __restrict__ amb_near) {
+                 IterState* st, int count_changes, unsigned int* __restrict__ amb_rows, float tol_rel, float tol_floor,
+                 float sx, float sxsb, unsigned int* __restrict__ moved_bits, uint4* __restrict__ amb_near) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_u32 = smem_u32(smem_raw);
   const uint32_t base = (raw_u32 + 1023u) & ~1023u;
@@ -458,7 +473,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             if (PRE) {
               const uint32_t a_smem = base + off_stage + (uint32_t)s * stage_bytes + (term == 1 ? 16384u : 0u) + kk * 32u;
               tc_mma_ss(acc, smem_desc_sw128(a_smem), bd, idesc, 1u);
-            } else if (!(dbg & 2)) {
+            } else {
               tc_mma_ts(acc, a_col, bd, idesc, 1u);
             }
           }
@@ -522,12 +537,8 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           lo[c * 2 + 0] = *reinterpret_cast<const uint32_t*>(&l01);
           lo[c * 2 + 1] = *reinterpret_cast<const uint32_t*>(&l23);
         }
-        if (!(dbg & 8)) {
-          tmem_st16(a_hi + p * 16u, hi);
-          tmem_st16(a_hi + 32u + p * 16u, lo);
-        } else if (hi[3] == 0x12345u && lo[7] == 0x54321u) {
-          labels[0] = 0;  // keeps the loads alive
-        }
+        tmem_st16(a_hi + p * 16u, hi);
+        tmem_st16(a_hi + 32u + p * 16u, lo);
       }
       tmem_wait_st();
       tc_fence_before();
@@ -583,22 +594,20 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       const uint32_t acc = tmem_base + lane_addr + (uint32_t)a * 128u;
       // pass 1: the smallest score of the row, two three-input minima per four columns
       float m0 = __int_as_float(0x7f800000), m1 = m0;
-      if (!(dbg & 4)) {
 #pragma unroll
-        for (int ch = 0; ch < kMaxNPad / 32; ++ch) {
-          const int c0 = ch * 32;
-          if (c0 < npad) {
-            uint32_t v[32];
-            const bool two = (c0 + 16 < npad);
-            tmem_ld16(acc + c0, v, 0);
-            if (two) tmem_ld16(acc + c0 + 16, v, 16);
-            tmem_wait_ld(v);
+      for (int ch = 0; ch < kMaxNPad / 32; ++ch) {
+        const int c0 = ch * 32;
+        if (c0 < npad) {
+          uint32_t v[32];
+          const bool two = (c0 + 16 < npad);
+          tmem_ld16(acc + c0, v, 0);
+          if (two) tmem_ld16(acc + c0 + 16, v, 16);
+          tmem_wait_ld(v);
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              if (j < 16 || two) {
-                m0 = fmin3(m0, __uint_as_float(v[j]), __uint_as_float(v[j + 1]));
-                m1 = fmin3(m1, __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-              }
+          for (int j = 0; j < 32; j += 4) {
+            if (j < 16 || two) {
+              m0 = fmin3(m0, __uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+              m1 = fmin3(m1, __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
             }
           }
         }
@@ -606,7 +615,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       const float best = fminf(m0, m1);
       // rows with a second score within the error bound of the split product (scores carry the
       // factor sx*sb) go to the exact re-evaluation pass; without that pass only exact ties count
-      const float tol = (amb_rows != nullptr) ? tol_rel * (xn + cn_max) * sxsb : 0.f;
+      const float tol = (amb_rows != nullptr) ? split_tolerance(tol_rel, tol_floor, xn, cn_max, sx, sxsb) : 0.f;
       const float thr = best + tol;
       // pass 2: one bit per column whose score is within the bound of the best
       uint32_t near[kMaxNPad / 32];
@@ -614,7 +623,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       for (int ch = 0; ch < kMaxNPad / 32; ++ch) {
         const int c0 = ch * 32;
         uint32_t mk = 0;
-        if (c0 < npad && !(dbg & 4)) {
+        if (c0 < npad) {
           uint32_t v[32];
           const bool two = (c0 + 16 < npad);
           tmem_ld16(acc + c0, v, 0);
@@ -636,7 +645,6 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         n_near += __popc(near[ch]);
         if (near[ch]) bidx = ch * 32 + __ffs(near[ch]) - 1;   // lowest column wins
       }
-      if (dbg & 4) { n_near = 1; bidx = 0; }  // timing experiments: nothing is ambiguous
       bool moved = false;
       if (row < n) {
         if (amb_rows != nullptr && n_near != 1) {

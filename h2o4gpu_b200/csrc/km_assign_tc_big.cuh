@@ -87,8 +87,8 @@ __global__ void __launch_bounds__(kBigThreads, 1)
 assign_tc_big_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmBhi,
                      const __grid_constant__ CUtensorMap tmBlo, const float* __restrict__ cn_pad,
                      const float* __restrict__ xnorm, int* __restrict__ labels, size_t n, int n_tiles, int kpad,
-                     IterState* st, int count_changes, unsigned int* __restrict__ amb_rows, float tol_rel, float sx,
-                     float sxsb) {
+                     IterState* st, int count_changes, unsigned int* __restrict__ amb_rows, float tol_rel,
+                     float tol_floor, float sx, float sxsb) {
   using Cf = BigCfg<D>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_u32 = smem_u32(smem_raw);
@@ -394,7 +394,7 @@ assign_tc_big_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         else rsecond = fminf(rsecond, ob);
         rsecond = fminf(rsecond, os);
         if (row < n) {
-          const float tol = tol_rel * (xn + cn_max) * sxsb;
+          const float tol = split_tolerance(tol_rel, tol_floor, xn, cn_max, sx, sxsb);
           if (amb_rows != nullptr && !(rsecond - rbest > tol)) {
             const unsigned int pos = atomicAdd(&st->amb_count, 1u);
             amb_rows[pos] = (unsigned int)row;

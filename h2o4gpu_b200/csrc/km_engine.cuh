@@ -127,6 +127,11 @@ struct Engine : EngineBase {
   std::vector<Shard<T>> shards;
   int world_rank0 = 0, world_size = 1;
   bool comm_cached = false;
+  // Communicators of a one-process device set are shared by every engine made for that set; NCCL
+  // communicators must not be used from two host threads at once, so an engine holds the set's
+  // lock from init() to destroy(): multi-GPU calls on the same devices from several threads
+  // run one after the other.
+  std::unique_lock<std::mutex> comm_lock;
   size_t n_total = 0;
   int d = 0, k = 0;
   int cur = 0;  // index of the current centroid buffer
@@ -174,9 +179,7 @@ struct Engine : EngineBase {
   bool tc_ok(int flags) const;
   int tc_refresh(Shard<T>& s);  // split the current centroids for the tensor-core kernel
   int launch_assign(Shard<T>& s, bool use_tc, bool count_changes);
-  int tc_mask_hi = 1;
   bool tc_split_build = false;   // the running fit has enough iterations to pay for the split copy of X
-  float tc_tol_rel = tc::kTolRel;
   float tc_sx = 1.f, tc_sb = 1.f;   // operand scales of the tensor-core kernel
   double cbound = 0;                // bound on |centroid coordinate|: max(|x|, |initial centroids|)
 
@@ -244,17 +247,24 @@ int Engine<T>::init(int n_local, const int* devs, int rank0, int world, const vo
       // Communicators of a one-process device set are kept for the life of the process:
       // creating them costs far more than a whole fit, and the reference's entry points
       // are called once per fit / predict.
+      struct CommSet { std::vector<ncclComm_t> comms; std::mutex in_use; };
       static std::mutex cache_mutex;
-      static std::map<std::vector<int>, std::vector<ncclComm_t>> cache;
-      std::lock_guard<std::mutex> lock(cache_mutex);
+      static std::map<std::vector<int>, std::unique_ptr<CommSet>> cache;   // entries are never removed
       std::vector<int> dl(devs, devs + n_local);
-      auto it = cache.find(dl);
-      if (it == cache.end()) {
+      CommSet* set = nullptr;
+      {
+        std::lock_guard<std::mutex> lock(cache_mutex);
+        auto it = cache.find(dl);
+        if (it == cache.end()) it = cache.emplace(dl, std::unique_ptr<CommSet>(new CommSet())).first;
+        set = it->second.get();
+      }
+      comm_lock = std::unique_lock<std::mutex>(set->in_use);
+      if (set->comms.empty()) {
         std::vector<ncclComm_t> comms(n_local);
         KM_NCCL(api, api->CommInitAll(comms.data(), n_local, dl.data()));
-        it = cache.emplace(dl, comms).first;
+        set->comms = comms;
       }
-      for (int i = 0; i < n_local; ++i) shards[i].comm = it->second[i];
+      for (int i = 0; i < n_local; ++i) shards[i].comm = set->comms[i];
       comm_cached = true;
     } else {
       if (!nccl_id) KM_FAIL(KM_EINVAL, "kmeans_create: nccl_id required when world_size > n_local");
@@ -296,6 +306,7 @@ void Engine<T>::destroy() {
     s.dev = -1;
   }
   shards.clear();
+  if (comm_lock.owns_lock()) comm_lock.unlock();
 }
 
 template <typename T>
@@ -502,7 +513,9 @@ int Engine<T>::upload_host_typed(const void* Xv, int src_dtype, size_t rows, siz
   const unsigned char* X = static_cast<const unsigned char*>(Xv);
   upload_t0 = now_s();
   const size_t g = shards.size();
-  const size_t per = (rows + g - 1) / g;
+  // balanced contiguous split: shard i holds rows / g rows, the first rows % g shards one more, so no
+  // shard is empty whenever rows >= g (a ceil split leaves the last ones empty, e.g. 9 rows on 8 devices)
+  const size_t per = rows / g, extra = rows % g;
   static const bool stage_enabled = [] {
     const char* e = std::getenv("H2O4GPU_KM_STAGED_UPLOAD");
     return !(e && e[0] == '0');
@@ -528,7 +541,7 @@ int Engine<T>::upload_host_typed(const void* Xv, int src_dtype, size_t rows, siz
   size_t off = 0;
   for (size_t i = 0; i < g; ++i) {
     Shard<T>& s = shards[i];
-    size_t r = (off < rows) ? std::min(per, rows - off) : 0;
+    const size_t r = per + (i < extra ? 1 : 0);
     if (r == 0) { upload_wait(); KM_FAIL(KM_EINVAL, "kmeans_upload_host: fewer rows than devices"); }
     DevGuard gd(s.dev);
     km_free(s.X_owned);
@@ -1095,7 +1108,7 @@ int Engine<T>::launch_assign(Shard<T>& s, bool use_tc, bool count_changes) {
   if constexpr (std::is_same<T, float>::value) {
     if (use_tc && !tc::shape_ok(k, d)) {
       launches += 2;
-      KM_TRY(tcb::big_launch(s.tcbp, s.tcp.xnorm, s.labels, s.st, count_changes, s.amb_rows, tc_tol_rel, s.num_sms,
+      KM_TRY(tcb::big_launch(s.tcbp, s.tcp.xnorm, s.labels, s.st, count_changes, s.amb_rows, tc::kTolRel, s.num_sms,
                              s.stream));
       tcb::refine_big_kernel<float><<<s.num_sms * 2, 256, 0, s.stream>>>(s.X, d, s.C[cur], k, s.amb_rows, s.st,
                                                                         s.labels, count_changes ? 1 : 0);
@@ -1105,7 +1118,7 @@ int Engine<T>::launch_assign(Shard<T>& s, bool use_tc, bool count_changes) {
     if (use_tc) {
       launches += 2;
       unsigned int* bits = (count_changes && s.labels_prev_cap >= s.rows) ? s.moved_bits : nullptr;
-      KM_TRY(tc::launch(s.tcp, s.labels, s.st, count_changes, s.amb_rows, tc_tol_rel, s.num_sms, tc_mask_hi,
+      KM_TRY(tc::launch(s.tcp, s.labels, s.st, count_changes, s.amb_rows, tc::kTolRel, s.num_sms,
                         s.stream, bits, s.amb_near, tc_split_build));
       s.moved_bits_valid = bits != nullptr;
       refine_near_kernel<float><<<s.num_sms * 4, kRefineThreads, 0, s.stream>>>(
@@ -1174,6 +1187,7 @@ int Engine<T>::allreduce_from(bool from_pure) {
           KM_CUDA(cudaGetLastError());
           ++launches;
         }
+        stats.allreduce_path = 1;
         return KM_OK;
       }
     }
@@ -1184,6 +1198,7 @@ int Engine<T>::allreduce_from(bool from_pure) {
     KM_NCCL(api, api->AllReduce(from_pure ? s.pacc : s.gacc, s.gacc, s.gacc_count(k, d), ncclInt64, ncclSum, s.comm,
                                 s.stream));
   KM_NCCL(api, api->GroupEnd());
+  stats.allreduce_path = 2;
   return KM_OK;
 }
 

@@ -157,7 +157,6 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
   // sixteen iterations save
   tc_split_build = max_iter >= 16 || (flags & KM_FIT_PRESPLIT);
   struct SplitBuildGuard { bool& f; ~SplitBuildGuard() { f = false; } } split_build_guard{tc_split_build};
-  if (const char* e = std::getenv("H2O4GPU_KM_TC_TOL")) tc_tol_rel = (float)std::atof(e);
   // incremental M-step (km_accumulate_delta.cuh): on unless the caller or the environment asks
   // for a full recomputation every iteration; a shard switches to it, on the device, in the
   // iterations where at most 1/16 of its labels moved
@@ -412,6 +411,11 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
       cudaEventElapsedTime(&ms, ev[0], ev[ev.size() - 2]);
       stats.ms_loop = ms;
     }
+    if (!(flags & KM_FIT_NO_FINAL_ASSIGN)) {
+      float mf = 0;
+      cudaEventElapsedTime(&mf, ev[ev.size() - 2], ev[ev.size() - 1]);
+      stats.ms_final_assign = mf;
+    }
   }
   free_events();
   stats.gpu_launches = launches;
@@ -469,16 +473,27 @@ int Engine<T>::transform_shard(int local, T* out_host, size_t ld) {
   batch = std::min(batch, (s.rows + 127) / 128 * 128);
   T* buf = nullptr;
   KM_CUDA(km_malloc(&buf, batch * (size_t)k * sizeof(T)));
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  cudaEventCreate(&e0);
+  cudaEventCreate(&e1);
+  float ms_kernels = 0;
   int rc = KM_OK;
   for (size_t r = 0; r < s.rows && rc == KM_OK; r += batch) {
     size_t nr = std::min(batch, s.rows - r);
+    cudaEventRecord(e0, s.stream);
     rc = launch_tiles(s, s.X + r * (size_t)d, nr, nullptr, MODE_TRANSFORM, buf, batch, false);
     if (rc != KM_OK) break;
+    cudaEventRecord(e1, s.stream);
     cudaError_t ce = cudaMemcpy2DAsync(out_host + r, ld * sizeof(T), buf, batch * sizeof(T), nr * sizeof(T), k,
                                        cudaMemcpyDeviceToHost, s.stream);
     if (ce == cudaSuccess) ce = cudaStreamSynchronize(s.stream);
     if (ce != cudaSuccess) { set_error(std::string("transform copy: ") + cudaGetErrorString(ce)); rc = KM_ECUDA; }
+    float ms = 0;
+    if (cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess) ms_kernels += ms;
   }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  if (local == 0) stats.ms_transform = ms_kernels;
   km_free(buf);
   return rc;
 }

@@ -183,14 +183,21 @@ inline int prep(Plan& pl, const float* C, const float* cnorm, cudaStream_t strea
   return KM_OK;
 }
 
-// tol_rel: a row goes to the exact pass when second - best <= tol_rel * (|x|^2 + max|c|^2).
-// Error of the split product: the low halves of x and of -2c are rounded to 11 bits
-// (2^-23 relative each), xl.bl is dropped (2^-22 |x||b|), fp32 accumulation of 3 d / 16
-// partial sums: below 2^-20.4 (|x|^2 + |c|^2) per score, twice that for a difference.
+// A row goes to the exact pass when second - best <= split_tolerance(...) (km_assign_tc.cuh):
+// kTolRel * (|x|^2 + max|c|^2) plus an absolute floor.  Error of the split product with
+// y = x sx = xh + xl + ex, b = -2c sb = bh + bl + eb: the kernel forms xh.bh + xl.bh + xh.bl, so a
+// score misses xl.bl + ex.b + y.eb per element.  While the low halves are normal fp16 numbers
+// |ex| <= 2^-22 |y|, |eb| <= 2^-22 |b|, |xl.bl| <= 2^-22 |y||b|: 3 * 2^-22 sum|y||b|
+// <= 3 * 2^-22 (|x|^2 + |c|^2) sx sb per score; with the fp32 accumulation of the 3 d / 16 partial
+// sums that is below 2^-20.4 (|x|^2 + |c|^2), twice that for a difference: kTolRel = 2^-19.
+// A low half below 2^-14 is an fp16 subnormal (quantum 2^-24): |ex|, |eb| <= 2^-25 absolute,
+// which adds 2^-25 (|y|_1 + |b|_1) per score; tol_floor_of(d) = 2^-23 sqrt(d) bounds twice that
+// for a difference through |v|_1 <= sqrt(d) |v|_2.
 constexpr float kTolRel = 1.9073486328125e-06f;
+inline float tol_floor_of(int d) { return 1.1920928955078125e-07f * std::sqrt((float)d); }
 
 inline int launch(Plan& pl, int* labels, IterState* st, bool count_changes, unsigned int* amb_rows, float tol_rel,
-                  int num_sms, int mask_hi, cudaStream_t stream, unsigned int* moved_bits, uint4* amb_near,
+                  int num_sms, cudaStream_t stream, unsigned int* moved_bits, uint4* amb_near,
                   bool allow_split_build) {
   const size_t tiles = (pl.x_rows + kBM - 1) / kBM;
   if (tiles > 0x7fffffffULL / kBM) KM_FAIL(KM_EINVAL, "shard too large for the tensor-core kernel");
@@ -199,17 +206,17 @@ inline int launch(Plan& pl, int* labels, IterState* st, bool count_changes, unsi
   if (pl.d == 32)
     assign_tc_kernel<32, false><<<grid, kThreads, smem_bytes(pl.d, pl.npad), stream>>>(
         pl.tmX, pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, pl.xnorm, labels, pl.x_rows, (int)tiles, pl.npad, st,
-        count_changes ? 1 : 0, amb_rows, tol_rel, pl.sx, pl.sx * pl.sb, mask_hi, count_changes ? moved_bits : nullptr,
+        count_changes ? 1 : 0, amb_rows, tol_rel, tol_floor_of(pl.d), pl.sx, pl.sx * pl.sb, count_changes ? moved_bits : nullptr,
         amb_near);
   else if (pre)
     assign_tc_kernel<64, true><<<grid, kThreads, smem_bytes(pl.d, pl.npad), stream>>>(
         pl.tmXh, pl.tmXl, pl.tmBhi, pl.tmBlo, pl.cn, pl.xnorm, labels, pl.x_rows, (int)tiles, pl.npad, st,
-        count_changes ? 1 : 0, amb_rows, tol_rel, pl.sx, pl.sx * pl.sb, mask_hi, count_changes ? moved_bits : nullptr,
+        count_changes ? 1 : 0, amb_rows, tol_rel, tol_floor_of(pl.d), pl.sx, pl.sx * pl.sb, count_changes ? moved_bits : nullptr,
         amb_near);
   else
     assign_tc_kernel<64, false><<<grid, kThreads, smem_bytes(pl.d, pl.npad), stream>>>(
         pl.tmX, pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, pl.xnorm, labels, pl.x_rows, (int)tiles, pl.npad, st,
-        count_changes ? 1 : 0, amb_rows, tol_rel, pl.sx, pl.sx * pl.sb, mask_hi, count_changes ? moved_bits : nullptr,
+        count_changes ? 1 : 0, amb_rows, tol_rel, tol_floor_of(pl.d), pl.sx, pl.sx * pl.sb, count_changes ? moved_bits : nullptr,
         amb_near);
   KM_CUDA(cudaGetLastError());
   return KM_OK;
@@ -288,7 +295,7 @@ inline void big_launch_d(BigPlan& pl, const float* xnorm, int* labels, IterState
                          unsigned int* amb_rows, float tol_rel, int grid, int tiles, cudaStream_t stream) {
   assign_tc_big_kernel<D><<<grid, kBigThreads, big_smem_bytes<D>(pl.kpad), stream>>>(
       pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, xnorm, labels, pl.x_rows, tiles, pl.kpad, st, count_changes, amb_rows,
-      tol_rel, pl.sx, pl.sx * pl.sb);
+      tol_rel, tc::tol_floor_of(pl.d), pl.sx, pl.sx * pl.sb);
 }
 
 inline int big_launch(BigPlan& pl, const float* xnorm, int* labels, IterState* st, bool count_changes,

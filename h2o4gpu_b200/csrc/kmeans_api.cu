@@ -287,12 +287,29 @@ int synth_impl(int gpu_id, T* dX, size_t rows, size_t cols, size_t row0, int kin
 template <typename T>
 static int assign_sync(km::Engine<T>* e) {
   KM_TRY(e->check_data());
-  KM_TRY(e->assign_all(0));
+  if (e->shards.empty()) KM_FAIL(KM_ESTATE, "no data attached to the handle");
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  {
+    km::DevGuard g(e->shards[0].dev);
+    KM_CUDA(cudaEventCreate(&e0));
+    KM_CUDA(cudaEventCreate(&e1));
+    cudaEventRecord(e0, e->shards[0].stream);
+  }
+  int rc = e->assign_all(0);
+  {
+    km::DevGuard g(e->shards[0].dev);
+    cudaEventRecord(e1, e->shards[0].stream);
+  }
   for (auto& s : e->shards) {
     km::DevGuard g(s.dev);
-    KM_CUDA(cudaStreamSynchronize(s.stream));
+    cudaError_t ce = cudaStreamSynchronize(s.stream);
+    if (ce != cudaSuccess && rc == KM_OK) { set_error(std::string("assign sync: ") + cudaGetErrorString(ce)); rc = KM_ECUDA; }
   }
-  return KM_OK;
+  float ms = 0;
+  if (rc == KM_OK && cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess) e->stats.ms_assign = ms;
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  return rc;
 }
 
 template <typename T>

@@ -13,12 +13,13 @@ def env_world():
 
 
 def shard_rows(n_total, rank, world):
-    """Contiguous ceil split that covers every row: (first row, row count) of `rank`.
-    The reference uses floor(n / g) rows per GPU and drops the remainder
-    (src/gpu/kmeans/kmeans_h2o4gpu.cu:649, 679)."""
-    per = -(-n_total // world)
-    start = min(n_total, rank * per)
-    return start, max(0, min(per, n_total - start))
+    """Balanced contiguous split that covers every row: (first row, row count) of `rank`; the first
+    n_total % world ranks hold one row more, so no rank is empty while n_total >= world (the split the
+    library itself applies to a host matrix).  The reference uses floor(n / g) rows per GPU and drops
+    the remainder (src/gpu/kmeans/kmeans_h2o4gpu.cu:649, 679)."""
+    per, extra = divmod(n_total, world)
+    start = rank * per + min(rank, extra)
+    return start, per + (1 if rank < extra else 0)
 
 
 def broadcast_bytes(payload, src=0, device=None):

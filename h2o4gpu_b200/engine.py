@@ -82,8 +82,8 @@ class ResidentKMeans(object):
         rows, cols = X.shape
         _lk.check(self._lib.kmeans_upload_host_typed(self._h, X.ctypes.data_as(ctypes.c_void_p),
                                                      DTYPE_CODES[X.dtype], rows, cols, order.encode()))
-        per = -(-rows // self.n_local)
-        self._rows = [min(per, rows - i * per) for i in range(self.n_local)]
+        per, extra = divmod(rows, self.n_local)   # the library's balanced contiguous split
+        self._rows = [per + (1 if i < extra else 0) for i in range(self.n_local)]
         self.cols = cols
 
     def set_sample_weight(self, w):

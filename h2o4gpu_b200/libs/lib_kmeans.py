@@ -35,10 +35,14 @@ class Stats(ctypes.Structure):
                 ("last_shift_sq", _c.c_double), ("inertia", _c.c_double),
                 ("seconds_upload", _c.c_double), ("seconds_fit", _c.c_double),
                 ("ms_assign", _c.c_float), ("ms_update", _c.c_float), ("ms_loop", _c.c_float),
-                ("reserved2", _c.c_float), ("refined_rows", _c.c_longlong)]
+                ("ms_final_assign", _c.c_float), ("refined_rows", _c.c_longlong),
+                ("ms_transform", _c.c_float), ("allreduce_path", _c.c_int)]
 
     def as_dict(self):
-        return {n: getattr(self, n) for n, _ in self._fields_ if not n.startswith("reserved")}
+        out = {n: getattr(self, n) for n, _ in self._fields_ if not n.startswith("reserved")}
+        out["allreduce_path_name"] = {0: "none (one rank)", 1: "one-shot push over peer memory",
+                                      2: "ncclAllReduce(int64)"}.get(self.allreduce_path)
+        return out
 
 
 # name -> (restype, argtypes); every symbol include/h2o4gpu_kmeans.h declares extern "C"

@@ -11,7 +11,8 @@ Differences, all deliberate:
 * ``inertia_`` and ``n_iter_`` are set by the GPU path (the reference leaves
   ``inertia_`` None, kmeans.py:187), ``n_init > 1`` keeps the run with the
   lowest inertia (the reference ignores ``n_init`` on the GPU, kmeans.py:722-725)
-  and ``score`` is computed on the GPU; ``sample_weight`` is not supported;
+  and ``score`` is computed on the GPU; ``fit(X, sample_weight=w)`` stays on the GPU too
+  (the reference hands it to scikit-learn, kmeans.py:800-804);
 * when the native library or a GPU is missing and the caller did not ask for
   CPU (``n_gpus=0`` / ``backend='sklearn'``), construction raises instead of
   silently falling back (kmeans.py:768-770 falls back);

@@ -118,7 +118,8 @@ int kmeans_nccl_unique_id(void* out128);
 int kmeans_attach_device(kmeans_handle_t h, int local, const void* dX, size_t rows, size_t cols,
                          size_t n_total);
 /* Upload a host matrix: rows are split contiguously over the local devices
- * (ceil split, every row covered).  order 'r' = row-major, 'c' = column-major
+ * (balanced split: rows / n rows each, the first rows % n devices one more; every row
+ * covered, no device empty while rows >= n).  order 'r' = row-major, 'c' = column-major
  * (the two layouts of copy_data, src/gpu/kmeans/kmeans_h2o4gpu.h:24-42). */
 int kmeans_upload_host(kmeans_handle_t h, const void* X, size_t rows, size_t cols, char order);
 /* The same for a host matrix of another element type.  The reference's wrapper converts every
@@ -165,7 +166,8 @@ int kmeans_set_sample_weight(kmeans_handle_t h, const void* weights, size_t coun
  * shift drops below it, or (with KM_FIT_CHECK_EVERY_ITER) when no label changed. */
 int kmeans_fit_resident(kmeans_handle_t h, int k, int max_iter, double threshold,
                         const void* init_centroids, int flags);
-/* One E-step on the resident shards with the handle's current centroids. */
+/* One E-step on the resident shards with the handle's current centroids (its CUDA-event time on
+ * device 0 is left in kmeans_stats.ms_assign). */
 int kmeans_assign_resident(kmeans_handle_t h);
 int kmeans_set_centroids(kmeans_handle_t h, int k, const void* centroids);
 /* Initial centroids from the attached data, computed on the device(s) of a one-process
@@ -200,10 +202,13 @@ typedef struct kmeans_stats {
   float ms_assign;         /* CUDA-event time of the distance+argmin kernel, summed  */
   float ms_update;         /* ... of the sum / count / finalize kernels              */
   float ms_loop;           /* ... of the whole iteration loop on device 0            */
-  float reserved2;
+  float ms_final_assign;   /* ... of the closing E-step of the last fit (0 if skipped) */
   long long refined_rows;  /* rows (device 0, summed over iterations) whose two best */
                            /* scores were within the fast kernel's error bound and   */
                            /* were re-evaluated exactly                              */
+  float ms_transform;      /* CUDA-event time of the kernels of the last kmeans_transform_resident */
+  int allreduce_path;      /* per-iteration exchange of the last fit: 0 none (one rank), 1 one-shot push
+                            * over peer memory, 2 ncclAllReduce                                   */
 } kmeans_stats;
 int kmeans_get_stats(kmeans_handle_t h, kmeans_stats* out);
 /* Sum of squared distances of every row to its assigned centre (direct

@@ -19,7 +19,9 @@ def load_golden(name):
     return np.load(os.path.join(GOLDEN, name + ".npz"))
 
 
-GOLDEN_CASES = ["blobs_n600_d5_k4", "blobs_n2000_d32_k8", "empty_n500_d3_k6", "blobs_n1500_d7_k17"]
+GOLDEN_CASES = ["blobs_n600_d5_k4", "blobs_n2000_d32_k8", "empty_n500_d3_k6", "blobs_n1500_d7_k17",
+                # shapes the tcgen05 kernels serve (resident and streamed centroid table)
+                "blobs_n3000_d64_k100", "blobs_n3600_d128_k300"]
 
 
 @pytest.fixture(scope="session")

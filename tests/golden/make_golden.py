@@ -2,6 +2,7 @@
 the library the reference's CPU k-means path (h2o4gpu.KMeans(n_gpus=0)) runs.
 
 Run from the repository root:  python tests/golden/make_golden.py
+(--tensor-core-cases writes only the two fixtures shaped for the tensor-core kernels).
 Recorded with the scikit-learn / numpy versions stored in each file.
 """
 import os
@@ -38,7 +39,22 @@ def record(name, X, init, T):
     print(name, X.shape, init.shape, "n_iter", out["n_iter_f32"], out["n_iter_f64"])
 
 
+def tensor_core_cases():
+    """Shapes that the tcgen05 kernels serve: d = 64, k = 100 (centroid table resident in shared memory)
+    and d = 128, k = 300 (table streamed).  Values lie on a grid of 1/32 so that the files compress;
+    T is large enough for scikit-learn to converge in float32 and float64 alike."""
+    rng = np.random.default_rng(20250311)
+    for name, n, d, k, spread, T in (("blobs_n3000_d64_k100", 3000, 64, 100, 10.0, 30),
+                                     ("blobs_n3600_d128_k300", 3600, 128, 300, 12.0, 30)):
+        X = np.round(blobs(rng, n, d, k, spread=spread) * 32.0) / 32.0
+        X = X.astype(np.float32)
+        record(name, X, X[np.sort(rng.choice(n, k, replace=False))].copy(), T)
+
+
 def main():
+    if "--tensor-core-cases" in sys.argv:
+        tensor_core_cases()
+        return
     rng = np.random.default_rng(20240607)
     X = blobs(rng, 600, 5, 4)
     record("blobs_n600_d5_k4", X, X[:4].copy(), 10)
@@ -51,6 +67,7 @@ def main():
     # odd sizes: d not a multiple of 4, k = 17 (> the fused-kernel bound)
     X = blobs(rng, 1500, 7, 17, spread=8.0)
     record("blobs_n1500_d7_k17", X, X[rng.choice(1500, 17, replace=False)].copy(), 12)
+    tensor_core_cases()
 
 
 if __name__ == "__main__":

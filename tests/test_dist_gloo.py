@@ -60,12 +60,15 @@ def test_two_rank_sharded_step_equals_whole():
 
 def test_shard_rows_cover_everything():
     from h2o4gpu_b200.dist import shard_rows
-    for n in (1, 7, 8, 1001, 10_000_000):
-        for w in (1, 2, 3, 8):
+    for n in (1, 5, 7, 8, 9, 41, 1001, 10_000_000):
+        for w in (1, 2, 3, 4, 8):
             parts = [shard_rows(n, r, w) for r in range(w)]
             assert sum(p[1] for p in parts) == n
             pos = 0
             for s, c in parts:
-                if c:
-                    assert s == pos
+                assert s == pos
                 pos += c
+            counts = [p[1] for p in parts]
+            assert max(counts) - min(counts) <= 1          # balanced: 9 rows on 8 ranks leave nobody empty
+            if n >= w:
+                assert min(counts) >= 1

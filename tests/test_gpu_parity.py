@@ -41,6 +41,24 @@ def eng(built_lib):
     return e
 
 
+def check_step(X, C_prev, got_C, got_labels, want_C, want_labels, want_moved, relocations, tol=F32_TOL):
+    """Labels and centroids of one GPU step against the oracle's step from the same centres.
+
+    Labels may differ only inside the near-tie band.  The centroids are always checked: when the
+    labels agree, against the oracle's; when near-tie rows differ, against the oracle's M-step
+    (sums, empty-cluster rule, averaging) recomputed from the GPU's labels.  Returns the number
+    of near-tie label differences."""
+    bad = check_labels(X, C_prev, got_labels, want_labels)
+    if bad:
+        k = C_prev.shape[0]
+        sums, counts = lloyd.sums_counts(X, got_labels, k)
+        want_moved = lloyd.relocate_empty(X, got_labels, C_prev, sums, counts, order="descending")
+        want_C = lloyd.average(sums, counts)
+    assert rel_err(got_C, want_C) < tol
+    assert relocations == len(want_moved)
+    return bad
+
+
 def one_step(eng, X, C, flags=0, dtype=None):
     """One Lloyd iteration on the GPU from centres C: (C_new, labels of the E-step)."""
     dtype = X.dtype if dtype is None else dtype
@@ -252,11 +270,7 @@ def test_teacher_forced_f32(eng, cfg, kw, steps):
         Cn, labn, _, moved = lloyd.step(X, C32.astype(np.float64), order="descending")
         h.fit(C32, 1, flags=eng.FIT_NO_FINAL_ASSIGN)
         got, lab = h.centroids(), h.labels()
-        bad = check_labels(X, C32.astype(np.float64), lab, labn)
-        ties += bad
-        if bad == 0:
-            assert rel_err(got, Cn) < F32_TOL
-            assert h.stats()["relocations"] == len(moved)
+        ties += check_step(X, C32.astype(np.float64), got, lab, Cn, labn, moved, h.stats()["relocations"])
         C = Cn
     h.close()
     print("near-tie label differences over the run:", ties)
@@ -334,10 +348,7 @@ def test_ragged_shapes(eng, n, d, k):
     init = X[rng.choice(n, k, replace=False)].copy()
     Cn, labn, _, moved = lloyd.step(X, init.astype(np.float64), order="descending")
     C, lab, st = one_step(eng, X, init)
-    bad = check_labels(X, init.astype(np.float64), lab, labn)
-    if bad == 0:
-        assert rel_err(C, Cn) < F32_TOL
-        assert st["relocations"] == len(moved)
+    check_step(X, init.astype(np.float64), C, lab, Cn, labn, moved, st["relocations"])
 
 
 def test_k_larger_than_rows_is_clamped(built_lib):
@@ -481,6 +492,31 @@ def test_multi_gpu_equals_single_gpu(eng):
     h2.fit(init, 5)
     assert h1.stats()["relocations"] == h2.stats()["relocations"] > 0
     assert np.array_equal(h1.centroids(), h2.centroids())      # integer sums: bit-identical
+    assert np.array_equal(h1.labels(), h2.all_labels())
+    h1.close()
+    h2.close()
+
+
+@pytest.mark.parametrize("n", [2, 5, 9, 41])
+def test_multi_gpu_ragged_row_counts(eng, n):
+    """Row counts that a ceil split would leave a device without (9 rows on 8 devices, 5 on 4): the balanced
+    split gives every device at least one row and the result equals the single-GPU one."""
+    from h2o4gpu_b200.libs import lib_kmeans
+    ndev = lib_kmeans.cdll().kmeans_device_count()
+    if ndev < 2:
+        pytest.skip("one GPU visible")
+    rng = np.random.default_rng(n)
+    X = rng.standard_normal((n, 3)).astype(np.float32)
+    init = X[:2].copy()
+    h1 = eng.ResidentKMeans()
+    h1.upload(X)
+    h1.fit(init, 3)
+    g = min(ndev, n, 8)
+    h2 = eng.ResidentKMeans(devices=list(range(g)))
+    h2.upload(X)
+    assert sum(h2._rows) == n and min(h2._rows) >= 1
+    h2.fit(init, 3)
+    assert np.array_equal(h1.centroids(), h2.centroids())
     assert np.array_equal(h1.labels(), h2.all_labels())
     h1.close()
     h2.close()
@@ -891,3 +927,127 @@ def test_presplit_tensor_core_kernel_matches_converting_kernel(eng, tmp_path):
     h.fit(init, 16)
     assert np.array_equal(C2, h.centroids()) and np.array_equal(lab2, h.labels())
     h.close()
+
+
+# ---- the tensor-core kernels at sizes that wrap their rings many times -------------------
+@pytest.mark.parametrize("cfg,kw,steps", [("c2", dict(n=1_200_000), 3), ("c3", dict(n=300_000), 2)])
+def test_teacher_forced_large_f32(eng, cfg, kw, steps):
+    """1.2e6 rows of the C2 shape are 9,375 row tiles on 148 persistent CTAs (63 tiles per CTA: the
+    five-stage ring, the two issuers' hand-over and the three accumulators all wrap a dozen times);
+    3e5 rows of the C3 shape walk the streamed centroid table 2,344 times."""
+    from h2o4gpu_b200 import synth
+    X, init, _ = synth.CONFIGS[cfg](**kw)
+    C = init.astype(np.float64)
+    h = eng.ResidentKMeans(dtype=np.float32)
+    h.upload(X)
+    ties = 0
+    for _ in range(steps):
+        C32 = C.astype(np.float32)
+        Cn, labn, _, moved = lloyd.step(X, C32.astype(np.float64), order="descending")
+        h.fit(C32, 1, flags=eng.FIT_NO_FINAL_ASSIGN)
+        st = h.stats()
+        assert st["path"] == 3
+        ties += check_step(X, C32.astype(np.float64), h.centroids(), h.labels(), Cn, labn, moved, st["relocations"])
+        C = Cn
+    h.close()
+    print("near-tie label differences over the run:", ties)
+
+
+@pytest.mark.parametrize("cfg,kw", [("c2", dict(n=2_000_000)), ("c3", dict(n=200_000)), ("c5", dict(n=30_000))])
+def test_tensor_core_labels_equal_float64_engine(eng, cfg, kw):
+    """The float32 tensor-core E-step re-evaluates its ambiguous rows in double, so its labels are the
+    float64 argmin on the float32 data: compared here with the float64 engine on X.astype(float64)."""
+    from h2o4gpu_b200 import synth
+    X, init, _ = synth.CONFIGS[cfg](**kw)
+    C32, lab32, st32 = one_step(eng, X, init)
+    assert st32["path"] == 3
+    C64, lab64, _ = one_step(eng, X.astype(np.float64), init.astype(np.float64))
+    bad = np.flatnonzero(lab32 != lab64)
+    print("rows re-evaluated: %d, labels that differ from the float64 engine: %d" % (st32["refined_rows"], bad.size))
+    assert bad.size <= 2
+    if bad.size:
+        assert lloyd.near_tie_mask(X[bad], init.astype(np.float64), rel=1e-12).all()
+    else:
+        assert rel_err(C32, C64.astype(np.float64)) < 1e-6
+
+
+# ---- data spanning many orders of magnitude ----------------------------------------------
+@pytest.mark.parametrize("case", ["outlier_1e4", "outlier_1e6", "outlier_1e8", "column_1e6"])
+def test_wide_dynamic_range_f32(eng, case):
+    """The tensor-core kernel scales X by one power of two taken from max|x| before it splits the values into
+    fp16 halves, so an element far above the rest pushes the low halves of ordinary elements below fp16's
+    normal range.  The ambiguity threshold carries an absolute term for that; labels must stay the float64
+    argmin outside the 1e-5 band.  Centroids: 1e-4 of the largest reference coordinate (the exact integer
+    sums resolve max|x| * 2^-30, not each centroid's own magnitude)."""
+    from h2o4gpu_b200 import synth
+    X, init, _ = synth.c2(n=30000)
+    X = X.copy()
+    if case.startswith("outlier"):
+        X[5, 7] = float(case.split("_")[1]) * 10.0
+    else:
+        X[:, 3] *= 1e6
+        init = X[np.sort(np.random.default_rng(3).choice(30000, 100, replace=False))].copy()
+    C = init.astype(np.float64)
+    h = eng.ResidentKMeans(dtype=np.float32)
+    h.upload(X)
+    refined = 0
+    for _ in range(3):
+        C32 = C.astype(np.float32)
+        Cn, labn, _, moved = lloyd.step(X, C32.astype(np.float64), order="descending")
+        h.fit(C32, 1, flags=eng.FIT_NO_FINAL_ASSIGN)
+        st = h.stats()
+        assert st["path"] == 3
+        refined += st["refined_rows"]
+        check_step(X, C32.astype(np.float64), h.centroids(), h.labels(), Cn, labn, moved, st["relocations"])
+        C = Cn
+    h.close()
+    print("%s: %d rows re-evaluated in double over 3 steps" % (case, refined))
+
+
+# ---- the reference header's own (C++-linkage) names, called ------------------------------
+def test_cxx_linkage_entry_points_are_callable(built_lib):
+    """src/include/solver/kmeans.h:56-76 declares the four functions without extern "C"; code compiled
+    against that header binds the mangled names.  Look them up with nm and call them."""
+    import re
+    import subprocess
+    out = subprocess.run(["nm", "-D", "--defined-only", built_lib], capture_output=True, text=True).stdout
+    sym = {}
+    for n in ("make_ptr_float_kmeans", "make_ptr_double_kmeans", "kmeans_transform_float", "kmeans_transform_double"):
+        sym[n] = re.search(r" T (_Z\d+%s\w*)" % n, out).group(1)
+    lib = ctypes.CDLL(built_lib)
+    g = load_golden("blobs_n600_d5_k4")
+    vp, sz, ci = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
+    for dtype, tag, cfloat in ((np.float32, "float", ctypes.c_float), (np.float64, "double", ctypes.c_double)):
+        X = g["X"].astype(dtype)
+        init = g["init"].astype(dtype)
+        rows, cols = X.shape
+        k = init.shape[0]
+        fit = getattr(lib, sym["make_ptr_%s_kmeans" % tag])
+        fit.restype = ci
+        fit.argtypes = [ci] * 5 + [sz, sz, ci, ci, ci, cfloat, vp, vp, vp, vp]
+        centers = np.zeros((k, cols), dtype)
+        labels = np.zeros(rows, np.int32)
+        pc, pl = vp(centers.ctypes.data), vp(labels.ctypes.data)
+        rc = fit(0, 0, 0, 0, 1, rows, cols, k, int(g["T"]), 2, 0.0, X.ctypes.data_as(vp), init.ctypes.data_as(vp),
+                 ctypes.byref(pc), ctypes.byref(pl))
+        assert rc == 0
+        f = "f32" if dtype == np.float32 else "f64"
+        ref = g["centers_" + f].astype(np.float64)
+        assert rel_err(centers, ref) < (F32_TOL if dtype == np.float32 else F64_TOL)
+        check_labels(X, ref, labels, g["labels_" + f])
+        # dopredict = 1 through the same symbol
+        pred = np.zeros(rows, np.int32)
+        pl = vp(pred.ctypes.data)
+        rc = fit(1, 0, 0, 0, 1, rows, cols, k, 0, 0, 0.0, X.ctypes.data_as(vp), centers.ctypes.data_as(vp),
+                 ctypes.byref(pc), ctypes.byref(pl))
+        assert rc == 0
+        check_labels(X, centers.astype(np.float64), pred, lloyd.assign(X, centers.astype(np.float64)))
+        tr = getattr(lib, sym["kmeans_transform_%s" % tag])
+        tr.restype = ci
+        tr.argtypes = [ci] * 3 + [sz, sz, ci, vp, vp, vp]
+        D = np.zeros(rows * k, dtype)
+        pp = vp(D.ctypes.data)
+        rc = tr(0, 0, 1, rows, cols, k, X.ctypes.data_as(vp), centers.ctypes.data_as(vp), ctypes.byref(pp))
+        assert rc == 0
+        want = lloyd.transform_sq_colmajor(X, centers)
+        assert np.abs(D - want).max() <= (1e-4 if dtype == np.float32 else 1e-10) * want.max()
