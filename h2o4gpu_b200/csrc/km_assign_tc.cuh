@@ -119,9 +119,11 @@ __device__ int g_wait_diag[16][4];
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
                                           int info = -1) {
-  // 150000 parked waits of at most 20 us each: gives up after about 3 s
+  // parked waits of at most 20 us each; their number (150000 by default: gives up after about 3 s)
+  // sits in the CTA's shared memory behind the abort word, written by the kernel's first thread
   int why = 1;
-  for (unsigned int it = 0; it < 150000u; ++it) {
+  const unsigned int limit = (unsigned int)abort_flag[3];
+  for (unsigned int it = 0; it < limit; ++it) {
     if (mbar_try_hint(bar, parity, 20000u)) return true;
     if (*abort_flag) { why = 2; break; }
   }
@@ -131,6 +133,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   g_wait_diag[code & 15][2] = (int)parity;
   g_wait_diag[code & 15][3] = why;
   return false;
+}
+
+// One warp waits on an mbarrier that nothing ever arrives at: the give-up path of mbar_wait,
+// run on its own (kmeans_selftest_wait_timeout).  The wait returns false after `wait_iters` parked
+// polls, the error word takes the wait's code, the kernel ends normally.
+__global__ void mbar_timeout_probe_kernel(int* error_word, unsigned int wait_iters) {
+  __shared__ __align__(8) unsigned long long bar_mem;
+  __shared__ int abort_words[4];
+  if (threadIdx.x == 0) {
+    abort_words[0] = 0;
+    abort_words[3] = (int)wait_iters;
+    mbar_init((uint32_t)__cvta_generic_to_shared(&bar_mem), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const bool ok = mbar_wait((uint32_t)__cvta_generic_to_shared(&bar_mem), 0, abort_words, 9, 0);
+    if (!ok) atomicMax(error_word, abort_words[0]);
+  }
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
@@ -334,7 +355,8 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                  const __grid_constant__ CUtensorMap tmBlo, const float* __restrict__ cn_pad,
                  const float* __restrict__ xnorm, int* __restrict__ labels, size_t n, int n_tiles, int npad,
                  IterState* st, int count_changes, unsigned int* __restrict__ amb_rows, float tol_rel, float tol_floor,
-                 float sx, float sxsb, unsigned int* __restrict__ moved_bits, uint4* __restrict__ amb_near) {
+                 float sx, float sxsb, unsigned int* __restrict__ moved_bits, uint4* __restrict__ amb_near,
+                 unsigned int wait_iters) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_u32 = smem_u32(smem_raw);
   const uint32_t base = (raw_u32 + 1023u) & ~1023u;
@@ -365,6 +387,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     for (int a = 0; a < kAcc; ++a) { mbar_init(bar(ACC_FULL + a), 1); mbar_init(bar(ACC_EMPTY + a), 128); }
     mbar_init(bar(B_FULL), 1);
     *abort_flag = 0;
+    abort_flag[3] = (int)wait_iters;
     issued_upto[0] = -1;
     issued_upto[1] = -1;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");

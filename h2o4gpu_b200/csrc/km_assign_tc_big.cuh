@@ -88,7 +88,7 @@ assign_tc_big_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
                      const __grid_constant__ CUtensorMap tmBlo, const float* __restrict__ cn_pad,
                      const float* __restrict__ xnorm, int* __restrict__ labels, size_t n, int n_tiles, int kpad,
                      IterState* st, int count_changes, unsigned int* __restrict__ amb_rows, float tol_rel,
-                     float tol_floor, float sx, float sxsb) {
+                     float tol_floor, float sx, float sxsb, unsigned int wait_iters) {
   using Cf = BigCfg<D>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_u32 = smem_u32(smem_raw);
@@ -125,6 +125,7 @@ assign_tc_big_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     mbar_init(bar(PT_FUL), 128);
     mbar_init(bar(PT_EMP), 128);
     *abort_flag = 0;
+    abort_flag[3] = (int)wait_iters;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   for (int i = tid; i < kpad; i += kBigThreads) cn_s[i] = cn_pad[i];

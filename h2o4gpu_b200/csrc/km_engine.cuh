@@ -98,6 +98,10 @@ struct Shard {
   IterState* st = nullptr;
   double* cand_val = nullptr;
   unsigned long long* cand_row = nullptr;
+  unsigned int* ticket = nullptr;     // CTAs of the running close_kernel that have finished (zero between launches)
+  unsigned char* reloc_rec = nullptr; // several ranks without the push path: this rank's candidate record ...
+  unsigned char* reloc_all = nullptr; // ... and the all-gathered ones (host-driven repair)
+  size_t reloc_cap = 0;
   double* sum_partials = nullptr;
   double* shift_log = nullptr;
   unsigned long long* changed_log = nullptr;
@@ -175,6 +179,9 @@ struct Engine : EngineBase {
   int inertia(double* out);
   int allreduce_acc();
   int relocate_multi(double scale, int seq, int* n_empty);
+  // operand table of the tensor-core kernels as close_kernel fills it (null members: not in use)
+  SplitTable split_table(Shard<T>& s, bool use_tc);
+  int launch_close(Shard<T>& s, int run_if, int it, double inv, bool use_tc);
   int poll_seq = 0;   // sequence number the finalize kernels publish to pinned memory
   bool tc_ok(int flags) const;
   int tc_refresh(Shard<T>& s);  // split the current centroids for the tensor-core kernel
@@ -237,8 +244,10 @@ int Engine<T>::init(int n_local, const int* devs, int rank0, int world, const vo
     KM_CUDA(cudaMallocHost(&s.host_pin, 8 * sizeof(double)));
     std::memset(s.host_pin, 0, 8 * sizeof(double));
     KM_CUDA(km_malloc(&s.cand_val, 1024 * sizeof(double)));
-    KM_CUDA(km_malloc(&s.cand_row, 1024 * sizeof(unsigned long long)));
+    KM_CUDA(km_malloc(&s.cand_row, 2048 * sizeof(unsigned long long)));   // also the exchange buffer of push_setup
     KM_CUDA(km_malloc(&s.sum_partials, 1024 * sizeof(double)));
+    KM_CUDA(km_malloc(&s.ticket, sizeof(unsigned int)));
+    KM_CUDA(cudaMemset(s.ticket, 0, sizeof(unsigned int)));
   }
   if (world > 1) {
     NcclApi* api = NcclApi::get();
@@ -300,6 +309,7 @@ void Engine<T>::destroy() {
     km_free(s.pacc); km_free(s.pflush); km_free(s.labels_prev); km_free(s.moved_bits);
     km_free(s.C[0]); km_free(s.C[1]); km_free(s.Cd[0]); km_free(s.Cd[1]); km_free(s.cnorm); km_free(s.shift_k); km_free(s.empties);
     km_free(s.st); km_free(s.cand_val); km_free(s.cand_row); km_free(s.sum_partials);
+    km_free(s.ticket); km_free(s.reloc_rec); km_free(s.reloc_all);
     km_free(s.shift_log); km_free(s.changed_log); km_free(s.reloc_log); km_free(s.xstat);
     if (s.host_pin) cudaFreeHost(s.host_pin);
     if (s.stream) cudaStreamDestroy(s.stream);
@@ -1173,7 +1183,8 @@ int Engine<T>::allreduce_from(bool from_pure) {
       return !(e && e[0] == '0');
     }();
     if (push_env && !push_failed && count * sizeof(long long) <= kPushMaxBytes) {
-      if (!shards[0].push.ready || shards[0].push.count != count) {
+      const size_t gslot = (((size_t)k * 32 + (size_t)k * d * sizeof(T)) + 15) / 16 * 16;
+      if (!shards[0].push.ready || shards[0].push.count != count || shards[0].push.gslot != gslot) {
         if (push_setup(count) != KM_OK) { push_release(); push_failed = true; }
       }
       if (!push_failed) {
@@ -1183,7 +1194,7 @@ int Engine<T>::allreduce_from(bool from_pure) {
           DevGuard g(s.dev);
           push_allreduce_kernel<<<kPushCtas, kPushThreads, 0, s.stream>>>(
               from_pure ? s.pacc : s.gacc, s.gacc, count, world_rank0 + (int)i, world_size, s.push.d_peer_mailbox,
-              s.push.d_peer_flags, s.push.mailbox, s.push.flags, s.push.done, seq, s.st);
+              s.push.d_peer_flags, s.push.mailbox, s.push.flags, s.push.done, seq, s.st, wait_limits().push_spins);
           KM_CUDA(cudaGetLastError());
           ++launches;
         }
@@ -1260,18 +1271,24 @@ int Engine<T>::launch_delta(Shard<T>& s, T scale, const unsigned long long* gate
 // Mailboxes of all ranks mapped into every local device.  Ranks of this process are reached
 // through peer access, ranks of other processes through CUDA IPC handles gathered with NCCL.
 // The mailboxes come from cudaMalloc, not from the pool: pool memory cannot be exported.
+// Every rank walks through the same collectives whatever fails locally: a local failure only clears
+// `ok`, the exchange then carries dummy handles, and the closing all-reduce of the failure words
+// tells everybody - either all ranks push or all stay with NCCL.  Nothing returns between the
+// first collective and the last (a rank that left early would leave its peers' NCCL kernels
+// spinning without a bound).
 template <typename T>
 int Engine<T>::push_setup(size_t count) {
   push_release();
   NcclApi* api = NcclApi::get();
-  if (!api || !api->AllGather) return KM_ENCCL;
+  if (!api || !api->AllGather) return KM_ENCCL;   // the same on every rank: nobody starts a collective
   const int W = world_size;
   const size_t g = shards.size();
-  struct Handles { cudaIpcMemHandle_t mailbox, flags; };
+  struct Handles { cudaIpcMemHandle_t mailbox, flags, gmail; };
   std::vector<Handles> all((size_t)W);
-  // A rank that fails locally still walks through the collectives below, and the last one
-  // tells everybody: either all ranks push or all stay with NCCL.
+  std::memset(all.data(), 0, all.size() * sizeof(Handles));
   bool ok = true;
+  // one candidate record per empty cluster, at most k of them: [val][id][label][weight] + the row
+  const size_t gslot = (((size_t)k * 32 + (size_t)k * d * sizeof(T)) + 15) / 16 * 16;
   // 1. allocate, clear, export
   for (size_t i = 0; i < g; ++i) {
     Shard<T>& s = shards[i];
@@ -1279,63 +1296,68 @@ int Engine<T>::push_setup(size_t count) {
     PushState& ps = s.push;
     ps.count = count;
     ps.world = W;
+    ps.gslot = gslot;
     ps.peers.assign((size_t)W, PushPeer());
-    const size_t mb = (size_t)2 * W * count * sizeof(long long), fb = (size_t)2 * W * sizeof(unsigned int);
-    if (cudaMalloc(&ps.done, sizeof(unsigned int)) != cudaSuccess) { cudaGetLastError(); return KM_ENOMEM; }
-    if (cudaMalloc(&ps.mailbox, mb) != cudaSuccess || cudaMalloc(&ps.flags, fb) != cudaSuccess ||
+    const size_t mb = (size_t)2 * W * count * sizeof(long long), fb = (size_t)3 * W * sizeof(unsigned int);
+    if (cudaMalloc(&ps.done, sizeof(unsigned int)) != cudaSuccess || cudaMalloc(&ps.mailbox, mb) != cudaSuccess ||
+        cudaMalloc(&ps.flags, fb) != cudaSuccess || cudaMalloc(&ps.gmail, gslot * W) != cudaSuccess ||
+        cudaMalloc(&ps.grec, gslot) != cudaSuccess ||
         cudaMalloc(&ps.d_peer_mailbox, W * sizeof(long long*)) != cudaSuccess ||
-        cudaMalloc(&ps.d_peer_flags, W * sizeof(unsigned int*)) != cudaSuccess) {
+        cudaMalloc(&ps.d_peer_flags, W * sizeof(unsigned int*)) != cudaSuccess ||
+        cudaMalloc(&ps.d_peer_gmail, W * sizeof(unsigned char*)) != cudaSuccess ||
+        cudaMalloc(&ps.d_peer_gflags, W * sizeof(unsigned int*)) != cudaSuccess) {
       cudaGetLastError();
       ok = false;
       continue;
     }
+    cudaMemsetAsync(ps.done, 0, sizeof(unsigned int), s.stream);
     cudaMemsetAsync(ps.mailbox, 0, mb, s.stream);
     cudaMemsetAsync(ps.flags, 0, fb, s.stream);
+    cudaMemsetAsync(ps.gmail, 0, gslot * W, s.stream);
     Handles& h = all[(size_t)world_rank0 + i];
     if (cudaIpcGetMemHandle(&h.mailbox, ps.mailbox) != cudaSuccess ||
-        cudaIpcGetMemHandle(&h.flags, ps.flags) != cudaSuccess) {
+        cudaIpcGetMemHandle(&h.flags, ps.flags) != cudaSuccess ||
+        cudaIpcGetMemHandle(&h.gmail, ps.gmail) != cudaSuccess) {
       cudaGetLastError();
       ok = false;
     }
   }
-  // 2. every rank's handles to every process (device buffers, one all-gather per local shard)
+  // 2. every rank's handles to every process (device buffers, one all-gather per local shard).  The
+  // exchange buffers are the engine's own candidate buffers (allocated when the engine was
+  // created), so no allocation can fail between here and the agreement below.
+  bool nccl_ok = true;
   if ((int)g != W) {
-    std::vector<unsigned char*> d_send(g, nullptr), d_recv(g, nullptr);
-    bool bufs = true;
+    static_assert(sizeof(Handles) * 64 <= 2048 * sizeof(unsigned long long), "exchange buffer too small for 64 ranks");
     for (size_t i = 0; i < g; ++i) {
       DevGuard gd(shards[i].dev);
-      if (cudaMalloc(&d_send[i], sizeof(Handles)) != cudaSuccess ||
-          cudaMalloc(&d_recv[i], sizeof(Handles) * W) != cudaSuccess) { cudaGetLastError(); bufs = false; break; }
-      cudaMemcpyAsync(d_send[i], &all[(size_t)world_rank0 + i], sizeof(Handles), cudaMemcpyHostToDevice,
-                      shards[i].stream);
+      if (cudaMemcpyAsync(shards[i].cand_val, &all[(size_t)world_rank0 + i], sizeof(Handles), cudaMemcpyHostToDevice,
+                          shards[i].stream) != cudaSuccess) { cudaGetLastError(); ok = false; }
     }
-    if (!bufs) return KM_ENOMEM;   // cannot even take part in the exchange: a collective failure
     ncclResult_t nr = api->GroupStart();
     for (size_t i = 0; i < g && nr == ncclSuccess; ++i)
-      nr = api->AllGather(d_send[i], d_recv[i], sizeof(Handles), ncclChar, shards[i].comm, shards[i].stream);
+      nr = api->AllGather(shards[i].cand_val, shards[i].cand_row, sizeof(Handles), ncclChar, shards[i].comm,
+                          shards[i].stream);
     if (nr == ncclSuccess) nr = api->GroupEnd();
-    int rc = (nr == ncclSuccess) ? KM_OK : KM_ENCCL;
-    if (rc == KM_OK) {
+    if (nr != ncclSuccess) nccl_ok = false;
+    if (nccl_ok) {
       DevGuard gd(shards[0].dev);
-      if (cudaMemcpyAsync(all.data(), d_recv[0], sizeof(Handles) * W, cudaMemcpyDeviceToHost, shards[0].stream) !=
-              cudaSuccess ||
-          cudaStreamSynchronize(shards[0].stream) != cudaSuccess) rc = KM_ECUDA;
+      if (cudaMemcpyAsync(all.data(), shards[0].cand_row, sizeof(Handles) * W, cudaMemcpyDeviceToHost,
+                          shards[0].stream) != cudaSuccess ||
+          cudaStreamSynchronize(shards[0].stream) != cudaSuccess) { cudaGetLastError(); ok = false; }
     }
     for (size_t i = 0; i < g; ++i) {
       DevGuard gd(shards[i].dev);
       cudaStreamSynchronize(shards[i].stream);
-      cudaFree(d_send[i]);
-      cudaFree(d_recv[i]);
     }
-    if (rc != KM_OK) return rc;
   }
   // 3. map every rank's mailbox into every local device
-  for (size_t i = 0; i < g && ok; ++i) {
+  for (size_t i = 0; i < g && ok && nccl_ok; ++i) {
     Shard<T>& s = shards[i];
     DevGuard gd(s.dev);
     PushState& ps = s.push;
     std::vector<long long*> pm((size_t)W);
-    std::vector<unsigned int*> pf((size_t)W);
+    std::vector<unsigned int*> pf((size_t)W), pgf((size_t)W);
+    std::vector<unsigned char*> pg((size_t)W);
     for (int r = 0; r < W && ok; ++r) {
       const int local = r - world_rank0;
       PushPeer& pp = ps.peers[(size_t)r];
@@ -1350,9 +1372,9 @@ int Engine<T>::push_setup(size_t count) {
         }
         pp.mailbox = o.push.mailbox;
         pp.flags = o.push.flags;
+        pp.gmail = o.push.gmail;
       } else {
         void* a = nullptr;
-        void* b = nullptr;
         if (cudaIpcOpenMemHandle(&a, all[(size_t)r].mailbox, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
           cudaGetLastError();
           ok = false;
@@ -1360,53 +1382,76 @@ int Engine<T>::push_setup(size_t count) {
         }
         pp.mailbox = static_cast<long long*>(a);
         pp.ipc_mailbox = true;
-        if (cudaIpcOpenMemHandle(&b, all[(size_t)r].flags, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        if (cudaIpcOpenMemHandle(&a, all[(size_t)r].flags, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
           cudaGetLastError();
           ok = false;
           break;
         }
-        pp.flags = static_cast<unsigned int*>(b);
+        pp.flags = static_cast<unsigned int*>(a);
         pp.ipc_flags = true;
+        if (cudaIpcOpenMemHandle(&a, all[(size_t)r].gmail, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+          cudaGetLastError();
+          ok = false;
+          break;
+        }
+        pp.gmail = static_cast<unsigned char*>(a);
+        pp.ipc_gmail = true;
       }
       pm[(size_t)r] = pp.mailbox;
       pf[(size_t)r] = pp.flags;
+      pg[(size_t)r] = pp.gmail;
+      pgf[(size_t)r] = pp.flags + (size_t)2 * W;   // the gather flags lie behind the all-reduce flags
     }
     if (!ok) break;
     if (cudaMemcpyAsync(ps.d_peer_mailbox, pm.data(), W * sizeof(long long*), cudaMemcpyHostToDevice, s.stream) !=
             cudaSuccess ||
         cudaMemcpyAsync(ps.d_peer_flags, pf.data(), W * sizeof(unsigned int*), cudaMemcpyHostToDevice, s.stream) !=
             cudaSuccess ||
+        cudaMemcpyAsync(ps.d_peer_gmail, pg.data(), W * sizeof(unsigned char*), cudaMemcpyHostToDevice, s.stream) !=
+            cudaSuccess ||
+        cudaMemcpyAsync(ps.d_peer_gflags, pgf.data(), W * sizeof(unsigned int*), cudaMemcpyHostToDevice, s.stream) !=
+            cudaSuccess ||
         cudaStreamSynchronize(s.stream) != cudaSuccess) {
       cudaGetLastError();
       ok = false;
     }
   }
-  // 4. agreement and barrier in one collective: the sum of the ranks' failure words.  Nobody
-  // pushes before every mailbox is cleared and mapped, and nobody pushes unless everybody can.
+  // 4. agreement and barrier in one collective: the sum of the ranks' failure words (in the
+  // engine's own small state buffer).  Nobody pushes before every mailbox is cleared and mapped,
+  // and nobody pushes unless everybody can.  A rank whose NCCL call itself failed cannot take part
+  // in a collective at all and reports the error; its peers run into NCCL's own error handling.
+  if (!nccl_ok) return KM_ENCCL;
   unsigned int failures = 0;
   {
     for (size_t i = 0; i < g; ++i) {
       DevGuard gd(shards[i].dev);
       const unsigned int mine = ok ? 0u : 1u;
-      KM_CUDA(cudaMemcpyAsync(shards[i].push.done, &mine, sizeof(mine), cudaMemcpyHostToDevice, shards[i].stream));
-      KM_CUDA(cudaStreamSynchronize(shards[i].stream));
+      unsigned int* word = reinterpret_cast<unsigned int*>(shards[i].sum_partials);
+      if (cudaMemcpyAsync(word, &mine, sizeof(mine), cudaMemcpyHostToDevice, shards[i].stream) != cudaSuccess ||
+          cudaStreamSynchronize(shards[i].stream) != cudaSuccess) {
+        // the word keeps whatever it held: poison it so that the sum cannot come out as zero
+        cudaGetLastError();
+        cudaMemsetAsync(word, 0x01, sizeof(unsigned int), shards[i].stream);
+        ok = false;
+      }
     }
     ncclResult_t nr = api->GroupStart();
-    for (size_t i = 0; i < g && nr == ncclSuccess; ++i)
-      nr = api->AllReduce(shards[i].push.done, shards[i].push.done, 1, ncclUint32, ncclSum, shards[i].comm,
-                          shards[i].stream);
+    for (size_t i = 0; i < g && nr == ncclSuccess; ++i) {
+      unsigned int* word = reinterpret_cast<unsigned int*>(shards[i].sum_partials);
+      nr = api->AllReduce(word, word, 1, ncclUint32, ncclSum, shards[i].comm, shards[i].stream);
+    }
     if (nr == ncclSuccess) nr = api->GroupEnd();
     if (nr != ncclSuccess) return KM_ENCCL;
     for (size_t i = 0; i < g; ++i) {
       DevGuard gd(shards[i].dev);
-      unsigned int f = 0;
-      KM_CUDA(cudaMemcpyAsync(&f, shards[i].push.done, sizeof(f), cudaMemcpyDeviceToHost, shards[i].stream));
-      KM_CUDA(cudaMemsetAsync(shards[i].push.done, 0, sizeof(unsigned int), shards[i].stream));
-      KM_CUDA(cudaStreamSynchronize(shards[i].stream));
+      unsigned int f = 1;
+      unsigned int* word = reinterpret_cast<unsigned int*>(shards[i].sum_partials);
+      if (cudaMemcpyAsync(&f, word, sizeof(f), cudaMemcpyDeviceToHost, shards[i].stream) != cudaSuccess ||
+          cudaStreamSynchronize(shards[i].stream) != cudaSuccess) { cudaGetLastError(); f = 1; }
       failures += f;
     }
   }
-  if (failures != 0) {
+  if (failures != 0 || !ok) {
     log_msg(verbose, 300, "push all-reduce not available on %u rank(s): staying with NCCL", failures);
     return KM_ESTATE;
   }
@@ -1424,9 +1469,11 @@ void Engine<T>::push_release() {
     for (auto& pp : ps.peers) {
       if (pp.ipc_mailbox && pp.mailbox) cudaIpcCloseMemHandle(pp.mailbox);
       if (pp.ipc_flags && pp.flags) cudaIpcCloseMemHandle(pp.flags);
+      if (pp.ipc_gmail && pp.gmail) cudaIpcCloseMemHandle(pp.gmail);
     }
     ps.peers.clear();
     cudaFree(ps.mailbox); cudaFree(ps.flags); cudaFree(ps.done); cudaFree(ps.d_peer_mailbox); cudaFree(ps.d_peer_flags);
+    cudaFree(ps.gmail); cudaFree(ps.grec); cudaFree(ps.d_peer_gmail); cudaFree(ps.d_peer_gflags);
     cudaGetLastError();
     ps = PushState();
   }

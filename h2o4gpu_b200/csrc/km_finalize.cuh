@@ -9,6 +9,7 @@
 #pragma once
 
 #include <cooperative_groups.h>
+#include <cuda_fp16.h>
 
 #include "km_common.cuh"
 #include "km_tiles.cuh"
@@ -364,23 +365,58 @@ relocate_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict_
   }
 }
 
-// ---- averaging, norms and per-cluster shift ------------------------------------
-// One CTA per cluster.  inv = 2^-(sa+15) turns the int64 pairs back into sums.
-// A cluster without members copies the largest cluster's row as the CPU path
-// leaves it at that moment: already averaged if its id is lower, raw sums if not.
+// ---- averaging, norms, shift, logs and the tensor-core operands in one kernel ----------
+// Where the split centroid table of the tensor-core distance kernels goes (null bhi: not used):
+// bhi / blo = fp16 halves of -2 c * sb, rows of `dp` halves (columns >= d zero), `npad` rows
+// (rows >= k zero); cn_pad[j] = |c_j|^2 * sxsb (+inf for padding rows), cn_pad[npad] = max |c_j|^2.
+struct SplitTable {
+  __half* bhi;
+  __half* blo;
+  float* cn_pad;
+  int npad, dp;
+  float sb, sxsb;
+};
+
+template <typename T>
+__device__ __forceinline__ void split_table_row(const SplitTable& tp, int j, int d, const T* c_row, T cn) {}
+template <>
+__device__ __forceinline__ void split_table_row<float>(const SplitTable& tp, int j, int d, const float* c_row,
+                                                       float cn) {
+  for (int t = threadIdx.x; t < tp.dp; t += blockDim.x) {
+    const float v = (t < d) ? -2.0f * c_row[t] * tp.sb : 0.0f;
+    const __half h = __float2half_rn(v);
+    tp.bhi[(size_t)j * tp.dp + t] = h;
+    tp.blo[(size_t)j * tp.dp + t] = __float2half_rn(v - __half2float(h));
+  }
+  if (threadIdx.x == 0) tp.cn_pad[j] = cn * tp.sxsb;
+}
+
+// One CTA per cluster closes an M-step: mean of the cluster in double -> T (inv = 2^-(sa+15) turns
+// the int64 pairs back into sums), |c|^2, the cluster's squared shift, and - for the tensor-core
+// distance kernels - the cluster's row of the split operand table.  A cluster without members
+// copies the largest cluster's row as the CPU path leaves it at that moment: already averaged if
+// its id is lower, raw sums if not.  The CTA that finishes last (a ticket counter) adds the
+// per-cluster shifts in a fixed order, logs the iteration, re-arms the label-change counter and
+// writes the padding rows and the largest |c|^2 of the operand table.
+// run_if: 0 = only when the M-step found no empty cluster, 1 = only when it found one (queued
+// behind the repair kernels), 2 = always.  The pair (0, 1) around the gated repair kernels lets the
+// stream decide on the device, so the host never waits for the count of empty clusters.
 template <typename T>
 __global__ void __launch_bounds__(128)
-average_kernel(const long long* __restrict__ gsums, const unsigned long long* __restrict__ gcounts,
-               int k, int d, double inv, const T* __restrict__ C_old, T* __restrict__ C_new,
-               T* __restrict__ cnorm, double* __restrict__ shift_k, const IterState* st,
-               double* __restrict__ C_new_double, int only_if_no_empty, double count_unit) {
+close_kernel(const long long* __restrict__ gsums, const unsigned long long* __restrict__ gcounts,
+             int k, int d, double inv, const T* __restrict__ C_old, T* __restrict__ C_new,
+             T* __restrict__ cnorm, double* __restrict__ shift_k, IterState* st,
+             double* __restrict__ C_new_double, int run_if, double count_unit,
+             double* __restrict__ shift_log, unsigned long long* __restrict__ changed_log,
+             int* __restrict__ reloc_log, unsigned int* __restrict__ amb_log, int it,
+             double* __restrict__ host_shift, unsigned long long* __restrict__ host_changed,
+             unsigned int* __restrict__ ticket, SplitTable tp) {
   constexpr int NP = Fixed<T>::NP;
   // count_unit: weight of one unit of gcounts (1 for plain counts, a power of two for sample weights)
-  // launched ahead of the host's look at n_empty when several ranks work together: it must
-  // not average sums that still wait for their empty clusters to be repaired
-  if (only_if_no_empty && st->n_empty != 0) return;
+  const int n_empty = st->n_empty;
+  if ((run_if == 0 && n_empty != 0) || (run_if == 1 && n_empty == 0)) return;
   __shared__ double red_n[4], red_s[4];
-  __shared__ int s_src;
+  __shared__ int s_src, s_last;
   const int j = blockIdx.x;
   unsigned long long cnt = gcounts[j];
   int src = j;
@@ -421,31 +457,52 @@ average_kernel(const long long* __restrict__ gsums, const unsigned long long* __
   ss = warp_sum(ss);
   if ((threadIdx.x & 31) == 0) { red_n[threadIdx.x >> 5] = sn; red_s[threadIdx.x >> 5] = ss; }
   __syncthreads();
+  const T cn = (T)(red_n[0] + red_n[1] + red_n[2] + red_n[3]);
   if (threadIdx.x == 0) {
-    cnorm[j] = (T)(red_n[0] + red_n[1] + red_n[2] + red_n[3]);
+    cnorm[j] = cn;
     shift_k[j] = red_s[0] + red_s[1] + red_s[2] + red_s[3];
   }
-}
-
-// Sums the per-cluster shifts in a fixed order, logs the iteration and re-arms
-// the label-change counter.
-__global__ void __launch_bounds__(256)
-iter_close_kernel(const double* __restrict__ shift_k, int k, IterState* st, double* __restrict__ shift_log,
-                  unsigned long long* __restrict__ changed_log, int* __restrict__ reloc_log,
-                  unsigned int* __restrict__ amb_log, int it,
-                  double* __restrict__ host_shift, unsigned long long* __restrict__ host_changed,
-                  int only_if_no_empty) {
-  if (only_if_no_empty && st->n_empty != 0) return;
-  __shared__ double red[256];
-  double s = 0;
-  for (int j = threadIdx.x; j < k; j += 256) s += shift_k[j];
-  red[threadIdx.x] = s;
+  if (tp.bhi != nullptr) {
+    __syncthreads();   // the row of C_new written above is read back by other threads
+    split_table_row<T>(tp, j, d, C_new + (size_t)j * d, cn);
+  }
+  // ---- the last CTA closes the iteration ----
+  __threadfence();
   __syncthreads();
-  for (int o = 128; o > 0; o >>= 1) {
-    if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+  if (threadIdx.x == 0) s_last = (atomicAdd(ticket, 1u) == gridDim.x - 1) ? 1 : 0;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  __shared__ double red[128];
+  __shared__ float redm[128];
+  double s = 0;
+  float m = 0.f;
+  for (int c = threadIdx.x; c < k; c += 128) {
+    s += __ldcg(shift_k + c);
+    if (tp.bhi != nullptr) m = fmaxf(m, (float)__ldcg(cnorm + c));
+  }
+  red[threadIdx.x] = s;
+  redm[threadIdx.x] = m;
+  __syncthreads();
+  for (int o = 64; o > 0; o >>= 1) {
+    if (threadIdx.x < o) {
+      red[threadIdx.x] += red[threadIdx.x + o];
+      redm[threadIdx.x] = fmaxf(redm[threadIdx.x], redm[threadIdx.x + o]);
+    }
     __syncthreads();
   }
+  if (tp.bhi != nullptr) {
+    for (int r = k; r < tp.npad; ++r) {
+      for (int t = threadIdx.x; t < tp.dp; t += 128) {
+        tp.bhi[(size_t)r * tp.dp + t] = __float2half_rn(0.f);
+        tp.blo[(size_t)r * tp.dp + t] = __float2half_rn(0.f);
+      }
+      if (threadIdx.x == 0) tp.cn_pad[r] = __int_as_float(0x7f800000);
+    }
+    if (threadIdx.x == 0) tp.cn_pad[tp.npad] = redm[0];
+  }
   if (threadIdx.x == 0) {
+    *ticket = 0;
     st->shift_sq = red[0];
     shift_log[it] = red[0];
     changed_log[it] = st->changed;
@@ -471,7 +528,13 @@ __global__ void __launch_bounds__(256)
 select_far_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict__ labels,
                   double* __restrict__ dist, int E, unsigned long long id_base,
                   double* __restrict__ cand_val, unsigned long long* __restrict__ cand_row,
-                  unsigned char* __restrict__ rec, const T* __restrict__ W) {
+                  unsigned char* __restrict__ rec, const T* __restrict__ W, const IterState* gate) {
+  // with a gate the number of empty clusters is read on the device (the same on every rank: the
+  // counts were all-reduced) and the kernel returns at once when there is none
+  if (gate != nullptr) {
+    E = gate->n_empty;
+    if (E == 0) return;
+  }
   cg::grid_group grid = cg::this_grid();
   __shared__ double s_v[256];
   __shared__ unsigned long long s_r[256];
@@ -545,11 +608,16 @@ select_far_kernel(const T* __restrict__ X, size_t n, int d, const int* __restric
   }
 }
 
-template <typename T>
-__global__ void __launch_bounds__(256)
-apply_far_kernel(const unsigned char* __restrict__ rec_all, int world, int E, size_t rec_bytes, int k, int d,
-                 long long* __restrict__ gsums, unsigned long long* __restrict__ gcounts,
-                 const int* __restrict__ empties, IterState* st, T scale, int weighted, T wscale) {
+// The E-way choice among the gathered records, applied to this rank's (all-reduced, hence
+// identical) sums: one CTA of 256 threads.  FRESH: the records were written by other GPUs into
+// memory this SM may have cached from an earlier exchange, so they are read past L1.
+template <typename V, bool FRESH>
+__device__ __forceinline__ V rec_load(const V* p) { return FRESH ? __ldcv(p) : *p; }
+
+template <typename T, bool FRESH>
+__device__ __forceinline__ void apply_far_body(const unsigned char* rec_all, int world, int E, size_t rec_stride, int k,
+                                               int d, long long* gsums, unsigned long long* gcounts,
+                                               const int* empties, IterState* st, T scale, int weighted, T wscale) {
   constexpr int NP = Fixed<T>::NP;
   __shared__ int head[64];
   __shared__ int s_w;
@@ -563,9 +631,10 @@ apply_far_kernel(const unsigned char* __restrict__ rec_all, int world, int E, si
       int bw = -1;
       for (int w = 0; w < world; ++w) {
         if (head[w] >= E) continue;
-        const unsigned char* rec = rec_all + (size_t)w * rec_bytes;
-        double v = reinterpret_cast<const double*>(rec)[head[w]];
-        unsigned long long id = reinterpret_cast<const unsigned long long*>(rec + (size_t)E * 8)[head[w]];
+        const unsigned char* rec = rec_all + (size_t)w * rec_stride;
+        double v = rec_load<double, FRESH>(reinterpret_cast<const double*>(rec) + head[w]);
+        unsigned long long id =
+            rec_load<unsigned long long, FRESH>(reinterpret_cast<const unsigned long long*>(rec + (size_t)E * 8) + head[w]);
         if (v > bv || (v == bv && id < bid)) { bv = v; bid = id; bw = w; }
       }
       s_w = bw;
@@ -574,11 +643,11 @@ apply_far_kernel(const unsigned char* __restrict__ rec_all, int world, int E, si
     __syncthreads();
     if (s_stop) break;
     const int w = s_w;
-    const unsigned char* rec = rec_all + (size_t)w * rec_bytes;
+    const unsigned char* rec = rec_all + (size_t)w * rec_stride;
     const int h = head[w];
-    const int old = (int)reinterpret_cast<const long long*>(rec + (size_t)E * 16)[h];
+    const int old = (int)rec_load<long long, FRESH>(reinterpret_cast<const long long*>(rec + (size_t)E * 16) + h);
     const T* x = reinterpret_cast<const T*>(rec + (size_t)E * 32) + (size_t)h * d;
-    const T wt = (T)reinterpret_cast<const double*>(rec + (size_t)E * 24)[h];
+    const T wt = (T)rec_load<double, FRESH>(reinterpret_cast<const double*>(rec + (size_t)E * 24) + h);
     long long units = 1;
     if (weighted) {
       int pw[2];
@@ -588,7 +657,8 @@ apply_far_kernel(const unsigned char* __restrict__ rec_all, int world, int E, si
     const int cid = empties[e];
     for (int t = threadIdx.x; t < d; t += 256) {
       int p[NP];
-      split_pieces<NP>(weighted ? x[t] * wt : x[t], scale, p);
+      const T xv = rec_load<T, FRESH>(x + t);
+      split_pieces<NP>(weighted ? xv * wt : xv, scale, p);
 #pragma unroll
       for (int q = 0; q < NP / 2; ++q) {
         long long v = (long long)p[2 * q] * (1LL << kPieceBits) + (long long)p[2 * q + 1];
@@ -605,6 +675,60 @@ apply_far_kernel(const unsigned char* __restrict__ rec_all, int world, int E, si
     }
     __syncthreads();
   }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+apply_far_kernel(const unsigned char* __restrict__ rec_all, int world, int E, size_t rec_bytes, int k, int d,
+                 long long* __restrict__ gsums, unsigned long long* __restrict__ gcounts,
+                 const int* __restrict__ empties, IterState* st, T scale, int weighted, T wscale) {
+  apply_far_body<T, false>(rec_all, world, E, rec_bytes, k, d, gsums, gcounts, empties, st, scale, weighted, wscale);
+}
+
+// Several ranks, decided on the device: when the M-step left empty clusters (st->n_empty, the same on
+// every rank) this one CTA stores the rank's candidate record into slot `rank` of every peer's gather
+// mailbox (plain peer stores), raises its flag there, waits - bounded by `spin_limit` polls - for all
+// ranks' flags in its own mailbox and applies the common choice.  No empty cluster: returns at once,
+// nothing is sent.  One mailbox generation is enough: two exchanges are always separated by an
+// all-reduce of the sums, which no rank passes before every rank has finished the earlier exchange.
+//   gmail[world][slot_bytes], gflags[world] (sequence number of the last record a rank delivered)
+template <typename T>
+__global__ void __launch_bounds__(256)
+gather_apply_kernel(const unsigned char* __restrict__ rec, size_t slot_bytes, int rank, int world,
+                    unsigned char* const* __restrict__ peer_gmail, unsigned int* const* __restrict__ peer_gflags,
+                    const unsigned char* my_gmail, const unsigned int* my_gflags, unsigned int seq,
+                    unsigned int spin_limit, int k, int d, long long* __restrict__ gsums,
+                    unsigned long long* __restrict__ gcounts, const int* __restrict__ empties, IterState* st,
+                    T scale, int weighted, T wscale) {
+  const int E = st->n_empty;
+  if (E == 0) return;
+  __shared__ int s_bad;
+  if (threadIdx.x == 0) s_bad = 0;
+  const size_t words = ((size_t)E * 32 + (size_t)E * d * sizeof(T)) / 4;
+  const unsigned int* src = reinterpret_cast<const unsigned int*>(rec);
+  for (int p = 0; p < world; ++p) {
+    unsigned int* dst = reinterpret_cast<unsigned int*>(peer_gmail[p] + (size_t)rank * slot_bytes);
+    for (size_t i = threadIdx.x; i < words; i += 256) dst[i] = src[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < world) {
+    *reinterpret_cast<volatile unsigned int*>(peer_gflags[threadIdx.x] + rank) = seq;
+    __threadfence_system();
+    const volatile unsigned int* f = my_gflags + threadIdx.x;
+    unsigned int spins = 0;
+    while (*f != seq) {
+      if (++spins > spin_limit) { s_bad = 1; break; }
+      __nanosleep(40);
+    }
+  }
+  __syncthreads();
+  if (s_bad) {
+    if (threadIdx.x == 0) atomicMax(&st->error, 12);
+    return;
+  }
+  __threadfence();
+  apply_far_body<T, true>(my_gmail, world, E, slot_bytes, k, d, gsums, gcounts, empties, st, scale, weighted, wscale);
 }
 
 }  // namespace km

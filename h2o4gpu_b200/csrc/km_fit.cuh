@@ -38,20 +38,14 @@ int Engine<T>::assign_all(int flags) {
   for (auto& s : shards) {
     if (!s.X) KM_FAIL(KM_ESTATE, "no data attached to the handle");
     DevGuard g(s.dev);
-    if (smallk_ok(false) && !(flags & KM_FIT_FORCE_SPLIT)) {
-      IterState* keep = s.st;
-      s.st = nullptr;
-      int rc = launch_smallk(s, false, (T)1);
-      s.st = keep;
-      KM_TRY(rc);
-    } else {
-      const bool use_tc = tc_ok(flags);
-      if (use_tc) {
-        KM_TRY(tc_refresh(s));
-        KM_CUDA(cudaMemsetAsync(&s.st->amb_count, 0, sizeof(unsigned int), s.stream));
-      }
-      KM_TRY(launch_assign(s, use_tc, false));
+    // the same dispatch as the E-step of a fit (launch_assign picks the streaming kernel for few
+    // centroids and wide rows, the small-k kernel for narrow ones)
+    const bool use_tc = !smallk_ok(false) && tc_ok(flags);
+    if (use_tc) {
+      KM_TRY(tc_refresh(s));
+      KM_CUDA(cudaMemsetAsync(&s.st->amb_count, 0, sizeof(unsigned int), s.stream));
     }
+    KM_TRY(launch_assign(s, use_tc, false));
   }
   return KM_OK;
 }
@@ -85,13 +79,11 @@ int Engine<T>::relocate_multi(double scale, int seq, int* n_empty) {
   *n_empty = ne;
   if (ne == 0) return KM_OK;
   const size_t rec_bytes = (size_t)ne * 32 + (size_t)ne * d * sizeof(T);
-  std::vector<unsigned char*> rec(g, nullptr), all(g, nullptr);
+  // the buffers were sized for k records when the fit began: no rank can fail to allocate between
+  // here and the all-gather and leave its peers waiting in it
   for (size_t i = 0; i < g; ++i) {
     Shard<T>& s = shards[i];
     DevGuard gd(s.dev);
-    KM_TRY(ensure_dist(s));
-    KM_CUDA(km_malloc(&rec[i], rec_bytes));
-    KM_CUDA(km_malloc(&all[i], rec_bytes * world_size));
     launch_rowdist(s, 1);
     KM_CUDA(cudaGetLastError());
     const T* Xp = s.X;
@@ -103,27 +95,52 @@ int Engine<T>::relocate_multi(double scale, int seq, int* n_empty) {
     unsigned long long id_base = (unsigned long long)(world_rank0 + (int)i) << 40;
     double* cv = s.cand_val;
     unsigned long long* cr = s.cand_row;
-    unsigned char* rp = rec[i];
+    unsigned char* rp = s.reloc_rec;
     const T* Wp = weighted ? s.w : nullptr;
-    void* args[] = {&Xp, &n, &dd, &lab, &dist, &ee, &id_base, &cv, &cr, &rp, &Wp};
+    const IterState* gate = nullptr;
+    void* args[] = {&Xp, &n, &dd, &lab, &dist, &ee, &id_base, &cv, &cr, &rp, &Wp, &gate};
     KM_CUDA(cudaLaunchCooperativeKernel((void*)select_far_kernel<T>, dim3(s.num_sms), dim3(256), args, 0, s.stream));
     launches += 2;
   }
   KM_NCCL(api, api->GroupStart());
   for (size_t i = 0; i < g; ++i)
-    KM_NCCL(api, api->AllGather(rec[i], all[i], rec_bytes, ncclChar, shards[i].comm, shards[i].stream));
+    KM_NCCL(api, api->AllGather(shards[i].reloc_rec, shards[i].reloc_all, rec_bytes, ncclChar, shards[i].comm,
+                                shards[i].stream));
   KM_NCCL(api, api->GroupEnd());
   for (size_t i = 0; i < g; ++i) {
     Shard<T>& s = shards[i];
     DevGuard gd(s.dev);
-    apply_far_kernel<T><<<1, 256, 0, s.stream>>>(all[i], world_size, ne, rec_bytes, k, d, s.sums(), s.counts(k, d),
-                                                 s.empties, s.st, (T)scale, weighted ? 1 : 0, (T)w_scale);
+    apply_far_kernel<T><<<1, 256, 0, s.stream>>>(s.reloc_all, world_size, ne, rec_bytes, k, d, s.sums(),
+                                                 s.counts(k, d), s.empties, s.st, (T)scale, weighted ? 1 : 0,
+                                                 (T)w_scale);
     KM_CUDA(cudaGetLastError());
     ++launches;
-    KM_CUDA(cudaStreamSynchronize(s.stream));
-    km_free(rec[i]);
-    km_free(all[i]);
   }
+  return KM_OK;
+}
+
+template <typename T>
+SplitTable Engine<T>::split_table(Shard<T>& s, bool use_tc) {
+  SplitTable tp{nullptr, nullptr, nullptr, 0, 0, 0.f, 0.f};
+  if constexpr (std::is_same<T, float>::value) {
+    if (use_tc && tc::shape_ok(k, d))
+      tp = SplitTable{s.tcp.bhi, s.tcp.blo, s.tcp.cn, s.tcp.npad, 64, s.tcp.sb, s.tcp.sx * s.tcp.sb};
+    else if (use_tc)
+      tp = SplitTable{s.tcbp.bhi, s.tcbp.blo, s.tcbp.cn, s.tcbp.kpad, s.tcbp.dp, s.tcbp.sb, s.tcbp.sx * s.tcbp.sb};
+  }
+  return tp;
+}
+
+// Closes iteration `it` on a shard: new centroids into C[cur ^ 1] (and the tensor-core operand table)
+template <typename T>
+int Engine<T>::launch_close(Shard<T>& s, int run_if, int it, double inv, bool use_tc) {
+  close_kernel<T><<<k, 128, 0, s.stream>>>(s.sums(), s.counts(k, d), k, d, inv, s.C[cur], s.C[cur ^ 1], s.cnorm,
+                                           s.shift_k, s.st, s.Cd[cur ^ 1], run_if, weighted ? count_unit : 1.0,
+                                           s.shift_log, s.changed_log, s.reloc_log, s.amb_log, it, &s.host_pin[0],
+                                           reinterpret_cast<unsigned long long*>(&s.host_pin[1]), s.ticket,
+                                           split_table(s, use_tc));
+  KM_CUDA(cudaGetLastError());
+  ++launches;
   return KM_OK;
 }
 
@@ -174,7 +191,20 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
   for (auto& s : shards) {
     DevGuard g(s.dev);
     KM_TRY(ensure_logs(s, std::max(max_iter, 1)));
-    if (!multi) KM_TRY(ensure_dist(s));
+    KM_TRY(ensure_dist(s));
+    if (multi) {
+      // candidate records of the host-driven repair (several ranks over NCCL only), sized for k
+      // records now so that no rank can fail to allocate once the ranks depend on one another
+      const size_t need = ((size_t)k_ * 32 + (size_t)k_ * d * sizeof(T) + 15) / 16 * 16;
+      if (s.reloc_cap < need) {
+        km_free(s.reloc_rec); km_free(s.reloc_all);
+        s.reloc_rec = s.reloc_all = nullptr;
+        s.reloc_cap = 0;
+        KM_CUDA(km_malloc(&s.reloc_rec, need));
+        KM_CUDA(km_malloc(&s.reloc_all, need * (size_t)world_size));
+        s.reloc_cap = need;
+      }
+    }
     KM_CUDA(cudaMemsetAsync(s.st, 0, sizeof(IterState), s.stream));
     KM_CUDA(cudaMemsetAsync(s.labels, 0xff, s.rows * sizeof(int), s.stream));
     if (delta && s.labels_prev_cap < s.rows) {
@@ -248,79 +278,78 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
     if (rc != KM_OK) break;
     const int seq = ++poll_seq;
     if (multi && (rc = allreduce_from(delta)) != KM_OK) break;
+    // Empty clusters are repaired on the device whenever the ranks can reach one another's memory
+    // (one rank, or the push path): the repair kernels are queued every iteration and return at
+    // once unless the M-step left a cluster empty, and the closing kernel is queued twice, before
+    // them for the usual case and behind them for the repaired one.  The host never waits.
+    // Several ranks over NCCL only: the host reads the count of empty clusters (a pinned word) and
+    // drives the repair, with the closing kernel queued ahead for the usual case.
+    const bool host_repair = multi && stats.allreduce_path != 1;
     for (size_t i = 0; i < shards.size() && rc == KM_OK; ++i) {
       Shard<T>& s = shards[i];
       DevGuard g(s.dev);
       prepare_kernel<<<1, 256, 0, s.stream>>>(s.counts(k, d), k, s.st, s.empties,
-                                             reinterpret_cast<int*>(&s.host_pin[2]),
-                                             reinterpret_cast<int*>(&s.host_pin[3]), seq);
+                                             host_repair ? reinterpret_cast<int*>(&s.host_pin[2]) : nullptr,
+                                             host_repair ? reinterpret_cast<int*>(&s.host_pin[3]) : nullptr, seq);
       ++launches;
+      rc = launch_close(s, 0, it, inv, use_tc);
+      if (rc != KM_OK || host_repair) continue;
+      launch_rowdist(s, 0);
+      ++launches;
+      const T* Xp = s.X;
+      size_t n = s.rows;
+      int dd = d, kk = k;
+      const int* lab = s.labels;
+      double* dist = s.dist;
+      double* cv = s.cand_val;
+      unsigned long long* cr = s.cand_row;
+      const T* Wp = weighted ? s.w : nullptr;
+      cudaError_t ce;
       if (!multi) {
-        launch_rowdist(s, 0);
-        const T* Xp = s.X;
-        size_t n = s.rows;
-        int dd = d, kk = k;
-        const int* lab = s.labels;
-        double* dist = s.dist;
         long long* gs = s.sums();
         unsigned long long* gc = s.counts(k, d);
         const int* em = s.empties;
         IterState* st = s.st;
-        double* cv = s.cand_val;
-        unsigned long long* cr = s.cand_row;
         T sc = scale;
-        const T* Wp = weighted ? s.w : nullptr;
         T wsc = (T)w_scale;
         void* args[] = {&Xp, &n, &dd, &lab, &kk, &dist, &gs, &gc, &em, &st, &cv, &cr, &sc, &Wp, &wsc};
-        cudaError_t ce = cudaLaunchCooperativeKernel((void*)relocate_kernel<T>, dim3(s.num_sms), dim3(256), args, 0,
-                                                     s.stream);
-        if (ce != cudaSuccess) { set_error(std::string("relocate launch: ") + cudaGetErrorString(ce)); rc = KM_ECUDA; }
+        ce = cudaLaunchCooperativeKernel((void*)relocate_kernel<T>, dim3(s.num_sms), dim3(256), args, 0, s.stream);
+        ++launches;
+      } else {
+        int ee = 0;
+        unsigned long long id_base = (unsigned long long)(world_rank0 + (int)i) << 40;
+        unsigned char* rp = s.push.grec;
+        const IterState* gate = s.st;
+        void* args[] = {&Xp, &n, &dd, &lab, &dist, &ee, &id_base, &cv, &cr, &rp, &Wp, &gate};
+        ce = cudaLaunchCooperativeKernel((void*)select_far_kernel<T>, dim3(s.num_sms), dim3(256), args, 0, s.stream);
+        if (ce == cudaSuccess) {
+          gather_apply_kernel<T><<<1, 256, 0, s.stream>>>(
+              s.push.grec, s.push.gslot, world_rank0 + (int)i, world_size, s.push.d_peer_gmail, s.push.d_peer_gflags,
+              s.push.gmail, s.push.flags + (size_t)2 * world_size, (unsigned int)seq, wait_limits().push_spins, k, d,
+              s.sums(), s.counts(k, d), s.empties, s.st, scale, weighted ? 1 : 0, (T)w_scale);
+          ce = cudaGetLastError();
+        }
         launches += 2;
       }
+      if (ce != cudaSuccess) { set_error(std::string("repair launch: ") + cudaGetErrorString(ce)); rc = KM_ECUDA; }
+      if (rc == KM_OK) rc = launch_close(s, 1, it, inv, use_tc);
     }
     if (rc != KM_OK) break;
-    // Several ranks: whether an empty cluster must be repaired is known on the host only (the
-    // repair needs a collective).  The averaging kernels are queued first, told to do nothing if
-    // a cluster is empty; then the host reads the count, and only in that rare case repairs and
-    // queues them again.  One rank: the repair kernels ran in the stream already.
-    auto close_iteration = [&](int only_if_no_empty) {
-      for (size_t i = 0; i < shards.size() && rc == KM_OK; ++i) {
-        Shard<T>& s = shards[i];
-        DevGuard g(s.dev);
-        average_kernel<T><<<k, 128, 0, s.stream>>>(s.sums(), s.counts(k, d), k, d, inv, s.C[cur], s.C[cur ^ 1],
-                                                 s.cnorm, s.shift_k, s.st, s.Cd[cur ^ 1], only_if_no_empty,
-                                                 weighted ? count_unit : 1.0);
-        iter_close_kernel<<<1, 256, 0, s.stream>>>(s.shift_k, k, s.st, s.shift_log, s.changed_log, s.reloc_log,
-                                                   s.amb_log, it, &s.host_pin[0],
-                                                   reinterpret_cast<unsigned long long*>(&s.host_pin[1]),
-                                                   only_if_no_empty);
-        launches += 2;
-        cudaError_t ce = cudaGetLastError();
-        if (ce != cudaSuccess) { set_error(std::string("iteration launch: ") + cudaGetErrorString(ce)); rc = KM_ECUDA; }
-      }
-    };
-    if (multi) {
-      close_iteration(1);
-      if (rc != KM_OK) break;
+    if (host_repair) {
       int ne = 0;
       if ((rc = relocate_multi((double)scale, seq, &ne)) != KM_OK) break;
-      if (ne > 0) close_iteration(0);
-    } else {
-      close_iteration(0);
+      if (ne > 0)
+        for (size_t i = 0; i < shards.size() && rc == KM_OK; ++i) {
+          DevGuard g(shards[i].dev);
+          rc = launch_close(shards[i], 1, it, inv, use_tc);
+        }
+      if (rc != KM_OK) break;
     }
-    if (rc != KM_OK) break;
     {
       DevGuard g(s0.dev);
       cudaEventRecord(ev[4 * it + 3], s0.stream);
     }
-    cur ^= 1;
-    if (use_tc) {
-      for (size_t i = 0; i < shards.size() && rc == KM_OK; ++i) {
-        DevGuard g(shards[i].dev);
-        rc = tc_refresh(shards[i]);
-      }
-      if (rc != KM_OK) break;
-    }
+    cur ^= 1;   // (the closing kernel also wrote the tensor-core kernels' operand table for these centroids)
     if (check) {
       DevGuard g(s0.dev);
       cudaError_t ce = cudaStreamSynchronize(s0.stream);

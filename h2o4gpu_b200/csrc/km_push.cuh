@@ -11,8 +11,11 @@
 //   flags[2][world]            sequence number of the generation a rank has delivered
 // Peers are other devices of this process (peer access) or other processes (CUDA IPC
 // handles, exchanged once through the NCCL communicator that exists anyway).  Every wait is
-// bounded: after about two seconds the kernel records an error word and returns, and the
-// host reports KM_ETIMEOUT.  Plain peer loads/stores only - no multimem, no TMA.
+// bounded: after `spin_limit` polls (about two seconds by default, see wait_limits()) the kernel
+// records an error word and returns, and the host reports KM_ETIMEOUT.  Plain peer loads/stores
+// only - no multimem, no TMA.
+// A second, single-generation mailbox carries the candidate records of the empty-cluster repair
+// (gather_apply_kernel in km_finalize.cuh).
 #pragma once
 
 #include <vector>
@@ -26,10 +29,23 @@ constexpr int kPushCtas = 16;
 constexpr int kPushThreads = 256;
 constexpr size_t kPushMaxBytes = (size_t)1 << 20;   // larger vectors stay with NCCL
 
+// Limits of the bounded device-side waits, process-wide.  Defaults: about two seconds for the
+// peer-flag polls (40 ns sleep per poll) and about three seconds for the mbarrier waits of the
+// tensor-core kernels (parked try_wait of at most 20 us each).  kmeans_set_wait_limits() changes them.
+struct WaitLimits {
+  unsigned int push_spins = 20000000u;
+  unsigned int mbar_iters = 150000u;
+};
+inline WaitLimits& wait_limits() {
+  static WaitLimits w;
+  return w;
+}
+
 struct PushPeer {
   long long* mailbox = nullptr;    // [2][world][count] of the peer, mapped into this device
-  unsigned int* flags = nullptr;   // [2][world]
-  bool ipc_mailbox = false, ipc_flags = false;
+  unsigned int* flags = nullptr;   // [2][world] all-reduce flags, then [world] gather flags
+  unsigned char* gmail = nullptr;  // [world][gslot] candidate records of the empty-cluster repair
+  bool ipc_mailbox = false, ipc_flags = false, ipc_gmail = false;
 };
 
 struct PushState {
@@ -41,6 +57,11 @@ struct PushState {
   unsigned int* done = nullptr;        // CTAs of the current launch that finished pushing
   long long** d_peer_mailbox = nullptr;   // device arrays [world]
   unsigned int** d_peer_flags = nullptr;
+  unsigned char* gmail = nullptr;         // this rank's gather mailbox
+  size_t gslot = 0;                       // bytes of one rank's slot in it
+  unsigned char* grec = nullptr;          // this rank's own record, before it is pushed
+  unsigned char** d_peer_gmail = nullptr;
+  unsigned int** d_peer_gflags = nullptr;
   std::vector<PushPeer> peers;
 };
 
@@ -48,7 +69,7 @@ __global__ void __launch_bounds__(kPushThreads)
 push_allreduce_kernel(const long long* __restrict__ src, long long* __restrict__ dst, size_t count, int rank, int world,
                       long long* const* __restrict__ peer_mailbox, unsigned int* const* __restrict__ peer_flags,
                       const long long* my_mailbox, const unsigned int* my_flags, unsigned int* done,
-                      unsigned int seq, IterState* st) {
+                      unsigned int seq, IterState* st, unsigned int spin_limit) {
   __shared__ int s_last, s_bad;
   const unsigned int buf = seq & 1u;
   const size_t total = (size_t)world * count;
@@ -78,7 +99,7 @@ push_allreduce_kernel(const long long* __restrict__ src, long long* __restrict__
     const volatile unsigned int* f = my_flags + (size_t)buf * world + threadIdx.x;
     unsigned int spins = 0;
     while (*f != seq) {
-      if (++spins > 20000000u) { s_bad = 1; break; }   // a second or two with the sleep below
+      if (++spins > spin_limit) { s_bad = 1; break; }
       __nanosleep(40);
     }
   }

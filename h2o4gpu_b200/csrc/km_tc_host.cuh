@@ -4,6 +4,7 @@
 #pragma once
 
 #include "km_assign_tc.cuh"
+#include "km_push.cuh"
 
 namespace km {
 namespace tc {
@@ -207,17 +208,17 @@ inline int launch(Plan& pl, int* labels, IterState* st, bool count_changes, unsi
     assign_tc_kernel<32, false><<<grid, kThreads, smem_bytes(pl.d, pl.npad), stream>>>(
         pl.tmX, pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, pl.xnorm, labels, pl.x_rows, (int)tiles, pl.npad, st,
         count_changes ? 1 : 0, amb_rows, tol_rel, tol_floor_of(pl.d), pl.sx, pl.sx * pl.sb, count_changes ? moved_bits : nullptr,
-        amb_near);
+        amb_near, wait_limits().mbar_iters);
   else if (pre)
     assign_tc_kernel<64, true><<<grid, kThreads, smem_bytes(pl.d, pl.npad), stream>>>(
         pl.tmXh, pl.tmXl, pl.tmBhi, pl.tmBlo, pl.cn, pl.xnorm, labels, pl.x_rows, (int)tiles, pl.npad, st,
         count_changes ? 1 : 0, amb_rows, tol_rel, tol_floor_of(pl.d), pl.sx, pl.sx * pl.sb, count_changes ? moved_bits : nullptr,
-        amb_near);
+        amb_near, wait_limits().mbar_iters);
   else
     assign_tc_kernel<64, false><<<grid, kThreads, smem_bytes(pl.d, pl.npad), stream>>>(
         pl.tmX, pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, pl.xnorm, labels, pl.x_rows, (int)tiles, pl.npad, st,
         count_changes ? 1 : 0, amb_rows, tol_rel, tol_floor_of(pl.d), pl.sx, pl.sx * pl.sb, count_changes ? moved_bits : nullptr,
-        amb_near);
+        amb_near, wait_limits().mbar_iters);
   KM_CUDA(cudaGetLastError());
   return KM_OK;
 }
@@ -295,7 +296,7 @@ inline void big_launch_d(BigPlan& pl, const float* xnorm, int* labels, IterState
                          unsigned int* amb_rows, float tol_rel, int grid, int tiles, cudaStream_t stream) {
   assign_tc_big_kernel<D><<<grid, kBigThreads, big_smem_bytes<D>(pl.kpad), stream>>>(
       pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, xnorm, labels, pl.x_rows, tiles, pl.kpad, st, count_changes, amb_rows,
-      tol_rel, tc::tol_floor_of(pl.d), pl.sx, pl.sx * pl.sb);
+      tol_rel, tc::tol_floor_of(pl.d), pl.sx, pl.sx * pl.sb, wait_limits().mbar_iters);
 }
 
 inline int big_launch(BigPlan& pl, const float* xnorm, int* labels, IterState* st, bool count_changes,

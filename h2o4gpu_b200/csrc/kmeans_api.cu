@@ -377,6 +377,69 @@ int kmeans_last_fit_info(int* iterations, double* inertia) {
   return KM_OK;
 }
 
+int kmeans_set_wait_limits(double peer_wait_ms, double mbarrier_wait_ms) {
+  km::WaitLimits def;
+  km::WaitLimits& w = km::wait_limits();
+  // a peer-flag poll sleeps 40 ns and reads one word (about 0.1 us per poll in all); an mbarrier
+  // poll parks the warp for at most 20 us
+  w.push_spins = peer_wait_ms > 0 ? (unsigned int)std::min(4.0e9, std::max(1.0, peer_wait_ms * 1e4)) : def.push_spins;
+  w.mbar_iters = mbarrier_wait_ms > 0 ? (unsigned int)std::min(2.0e9, std::max(1.0, mbarrier_wait_ms * 50.0)) : def.mbar_iters;
+  return KM_OK;
+}
+
+int kmeans_selftest_wait_timeout(int gpu_id, int which, int* device_code) {
+  int visible = 0;
+  if (cudaGetDeviceCount(&visible) != cudaSuccess || gpu_id < 0 || gpu_id >= visible)
+    KM_FAIL(KM_ENODEV, "kmeans_selftest_wait_timeout: bad device");
+  if (which != 0 && which != 1) KM_FAIL(KM_EINVAL, "kmeans_selftest_wait_timeout: which must be 0 or 1");
+  km::DevGuard g(gpu_id);
+  km::IterState* st = nullptr;
+  KM_CUDA(km_malloc(&st, sizeof(km::IterState)));
+  cudaError_t ce = cudaMemset(st, 0, sizeof(km::IterState));
+  long long* mailbox = nullptr;
+  unsigned int* flags = nullptr;
+  unsigned int* done = nullptr;
+  long long** pm = nullptr;
+  unsigned int** pf = nullptr;
+  long long* vec = nullptr;
+  if (which == 0) {
+    // a world of two ranks on one device: both "peers" are this rank's own mailbox, and the second rank never
+    // delivers, so the wait for its flag must give up
+    const size_t count = 8;
+    if (ce == cudaSuccess) ce = km_malloc(&mailbox, 2 * 2 * count * sizeof(long long));
+    if (ce == cudaSuccess) ce = km_malloc(&flags, 2 * 2 * sizeof(unsigned int));
+    if (ce == cudaSuccess) ce = km_malloc(&done, sizeof(unsigned int));
+    if (ce == cudaSuccess) ce = km_malloc(&pm, 2 * sizeof(long long*));
+    if (ce == cudaSuccess) ce = km_malloc(&pf, 2 * sizeof(unsigned int*));
+    if (ce == cudaSuccess) ce = km_malloc(&vec, 2 * count * sizeof(long long));
+    if (ce == cudaSuccess) ce = cudaMemset(mailbox, 0, 2 * 2 * count * sizeof(long long));
+    if (ce == cudaSuccess) ce = cudaMemset(flags, 0, 2 * 2 * sizeof(unsigned int));
+    if (ce == cudaSuccess) ce = cudaMemset(done, 0, sizeof(unsigned int));
+    if (ce == cudaSuccess) ce = cudaMemset(vec, 0, 2 * count * sizeof(long long));
+    long long* hm[2] = {mailbox, mailbox};
+    unsigned int* hf[2] = {flags, flags};
+    if (ce == cudaSuccess) ce = cudaMemcpy(pm, hm, sizeof(hm), cudaMemcpyHostToDevice);
+    if (ce == cudaSuccess) ce = cudaMemcpy(pf, hf, sizeof(hf), cudaMemcpyHostToDevice);
+    if (ce == cudaSuccess) {
+      km::push_allreduce_kernel<<<km::kPushCtas, km::kPushThreads>>>(vec, vec + count, count, 0, 2, pm, pf, mailbox, flags,
+                                                                     done, 1u, st, km::wait_limits().push_spins);
+      ce = cudaGetLastError();
+    }
+  } else if (ce == cudaSuccess) {
+    km::tc::mbar_timeout_probe_kernel<<<1, 32>>>(&st->error, km::wait_limits().mbar_iters);
+    ce = cudaGetLastError();
+  }
+  if (ce == cudaSuccess) ce = cudaDeviceSynchronize();
+  km::IterState hs{};
+  if (ce == cudaSuccess) ce = cudaMemcpy(&hs, st, sizeof(hs), cudaMemcpyDeviceToHost);
+  km_free(st); km_free(mailbox); km_free(flags); km_free(done); km_free(pm); km_free(pf); km_free(vec);
+  if (ce != cudaSuccess) KM_FAIL(KM_ECUDA, std::string("kmeans_selftest_wait_timeout: ") + cudaGetErrorString(ce));
+  if (device_code) *device_code = hs.error;
+  if (hs.error != 0)
+    KM_FAIL(KM_ETIMEOUT, "a bounded device-side wait gave up (code " + std::to_string(hs.error) + ")");
+  return KM_OK;
+}
+
 int kmeans_device_count(void) {
   int n = 0;
   if (cudaGetDeviceCount(&n) != cudaSuccess) return 0;

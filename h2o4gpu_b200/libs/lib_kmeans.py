@@ -49,6 +49,8 @@ class Stats(ctypes.Structure):
 SIGNATURES = {
     "kmeans_last_error": (_c.c_char_p, []),
     "kmeans_trim_memory": (_c.c_int, []),
+    "kmeans_set_wait_limits": (_c.c_int, [_c.c_double, _c.c_double]),
+    "kmeans_selftest_wait_timeout": (_c.c_int, [_c.c_int, _c.c_int, _c.POINTER(_c.c_int)]),
     "kmeans_last_fit_info": (_c.c_int, [_c.POINTER(_c.c_int), _c.POINTER(_c.c_double)]),
     "kmeans_fit_f32": (_c.c_int, [_c.c_int] * 4 + [_sz, _sz, _c.c_int, _c.c_int, _c.c_int, _c.c_float, _vp, _vp, _vp, _vp]),
     "kmeans_fit_f64": (_c.c_int, [_c.c_int] * 4 + [_sz, _sz, _c.c_int, _c.c_int, _c.c_int, _c.c_double, _vp, _vp, _vp, _vp]),

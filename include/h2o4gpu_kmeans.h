@@ -48,6 +48,19 @@ int kmeans_last_fit_info(int* iterations, double* inertia);
  * pools off. */
 int kmeans_trim_memory(void);
 
+/* Every wait inside a kernel (for a peer GPU's flag in the multi-GPU exchanges, for an mbarrier in the
+ * tensor-core kernels) is bounded: when it runs out the kernel records a code, finishes normally and
+ * the call returns KM_ETIMEOUT; the reference exit()s on any device error
+ * (src/gpu/kmeans/kmeans_general.h:20-29).  This sets the two limits for the process, in milliseconds
+ * (defaults: about 2000 and 3000; a value <= 0 restores the default). */
+int kmeans_set_wait_limits(double peer_wait_ms, double mbarrier_wait_ms);
+/* Runs one such wait into its limit on device gpu_id, with nothing faulting: which = 0 launches the
+ * push all-reduce kernel for a world of two ranks of which the second never delivers, which = 1 a
+ * one-warp kernel that waits on an mbarrier nothing arrives at.  Returns KM_ETIMEOUT (the expected
+ * outcome; *device_code receives the code the kernel recorded: 11 peer flag, 9 mbarrier) and leaves
+ * the device usable.  Set short limits first. */
+int kmeans_selftest_wait_timeout(int gpu_id, int which, int* device_code);
+
 /* ---- 1. the reference's entry points ------------------------------------ */
 
 /* Fit (dopredict == 0) or predict (dopredict == 1).

@@ -1051,3 +1051,34 @@ def test_cxx_linkage_entry_points_are_callable(built_lib):
         assert rc == 0
         want = lloyd.transform_sq_colmajor(X, centers)
         assert np.abs(D - want).max() <= (1e-4 if dtype == np.float32 else 1e-10) * want.max()
+
+
+# ---- failure detection: a bounded device-side wait that runs out ------------------------
+def test_bounded_waits_give_up_and_leave_the_device_usable(eng, built_lib):
+    """Nothing faults: a kernel waits for a flag that nothing raises, the wait's limit (set to about 10 ms)
+    runs out, the kernel records its code and ends, the call returns KM_ETIMEOUT, and the handle made
+    before still fits afterwards with the same result."""
+    import time
+    from h2o4gpu_b200 import synth
+    from h2o4gpu_b200.libs import lib_kmeans
+    lib = lib_kmeans.cdll()
+    X, init, _ = synth.c2(n=20000)
+    h = eng.ResidentKMeans()
+    h.upload(X)
+    h.fit(init, 3)
+    before = h.centroids()
+    assert lib.kmeans_set_wait_limits(10.0, 10.0) == 0
+    try:
+        for which, code in ((0, 11), (1, 9)):
+            got = ctypes.c_int(0)
+            t0 = time.perf_counter()
+            rc = lib.kmeans_selftest_wait_timeout(0, which, ctypes.byref(got))
+            dt = time.perf_counter() - t0
+            assert rc == -7 and got.value == code, (rc, got.value)      # KM_ETIMEOUT, the wait's code
+            assert b"gave up" in lib.kmeans_last_error()
+            assert dt < 1.5, dt                                          # the short limit was honoured
+    finally:
+        assert lib.kmeans_set_wait_limits(0.0, 0.0) == 0                 # defaults back
+    h.fit(init, 3)
+    assert np.array_equal(h.centroids(), before)
+    h.close()
