@@ -64,6 +64,7 @@ struct Shard {
   int cc_major = 0;
   tc::Plan tcp;  // tensor-core path (float only)
   tcb::BigPlan tcbp;  // tensor-core path for large centroid tables
+  tcw::WidePlan tcwp; // tensor-core path for few centroids and wide rows
   unsigned int* amb_rows = nullptr;  // rows handed to the exact re-evaluation pass
   size_t amb_cap = 0;
   uint4* amb_near = nullptr;         // per listed row: bit mask of the candidate centroids (small tables)
@@ -304,6 +305,7 @@ void Engine<T>::destroy() {
     }
     s.tcp.release();
     s.tcbp.release();
+    s.tcwp.release();
     km_free(s.amb_rows); km_free(s.amb_near); km_free(s.amb_log);
     km_free(s.X_owned); km_free(s.raw); km_free(s.w); km_free(s.labels); km_free(s.dist); km_free(s.gacc);
     km_free(s.pacc); km_free(s.pflush); km_free(s.labels_prev); km_free(s.moved_bits);
@@ -337,6 +339,7 @@ int Engine<T>::attach_device(int local, const T* dX, size_t rows, size_t cols, s
   s.tcp.xsplit_of = nullptr;
   s.tcp.ready = false;
   s.tcbp.ready = false;
+  s.tcwp.ready = false;
   if ((int)cols != d) have_centroids = false;
   d = (int)cols;
   n_total = ntot;
@@ -1009,7 +1012,8 @@ static int try_sorted_accumulate(Shard<T>& s, int d, int k, T scale, bool vec, b
     else if (dv <= 32) rc = launch_sorted_gs<32>(s.X, s.rows, d, s.labels, k, gs, gc, scale30, p, s.stream, gate, limit);
     else if (dv <= 64) rc = launch_sorted_gs<64>(s.X, s.rows, d, s.labels, k, gs, gc, scale30, p, s.stream, gate, limit);
     else if (dv <= 128) rc = launch_sorted_gs<128>(s.X, s.rows, d, s.labels, k, gs, gc, scale30, p, s.stream, gate, limit);
-    else rc = launch_sorted_gs<256>(s.X, s.rows, d, s.labels, k, gs, gc, scale30, p, s.stream, gate, limit);
+    else if (dv <= 256) rc = launch_sorted_gs<256>(s.X, s.rows, d, s.labels, k, gs, gc, scale30, p, s.stream, gate, limit);
+    else rc = launch_sorted_gs<512>(s.X, s.rows, d, s.labels, k, gs, gc, scale30, p, s.stream, gate, limit);   // d <= 2048 (the plan's bound)
     KM_TRY(rc);
     *done = true;
   }
@@ -1067,7 +1071,7 @@ int Engine<T>::launch_accumulate(Shard<T>& s, T scale, long long* dst, const uns
 template <typename T>
 bool Engine<T>::tc_ok(int flags) const {
   if (!std::is_same<T, float>::value || (flags & KM_FIT_FORCE_SIMT)) return false;
-  if (!tc::shape_ok(k, d) && !tcb::big_shape_ok(k, d)) return false;
+  if (!tc::shape_ok(k, d) && !tcb::big_shape_ok(k, d) && !tcw::wide_shape_ok(k, d)) return false;
   for (const auto& s : shards)
     if (s.cc_major != 10 || (reinterpret_cast<uintptr_t>(s.X) & 15) != 0 || !s.x_checked) return false;
   double xmax = 0;
@@ -1096,7 +1100,13 @@ int Engine<T>::tc_refresh(Shard<T>& s) {
       KM_CUDA(km_malloc(&s.amb_near, s.rows * sizeof(uint4)));
       s.amb_near_cap = s.rows;
     }
-    if (tc::shape_ok(k, d)) {
+    if (tcw::wide_shape_ok(k, d)) {
+      KM_TRY(tc::ensure_xnorm(s.tcp, s.X, s.rows, d, s.num_sms, s.stream));
+      KM_TRY(tcw::wide_setup(s.tcwp, s.X, s.rows, k, d));
+      s.tcwp.sx = tc_sx;
+      s.tcwp.sb = tc_sb;
+      KM_TRY(tcw::wide_prep(s.tcwp, s.C[cur], s.cnorm, s.stream));
+    } else if (tc::shape_ok(k, d)) {
       KM_TRY(tc::setup(s.tcp, s.X, s.rows, k, d, s.num_sms, s.stream));
       s.tcp.sx = tc_sx;
       s.tcp.sb = tc_sb;
@@ -1116,6 +1126,15 @@ int Engine<T>::tc_refresh(Shard<T>& s) {
 template <typename T>
 int Engine<T>::launch_assign(Shard<T>& s, bool use_tc, bool count_changes) {
   if constexpr (std::is_same<T, float>::value) {
+    if (use_tc && tcw::wide_shape_ok(k, d)) {
+      launches += 2;
+      KM_TRY(tcw::wide_launch(s.tcwp, s.tcp.xnorm, s.labels, s.st, count_changes, s.amb_rows, tc::kTolRel, s.num_sms,
+                              s.stream));
+      tcb::refine_big_kernel<float><<<s.num_sms * 2, 256, 0, s.stream>>>(s.X, d, s.C[cur], k, s.amb_rows, s.st,
+                                                                        s.labels, count_changes ? 1 : 0);
+      KM_CUDA(cudaGetLastError());
+      return KM_OK;
+    }
     if (use_tc && !tc::shape_ok(k, d)) {
       launches += 2;
       KM_TRY(tcb::big_launch(s.tcbp, s.tcp.xnorm, s.labels, s.st, count_changes, s.amb_rows, tc::kTolRel, s.num_sms,

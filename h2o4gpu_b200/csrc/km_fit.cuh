@@ -5,6 +5,13 @@
 
 namespace km {
 
+// The incremental M-step takes an iteration when at most 1 / kDeltaFraction of the shard's labels moved.
+// Moving a row costs about three times its share of a full pass (two clusters touched, scattered
+// reads), so the break-even lies near a third of the rows on wide rows and near a sixth on narrow
+// ones (measured: 784 columns, 5.8 % moved: 0.35 ms against 2.39 ms for the full pass; 64 columns,
+// 5.8 % moved: 0.24 ms against 0.63 ms).
+constexpr unsigned long long kDeltaFraction = 8;
+
 template <typename T>
 static int ensure_dist(Shard<T>& s) {
   if (s.dist_cap < s.rows) {
@@ -40,7 +47,7 @@ int Engine<T>::assign_all(int flags) {
     DevGuard g(s.dev);
     // the same dispatch as the E-step of a fit (launch_assign picks the streaming kernel for few
     // centroids and wide rows, the small-k kernel for narrow ones)
-    const bool use_tc = !smallk_ok(false) && tc_ok(flags);
+    const bool use_tc = tc_ok(flags) && (!smallk_ok(false) || tcw::wide_shape_ok(k, d));
     if (use_tc) {
       KM_TRY(tc_refresh(s));
       KM_CUDA(cudaMemsetAsync(&s.st->amb_count, 0, sizeof(unsigned int), s.stream));
@@ -123,7 +130,9 @@ template <typename T>
 SplitTable Engine<T>::split_table(Shard<T>& s, bool use_tc) {
   SplitTable tp{nullptr, nullptr, nullptr, 0, 0, 0.f, 0.f};
   if constexpr (std::is_same<T, float>::value) {
-    if (use_tc && tc::shape_ok(k, d))
+    if (use_tc && tcw::wide_shape_ok(k, d))
+      tp = SplitTable{s.tcwp.bhi, s.tcwp.blo, s.tcwp.cn, tcw::kNPad, s.tcwp.dp, s.tcwp.sb, s.tcwp.sx * s.tcwp.sb};
+    else if (use_tc && tc::shape_ok(k, d))
       tp = SplitTable{s.tcp.bhi, s.tcp.blo, s.tcp.cn, s.tcp.npad, 64, s.tcp.sb, s.tcp.sx * s.tcp.sb};
     else if (use_tc)
       tp = SplitTable{s.tcbp.bhi, s.tcbp.blo, s.tcbp.cn, s.tcbp.kpad, s.tcbp.dp, s.tcbp.sb, s.tcbp.sx * s.tcbp.sb};
@@ -176,7 +185,7 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
   struct SplitBuildGuard { bool& f; ~SplitBuildGuard() { f = false; } } split_build_guard{tc_split_build};
   // incremental M-step (km_accumulate_delta.cuh): on unless the caller or the environment asks
   // for a full recomputation every iteration; a shard switches to it, on the device, in the
-  // iterations where at most 1/16 of its labels moved
+  // iterations where at most 1/8 of its labels moved (kDeltaFraction)
   static const bool delta_env = [] {
     const char* e = std::getenv("H2O4GPU_KM_DELTA_SUMS");
     return !(e && e[0] == '0');
@@ -250,7 +259,7 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
         if (i == 0) cudaEventRecord(ev[4 * it + 1], s.stream);
         // both branches are launched; the label-change counter decides on the device which one works
         const unsigned long long* gate = (it == 0) ? nullptr : &s.st->changed;
-        const unsigned long long limit = s.rows / 16;
+        const unsigned long long limit = s.rows / kDeltaFraction;
         if (rc == KM_OK) {
           full_prologue_kernel<<<s.num_sms * 4, 256, 0, s.stream>>>(s.pacc, s.gacc_count(k, d), s.labels,
                                                                      s.labels_prev, s.rows, gate, limit);
@@ -422,7 +431,7 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
       }
       for (int i = 0; i < done; ++i) stats.relocations += rl[i];
       if (delta)
-        for (int i = 1; i < done; ++i) stats.incremental_iterations += (ch[i] <= s0.rows / 16);
+        for (int i = 1; i < done; ++i) stats.incremental_iterations += (ch[i] <= s0.rows / kDeltaFraction);
       float a = 0, u = 0, ms = 0;
       static const bool trace = std::getenv("H2O4GPU_KM_TRACE") != nullptr;
       for (int i = 0; i < done; ++i) {
@@ -495,9 +504,16 @@ int Engine<T>::transform_shard(int local, T* out_host, size_t ld) {
   if (!have_centroids) KM_FAIL(KM_ESTATE, "no centroids set");
   Shard<T>& s = shards[local];
   if (ld < s.rows) KM_FAIL(KM_EINVAL, "kmeans_transform_resident: ld smaller than the shard");
+  // max|x| (the tensor-core kernel's operand scale) is known after the data check; with several
+  // processes that check is a collective and is left to the fit
+  if (world_size == (int)shards.size()) KM_TRY(check_data());
   DevGuard g(s.dev);
   // row batches bound the device block to about 256 MB
   size_t batch = std::max<size_t>(128, ((size_t)1 << 28) / ((size_t)k * sizeof(T)));
+  if (const char* e = std::getenv("H2O4GPU_KM_TRANSFORM_BATCH_ROWS")) {   // smaller blocks (tests of the batching)
+    const long long v = std::atoll(e);
+    if (v > 0) batch = (size_t)v;
+  }
   batch = (batch + 127) / 128 * 128;
   batch = std::min(batch, (s.rows + 127) / 128 * 128);
   T* buf = nullptr;
@@ -507,10 +523,26 @@ int Engine<T>::transform_shard(int local, T* out_host, size_t ld) {
   cudaEventCreate(&e1);
   float ms_kernels = 0;
   int rc = KM_OK;
+  bool wide = false;
+  if constexpr (std::is_same<T, float>::value) {
+    // few centroids, wide rows: the tensor-core kernel with its store epilogue (needs max|x| for the
+    // operand scales, i.e. a checked matrix)
+    if (tcw::wide_shape_ok(k, d) && tc_ok(0)) {
+      rc = tc_refresh(s);
+      wide = rc == KM_OK;
+    }
+  }
   for (size_t r = 0; r < s.rows && rc == KM_OK; r += batch) {
     size_t nr = std::min(batch, s.rows - r);
     cudaEventRecord(e0, s.stream);
-    rc = launch_tiles(s, s.X + r * (size_t)d, nr, nullptr, MODE_TRANSFORM, buf, batch, false);
+    if constexpr (std::is_same<T, float>::value) {
+      if (wide) {
+        rc = tcw::wide_launch(s.tcwp, s.tcp.xnorm, nullptr, s.st, false, nullptr, tc::kTolRel, s.num_sms, s.stream, r, nr,
+                              buf, batch);
+        ++launches;
+      }
+    }
+    if (!wide) rc = launch_tiles(s, s.X + r * (size_t)d, nr, nullptr, MODE_TRANSFORM, buf, batch, false);
     if (rc != KM_OK) break;
     cudaEventRecord(e1, s.stream);
     cudaError_t ce = cudaMemcpy2DAsync(out_host + r, ld * sizeof(T), buf, batch * sizeof(T), nr * sizeof(T), k,

@@ -249,10 +249,12 @@ struct BigPlan {
   }
 };
 
-// float32, d in {32, 64, 128, 256}; the |c|^2 table of all centroids must fit shared memory
-inline bool big_shape_ok(int k, int d) {
-  return (d == 32 || d == 64 || d == 128 || d == 256) && k > 16 && k <= 6144;
-}
+// float32, rows of at most 256 columns with 16-byte alignment (d % 4 == 0); the |c|^2 table of all
+// centroids must fit shared memory.  The kernel is compiled for 32, 64, 128 and 256 columns; other
+// widths run the next larger variant: the copy engine zero-fills the columns of an X tile that lie
+// beyond d and the split centroid table is zero there too, so the products are unchanged.
+inline bool big_shape_ok(int k, int d) { return d >= 32 && d <= 256 && d % 4 == 0 && k > 16 && k <= 6144; }
+inline int big_variant(int d) { return d <= 32 ? 32 : (d <= 64 ? 64 : (d <= 128 ? 128 : 256)); }
 
 template <int D>
 inline int big_set_attr(int kpad) {
@@ -263,7 +265,8 @@ inline int big_set_attr(int kpad) {
 
 inline int big_setup(BigPlan& pl, const float* X, size_t rows, int k, int d) {
   const int kpad = (k + kNT - 1) / kNT * kNT;
-  const int dp = d < 64 ? 64 : d;
+  const int dv = big_variant(d);
+  const int dp = dv < 64 ? 64 : dv;
   if (pl.ready && pl.k == k && pl.d == d && pl.x_base == X && pl.x_rows == rows) return KM_OK;
   if (!(pl.bhi && pl.k == k && pl.d == d)) {
     pl.release();
@@ -275,9 +278,9 @@ inline int big_setup(BigPlan& pl, const float* X, size_t rows, int k, int d) {
   KM_TRY(tc::make_map(&pl.tmX, X, rows, d, kBM, 4));
   KM_TRY(tc::make_map(&pl.tmBhi, pl.bhi, kpad, dp, kNT, 2));
   KM_TRY(tc::make_map(&pl.tmBlo, pl.blo, kpad, dp, kNT, 2));
-  if (d == 32) KM_TRY(big_set_attr<32>(kpad));
-  else if (d == 64) KM_TRY(big_set_attr<64>(kpad));
-  else if (d == 128) KM_TRY(big_set_attr<128>(kpad));
+  if (dv == 32) KM_TRY(big_set_attr<32>(kpad));
+  else if (dv == 64) KM_TRY(big_set_attr<64>(kpad));
+  else if (dv == 128) KM_TRY(big_set_attr<128>(kpad));
   else KM_TRY(big_set_attr<256>(kpad));
   pl.ready = true;
   return KM_OK;
@@ -305,13 +308,96 @@ inline int big_launch(BigPlan& pl, const float* xnorm, int* labels, IterState* s
   if (tiles > 0x7fffffffULL / kBM) KM_FAIL(KM_EINVAL, "shard too large for the tensor-core kernel");
   const int grid = (int)std::min<size_t>(tiles, (size_t)num_sms);
   const int cc = count_changes ? 1 : 0;
-  if (pl.d == 32) big_launch_d<32>(pl, xnorm, labels, st, cc, amb_rows, tol_rel, grid, (int)tiles, stream);
-  else if (pl.d == 64) big_launch_d<64>(pl, xnorm, labels, st, cc, amb_rows, tol_rel, grid, (int)tiles, stream);
-  else if (pl.d == 128) big_launch_d<128>(pl, xnorm, labels, st, cc, amb_rows, tol_rel, grid, (int)tiles, stream);
+  const int dv = big_variant(pl.d);
+  if (dv == 32) big_launch_d<32>(pl, xnorm, labels, st, cc, amb_rows, tol_rel, grid, (int)tiles, stream);
+  else if (dv == 64) big_launch_d<64>(pl, xnorm, labels, st, cc, amb_rows, tol_rel, grid, (int)tiles, stream);
+  else if (dv == 128) big_launch_d<128>(pl, xnorm, labels, st, cc, amb_rows, tol_rel, grid, (int)tiles, stream);
   else big_launch_d<256>(pl, xnorm, labels, st, cc, amb_rows, tol_rel, grid, (int)tiles, stream);
   KM_CUDA(cudaGetLastError());
   return KM_OK;
 }
 
 }  // namespace tcb
+}  // namespace km
+
+#include "km_assign_tc_wide.cuh"
+
+namespace km {
+namespace tcw {
+
+struct WidePlan {
+  __half* bhi = nullptr;
+  __half* blo = nullptr;
+  float* cn = nullptr;
+  int k = 0, d = 0, dp = 0, n_chunks = 0, stages = 0;
+  const float* x_base = nullptr;
+  size_t x_rows = 0;
+  float sx = 1.f, sb = 1.f;
+  CUtensorMap tmX, tmBhi, tmBlo;
+  bool ready = false;
+  void release() {
+    km_free(bhi); km_free(blo); km_free(cn);
+    bhi = blo = nullptr;
+    cn = nullptr;
+    ready = false;
+  }
+};
+
+// ring depth for d columns: as deep as shared memory allows, 3 to 5 stages
+inline int wide_stages(int d) {
+  const int n_chunks = (d + kChunk - 1) / kChunk;
+  for (int s = kMaxStages; s >= 3; --s)
+    if (wide_smem_bytes(n_chunks, s) <= (size_t)227 * 1024) return s;
+  return 0;
+}
+// float32, at most 16 centroids, rows of 128 or more columns (16-byte aligned rows: d % 4 == 0)
+inline bool wide_shape_ok(int k, int d) { return k >= 1 && k <= kNPad && d >= 128 && d % 4 == 0 && wide_stages(d) > 0; }
+
+inline int wide_setup(WidePlan& pl, const float* X, size_t rows, int k, int d) {
+  if (pl.ready && pl.k == k && pl.d == d && pl.x_base == X && pl.x_rows == rows) return KM_OK;
+  const int n_chunks = (d + kChunk - 1) / kChunk;
+  const int dp = n_chunks * kChunk;
+  if (!(pl.bhi && pl.k == k && pl.d == d)) {
+    pl.release();
+    KM_CUDA(km_malloc(&pl.bhi, (size_t)kNPad * dp * sizeof(__half)));
+    KM_CUDA(km_malloc(&pl.blo, (size_t)kNPad * dp * sizeof(__half)));
+    KM_CUDA(km_malloc(&pl.cn, (size_t)(kNPad + 1) * sizeof(float)));
+  }
+  pl.k = k; pl.d = d; pl.dp = dp; pl.n_chunks = n_chunks; pl.stages = wide_stages(d);
+  pl.x_base = X; pl.x_rows = rows;
+  KM_TRY(tc::make_map(&pl.tmX, X, rows, d, kBM, 4));
+  KM_TRY(tc::make_map(&pl.tmBhi, pl.bhi, kNPad, dp, kNPad, 2));
+  KM_TRY(tc::make_map(&pl.tmBlo, pl.blo, kNPad, dp, kNPad, 2));
+  KM_CUDA(cudaFuncSetAttribute(assign_tc_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)wide_smem_bytes(n_chunks, pl.stages)));
+  pl.ready = true;
+  return KM_OK;
+}
+
+inline int wide_prep(WidePlan& pl, const float* C, const float* cnorm, cudaStream_t stream) {
+  KM_CUDA(cudaMemsetAsync(pl.cn + kNPad, 0, sizeof(float), stream));
+  tcb::big_prep_kernel<<<kNPad, 256, 0, stream>>>(C, cnorm, pl.k, pl.d, pl.dp, kNPad, pl.sb, pl.sx * pl.sb, pl.bhi,
+                                                  pl.blo, pl.cn);
+  KM_CUDA(cudaGetLastError());
+  return KM_OK;
+}
+
+// labels of rows [row0, row0 + nrows) (row0 a multiple of 128), or - with `out` - their squared distances to
+// the k centroids as a column-major block with leading dimension ld_out
+inline int wide_launch(WidePlan& pl, const float* xnorm, int* labels, IterState* st, bool count_changes,
+                       unsigned int* amb_rows, float tol_rel, int num_sms, cudaStream_t stream, size_t row0 = 0,
+                       size_t nrows = 0, float* out = nullptr, size_t ld_out = 0) {
+  if (nrows == 0) nrows = pl.x_rows - row0;
+  const size_t tiles = (nrows + kBM - 1) / kBM;
+  if ((pl.x_rows + kBM - 1) / kBM > 0x7fffffffULL / kBM) KM_FAIL(KM_EINVAL, "shard too large for the tensor-core kernel");
+  const int grid = (int)std::min<size_t>(tiles, (size_t)num_sms);
+  assign_tc_wide_kernel<<<grid, kWThreads, wide_smem_bytes(pl.n_chunks, pl.stages), stream>>>(
+      pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, xnorm, labels, std::min(pl.x_rows, row0 + nrows), (int)(row0 / kBM), (int)tiles,
+      pl.n_chunks, pl.stages, pl.k, st, count_changes ? 1 : 0, amb_rows, tol_rel, tc::tol_floor_of(pl.d), pl.sx,
+      pl.sx * pl.sb, wait_limits().mbar_iters, out, ld_out);
+  KM_CUDA(cudaGetLastError());
+  return KM_OK;
+}
+
+}  // namespace tcw
 }  // namespace km

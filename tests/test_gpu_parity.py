@@ -341,7 +341,9 @@ def test_incremental_sums_equal_full_recompute_bitwise(eng, dtype, cfg, kw, iter
 
 # ---- edge cases ------------------------------------------------------------------------
 @pytest.mark.parametrize("n,d,k", [(1, 1, 1), (3, 2, 2), (5, 3, 5), (129, 7, 3), (257, 33, 17), (1000, 130, 20),
-                                   (300, 4, 16), (300, 4, 18), (2049, 64, 100), (700, 1030, 6)])
+                                   (300, 4, 16), (300, 4, 18), (2049, 64, 100), (700, 1030, 6),
+                                   # few centroids, wide rows: the chunked tensor-core kernel (d % 4 == 0, d >= 128)
+                                   (1000, 132, 5), (257, 784, 16), (3000, 2048, 3), (129, 128, 1), (40000, 200, 10)])
 def test_ragged_shapes(eng, n, d, k):
     rng = np.random.default_rng(n * 1000 + d * 10 + k)
     X = rng.standard_normal((n, d)).astype(np.float32) * 3
@@ -1081,4 +1083,64 @@ def test_bounded_waits_give_up_and_leave_the_device_usable(eng, built_lib):
         assert lib.kmeans_set_wait_limits(0.0, 0.0) == 0                 # defaults back
     h.fit(init, 3)
     assert np.array_equal(h.centroids(), before)
+    h.close()
+
+
+# ---- few centroids, wide rows: tensor-core kernel against the FMA kernel, and its transform ---------
+def test_wide_rows_tensor_core_kernel_matches_simt_kernel_and_transform(eng, tmp_path):
+    from h2o4gpu_b200 import synth
+    X, init, _ = synth.c4(n=50000)
+    C0 = init.astype(np.float64)
+    a = one_step(eng, X, init)
+    b = one_step(eng, X, init, flags=eng.FIT_FORCE_SIMT)
+    assert a[2]["path"] == 3 and b[2]["path"] == 2
+    bad = check_labels(X, C0, a[1], b[1])
+    if bad == 0:
+        assert np.array_equal(a[0], b[0])          # integer sums: same labels -> same bits
+    # transform on the fitted centroids: one block, and row batches that are not the whole shard
+    import os
+    import subprocess
+    import sys
+    h = eng.ResidentKMeans()
+    h.upload(X)
+    h.fit(init, 3)
+    C = h.centroids()
+    D = h.transform()
+    h.close()
+    want = lloyd.transform_sq_exact(X, C.astype(np.float64))
+    floor = np.finfo(np.float32).eps * ((X.astype(np.float64) ** 2).sum(1)[:, None] + (C.astype(np.float64) ** 2).sum(1)[None, :])
+    assert (np.abs(D - want) <= 1e-4 * want + 8 * floor).all()
+    code = ("import sys, numpy as np; sys.path.insert(0, %r); import h2o4gpu_b200.engine as e; "
+            "X = np.load(%r); C = np.load(%r); h = e.ResidentKMeans(); h.upload(X); h.set_centroids(C); "
+            "np.save(%r, h.transform())")
+    np.save(tmp_path / "X.npy", X)
+    np.save(tmp_path / "C.npy", C)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, H2O4GPU_KM_TRANSFORM_BATCH_ROWS="12800")
+    subprocess.run([sys.executable, "-c", code % (root, str(tmp_path / "X.npy"), str(tmp_path / "C.npy"),
+                                                  str(tmp_path / "D.npy"))], check=True, env=env)
+    assert np.array_equal(np.load(tmp_path / "D.npy"), D)          # batching changes no value
+
+
+# ---- row widths between the compiled variants of the tensor-core kernels --------------------
+@pytest.mark.parametrize("n,d,k", [(20000, 48, 100), (30000, 100, 17), (20000, 100, 300), (9000, 200, 1000),
+                                   (5000, 36, 129), (7000, 252, 6144)])
+def test_any_row_width_reaches_the_tensor_cores(eng, n, d, k):
+    """16-byte aligned rows of up to 256 columns take the tcgen05 kernel compiled for the next of 32 / 64 /
+    128 / 256 columns (the copy engine zero-fills the missing columns); results as for any other shape."""
+    rng = np.random.default_rng(n + d + k)
+    centers = rng.uniform(-8, 8, (max(k // 3, 5), d))
+    X = (centers[rng.integers(0, centers.shape[0], n)] + rng.standard_normal((n, d))).astype(np.float32)
+    init = X[np.sort(rng.choice(n, k, replace=False))].copy()
+    C = init.astype(np.float64)
+    h = eng.ResidentKMeans(dtype=np.float32)
+    h.upload(X)
+    for _ in range(2):
+        C32 = C.astype(np.float32)
+        Cn, labn, _, moved = lloyd.step(X, C32.astype(np.float64), order="descending")
+        h.fit(C32, 1, flags=eng.FIT_NO_FINAL_ASSIGN)
+        st = h.stats()
+        assert st["path"] == 3
+        check_step(X, C32.astype(np.float64), h.centroids(), h.labels(), Cn, labn, moved, st["relocations"])
+        C = Cn
     h.close()
