@@ -97,21 +97,12 @@ __device__ __forceinline__ unsigned long long gtime_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// try_wait that lets the hardware park the warp for up to `ns` nanoseconds (it wakes
-// as soon as the phase completes), so waiting costs no issue slots.
-__device__ __forceinline__ bool mbar_try_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(ns)
-      : "memory");
-  return ok != 0;
-}
 // Bounded wait.  Returns false when the CTA is aborting (this wait or another one
-// gave up); the caller leaves its loop.
+// gave up); the caller leaves its loop.  The poll is mbarrier.try_wait without a suspend-time
+// hint: the hardware parks the warp for a short, implementation-defined time and wakes it when
+// the phase completes.  With a 20 us hint the wake-up was slow enough to cost the streamed-table
+// kernel a tenth of its time (accumulator hand-overs between the issuer and the epilogue warps are
+// on its critical path); spinning on test_wait instead took issue slots from the working warps.
 // Where the waits of an aborting CTA stood, one record per wait site (code): CTA, the
 // caller's tile counter, the parity waited for, 1 = this wait gave up / 2 = it saw the abort.
 // Read back by the host only to word the error message.
@@ -119,13 +110,19 @@ __device__ int g_wait_diag[16][4];
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
                                           int info = -1) {
-  // parked waits of at most 20 us each; their number (150000 by default: gives up after about 3 s)
-  // sits in the CTA's shared memory behind the abort word, written by the kernel's first thread
+  // the limit (150000 units of 20 us by default: gives up after about 3 s) sits in the CTA's shared
+  // memory behind the abort word, written by the kernel's first thread
   int why = 1;
-  const unsigned int limit = (unsigned int)abort_flag[3];
-  for (unsigned int it = 0; it < limit; ++it) {
-    if (mbar_try_hint(bar, parity, 20000u)) return true;
-    if (*abort_flag) { why = 2; break; }
+  // limit in units of 20 us (kmeans_set_wait_limits), measured on the global timer every 32 polls
+  if (mbar_try(bar, parity)) return true;
+  const unsigned long long lim_ns = (unsigned long long)(unsigned int)abort_flag[3] * 20000ull;
+  const unsigned long long t0 = gtime_ns();
+  for (unsigned int it = 0; it < 0x7fffffffu; ++it) {
+    if (mbar_try(bar, parity)) return true;
+    if ((it & 31u) == 31u) {
+      if (*abort_flag) { why = 2; break; }
+      if (gtime_ns() - t0 > lim_ns) break;
+    }
   }
   if (why == 1) *abort_flag = code;
   g_wait_diag[code & 15][0] = (int)blockIdx.x;

@@ -26,12 +26,7 @@ using namespace km::tc;
 
 constexpr int kNT = 128;        // centroids per tile = accumulator columns
 constexpr int kBigThreads = 512;
-// The centroid panels arrive from L2 in slices of 64 K-columns (hi + lo panels: 32 KB) through a ring of
-// four stages.  A slice is consumed by 12 MMAs (about 770 clocks); with two stages of 128 columns the
-// refill of a stage had only one stage's MMAs (1,540 clocks) to cross the L2 and the tensor pipe waited
-// for it a third of the time (62.8 % active, L2 and crossbar a fifth busy); four stages give the copy
-// three slices of cover for the same shared memory.
-constexpr int kBStages = 4;
+constexpr int kBStages = 2;
 
 // barriers
 enum BBar { X_FULL = 0, X_EMPTY = 1, A_RDY = 2, A_EMP = 4, B_FUL = 6, B_EMP = 6 + kBStages,
@@ -40,7 +35,7 @@ enum BBar { X_FULL = 0, X_EMPTY = 1, A_RDY = 2, A_EMP = 4, B_FUL = 6, B_EMP = 6 
 
 template <int D> struct BigCfg {
   static constexpr int DP = D < 64 ? 64 : D;          // fp16 columns of the centroid panels (padded to 64)
-  static constexpr int KC = 64;                       // K columns per B stage
+  static constexpr int KC = DP < 128 ? DP : 128;      // K columns per B stage
   static constexpr int NKC = DP / KC;                 // B stages per centroid tile
   static constexpr int XC = D < 128 ? D : 128;        // fp32 columns per X chunk
   static constexpr int NXC = D / XC;                  // X chunks per row tile

@@ -100,6 +100,8 @@ struct Shard {
   double* cand_val = nullptr;
   unsigned long long* cand_row = nullptr;
   unsigned int* ticket = nullptr;     // CTAs of the running close_kernel that have finished (zero between launches)
+  FarScratch far{};                   // two-pass selection of the farthest rows (empty-cluster repair)
+  int far_out_cap = 0;
   unsigned char* reloc_rec = nullptr; // several ranks without the push path: this rank's candidate record ...
   unsigned char* reloc_all = nullptr; // ... and the all-gathered ones (host-driven repair)
   size_t reloc_cap = 0;
@@ -249,6 +251,13 @@ int Engine<T>::init(int n_local, const int* devs, int rank0, int world, const vo
     KM_CUDA(km_malloc(&s.sum_partials, 1024 * sizeof(double)));
     KM_CUDA(km_malloc(&s.ticket, sizeof(unsigned int)));
     KM_CUDA(cudaMemset(s.ticket, 0, sizeof(unsigned int)));
+    s.far.cap = 32768;
+    KM_CUDA(km_malloc(&s.far.tmax, (size_t)s.num_sms * 256 * sizeof(double)));
+    KM_CUDA(km_malloc(&s.far.trow, (size_t)s.num_sms * 256 * sizeof(unsigned long long)));
+    KM_CUDA(km_malloc(&s.far.cval, (size_t)s.far.cap * sizeof(double)));
+    KM_CUDA(km_malloc(&s.far.crow, (size_t)s.far.cap * sizeof(unsigned long long)));
+    KM_CUDA(km_malloc(&s.far.counters, 2 * sizeof(unsigned int)));
+    KM_CUDA(km_malloc(&s.far.thr, sizeof(double)));
   }
   if (world > 1) {
     NcclApi* api = NcclApi::get();
@@ -312,6 +321,8 @@ void Engine<T>::destroy() {
     km_free(s.C[0]); km_free(s.C[1]); km_free(s.Cd[0]); km_free(s.Cd[1]); km_free(s.cnorm); km_free(s.shift_k); km_free(s.empties);
     km_free(s.st); km_free(s.cand_val); km_free(s.cand_row); km_free(s.sum_partials);
     km_free(s.ticket); km_free(s.reloc_rec); km_free(s.reloc_all);
+    km_free(s.far.tmax); km_free(s.far.trow); km_free(s.far.cval); km_free(s.far.crow); km_free(s.far.counters);
+    km_free(s.far.thr); km_free(s.far.oval); km_free(s.far.orow);
     km_free(s.shift_log); km_free(s.changed_log); km_free(s.reloc_log); km_free(s.xstat);
     if (s.host_pin) cudaFreeHost(s.host_pin);
     if (s.stream) cudaStreamDestroy(s.stream);
@@ -710,6 +721,13 @@ int Engine<T>::ensure_buffers(int k_) {
       KM_CUDA(km_malloc(&s.cnorm, k_ * sizeof(T)));
       KM_CUDA(km_malloc(&s.shift_k, k_ * sizeof(double)));
       KM_CUDA(km_malloc(&s.empties, k_ * sizeof(int)));
+      if (s.far_out_cap < k_) {
+        km_free(s.far.oval); km_free(s.far.orow);
+        s.far.oval = nullptr; s.far.orow = nullptr;
+        KM_CUDA(km_malloc(&s.far.oval, (size_t)k_ * sizeof(double)));
+        KM_CUDA(km_malloc(&s.far.orow, (size_t)k_ * sizeof(unsigned long long)));
+        s.far_out_cap = k_;
+      }
       s.k_cap = k_;
       s.d_cap = d;
     }

@@ -105,7 +105,8 @@ int Engine<T>::relocate_multi(double scale, int seq, int* n_empty) {
     unsigned char* rp = s.reloc_rec;
     const T* Wp = weighted ? s.w : nullptr;
     const IterState* gate = nullptr;
-    void* args[] = {&Xp, &n, &dd, &lab, &dist, &ee, &id_base, &cv, &cr, &rp, &Wp, &gate};
+    FarScratch fs = s.far;
+    void* args[] = {&Xp, &n, &dd, &lab, &dist, &ee, &id_base, &cv, &cr, &rp, &Wp, &gate, &fs};
     KM_CUDA(cudaLaunchCooperativeKernel((void*)select_far_kernel<T>, dim3(s.num_sms), dim3(256), args, 0, s.stream));
     launches += 2;
   }
@@ -321,7 +322,8 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
         IterState* st = s.st;
         T sc = scale;
         T wsc = (T)w_scale;
-        void* args[] = {&Xp, &n, &dd, &lab, &kk, &dist, &gs, &gc, &em, &st, &cv, &cr, &sc, &Wp, &wsc};
+        FarScratch fs = s.far;
+        void* args[] = {&Xp, &n, &dd, &lab, &kk, &dist, &gs, &gc, &em, &st, &cv, &cr, &sc, &Wp, &wsc, &fs};
         ce = cudaLaunchCooperativeKernel((void*)relocate_kernel<T>, dim3(s.num_sms), dim3(256), args, 0, s.stream);
         ++launches;
       } else {
@@ -329,7 +331,8 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
         unsigned long long id_base = (unsigned long long)(world_rank0 + (int)i) << 40;
         unsigned char* rp = s.push.grec;
         const IterState* gate = s.st;
-        void* args[] = {&Xp, &n, &dd, &lab, &dist, &ee, &id_base, &cv, &cr, &rp, &Wp, &gate};
+        FarScratch fs = s.far;
+        void* args[] = {&Xp, &n, &dd, &lab, &dist, &ee, &id_base, &cv, &cr, &rp, &Wp, &gate, &fs};
         ce = cudaLaunchCooperativeKernel((void*)select_far_kernel<T>, dim3(s.num_sms), dim3(256), args, 0, s.stream);
         if (ce == cudaSuccess) {
           gather_apply_kernel<T><<<1, 256, 0, s.stream>>>(
