@@ -1,11 +1,11 @@
 // Centroid sums for callers that must not allocate.
 //
-// Some callers cannot tolerate a device allocation on their hot path: code that
-// runs between cudaStreamBeginCapture and EndCapture (an allocation there is an
-// error), serving loops whose memory budget is frozen after start-up, and hosts
-// that forbid the implicit device synchronisation a cudaMalloc / cudaFree may
-// cause.  For them this file offers the M-step reduction (per-cluster sums and
-// counts of a labelled shard) with every byte of working memory in one
+// Some callers cannot call cudaMalloc where they call this library: serving loops
+// whose device-memory budget is fixed after start-up (an allocation could fail or
+// evict what the budget promised to others), and hosts that forbid the implicit
+// device-wide synchronisation a cudaMalloc / cudaFree may cause in the middle of
+// their pipeline.  For them this file offers the M-step reduction (per-cluster sums
+// and counts of a labelled shard) with every byte of working memory in one
 // file-scope device array: the call takes device pointers for its inputs and
 // outputs, enqueues five small operations on the caller's stream and returns;
 // it never calls cudaMalloc, cudaFree or any library routine that allocates.
@@ -15,12 +15,13 @@
 //     The array is 229,440 bytes and every GPU that loads the library holds it
 //     until the process exits.
 //   * The first call on a device looks up the array's device address and raises
-//     the kernel's shared-memory limit; make that first call outside any stream
-//     capture.  Later calls do no set-up.
+//     the kernel's shared-memory limit; that first call should come before any
+//     stream capture.  Later calls do no set-up.
 //   * All calls on a device share the array.  It still holds the previous call's
 //     numbers, so each call clears the part it uses first; two calls whose work
-//     overlaps on the GPU (different streams, or graphs replayed concurrently)
-//     race on it and must be serialised by the caller.
+//     overlaps on the GPU (different streams) race on it and must be serialised
+//     by the caller.
+#include <atomic>
 #include <mutex>
 
 #include "km_common.cuh"
@@ -127,16 +128,18 @@ __global__ void na_export_kernel(const unsigned long long* __restrict__ scratch,
 struct NaDevice {
   unsigned long long* scratch = nullptr;  // device address of g_na_scratch on this device
   int num_sms = 0;
-  bool ready = false;
+  std::atomic<bool> ready{false};
 };
 NaDevice g_na_dev[64];
 std::mutex g_na_mutex;
 
-// Once per device, with that device current.
+// Once per device, with that device current; later calls only read the flag.
 int na_setup(int dev, NaDevice** out) {
-  std::lock_guard<std::mutex> lock(g_na_mutex);
   NaDevice& nd = g_na_dev[dev];
-  if (!nd.ready) {
+  *out = &nd;
+  if (nd.ready.load(std::memory_order_acquire)) return KM_OK;
+  std::lock_guard<std::mutex> lock(g_na_mutex);
+  if (!nd.ready.load(std::memory_order_relaxed)) {
     unsigned long long* ptr = nullptr;
     KM_CUDA(cudaGetSymbolAddress((void**)&ptr, g_na_scratch));
     KM_CUDA(cudaDeviceGetAttribute(&nd.num_sms, cudaDevAttrMultiProcessorCount, dev));
@@ -144,9 +147,8 @@ int na_setup(int dev, NaDevice** out) {
     KM_CUDA(cudaFuncSetAttribute(na_accumulate_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max));
     KM_CUDA(cudaFuncSetAttribute(na_accumulate_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max));
     nd.scratch = ptr;
-    nd.ready = true;
+    nd.ready.store(true, std::memory_order_release);
   }
-  *out = &nd;
   return KM_OK;
 }
 

@@ -239,10 +239,10 @@ int kmeans_centroid_sums_f64(int gpu_id, const double* X, const int32_t* labels,
                              size_t cols, int k, double* sums, int64_t* counts);
 
 /* No counterpart in the reference.  Same result as kmeans_centroid_sums_f32 for a
- * shard that already lives on the current device, for callers that must not
- * allocate device memory where they call it: between cudaStreamBeginCapture and
- * EndCapture, in a serving loop whose memory budget is frozen, or where the
- * implicit synchronisation of cudaMalloc / cudaFree is not acceptable.  All
+ * shard that already lives on the current device, for callers that cannot call
+ * cudaMalloc where they call it: a serving loop whose device-memory budget is
+ * fixed after start-up, or a host that does not accept the implicit device-wide
+ * synchronisation of cudaMalloc / cudaFree in the middle of its pipeline.  All
  * working memory is one static device array inside the library (229,440 bytes,
  * held by every GPU that loads the library until the process exits), hence the
  * limit k * cols <= 24576 and k <= 4096; larger sizes return KM_EINVAL.
@@ -251,11 +251,10 @@ int kmeans_centroid_sums_f64(int gpu_id, const double* X, const int32_t* labels,
  * stream).  The work is enqueued on that stream and the call returns without
  * waiting; it calls no cudaMalloc / cudaFree.  Rows whose label is outside [0, k)
  * are skipped; the data must be finite.  The first call on a device looks up
- * the array's address and raises a shared-memory limit: make it outside any
- * stream capture.  Every call on a device uses the same array, which keeps the
+ * the array's address and raises a shared-memory limit: it should come before
+ * any stream capture.  Every call on a device uses the same array, which keeps the
  * previous call's contents until the next call clears them: calls whose GPU
- * work overlaps (other streams, concurrent graph replays) race and must be
- * serialised by the caller. */
+ * work overlaps (other streams) race and must be serialised by the caller. */
 int kmeans_centroid_sums_noalloc_f32(const float* dX, const int32_t* dLabels, size_t rows, size_t cols,
                                      int k, double* dSums, long long* dCounts, void* stream);
 

@@ -4,9 +4,9 @@ Collected last on purpose (file name): if it fails, a run that stops at the firs
 failure has already been through every other test.
 
 Who needs it: callers that may not allocate device memory at the point of the call,
-for instance while a CUDA stream is being captured, in a serving loop whose memory
-is fixed after start-up, or where the synchronisation hidden in cudaMalloc/cudaFree
-would stall other streams.  The test drives it with device pointers only (inputs and
+for instance a serving loop whose memory is fixed after start-up, or a host where the
+synchronisation hidden in cudaMalloc/cudaFree would stall other streams.  The test
+drives it with device pointers only (inputs and
 outputs are torch tensors made beforehand) and checks two consecutive calls, since
 the static scratch array keeps the previous call's numbers until it is cleared.
 """
@@ -23,7 +23,7 @@ def _ordinary(X, labels, k):
     return engine.centroid_sums(X, labels, k)
 
 
-def _no_alloc(lib, X, labels, k):
+def _no_alloc(lib, X, labels, k, check_driver_free=False):
     import torch
     dev = torch.device("cuda", 0)
     dX = torch.from_numpy(X).to(dev)
@@ -32,12 +32,15 @@ def _no_alloc(lib, X, labels, k):
     dC = torch.full((k,), -7, dtype=torch.int64, device=dev)
     torch.cuda.synchronize()
     before = torch.cuda.memory_allocated()
+    free_before = torch.cuda.mem_get_info()[0]      # the driver's view: sees any allocation, not only torch's
     rc = lib.kmeans_centroid_sums_noalloc_f32(ctypes.c_void_p(dX.data_ptr()), ctypes.c_void_p(dL.data_ptr()),
                                               X.shape[0], X.shape[1], k, ctypes.c_void_p(dS.data_ptr()),
                                               ctypes.c_void_p(dC.data_ptr()), None)
     assert rc == 0, lib.kmeans_last_error()
     torch.cuda.synchronize()
     assert torch.cuda.memory_allocated() == before
+    if check_driver_free:
+        assert torch.cuda.mem_get_info()[0] == free_before
     return dS.cpu().numpy(), dC.cpu().numpy()
 
 
@@ -65,7 +68,7 @@ def test_no_alloc_matches_ordinary_entry_point_twice(built_lib):
     X = (np.random.default_rng(5).standard_normal((n, d)) * 2).astype(np.float32)
     labels = np.random.default_rng(6).integers(0, k, n).astype(np.int32)
     a = _no_alloc(lib, X, labels, k)
-    b = _no_alloc(lib, X, labels, k)
+    b = _no_alloc(lib, X, labels, k, check_driver_free=True)   # a warm call leaves the device's free memory as it was
     assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
 
 
