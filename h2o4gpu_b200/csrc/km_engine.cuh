@@ -51,6 +51,39 @@ struct DevGuard {
   }
 };
 
+// Small pinned host blocks (64 bytes: the words the closing kernels publish to the host), kept for
+// the life of the process: pinning and unpinning memory costs about a millisecond per engine, a
+// visible share of a host-pointer call that builds and tears down an engine around one fit.
+struct PinnedWords {
+  std::mutex m;
+  std::vector<double*> free_list;
+  static PinnedWords& get() {
+    static PinnedWords* p = new PinnedWords();   // never destroyed: the CUDA runtime may be gone at exit
+    return *p;
+  }
+  double* take() {
+    {
+      std::lock_guard<std::mutex> lock(m);
+      if (!free_list.empty()) {
+        double* b = free_list.back();
+        free_list.pop_back();
+        return b;
+      }
+    }
+    double* b = nullptr;
+    if (cudaHostAlloc(&b, 8 * sizeof(double), cudaHostAllocPortable) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    return b;
+  }
+  void give(double* b) {
+    if (!b) return;
+    std::lock_guard<std::mutex> lock(m);
+    free_list.push_back(b);
+  }
+};
+
 inline double now_s() {
   return std::chrono::duration<double>(std::chrono::steady_clock::now().time_since_epoch()).count();
 }
@@ -180,6 +213,8 @@ struct Engine : EngineBase {
   int assign_all(int flags);
   int transform_shard(int local, T* out_host, size_t ld);
   int inertia(double* out);
+  int inertia_launch();
+  int inertia_collect(double* out);
   int allreduce_acc();
   int relocate_multi(double scale, int seq, int* n_empty);
   // operand table of the tensor-core kernels as close_kernel fills it (null members: not in use)
@@ -244,7 +279,8 @@ int Engine<T>::init(int n_local, const int* devs, int rank0, int world, const vo
     KM_CUDA(km_malloc(&s.st, sizeof(IterState)));
     KM_CUDA(cudaMemset(s.st, 0, sizeof(IterState)));
     KM_CUDA(km_malloc(&s.xstat, 2 * sizeof(double)));
-    KM_CUDA(cudaMallocHost(&s.host_pin, 8 * sizeof(double)));
+    s.host_pin = PinnedWords::get().take();
+    if (!s.host_pin) KM_FAIL(KM_ENOMEM, "kmeans_create: no pinned host memory");
     std::memset(s.host_pin, 0, 8 * sizeof(double));
     KM_CUDA(km_malloc(&s.cand_val, 1024 * sizeof(double)));
     KM_CUDA(km_malloc(&s.cand_row, 2048 * sizeof(unsigned long long)));   // also the exchange buffer of push_setup
@@ -324,7 +360,8 @@ void Engine<T>::destroy() {
     km_free(s.far.tmax); km_free(s.far.trow); km_free(s.far.cval); km_free(s.far.crow); km_free(s.far.counters);
     km_free(s.far.thr); km_free(s.far.oval); km_free(s.far.orow);
     km_free(s.shift_log); km_free(s.changed_log); km_free(s.reloc_log); km_free(s.xstat);
-    if (s.host_pin) cudaFreeHost(s.host_pin);
+    PinnedWords::get().give(s.host_pin);
+    s.host_pin = nullptr;
     if (s.stream) cudaStreamDestroy(s.stream);
     s.dev = -1;
   }

@@ -468,8 +468,14 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
 // differences, double), all local shards; all-reduced over ranks.
 template <typename T>
 int Engine<T>::inertia(double* out) {
+  KM_TRY(inertia_launch());
+  return inertia_collect(out);
+}
+
+// the kernels of the inertia pass, queued; inertia_collect() waits for them and reads the sum
+template <typename T>
+int Engine<T>::inertia_launch() {
   if (!have_centroids) KM_FAIL(KM_ESTATE, "no centroids set");
-  double total = 0;
   for (auto& s : shards) {
     DevGuard g(s.dev);
     KM_TRY(ensure_dist(s));
@@ -485,6 +491,14 @@ int Engine<T>::inertia(double* out) {
     for (auto& s : shards)
       KM_NCCL(api, api->AllReduce(&s.st->inertia, &s.st->inertia, 1, ncclDouble, ncclSum, s.comm, s.stream));
     KM_NCCL(api, api->GroupEnd());
+  }
+  return KM_OK;
+}
+
+template <typename T>
+int Engine<T>::inertia_collect(double* out) {
+  double total = 0;
+  if (world_size > 1) {
     Shard<T>& s = shards[0];
     DevGuard g(s.dev);
     KM_CUDA(cudaMemcpyAsync(&total, &s.st->inertia, sizeof(double), cudaMemcpyDeviceToHost, s.stream));

@@ -132,28 +132,50 @@ int fit_impl(int verbose, int seed, int gpu_id, int n_gpu, size_t rows, size_t c
   KM_TRY(e->fit(k, max_iter, (double)threshold, init_ptr, flags));
   const double e_fit_s = e->stats.seconds_fit;
   const float e_loop_ms = e->stats.ms_loop;
-  {
-    // what sklearn reports as n_iter_ and inertia_ (the reference leaves inertia_ unset,
-    // src/interface_py/h2o4gpu/solvers/kmeans.py:187): one more pass over X
-    double inertia = -1.0;
-    KM_TRY(e->inertia(&inertia));
-    km::g_last_iterations = e->stats.n_iter_converged > 0 ? e->stats.n_iter_converged : e->stats.iterations;
-    km::g_last_inertia = inertia;
-  }
   bool a1 = false, a2 = false;
   KM_TRY(out_buffer(pred_centroids, (size_t)k * cols, &a1));
   int rc = out_buffer(pred_labels, rows, &a2);
   if (rc != KM_OK) { if (a1) { std::free(*pred_centroids); *pred_centroids = nullptr; } return rc; }
+  // what sklearn reports as n_iter_ and inertia_ (the reference leaves inertia_ unset,
+  // src/interface_py/h2o4gpu/solvers/kmeans.py:187) takes one more pass over X: its kernels are queued
+  // first, and the labels (final: the fit has synchronised its streams) go back to the host on a
+  // stream of their own meanwhile - a copy into pageable memory keeps the calling thread busy
+  rc = e->inertia_launch();
+  std::vector<cudaStream_t> side(e->shards.size(), nullptr);
+  if (rc == KM_OK) {
+    size_t off = 0;
+    for (size_t i = 0; i < e->shards.size(); ++i) {
+      km::Shard<T>& s = e->shards[i];
+      km::DevGuard g(s.dev);
+      if (cudaStreamCreateWithFlags(&side[i], cudaStreamNonBlocking) != cudaSuccess) { cudaGetLastError(); side[i] = nullptr; }
+      cudaError_t ce = cudaMemcpyAsync(*pred_labels + off, s.labels, s.rows * sizeof(int), cudaMemcpyDeviceToHost,
+                                       side[i] ? side[i] : s.stream);
+      if (ce != cudaSuccess) rc = KM_ECUDA;
+      off += s.rows;
+    }
+  }
+  double inertia = -1.0;
+  if (rc == KM_OK) {
+    rc = e->inertia_collect(&inertia);
+    km::g_last_iterations = e->stats.n_iter_converged > 0 ? e->stats.n_iter_converged : e->stats.iterations;
+    km::g_last_inertia = inertia;
+  }
+  for (size_t i = 0; i < e->shards.size(); ++i) {
+    km::Shard<T>& s = e->shards[i];
+    km::DevGuard g(s.dev);
+    cudaError_t ce = cudaStreamSynchronize(side[i] ? side[i] : s.stream);
+    if (side[i]) cudaStreamDestroy(side[i]);
+    if (ce != cudaSuccess && rc == KM_OK) { set_error(std::string("labels to host: ") + cudaGetErrorString(ce)); rc = KM_ECUDA; }
+  }
+  if (rc != KM_OK) {
+    if (a1) { std::free(*pred_centroids); *pred_centroids = nullptr; }
+    if (a2) { std::free(*pred_labels); *pred_labels = nullptr; }
+    return rc;
+  }
   {
     km::Shard<T>& s0 = e->shards[0];
     km::DevGuard g(s0.dev);
     KM_CUDA(cudaMemcpy(*pred_centroids, s0.C[e->cur], (size_t)k * cols * sizeof(T), cudaMemcpyDeviceToHost));
-  }
-  size_t off = 0;
-  for (auto& s : e->shards) {
-    km::DevGuard g(s.dev);
-    KM_CUDA(cudaMemcpy(*pred_labels + off, s.labels, s.rows * sizeof(int), cudaMemcpyDeviceToHost));
-    off += s.rows;
   }
   km::log_msg(verbose, 300, "fit: %d iterations, %.3f s upload, %.3f s fit", e->stats.iterations,
               e->stats.seconds_upload, e->stats.seconds_fit);
