@@ -277,7 +277,9 @@ def roofline_of(args_workload, r, hbm_peak, tensor_peak, peak_kind):
     st = r["stats"]
     alg_bytes = n * (d * 4 + 4)
     a_ms, u_ms = r["assign_ms"], r["update_ms"]
-    top = max(a_ms, u_ms) if st["path"] != 1 else a_ms
+    # the dominant kernel is the one that streams X every iteration: distance + argmin (with the fused
+    # small-k kernel it also forms the sums); the M-step moves only the rows whose label changed
+    top = a_ms
     achieved = alg_bytes / (top * 1e-3) / 1e9
     flops = 2.0 * n * k * d
     # DRAM bytes per row of the dominant kernel from the committed ncu captures (profiles/), taken on
@@ -288,7 +290,7 @@ def roofline_of(args_workload, r, hbm_peak, tensor_peak, peak_kind):
             "peak_tflops": tensor_peak, "frac": 3 * flops / (a_ms * 1e-3) / 1e12 / tensor_peak}
     hbm = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
            "traffic": traffic, "peak_kind": "of " + peak_kind,
-           "kernel": "distance+argmin" if a_ms >= u_ms else "centroid sums",
+           "kernel": "distance+argmin" if st["path"] != 1 else "distance+argmin+sums (fused)",
            "algorithmic_bytes_per_launch": alg_bytes,
            "whole_step_frac": alg_bytes / (r["ms_per_step"] * 1e-3) / 1e9 / hbm_peak}
     if st["path"] == 3 and tens["frac"] > hbm["frac"]:

@@ -58,7 +58,6 @@ constexpr int kAcc = 3;        // TMEM accumulators
 constexpr int kMaxD = 64;
 constexpr int kMaxNPad = 128;
 constexpr int kTmemCols = 512;
-constexpr unsigned long long kWaitLimitNs = 2000000000ULL;  // 2 s (abort drain loops)
 
 enum Bar { FULL = 0, EMPTY = kStages, A_READY = 2 * kStages, A_EMPTY = 2 * kStages + 2,
            ACC_FULL = 2 * kStages + 4, ACC_EMPTY = 2 * kStages + 4 + kAcc, B_FULL = 2 * kStages + 4 + 2 * kAcc,
@@ -92,11 +91,6 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ unsigned long long gtime_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
 // Bounded wait.  Returns false when the CTA is aborting (this wait or another one
 // gave up); the caller leaves its loop.  The poll is mbarrier.try_wait without a suspend-time
 // hint: the hardware parks the warp for a short, implementation-defined time and wakes it when
@@ -113,15 +107,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   // the limit (150000 units of 20 us by default: gives up after about 3 s) sits in the CTA's shared
   // memory behind the abort word, written by the kernel's first thread
   int why = 1;
-  // limit in units of 20 us (kmeans_set_wait_limits), measured on the global timer every 32 polls
+  // The limit (units of 20 us, kmeans_set_wait_limits) is measured on the SM's own cycle counter
+  // (at most 2 GHz: 40,000 cycles per unit) every 32 polls, and a wait only gives up after a minimum
+  // number of polls as well (40 per unit: a tenth of the limit even if a poll took only 50 ns), so
+  // that a single odd timer reading cannot end a wait that has barely begun.
   if (mbar_try(bar, parity)) return true;
-  const unsigned long long lim_ns = (unsigned long long)(unsigned int)abort_flag[3] * 20000ull;
-  const unsigned long long t0 = gtime_ns();
+  const unsigned int units = (unsigned int)abort_flag[3];
+  const long long lim_cycles = (long long)units * 40000ll;
+  const unsigned int min_polls = units < 0x1ffffffu ? units * 40u : 0x7ffffff0u;
+  const long long c0 = clock64();
   for (unsigned int it = 0; it < 0x7fffffffu; ++it) {
     if (mbar_try(bar, parity)) return true;
     if ((it & 31u) == 31u) {
       if (*abort_flag) { why = 2; break; }
-      if (gtime_ns() - t0 > lim_ns) break;
+      if (it > min_polls && clock64() - c0 > lim_cycles) break;
     }
   }
   if (why == 1) *abort_flag = code;
@@ -130,6 +129,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   g_wait_diag[code & 15][2] = (int)parity;
   g_wait_diag[code & 15][3] = why;
   return false;
+}
+
+// Wait of an aborting CTA for work it has already issued (TMA copies, MMAs) to land: that work signals
+// the barrier on its own, so this only returns early after about two seconds of SM cycles.
+__device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
+  const long long c0 = clock64();
+  for (unsigned int it = 0; it < 0x7fffffffu; ++it) {
+    if (mbar_try(bar, parity)) return;
+    if ((it & 1023u) == 1023u && it > 4000000u && clock64() - c0 > 4000000000ll) return;
+  }
 }
 
 // One warp waits on an mbarrier that nothing ever arrives at: the give-up path of mbar_wait,
@@ -437,9 +446,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         mbar_wait(bar(B_FULL), 0, abort_flag, 0);
         const int lo = (i > kStages) ? i - kStages : 0;
         for (int j = lo; j < i; ++j) {
-          const unsigned long long t0 = gtime_ns();
-          while (!mbar_try(bar(FULL + j % kStages), (uint32_t)(j / kStages) & 1u))
-            if (gtime_ns() - t0 > kWaitLimitNs) break;
+          mbar_drain(bar(FULL + j % kStages), (uint32_t)(j / kStages) & 1u);
         }
       }
     }
@@ -507,9 +514,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       }
       if (!ok && i >= 2 + grp) {
         // aborting: the MMAs already issued must retire before TMEM is freed
-        const unsigned long long t0 = gtime_ns();
-        while (!mbar_try(bar(ACC_FULL + last_acc), last_ph))
-          if (gtime_ns() - t0 > kWaitLimitNs) break;
+        mbar_drain(bar(ACC_FULL + last_acc), last_ph);
       }
     }
   } else if (warp == 3) {
@@ -529,8 +534,11 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       const int s = i % kStages;
       const uint32_t ph = (uint32_t)(i / kStages) & 1u;
       const uint32_t phb = (uint32_t)(i >> 1) & 1u;
-      ok = mbar_wait(bar(FULL + s), ph, abort_flag, 5, i);
-      if (ok && i >= 2) ok = mbar_wait(bar(A_EMPTY + grp), phb ^ 1u, abort_flag, 6, i);
+      // The A buffer first: its release (MMAs of this group's tile i - 2 retired) implies that tile i - 5,
+      // the previous user of this stage and a tile of the OTHER group, has been consumed, so the stage's
+      // barrier has left that phase - a one-bit parity could not tell it from the one waited for here.
+      if (i >= 2) ok = mbar_wait(bar(A_EMPTY + grp), phb ^ 1u, abort_flag, 6, i);
+      if (ok) ok = mbar_wait(bar(FULL + s), ph, abort_flag, 5, i);
       ok = __all_sync(0xffffffffu, ok);  // the tcgen05.st below needs the whole warp
       if (!ok) break;
       tc_fence_after();

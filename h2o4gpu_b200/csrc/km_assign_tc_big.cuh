@@ -31,7 +31,7 @@ constexpr int kBStages = 2;
 // barriers
 enum BBar { X_FULL = 0, X_EMPTY = 1, A_RDY = 2, A_EMP = 4, B_FUL = 6, B_EMP = 6 + kBStages,
             AC_FUL = 6 + 2 * kBStages, AC_EMP = 8 + 2 * kBStages, PT_FUL = 10 + 2 * kBStages,
-            PT_EMP = 11 + 2 * kBStages, NBARS = 12 + 2 * kBStages };
+            PT_EMP = 11 + 2 * kBStages, DRAIN = 12 + 2 * kBStages, NBARS = 13 + 2 * kBStages };
 
 template <int D> struct BigCfg {
   static constexpr int DP = D < 64 ? 64 : D;          // fp16 columns of the centroid panels (padded to 64)
@@ -124,6 +124,7 @@ assign_tc_big_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     for (int s = 0; s < kBStages; ++s) { mbar_init(bar(B_FUL + s), 1); mbar_init(bar(B_EMP + s), 1); }
     mbar_init(bar(PT_FUL), 128);
     mbar_init(bar(PT_EMP), 128);
+    mbar_init(bar(DRAIN), 1);
     *abort_flag = 0;
     abort_flag[3] = (int)wait_iters;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -158,9 +159,7 @@ assign_tc_big_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         }
       }
       if (!ok && xi > 0) {
-        const unsigned long long t0 = gtime_ns();
-        while (!mbar_try(bar(X_FULL), (uint32_t)(xi - 1) & 1u))
-          if (gtime_ns() - t0 > kWaitLimitNs) break;
+        mbar_drain(bar(X_FULL), (uint32_t)(xi - 1) & 1u);
       }
     }
   } else if (warp == 2) {
@@ -188,9 +187,7 @@ assign_tc_big_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       if (!ok) {
         const int lo = (bs > kBStages) ? bs - kBStages : 0;
         for (int j = lo; j < bs; ++j) {
-          const unsigned long long t0 = gtime_ns();
-          while (!mbar_try(bar(B_FUL + j % kBStages), (uint32_t)(j / kBStages) & 1u))
-            if (gtime_ns() - t0 > kWaitLimitNs) break;
+          mbar_drain(bar(B_FUL + j % kBStages), (uint32_t)(j / kBStages) & 1u);
         }
       }
     }
@@ -199,8 +196,6 @@ assign_tc_big_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     if (lane == 0) {
       bool ok = true;
       int it = 0, bs = 0, j = 0;
-      int last_acc = -1;
-      uint32_t last_ph = 0;
       // constant upper word of every centroid-panel descriptor
       const uint32_t desc_hi = (uint32_t)(smem_desc_sw128(0) >> 32);
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
@@ -234,16 +229,16 @@ assign_tc_big_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
           }
           if (!ok) break;
           tc_commit(bar(AC_FUL + ac));
-          last_acc = ac;
-          last_ph = (uint32_t)(j >> 1) & 1u;
         }
         if (ok) tc_commit(bar(A_EMP + a));
       }
-      if (!ok && last_acc >= 0) {
-        const unsigned long long t0 = gtime_ns();
-        while (!mbar_try(bar(AC_FUL + last_acc), last_ph))
-          if (gtime_ns() - t0 > kWaitLimitNs) break;
+      if (!ok) {
+        // aborting, possibly in the middle of a centroid tile: every MMA issued so far must retire before
+        // TMEM is freed
+        tc_commit(bar(DRAIN));
+        mbar_drain(bar(DRAIN), 0);
       }
+
     }
   } else if (warp == 3) {
     // spare

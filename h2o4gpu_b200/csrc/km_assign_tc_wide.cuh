@@ -38,13 +38,13 @@ constexpr uint32_t kPanelBytes = kNPad * 128;               // one fp16 panel of
 
 enum WBar { W_FULL = 0, W_EMPTY = kMaxStages, W_ARDY = 2 * kMaxStages, W_AEMP = 2 * kMaxStages + kNA,
             W_ACF = 2 * kMaxStages + 2 * kNA, W_ACE = 2 * kMaxStages + 2 * kNA + 2, W_BFUL = 2 * kMaxStages + 2 * kNA + 4,
-            W_NBARS = 2 * kMaxStages + 2 * kNA + 5 };
+            W_DRAIN = 2 * kMaxStages + 2 * kNA + 5, W_NBARS = 2 * kMaxStages + 2 * kNA + 6 };
 
 inline size_t wide_smem_bytes(int n_chunks, int stages) {
   return 1024 + (size_t)2 * n_chunks * kPanelBytes + (size_t)stages * kStageBytes + kNPad * 4 + W_NBARS * 8 + 64;
 }
 
-// n_chunks = ceil(d / 64); stages: X ring depth (4 or 5, whatever shared memory allows)
+// n_chunks = ceil(d / 64); stages: X ring depth, even (4 or 2: a stage always serves the same converter group)
 // out != nullptr: transform - out[j * ld_out + (row - row0)] = |xn + score_j|, labels untouched
 __global__ void __launch_bounds__(kWThreads, 1)
 assign_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmBhi,
@@ -77,6 +77,7 @@ assign_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     for (int b = 0; b < kNA; ++b) { mbar_init(bar(W_ARDY + b), 128); mbar_init(bar(W_AEMP + b), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(bar(W_ACF + a), 1); mbar_init(bar(W_ACE + a), 128); }
     mbar_init(bar(W_BFUL), 1);
+    mbar_init(bar(W_DRAIN), 1);
     *abort_flag = 0;
     abort_flag[3] = (int)wait_iters;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -123,9 +124,7 @@ assign_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         mbar_wait(bar(W_BFUL), 0, abort_flag, 0);
         const int lo = (c > stages) ? c - stages : 0;
         for (int j = lo; j < c; ++j) {
-          const unsigned long long t0 = gtime_ns();
-          while (!mbar_try(bar(W_FULL + j % stages), (uint32_t)(j / stages) & 1u))
-            if (gtime_ns() - t0 > kWaitLimitNs) break;
+          mbar_drain(bar(W_FULL + j % stages), (uint32_t)(j / stages) & 1u);
         }
       }
     }
@@ -134,8 +133,6 @@ assign_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     if (lane == 0) {
       bool ok = mbar_wait(bar(W_BFUL), 0, abort_flag, 2);
       int c = 0, i = 0;
-      int last_acc = -1;
-      uint32_t last_ph = 0;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++i) {
         const int a = i & 1;
         if (i >= 2) ok = mbar_wait(bar(W_ACE + a), (uint32_t)((i >> 1) - 1) & 1u, abort_flag, 4, i);
@@ -161,14 +158,12 @@ assign_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         }
         if (!ok) break;
         tc_commit(bar(W_ACF + a));
-        last_acc = a;
-        last_ph = (uint32_t)(i >> 1) & 1u;
       }
-      if (!ok && last_acc >= 0) {
-        // aborting: the MMAs already issued must retire before TMEM is freed
-        const unsigned long long t0 = gtime_ns();
-        while (!mbar_try(bar(W_ACF + last_acc), last_ph))
-          if (gtime_ns() - t0 > kWaitLimitNs) break;
+      if (!ok) {
+        // aborting, possibly in the middle of a tile: every MMA issued so far must retire before TMEM is
+        // freed and the CTA's shared memory goes away
+        tc_commit(bar(W_DRAIN));
+        mbar_drain(bar(W_DRAIN), 0);
       }
     }
   } else if (warp < 4) {
@@ -277,7 +272,10 @@ assign_tc_wide_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         const float tol = split_tolerance(tol_rel, tol_floor, xn, cn_max, sx, sxsb);
         if (amb_rows != nullptr && !(second - best > tol)) {
           const unsigned int pos = atomicAdd(&st->amb_count, 1u);
-          amb_rows[pos] = (unsigned int)row;
+          // (a row is listed at most once per launch, so the list cannot pass n entries; checked all the
+          // same: an entry beyond the list's end would be a write outside the buffer)
+          if (pos < n) amb_rows[pos] = (unsigned int)row;
+          else atomicMax(&st->error, 31);
         } else {
           changed += (old_label != bidx);
           labels[row] = bidx;

@@ -343,10 +343,15 @@ struct WidePlan {
   }
 };
 
-// ring depth for d columns: as deep as shared memory allows, 3 to 5 stages
+// Ring depth for d columns: four stages, or two when shared memory is short.  EVEN on purpose: chunks
+// alternate between the two converter groups, so with an even depth a stage always serves the same
+// group and every "stage full" barrier has one waiter that takes its phases in order.  With an odd
+// depth the two groups would share a stage's barrier without being ordered against each other, and a
+// one-bit phase parity cannot tell "the phase I wait for" from "the phase before the previous one":
+// a group that ran ahead of a late copy took the stage early (a device fault at 2e6 rows x 784).
 inline int wide_stages(int d) {
   const int n_chunks = (d + kChunk - 1) / kChunk;
-  for (int s = kMaxStages; s >= 3; --s)
+  for (int s = 4; s >= 2; s -= 2)
     if (wide_smem_bytes(n_chunks, s) <= (size_t)227 * 1024) return s;
   return 0;
 }
