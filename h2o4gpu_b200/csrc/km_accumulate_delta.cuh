@@ -118,14 +118,24 @@ delta_accumulate_kernel(const T* __restrict__ X, size_t n, int d, const int* __r
 // dense layout (16 sums per line) the drain alone took longer than the netting.
 // fold_flush_kernel adds the padded array into the dense sums and clears it.
 constexpr int kFlushPad = 16;
-constexpr int kDeltaThreads = 512;    // two CTAs per SM: room for the registers of a prefetched step
+constexpr int kDeltaThreads = 512;    // two CTAs per SM
 constexpr int kDeltaChunk = 32768;   // rows between two drains: the int32 accumulators hold 2^15 rows of 2^15-sized pieces
+constexpr int kDeltaStepRows = (kDeltaThreads / 32) * 128;   // rows a CTA scans between two passes over its list
 
 template <typename T>
 inline size_t delta_smem_bytes(int k, int d) {
-  return (size_t)Fixed<T>::NP * k * d * sizeof(int) + (size_t)2 * k * sizeof(int) + 16;
+  const size_t acc = (size_t)Fixed<T>::NP * k * d * sizeof(int) + (size_t)2 * k * sizeof(int);
+  return (acc + 15) / 16 * 16 + (size_t)kDeltaStepRows * sizeof(uint2);
 }
 
+// A CTA alternates between two phases over steps of kDeltaStepRows rows.  Scan: every warp compares
+// the two label arrays for 128 rows (one 16-byte load per lane and array, the next step's loads
+// already in flight) and appends the rows that moved - offset, new and old label - to a list in
+// shared memory.  Apply: the list is cut into items of one row segment each (the lpr lanes of a group
+// times V columns) that the warps take in turn, two items per group in flight; a wide row is thus
+// spread over several warps, and the moved rows of a step over all of them, wherever they sat in the
+// step.  (Before, a warp worked through the moved rows of its own 256 rows one after the other:
+// with 784 columns and 8 % of the labels moving that was 0.15 ms for 250,000 rows.)
 template <typename T, int V>
 __global__ void __launch_bounds__(kDeltaThreads, 2)
 delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict__ labels,
@@ -138,12 +148,14 @@ delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int
   extern __shared__ __align__(16) unsigned char smem_raw[];
   int* acc = reinterpret_cast<int*>(smem_raw);      // [NP][k][d]
   int* cnt = acc + (size_t)NP * k * d;              // [2][k]: units, then units * 2^15 (sample weights)
+  uint2* list = reinterpret_cast<uint2*>(smem_raw + (((size_t)NP * k * d + 2 * k) * sizeof(int) + 15) / 16 * 16);
   __shared__ int s_touched;                         // rows netted since the last drain
+  __shared__ int s_list_n[2];                       // entries of the list, by parity of the step
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
   constexpr int NWARP = kDeltaThreads / 32;
-  static_assert(kDeltaChunk % (NWARP * 256) == 0, "whole 256-row steps per warp and chunk");
+  static_assert(kDeltaChunk % kDeltaStepRows == 0, "whole steps per chunk");
   const int dv = d / V;
   const size_t pstride = (size_t)k * d;
   int lpr = 1;
@@ -151,6 +163,7 @@ delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int
   const int groups = 32 / lpr;
   const int g = lane / lpr;
   const int l = lane % lpr;
+  const int nseg = (dv + lpr - 1) / lpr;
 
   size_t per = (n + gridDim.x - 1) / gridDim.x;
   per = (per + 31) / 32 * 32;
@@ -159,107 +172,102 @@ delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int
 
   for (int i = tid; i < NP * k * d; i += kDeltaThreads) acc[i] = 0;
   for (int i = tid; i < 2 * k; i += kDeltaThreads) cnt[i] = 0;
-  if (tid == 0) s_touched = 0;
+  if (tid == 0) { s_touched = 0; s_list_n[0] = 0; s_list_n[1] = 0; }
   __syncthreads();
 
-  for (size_t c0 = r_begin; c0 < r_end; c0 += kDeltaChunk) {
-    const size_t c1 = min(r_end, c0 + (size_t)kDeltaChunk);
-    // a warp takes 256 rows per step, eight per lane, all label loads in flight together
-    // (c0 is a multiple of 32 rows, so the 16-byte loads are aligned); between two drains the
-    // warps run free of one another
-    auto load_step = [&](size_t wb, int (&nw)[8], int (&od)[8]) {
+  // labels of this lane's four rows of a step (r_begin is a multiple of 32 rows: aligned 16-byte loads)
+  auto load_step = [&](size_t sb, int (&nw)[4], int (&od)[4]) {
+    const size_t r4 = sb + (size_t)warp * 128 + lane * 4;
+    if (r4 + 3 < r_end) {
+      const int4 a = *reinterpret_cast<const int4*>(labels + r4);
+      const int4 b = *reinterpret_cast<const int4*>(prev + r4);
+      nw[0] = a.x; nw[1] = a.y; nw[2] = a.z; nw[3] = a.w;
+      od[0] = b.x; od[1] = b.y; od[2] = b.z; od[3] = b.w;
+    } else {
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const size_t r4 = wb + h * 128 + lane * 4;
-        if (r4 + 3 < c1) {
-          const int4 a = *reinterpret_cast<const int4*>(labels + r4);
-          const int4 b = *reinterpret_cast<const int4*>(prev + r4);
-          nw[4 * h + 0] = a.x; nw[4 * h + 1] = a.y; nw[4 * h + 2] = a.z; nw[4 * h + 3] = a.w;
-          od[4 * h + 0] = b.x; od[4 * h + 1] = b.y; od[4 * h + 2] = b.z; od[4 * h + 3] = b.w;
-        } else {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const bool in = r4 + j < c1;
-            nw[4 * h + j] = in ? labels[r4 + j] : -1;
-            od[4 * h + j] = in ? prev[r4 + j] : -1;
-          }
-        }
+      for (int j = 0; j < 4; ++j) {
+        const bool in = r4 + j < r_end;
+        nw[j] = in ? labels[r4 + j] : -1;
+        od[j] = in ? prev[r4 + j] : -1;
       }
-    };
-    int nwn[8], odn[8];
-    {
-      const size_t wb0 = c0 + (size_t)warp * 256;
-      if (wb0 < c1) load_step(wb0, nwn, odn);
     }
-    for (size_t wb = c0 + (size_t)warp * 256; wb < c1; wb += (size_t)NWARP * 256) {
-    int nw[8], od[8];
+  };
+  int nwn[4], odn[4];
+  if (r_begin < r_end) load_step(r_begin, nwn, odn);
+  int parity = 0;
+  int since_drain = 0;
+
+  for (size_t sb = r_begin; sb < r_end; sb += kDeltaStepRows, parity ^= 1) {
+    // ---- scan ----
+    int nw[4], od[4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { nw[j] = nwn[j]; od[j] = odn[j]; }
-    {
-      // the next step's labels are requested before this step's rows are worked on
-      const size_t wbn = wb + (size_t)NWARP * 256;
-      if (wbn < c1) load_step(wbn, nwn, odn);
-    }
-    // which of the eight label pairs of every lane moved: lane j keeps the ballot of pair j, so
-    // that the loop over the pairs below need not be unrolled (its body is long, and eight copies
-    // of it made the kernel wait for instruction fetches more than for memory)
-    unsigned int my_ballot = 0;
-    bool any = false;
+    for (int j = 0; j < 4; ++j) { nw[j] = nwn[j]; od[j] = odn[j]; }
+    if (sb + kDeltaStepRows < r_end) load_step(sb + kDeltaStepRows, nwn, odn);
+    const unsigned int off0 = (unsigned int)(warp * 128 + lane * 4);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const unsigned int m = __ballot_sync(0xffffffffu, nw[j] != od[j]);
-      if (lane == j) my_ballot = m;
-      any |= (m != 0);
-    }
-    if (any) {
-#pragma unroll 1
-      for (int j = 0; j < 8; ++j) {
-        unsigned int mask = __shfl_sync(0xffffffffu, my_ballot, j);
-        if (mask == 0) continue;
-        const size_t jb = wb + (j >> 2) * 128 + (j & 3);   // row of lane 0 for this pair; lane s holds jb + 4 s
-        if (lane == 0) atomicAdd(&s_touched, __popc(mask));
-        while (mask) {
-          const unsigned int src = __fns(mask, 0, g + 1);   // lane of this group's row
-          const bool have = (src != 0xffffffffu);
-          if (have) {
-            // the two labels are read again (they are in L1) rather than indexed out of registers
-            const size_t row = jb + (size_t)src * 4;
-            const int to = labels[row], from = prev[row];
-            const bool to_ok = (unsigned)to < (unsigned)k, from_ok = (unsigned)from < (unsigned)k;
-            const T* xr = X + row * (size_t)d;
-            const T w = W ? W[row] : (T)1;
-            for (int idx = l; idx < dv; idx += lpr) {
-              T x[V], y[V];
-              VecLoad<T, V>::ld(xr + (size_t)idx * V, x);
-              if (W) {
-#pragma unroll
-                for (int e = 0; e < V; ++e) x[e] *= w;
-              }
-#pragma unroll
-              for (int e = 0; e < V; ++e) y[e] = -x[e];
-              if (to_ok) add_vec_fixed<T, V, NP>(acc + (size_t)to * d, pstride, dv, idx, g & (V - 1), x, scale);
-              if (from_ok) add_vec_fixed<T, V, NP>(acc + (size_t)from * d, pstride, dv, idx, g & (V - 1), y, scale);
-            }
-            if (l == 0) {
-              int pw[2] = {0, 1};
-              if (W) split_pieces<2>(w, wscale, pw);
-              if (to_ok) { atomicAdd(&cnt[to], pw[1]); if (pw[0]) atomicAdd(&cnt[k + to], pw[0]); }
-              if (from_ok) { atomicAdd(&cnt[from], -pw[1]); if (pw[0]) atomicAdd(&cnt[k + from], -pw[0]); }
-            }
-          }
-          for (int i = 0; i < groups && mask; ++i) mask &= mask - 1;
-        }
+    for (int j = 0; j < 4; ++j) {
+      const bool moved = nw[j] != od[j];
+      const unsigned int mask = __ballot_sync(0xffffffffu, moved);
+      if (mask == 0) continue;
+      int base = 0;
+      if (lane == 0) base = atomicAdd(&s_list_n[parity], __popc(mask));
+      base = __shfl_sync(0xffffffffu, base, 0);
+      if (moved) {
+        const unsigned int to = (unsigned)nw[j] < (unsigned)k ? (unsigned)nw[j] : 0xffffu;
+        const unsigned int from = (unsigned)od[j] < (unsigned)k ? (unsigned)od[j] : 0xffffu;
+        list[base + __popc(mask & ((1u << lane) - 1u))] = make_uint2(off0 + j, (to << 16) | from);
+        prev[sb + off0 + j] = nw[j];
       }
-      // the snapshot follows once every group has read the old labels
-      __syncwarp();
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (nw[j] != od[j]) prev[wb + (j >> 2) * 128 + lane * 4 + (j & 3)] = nw[j];
-    }
     }
     __syncthreads();
-    // every piece is at most 2^15 in magnitude and a chunk has 2^15 rows: drain after each
-    {
+    const int n_list = s_list_n[parity];
+    if (tid == 0) { s_list_n[parity ^ 1] = 0; s_touched += n_list; }
+    // ---- apply ----
+    const int items = n_list * nseg;
+    for (int it0 = warp * groups; it0 < items; it0 += 2 * NWARP * groups) {
+      T x[2][V];
+      uint2 en[2];
+      int idx[2];
+      bool have[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int it = it0 + u * NWARP * groups + g;
+        have[u] = it < items;
+        idx[u] = 0;
+        en[u] = make_uint2(0u, 0u);
+        if (have[u]) {
+          const int e = (nseg == 1) ? it : it / nseg;
+          idx[u] = (it - e * nseg) * lpr + l;
+          en[u] = list[e];
+          have[u] = idx[u] < dv;
+        }
+        if (have[u]) VecLoad<T, V>::ld(X + (sb + en[u].x) * (size_t)d + (size_t)idx[u] * V, x[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (!have[u]) continue;
+        const unsigned int to = en[u].y >> 16, from = en[u].y & 0xffffu;
+        const bool to_ok = to != 0xffffu, from_ok = from != 0xffffu;
+        const T w = W ? W[sb + en[u].x] : (T)1;
+        if (W) {
+#pragma unroll
+          for (int e = 0; e < V; ++e) x[u][e] *= w;
+        }
+        move_vec_fixed<T, V, NP>(to_ok ? acc + (size_t)to * d : nullptr, from_ok ? acc + (size_t)from * d : nullptr,
+                                 pstride, dv, idx[u], g & (V - 1), x[u], scale);
+        if (idx[u] == 0) {
+          int pw[2] = {0, 1};
+          if (W) split_pieces<2>(w, wscale, pw);
+          if (to_ok) { atomicAdd(&cnt[to], pw[1]); if (pw[0]) atomicAdd(&cnt[k + to], pw[0]); }
+          if (from_ok) { atomicAdd(&cnt[from], -pw[1]); if (pw[0]) atomicAdd(&cnt[k + from], -pw[0]); }
+        }
+      }
+    }
+    __syncthreads();
+    since_drain += kDeltaStepRows;
+    // every piece is at most 2^15 in magnitude: drain after 2^15 rows at the latest, and at the end
+    if (since_drain >= kDeltaChunk || sb + kDeltaStepRows >= r_end) {
+      since_drain = 0;
       if (s_touched > 0) {
         for (int i = tid; i < k * d; i += kDeltaThreads) {
           const int c = i / d;

@@ -46,6 +46,13 @@ inline bool sorted_accumulate_plan(size_t rows, int d, int k, int num_sms, size_
   tile = std::min<size_t>(tile, p->smem_acc ? 8192 : 32768);
   tile = tile / 32 * 32;
   if (tile < 1024) return false;
+  // whole waves of equal tiles: with the largest tile the last wave is ragged (C2: 4.1 waves cost
+  // five) and a small shard leaves most SMs without a tile (250,000 rows of 784 columns: 56 tiles)
+  const size_t slots = (size_t)num_sms * (p->smem_acc ? 2 : 1);
+  const size_t waves = std::max<size_t>(1, (rows + slots * tile - 1) / (slots * tile));
+  size_t even = (rows + waves * slots - 1) / (waves * slots);
+  even = std::max<size_t>((even + 31) / 32 * 32, 256);
+  tile = std::min(tile, even);
   p->tile_rows = (int)tile;
   p->smem_bytes = fixed + (p->smem_acc ? acc_bytes : 0) + tile * sizeof(unsigned);
   size_t tiles = (rows + tile - 1) / tile;

@@ -241,7 +241,15 @@ struct Engine : EngineBase {
   void launch_rowdist(Shard<T>& s, int force) {
     constexpr int V = VecOf<T>::N;
     const double* cd = std::is_same<T, double>::value ? reinterpret_cast<const double*>(s.C[cur]) : s.Cd[cur];
-    if (vec_ok(s))
+    const size_t table_bytes = (size_t)k * d * sizeof(double);
+    if (vec_ok(s) && table_bytes <= (size_t)96 * 1024) {
+      // small tables: gather from a copy in shared memory, as many CTAs per SM as fit beside it
+      cudaFuncSetAttribute(rowdist_kernel<T, V, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      int per_sm = (int)((size_t)200 * 1024 / (table_bytes + 1024));
+      per_sm = per_sm > 8 ? 8 : (per_sm < 1 ? 1 : per_sm);
+      rowdist_kernel<T, V, true><<<s.num_sms * per_sm, 256, table_bytes, s.stream>>>(s.X, s.rows, d, s.labels, cd,
+                                                                                    s.dist, s.st, force, k);
+    } else if (vec_ok(s))
       rowdist_kernel<T, V><<<s.num_sms * 8, 256, 0, s.stream>>>(s.X, s.rows, d, s.labels, cd, s.dist, s.st, force);
     else
       rowdist_kernel<T, 1><<<s.num_sms * 8, 256, 0, s.stream>>>(s.X, s.rows, d, s.labels, cd, s.dist, s.st, force);

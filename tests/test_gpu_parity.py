@@ -318,12 +318,22 @@ def test_deterministic_across_runs(eng):
 @pytest.mark.parametrize("dtype,cfg,kw,iters", [(np.float32, "c2", dict(n=60000), 12),
                                                 (np.float64, "c2", dict(n=30000), 10),
                                                 (np.float32, "c3", dict(n=30000, k=300), 8),
-                                                (np.float32, "c5", dict(n=8000, k=512), 6)])
+                                                (np.float32, "c5", dict(n=8000, k=512), 6),
+                                                # wide rows: a moved row is spread over several warps;
+                                                # overlapping blobs keep 0.03-10 % of the labels moving
+                                                (np.float32, "wide", dict(n=20011, d=784, k=10, scale=0.15), 10),
+                                                (np.float32, "wide", dict(n=3001, d=1000, k=12, scale=0.12), 10)])
 def test_incremental_sums_equal_full_recompute_bitwise(eng, dtype, cfg, kw, iters):
     """The M-step that moves only the rows whose label changed gives the same integers as a
     full pass: centroids and labels of every iteration count agree bit for bit."""
     from h2o4gpu_b200 import synth
-    X, init, _ = getattr(synth, cfg)(**kw)
+    if cfg == "wide":
+        rng = np.random.default_rng(5)
+        centers = kw["scale"] * rng.standard_normal((kw["k"], kw["d"]))
+        X = (centers[rng.integers(0, kw["k"], kw["n"])] + rng.standard_normal((kw["n"], kw["d"]))).astype(np.float32)
+        init = X[:kw["k"]].copy()
+    else:
+        X, init, _ = getattr(synth, cfg)(**kw)
     X = X.astype(dtype)
     init = init.astype(dtype)
     outs = []
