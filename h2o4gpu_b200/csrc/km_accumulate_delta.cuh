@@ -249,12 +249,15 @@ delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int
         const unsigned int to = en[u].y >> 16, from = en[u].y & 0xffffu;
         const bool to_ok = to != 0xffffu, from_ok = from != 0xffffu;
         const T w = W ? W[sb + en[u].x] : (T)1;
+        T y[V];
         if (W) {
 #pragma unroll
           for (int e = 0; e < V; ++e) x[u][e] *= w;
         }
-        move_vec_fixed<T, V, NP>(to_ok ? acc + (size_t)to * d : nullptr, from_ok ? acc + (size_t)from * d : nullptr,
-                                 pstride, dv, idx[u], g & (V - 1), x[u], scale);
+#pragma unroll
+        for (int e = 0; e < V; ++e) y[e] = -x[u][e];
+        if (to_ok) add_vec_fixed<T, V, NP>(acc + (size_t)to * d, pstride, dv, idx[u], g & (V - 1), x[u], scale);
+        if (from_ok) add_vec_fixed<T, V, NP>(acc + (size_t)from * d, pstride, dv, idx[u], g & (V - 1), y, scale);
         if (idx[u] == 0) {
           int pw[2] = {0, 1};
           if (W) split_pieces<2>(w, wscale, pw);

@@ -203,34 +203,6 @@ __device__ __forceinline__ void add_vec_fixed(int* a0, size_t pstride, int dv, i
     for (int q = 0; q < NP; ++q) atomicAdd(a + q * pstride, p[q]);
   }
 }
-// Moves x[0..V) from the cluster at a_from to the cluster at a_to (either may be null): the pieces
-// are formed once and added to one, subtracted from the other (rint is odd, so the pieces of -x are
-// minus those of x - the same integers as adding -x).
-template <typename T, int V, int NP>
-__device__ __forceinline__ void move_vec_fixed(int* a_to, int* a_from, size_t pstride, int dv, int c4, int rot,
-                                               const T (&x)[V], T scale) {
-  T y[V];
-#pragma unroll
-  for (int e = 0; e < V; ++e) y[e] = x[e];
-  if (V == 4) {
-    if (rot & 1) { T t = y[0]; y[0] = y[1]; y[1] = y[2]; y[2] = y[3]; y[3] = t; }
-    if (rot & 2) { T t = y[0]; y[0] = y[2]; y[2] = t; t = y[1]; y[1] = y[3]; y[3] = t; }
-  } else if (V == 2) {
-    if (rot & 1) { T t = y[0]; y[0] = y[1]; y[1] = t; }
-  }
-#pragma unroll
-  for (int ee = 0; ee < V; ++ee) {
-    const int e = (ee + rot) & (V - 1);
-    int p[NP];
-    split_pieces<NP>(y[ee], scale, p);
-    const int off = e * dv + c4;
-#pragma unroll
-    for (int q = 0; q < NP; ++q) {
-      if (a_to) atomicAdd(a_to + off + q * pstride, p[q]);
-      if (a_from) atomicSub(a_from + off + q * pstride, p[q]);
-    }
-  }
-}
 // column of position `pos`
 __device__ __forceinline__ int pos_to_col(int pos, int dv, int V) { return (pos % dv) * V + pos / dv; }
 
