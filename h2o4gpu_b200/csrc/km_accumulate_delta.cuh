@@ -120,22 +120,25 @@ delta_accumulate_kernel(const T* __restrict__ X, size_t n, int d, const int* __r
 constexpr int kFlushPad = 16;
 constexpr int kDeltaThreads = 512;    // two CTAs per SM
 constexpr int kDeltaChunk = 32768;   // rows between two drains: the int32 accumulators hold 2^15 rows of 2^15-sized pieces
-constexpr int kDeltaStepRows = (kDeltaThreads / 32) * 128;   // rows a CTA scans between two passes over its list
+constexpr int kDeltaStepRows = (kDeltaThreads / 32) * 128;   // rows a CTA scans in one step
+constexpr int kDeltaListCap = 2 * kDeltaStepRows;            // entries of the moved-row list
 
 template <typename T>
 inline size_t delta_smem_bytes(int k, int d) {
   const size_t acc = (size_t)Fixed<T>::NP * k * d * sizeof(int) + (size_t)2 * k * sizeof(int);
-  return (acc + 15) / 16 * 16 + (size_t)kDeltaStepRows * sizeof(uint2);
+  return (acc + 15) / 16 * 16 + (size_t)kDeltaListCap * sizeof(uint2);
 }
 
-// A CTA alternates between two phases over steps of kDeltaStepRows rows.  Scan: every warp compares
-// the two label arrays for 128 rows (one 16-byte load per lane and array, the next step's loads
-// already in flight) and appends the rows that moved - offset, new and old label - to a list in
-// shared memory.  Apply: the list is cut into items of one row segment each (the lpr lanes of a group
-// times V columns) that the warps take in turn, two items per group in flight; a wide row is thus
-// spread over several warps, and the moved rows of a step over all of them, wherever they sat in the
-// step.  (Before, a warp worked through the moved rows of its own 256 rows one after the other:
-// with 784 columns and 8 % of the labels moving that was 0.15 ms for 250,000 rows.)
+// A CTA scans its rows in steps of kDeltaStepRows.  Scan: every warp compares the two label arrays
+// for 128 rows (one 16-byte load per lane and array, the next step's loads already in flight) and
+// appends the rows that moved - offset, new and old label - to a list in shared memory.  Apply, once
+// the list could not take another step's rows or the accumulators are due to be drained: the list is
+// cut into items of one row segment each (the lpr lanes of a group times V columns) that the warps
+// take in turn, two items per group in flight; a wide row is thus spread over several warps, and the
+// moved rows over all of them, wherever they sat.  (Before, a warp worked through the moved rows of
+// its own 256 rows one after the other: with 784 columns and 8 % of the labels moving that was
+// 0.15 ms for 250,000 rows.  Applying after every step cost a memory latency per step: with 0.1 % of
+// 1e7 x 64 rows moving the kernel took 43 us, the label scan alone needs 15.)
 template <typename T, int V>
 __global__ void __launch_bounds__(kDeltaThreads, 2)
 delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int* __restrict__ labels,
@@ -150,7 +153,7 @@ delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int
   int* cnt = acc + (size_t)NP * k * d;              // [2][k]: units, then units * 2^15 (sample weights)
   uint2* list = reinterpret_cast<uint2*>(smem_raw + (((size_t)NP * k * d + 2 * k) * sizeof(int) + 15) / 16 * 16);
   __shared__ int s_touched;                         // rows netted since the last drain
-  __shared__ int s_list_n[2];                       // entries of the list, by parity of the step
+  __shared__ int s_list_n;                          // entries of the list
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
@@ -172,7 +175,7 @@ delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int
 
   for (int i = tid; i < NP * k * d; i += kDeltaThreads) acc[i] = 0;
   for (int i = tid; i < 2 * k; i += kDeltaThreads) cnt[i] = 0;
-  if (tid == 0) { s_touched = 0; s_list_n[0] = 0; s_list_n[1] = 0; }
+  if (tid == 0) { s_touched = 0; s_list_n = 0; }
   __syncthreads();
 
   // labels of this lane's four rows of a step (r_begin is a multiple of 32 rows: aligned 16-byte loads)
@@ -194,82 +197,86 @@ delta_accumulate_smem_kernel(const T* __restrict__ X, size_t n, int d, const int
   };
   int nwn[4], odn[4];
   if (r_begin < r_end) load_step(r_begin, nwn, odn);
-  int parity = 0;
   int since_drain = 0;
 
-  for (size_t sb = r_begin; sb < r_end; sb += kDeltaStepRows, parity ^= 1) {
+  for (size_t sb = r_begin; sb < r_end; sb += kDeltaStepRows) {
     // ---- scan ----
     int nw[4], od[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) { nw[j] = nwn[j]; od[j] = odn[j]; }
     if (sb + kDeltaStepRows < r_end) load_step(sb + kDeltaStepRows, nwn, odn);
-    const unsigned int off0 = (unsigned int)(warp * 128 + lane * 4);
+    const unsigned int off0 = (unsigned int)(sb - r_begin) + (unsigned int)(warp * 128 + lane * 4);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const bool moved = nw[j] != od[j];
       const unsigned int mask = __ballot_sync(0xffffffffu, moved);
       if (mask == 0) continue;
       int base = 0;
-      if (lane == 0) base = atomicAdd(&s_list_n[parity], __popc(mask));
+      if (lane == 0) base = atomicAdd(&s_list_n, __popc(mask));
       base = __shfl_sync(0xffffffffu, base, 0);
       if (moved) {
         const unsigned int to = (unsigned)nw[j] < (unsigned)k ? (unsigned)nw[j] : 0xffffu;
         const unsigned int from = (unsigned)od[j] < (unsigned)k ? (unsigned)od[j] : 0xffffu;
         list[base + __popc(mask & ((1u << lane) - 1u))] = make_uint2(off0 + j, (to << 16) | from);
-        prev[sb + off0 + j] = nw[j];
+        prev[r_begin + off0 + j] = nw[j];
       }
     }
     __syncthreads();
-    const int n_list = s_list_n[parity];
-    if (tid == 0) { s_list_n[parity ^ 1] = 0; s_touched += n_list; }
-    // ---- apply ----
-    const int items = n_list * nseg;
-    for (int it0 = warp * groups; it0 < items; it0 += 2 * NWARP * groups) {
-      T x[2][V];
-      uint2 en[2];
-      int idx[2];
-      bool have[2];
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int it = it0 + u * NWARP * groups + g;
-        have[u] = it < items;
-        idx[u] = 0;
-        en[u] = make_uint2(0u, 0u);
-        if (have[u]) {
-          const int e = (nseg == 1) ? it : it / nseg;
-          idx[u] = (it - e * nseg) * lpr + l;
-          en[u] = list[e];
-          have[u] = idx[u] < dv;
-        }
-        if (have[u]) VecLoad<T, V>::ld(X + (sb + en[u].x) * (size_t)d + (size_t)idx[u] * V, x[u]);
-      }
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        if (!have[u]) continue;
-        const unsigned int to = en[u].y >> 16, from = en[u].y & 0xffffu;
-        const bool to_ok = to != 0xffffu, from_ok = from != 0xffffu;
-        const T w = W ? W[sb + en[u].x] : (T)1;
-        T y[V];
-        if (W) {
-#pragma unroll
-          for (int e = 0; e < V; ++e) x[u][e] *= w;
-        }
-#pragma unroll
-        for (int e = 0; e < V; ++e) y[e] = -x[u][e];
-        if (to_ok) add_vec_fixed<T, V, NP>(acc + (size_t)to * d, pstride, dv, idx[u], g & (V - 1), x[u], scale);
-        if (from_ok) add_vec_fixed<T, V, NP>(acc + (size_t)from * d, pstride, dv, idx[u], g & (V - 1), y, scale);
-        if (idx[u] == 0) {
-          int pw[2] = {0, 1};
-          if (W) split_pieces<2>(w, wscale, pw);
-          if (to_ok) { atomicAdd(&cnt[to], pw[1]); if (pw[0]) atomicAdd(&cnt[k + to], pw[0]); }
-          if (from_ok) { atomicAdd(&cnt[from], -pw[1]); if (pw[0]) atomicAdd(&cnt[k + from], -pw[0]); }
-        }
-      }
-    }
-    __syncthreads();
+    const int n_list = s_list_n;
     since_drain += kDeltaStepRows;
     // every piece is at most 2^15 in magnitude: drain after 2^15 rows at the latest, and at the end
-    if (since_drain >= kDeltaChunk || sb + kDeltaStepRows >= r_end) {
+    const bool drain_due = since_drain >= kDeltaChunk || sb + kDeltaStepRows >= r_end;
+    const bool apply = n_list > 0 && (drain_due || n_list > kDeltaListCap - kDeltaStepRows);
+    __syncthreads();   // everybody has read the count before the next scan can add to it
+    if (apply) {
+      const int items = n_list * nseg;
+      for (int it0 = warp * groups; it0 < items; it0 += 2 * NWARP * groups) {
+        T x[2][V];
+        uint2 en[2];
+        int idx[2];
+        bool have[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int it = it0 + u * NWARP * groups + g;
+          have[u] = it < items;
+          idx[u] = 0;
+          en[u] = make_uint2(0u, 0u);
+          if (have[u]) {
+            const int e = (nseg == 1) ? it : it / nseg;
+            idx[u] = (it - e * nseg) * lpr + l;
+            en[u] = list[e];
+            have[u] = idx[u] < dv;
+          }
+          if (have[u]) VecLoad<T, V>::ld(X + (r_begin + en[u].x) * (size_t)d + (size_t)idx[u] * V, x[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (!have[u]) continue;
+          const unsigned int to = en[u].y >> 16, from = en[u].y & 0xffffu;
+          const bool to_ok = to != 0xffffu, from_ok = from != 0xffffu;
+          const T w = W ? W[r_begin + en[u].x] : (T)1;
+          T y[V];
+          if (W) {
+#pragma unroll
+            for (int e = 0; e < V; ++e) x[u][e] *= w;
+          }
+#pragma unroll
+          for (int e = 0; e < V; ++e) y[e] = -x[u][e];
+          if (to_ok) add_vec_fixed<T, V, NP>(acc + (size_t)to * d, pstride, dv, idx[u], g & (V - 1), x[u], scale);
+          if (from_ok) add_vec_fixed<T, V, NP>(acc + (size_t)from * d, pstride, dv, idx[u], g & (V - 1), y, scale);
+          if (idx[u] == 0) {
+            int pw[2] = {0, 1};
+            if (W) split_pieces<2>(w, wscale, pw);
+            if (to_ok) { atomicAdd(&cnt[to], pw[1]); if (pw[0]) atomicAdd(&cnt[k + to], pw[0]); }
+            if (from_ok) { atomicAdd(&cnt[from], -pw[1]); if (pw[0]) atomicAdd(&cnt[k + from], -pw[0]); }
+          }
+        }
+      }
+      __syncthreads();
+      if (tid == 0) { s_touched += n_list; s_list_n = 0; }
+      __syncthreads();
+    }
+    if (drain_due) {
       since_drain = 0;
       if (s_touched > 0) {
         for (int i = tid; i < k * d; i += kDeltaThreads) {
