@@ -556,6 +556,25 @@ def main():
             extra["c4"]["scaling"] = "strong: 2e6 rows / N GPUs"
             extra["c4_predict"] = r4["after"]["predict"]
             extra["c4_transform"] = r4["after"]["transform"]
+        # wide rows with many centroids (d = 784, k = 100: the kernel that streams both operands), 5e5 rows per
+        # GPU, and transform of the C2 shape (2e6 rows per GPU) through the same kernel's store epilogue
+        w6 = dict(WORKLOADS["c4"])
+        w6["k"], w6["n"] = 100, 500_000
+        r6, X6 = run_case(ctx, w6, 10, 2, 0, min_seconds=0.3, min_repeats=2, max_repeats=5, after_fit=c4_after)
+        del X6
+        torch.cuda.empty_cache()
+        w7 = dict(WORKLOADS["c2"])
+        w7["n"] = 2_000_000
+        r7, X7 = run_case(ctx, w7, 5, 2, 0, min_seconds=0.2, min_repeats=2, max_repeats=3, after_fit=c4_after)
+        del X7
+        torch.cuda.empty_cache()
+        if rank == 0:
+            roof6, _ = roofline_of("c4_k100", r6, hbm_peak, tensor_peak, peak_kind)
+            extra["c4_k100"] = brief(r6, roof6)
+            extra["c4_k100"]["scaling"] = "weak: 5e5 rows per GPU"
+            extra["c4_k100_transform"] = r6["after"]["transform"]
+            extra["c2_transform"] = r7["after"]["transform"]
+            extra["c2_transform"]["rows_per_gpu"] = w7["n"]
             line["extra"] = extra
 
     if rank == 0 and world == 1 and not args.no_cpu:

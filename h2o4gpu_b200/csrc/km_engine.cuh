@@ -98,6 +98,7 @@ struct Shard {
   tc::Plan tcp;  // tensor-core path (float only)
   tcb::BigPlan tcbp;  // tensor-core path for large centroid tables
   tcw::WidePlan tcwp; // tensor-core path for few centroids and wide rows
+  tcs::StreamPlan tcsp;  // tensor-core path with both operands streamed: wide rows and many centroids, transform
   unsigned int* amb_rows = nullptr;  // rows handed to the exact re-evaluation pass
   size_t amb_cap = 0;
   uint4* amb_near = nullptr;         // per listed row: bit mask of the candidate centroids (small tables)
@@ -222,6 +223,16 @@ struct Engine : EngineBase {
   int launch_close(Shard<T>& s, int run_if, int it, double inv, bool use_tc);
   int poll_seq = 0;   // sequence number the finalize kernels publish to pinned memory
   bool tc_ok(int flags) const;
+  // which tensor-core distance kernel labels this shape: 1 table resident (d 32/64, k <= 128), 2 table streamed
+  // (d <= 256), 3 few centroids and wide rows, 4 both operands streamed (wider rows, many centroids), 0 none
+  int tc_kind() const {
+    if (tcw::wide_shape_ok(k, d)) return 3;
+    if (tc::shape_ok(k, d)) return 1;
+    if (tcb::big_shape_ok(k, d)) return 2;
+    if (tcs::stream_shape_ok(k, d)) return 4;
+    return 0;
+  }
+  int stream_refresh(Shard<T>& s);   // operand table and plan of the streaming kernel for the current centroids
   int tc_refresh(Shard<T>& s);  // split the current centroids for the tensor-core kernel
   int launch_assign(Shard<T>& s, bool use_tc, bool count_changes);
   bool tc_split_build = false;   // the running fit has enough iterations to pay for the split copy of X
@@ -359,6 +370,7 @@ void Engine<T>::destroy() {
     s.tcp.release();
     s.tcbp.release();
     s.tcwp.release();
+    s.tcsp.release();
     km_free(s.amb_rows); km_free(s.amb_near); km_free(s.amb_log);
     km_free(s.X_owned); km_free(s.raw); km_free(s.w); km_free(s.labels); km_free(s.dist); km_free(s.gacc);
     km_free(s.pacc); km_free(s.pflush); km_free(s.labels_prev); km_free(s.moved_bits);
@@ -396,6 +408,7 @@ int Engine<T>::attach_device(int local, const T* dX, size_t rows, size_t cols, s
   s.tcp.ready = false;
   s.tcbp.ready = false;
   s.tcwp.ready = false;
+  s.tcsp.ready = false;
   if ((int)cols != d) have_centroids = false;
   d = (int)cols;
   n_total = ntot;
@@ -1134,7 +1147,7 @@ int Engine<T>::launch_accumulate(Shard<T>& s, T scale, long long* dst, const uns
 template <typename T>
 bool Engine<T>::tc_ok(int flags) const {
   if (!std::is_same<T, float>::value || (flags & KM_FIT_FORCE_SIMT)) return false;
-  if (!tc::shape_ok(k, d) && !tcb::big_shape_ok(k, d) && !tcw::wide_shape_ok(k, d)) return false;
+  if (tc_kind() == 0) return false;
   for (const auto& s : shards)
     if (s.cc_major != 10 || (reinterpret_cast<uintptr_t>(s.X) & 15) != 0 || !s.x_checked) return false;
   double xmax = 0;
@@ -1163,13 +1176,16 @@ int Engine<T>::tc_refresh(Shard<T>& s) {
       KM_CUDA(km_malloc(&s.amb_near, s.rows * sizeof(uint4)));
       s.amb_near_cap = s.rows;
     }
-    if (tcw::wide_shape_ok(k, d)) {
+    const int kind = tc_kind();
+    if (kind == 3) {
       KM_TRY(tc::ensure_xnorm(s.tcp, s.X, s.rows, d, s.num_sms, s.stream));
       KM_TRY(tcw::wide_setup(s.tcwp, s.X, s.rows, k, d));
       s.tcwp.sx = tc_sx;
       s.tcwp.sb = tc_sb;
       KM_TRY(tcw::wide_prep(s.tcwp, s.C[cur], s.cnorm, s.stream));
-    } else if (tc::shape_ok(k, d)) {
+    } else if (kind == 4) {
+      KM_TRY(stream_refresh(s));
+    } else if (kind == 1) {
       KM_TRY(tc::setup(s.tcp, s.X, s.rows, k, d, s.num_sms, s.stream));
       s.tcp.sx = tc_sx;
       s.tcp.sb = tc_sb;
@@ -1187,11 +1203,32 @@ int Engine<T>::tc_refresh(Shard<T>& s) {
 }
 
 template <typename T>
+int Engine<T>::stream_refresh(Shard<T>& s) {
+  if constexpr (std::is_same<T, float>::value) {
+    KM_TRY(tc::ensure_xnorm(s.tcp, s.X, s.rows, d, s.num_sms, s.stream));
+    KM_TRY(tcs::stream_setup(s.tcsp, s.X, s.rows, k, d));
+    s.tcsp.sx = tc_sx;
+    s.tcsp.sb = tc_sb;
+    KM_TRY(tcs::stream_prep(s.tcsp, s.C[cur], s.cnorm, s.stream));
+  }
+  return KM_OK;
+}
+
+template <typename T>
 int Engine<T>::launch_assign(Shard<T>& s, bool use_tc, bool count_changes) {
   if constexpr (std::is_same<T, float>::value) {
+    if (use_tc && tc_kind() == 4) {
+      launches += 2;
+      KM_TRY(tcs::stream_launch(s.tcsp, s.tcp.xnorm, s.labels, s.st, count_changes, s.amb_rows, tc::tol_rel_of(d), s.num_sms,
+                                s.stream));
+      tcb::refine_big_kernel<float><<<s.num_sms * 2, 256, 0, s.stream>>>(s.X, d, s.C[cur], k, s.amb_rows, s.st,
+                                                                        s.labels, count_changes ? 1 : 0);
+      KM_CUDA(cudaGetLastError());
+      return KM_OK;
+    }
     if (use_tc && tcw::wide_shape_ok(k, d)) {
       launches += 2;
-      KM_TRY(tcw::wide_launch(s.tcwp, s.tcp.xnorm, s.labels, s.st, count_changes, s.amb_rows, tc::kTolRel, s.num_sms,
+      KM_TRY(tcw::wide_launch(s.tcwp, s.tcp.xnorm, s.labels, s.st, count_changes, s.amb_rows, tc::tol_rel_of(d), s.num_sms,
                               s.stream));
       tcb::refine_big_kernel<float><<<s.num_sms * 2, 256, 0, s.stream>>>(s.X, d, s.C[cur], k, s.amb_rows, s.st,
                                                                         s.labels, count_changes ? 1 : 0);
@@ -1200,7 +1237,7 @@ int Engine<T>::launch_assign(Shard<T>& s, bool use_tc, bool count_changes) {
     }
     if (use_tc && !tc::shape_ok(k, d)) {
       launches += 2;
-      KM_TRY(tcb::big_launch(s.tcbp, s.tcp.xnorm, s.labels, s.st, count_changes, s.amb_rows, tc::kTolRel, s.num_sms,
+      KM_TRY(tcb::big_launch(s.tcbp, s.tcp.xnorm, s.labels, s.st, count_changes, s.amb_rows, tc::tol_rel_of(d), s.num_sms,
                              s.stream));
       tcb::refine_big_kernel<float><<<s.num_sms * 2, 256, 0, s.stream>>>(s.X, d, s.C[cur], k, s.amb_rows, s.st,
                                                                         s.labels, count_changes ? 1 : 0);
@@ -1210,7 +1247,7 @@ int Engine<T>::launch_assign(Shard<T>& s, bool use_tc, bool count_changes) {
     if (use_tc) {
       launches += 2;
       unsigned int* bits = (count_changes && s.labels_prev_cap >= s.rows) ? s.moved_bits : nullptr;
-      KM_TRY(tc::launch(s.tcp, s.labels, s.st, count_changes, s.amb_rows, tc::kTolRel, s.num_sms,
+      KM_TRY(tc::launch(s.tcp, s.labels, s.st, count_changes, s.amb_rows, tc::tol_rel_of(d), s.num_sms,
                         s.stream, bits, s.amb_near, tc_split_build));
       s.moved_bits_valid = bits != nullptr;
       refine_near_kernel<float><<<s.num_sms * 4, kRefineThreads, 0, s.stream>>>(

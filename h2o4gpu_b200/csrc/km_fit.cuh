@@ -131,7 +131,9 @@ template <typename T>
 SplitTable Engine<T>::split_table(Shard<T>& s, bool use_tc) {
   SplitTable tp{nullptr, nullptr, nullptr, 0, 0, 0.f, 0.f};
   if constexpr (std::is_same<T, float>::value) {
-    if (use_tc && tcw::wide_shape_ok(k, d))
+    if (use_tc && tc_kind() == 4)
+      tp = SplitTable{s.tcsp.bhi, s.tcsp.blo, s.tcsp.cn, s.tcsp.kpad, s.tcsp.dp, s.tcsp.sb, s.tcsp.sx * s.tcsp.sb};
+    else if (use_tc && tcw::wide_shape_ok(k, d))
       tp = SplitTable{s.tcwp.bhi, s.tcwp.blo, s.tcwp.cn, tcw::kNPad, s.tcwp.dp, s.tcwp.sb, s.tcwp.sx * s.tcwp.sb};
     else if (use_tc && tc::shape_ok(k, d))
       tp = SplitTable{s.tcp.bhi, s.tcp.blo, s.tcp.cn, s.tcp.npad, 64, s.tcp.sb, s.tcp.sx * s.tcp.sb};
@@ -540,13 +542,26 @@ int Engine<T>::transform_shard(int local, T* out_host, size_t ld) {
   cudaEventCreate(&e1);
   float ms_kernels = 0;
   int rc = KM_OK;
-  bool wide = false;
+  bool wide = false, streamed = false;
   if constexpr (std::is_same<T, float>::value) {
-    // few centroids, wide rows: the tensor-core kernel with its store epilogue (needs max|x| for the
-    // operand scales, i.e. a checked matrix)
+    // tensor-core kernels with a store epilogue (they need max|x| for the operand scales, i.e. a checked
+    // matrix): the wide-row kernel for few centroids, the kernel that streams both operands for the rest
     if (tcw::wide_shape_ok(k, d) && tc_ok(0)) {
       rc = tc_refresh(s);
       wide = rc == KM_OK;
+    } else if (tcs::stream_shape_ok(k, d) && tc_ok(0)) {
+      if (tc_kind() == 4) {
+        rc = tc_refresh(s);
+      } else {
+        // the shape's own labelling kernel keeps its plan; the streaming kernel gets one beside it
+        double xmax = 0;
+        for (const auto& sh : shards) xmax = std::max(xmax, sh.xmax);
+        if (!tc::pick_scales(xmax, std::max(xmax, cbound), &tc_sx, &tc_sb)) rc = KM_EINVAL;
+        if (rc == KM_OK) rc = stream_refresh(s);
+        if (rc == KM_OK) ++launches;
+      }
+      streamed = rc == KM_OK;
+      if (!streamed) rc = KM_OK;   // fall back to the FMA tile kernel
     }
   }
   for (size_t r = 0; r < s.rows && rc == KM_OK; r += batch) {
@@ -554,12 +569,16 @@ int Engine<T>::transform_shard(int local, T* out_host, size_t ld) {
     cudaEventRecord(e0, s.stream);
     if constexpr (std::is_same<T, float>::value) {
       if (wide) {
-        rc = tcw::wide_launch(s.tcwp, s.tcp.xnorm, nullptr, s.st, false, nullptr, tc::kTolRel, s.num_sms, s.stream, r, nr,
+        rc = tcw::wide_launch(s.tcwp, s.tcp.xnorm, nullptr, s.st, false, nullptr, tc::tol_rel_of(d), s.num_sms, s.stream, r, nr,
                               buf, batch);
+        ++launches;
+      } else if (streamed) {
+        rc = tcs::stream_launch(s.tcsp, s.tcp.xnorm, nullptr, s.st, false, nullptr, tc::tol_rel_of(d), s.num_sms, s.stream, r,
+                                nr, buf, batch);
         ++launches;
       }
     }
-    if (!wide) rc = launch_tiles(s, s.X + r * (size_t)d, nr, nullptr, MODE_TRANSFORM, buf, batch, false);
+    if (!wide && !streamed) rc = launch_tiles(s, s.X + r * (size_t)d, nr, nullptr, MODE_TRANSFORM, buf, batch, false);
     if (rc != KM_OK) break;
     cudaEventRecord(e1, s.stream);
     cudaError_t ce = cudaMemcpy2DAsync(out_host + r, ld * sizeof(T), buf, batch * sizeof(T), nr * sizeof(T), k,
@@ -571,7 +590,10 @@ int Engine<T>::transform_shard(int local, T* out_host, size_t ld) {
   }
   cudaEventDestroy(e0);
   cudaEventDestroy(e1);
-  if (local == 0) stats.ms_transform = ms_kernels;
+  if (local == 0) {
+    stats.ms_transform = ms_kernels;
+    stats.path = (wide || streamed) ? 3 : 2;
+  }
   km_free(buf);
   return rc;
 }

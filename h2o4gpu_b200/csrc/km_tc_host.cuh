@@ -194,7 +194,17 @@ inline int prep(Plan& pl, const float* C, const float* cnorm, cudaStream_t strea
 // A low half below 2^-14 is an fp16 subnormal (quantum 2^-24): |ex|, |eb| <= 2^-25 absolute,
 // which adds 2^-25 (|y|_1 + |b|_1) per score; tol_floor_of(d) = 2^-23 sqrt(d) bounds twice that
 // for a difference through |v|_1 <= sqrt(d) |v|_2.
+// The accumulation term grows with the row width: the tensor core adds every K = 16 slice into the fp32
+// accumulator with truncation, a one-sided error per step.  Measured on the worst case for it (all
+// coordinates near a common offset, so that |x.c| = |x||c|), the largest error of a single score was
+// e1(d) = (0.38 + d / 210) * 2^-19 (|x|^2 + |c|^2): 2^-19.5 at d = 64, 2^-18.4 at 256, 2^-17.1 at 784,
+// 2^-15.6 at 2048, and with the flat 2^-19 rows of 2048 columns were mislabelled (3 of 40,000, gaps up
+// to 3e-4 relative; none seen up to 784 columns).  The errors of two scores that are nearly tied have the
+// same sign (their accumulators differ by the difference of the two |c|^2 only), so their difference is
+// off by at most the larger of the two: tol_rel_of(d) = 2^-19 max(1, 0.45 + d / 190) keeps 10 % above
+// e1(d) from 128 columns on and is the old 2^-19 (1.4 e1) below.
 constexpr float kTolRel = 1.9073486328125e-06f;
+inline float tol_rel_of(int d) { return kTolRel * std::max(1.0f, 0.45f + (float)d / 190.0f); }
 inline float tol_floor_of(int d) { return 1.1920928955078125e-07f * std::sqrt((float)d); }
 
 inline int launch(Plan& pl, int* labels, IterState* st, bool count_changes, unsigned int* amb_rows, float tol_rel,
@@ -405,4 +415,95 @@ inline int wide_launch(WidePlan& pl, const float* xnorm, int* labels, IterState*
 }
 
 }  // namespace tcw
+}  // namespace km
+
+#include "km_assign_tc_stream.cuh"
+
+namespace km {
+namespace tcs {
+
+struct StreamPlan {
+  __half* bhi = nullptr;
+  __half* blo = nullptr;
+  float* cn = nullptr;
+  int k = 0, d = 0, dp = 0, n_chunks = 0, npad = 0, n_pass = 0, kpad = 0;
+  const float* x_base = nullptr;
+  size_t x_rows = 0;
+  float sx = 1.f, sb = 1.f;
+  CUtensorMap tmX, tmBhi, tmBlo;
+  bool ready = false;
+  void release() {
+    km_free(bhi); km_free(blo); km_free(cn);
+    bhi = blo = nullptr;
+    cn = nullptr;
+    ready = false;
+  }
+};
+
+// float32, more than 16 centroids, 16-byte aligned rows of 32 to 4096 columns.  Up to 128 centroids run
+// with N = 128 and two accumulators, more with N = 256 (one pass per 256 centroids).
+inline bool stream_shape_ok(int k, int d) { return k > 16 && k <= 6144 && d >= 32 && d <= 4096 && d % 4 == 0; }
+inline int stream_npad(int k) { return k <= 128 ? 128 : 256; }
+
+inline int stream_setup(StreamPlan& pl, const float* X, size_t rows, int k, int d) {
+  if (pl.ready && pl.k == k && pl.d == d && pl.x_base == X && pl.x_rows == rows) return KM_OK;
+  const int n_chunks = (d + kSChunk - 1) / kSChunk;
+  const int dp = n_chunks * kSChunk;
+  const int npad = stream_npad(k);
+  const int n_pass = (k + npad - 1) / npad;
+  const int kpad = n_pass * npad;
+  if (!(pl.bhi && pl.k == k && pl.d == d)) {
+    pl.release();
+    KM_CUDA(km_malloc(&pl.bhi, (size_t)kpad * dp * sizeof(__half)));
+    KM_CUDA(km_malloc(&pl.blo, (size_t)kpad * dp * sizeof(__half)));
+    KM_CUDA(km_malloc(&pl.cn, (size_t)(kpad + 1) * sizeof(float)));
+  }
+  pl.k = k; pl.d = d; pl.dp = dp; pl.n_chunks = n_chunks; pl.npad = npad; pl.n_pass = n_pass; pl.kpad = kpad;
+  pl.x_base = X; pl.x_rows = rows;
+  KM_TRY(tc::make_map(&pl.tmX, X, rows, d, kBM, 4));
+  KM_TRY(tc::make_map(&pl.tmBhi, pl.bhi, kpad, dp, npad, 2));
+  KM_TRY(tc::make_map(&pl.tmBlo, pl.blo, kpad, dp, npad, 2));
+  if (npad == 128)
+    KM_CUDA(cudaFuncSetAttribute(assign_tc_stream_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)stream_smem_bytes<128>()));
+  else
+    KM_CUDA(cudaFuncSetAttribute(assign_tc_stream_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)stream_smem_bytes<256>()));
+  pl.ready = true;
+  return KM_OK;
+}
+
+inline int stream_prep(StreamPlan& pl, const float* C, const float* cnorm, cudaStream_t stream) {
+  KM_CUDA(cudaMemsetAsync(pl.cn + pl.kpad, 0, sizeof(float), stream));
+  tcb::big_prep_kernel<<<pl.kpad, 256, 0, stream>>>(C, cnorm, pl.k, pl.d, pl.dp, pl.kpad, pl.sb, pl.sx * pl.sb, pl.bhi,
+                                                   pl.blo, pl.cn);
+  KM_CUDA(cudaGetLastError());
+  return KM_OK;
+}
+
+// labels of rows [row0, row0 + nrows) (row0 a multiple of 128), or - with `out` - their squared distances to
+// the k centroids as a column-major block with leading dimension ld_out
+inline int stream_launch(StreamPlan& pl, const float* xnorm, int* labels, IterState* st, bool count_changes,
+                         unsigned int* amb_rows, float tol_rel, int num_sms, cudaStream_t stream, size_t row0 = 0,
+                         size_t nrows = 0, float* out = nullptr, size_t ld_out = 0) {
+  if (nrows == 0) nrows = pl.x_rows - row0;
+  const size_t tiles = (nrows + kBM - 1) / kBM;
+  if ((pl.x_rows + kBM - 1) / kBM > 0x7fffffffULL / kBM) KM_FAIL(KM_EINVAL, "shard too large for the tensor-core kernel");
+  const int grid = (int)std::min<size_t>(tiles, (size_t)num_sms);
+  const size_t n_end = std::min(pl.x_rows, row0 + nrows);
+  if (pl.npad == 128)
+    assign_tc_stream_kernel<128><<<grid, kSThreads, stream_smem_bytes<128>(), stream>>>(
+        pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, xnorm, labels, n_end, (int)(row0 / kBM), (int)tiles, pl.n_chunks, pl.n_pass,
+        pl.k, st, count_changes ? 1 : 0, amb_rows, tol_rel, tc::tol_floor_of(pl.d), pl.sx, pl.sx * pl.sb,
+        wait_limits().mbar_iters, out, ld_out);
+  else
+    assign_tc_stream_kernel<256><<<grid, kSThreads, stream_smem_bytes<256>(), stream>>>(
+        pl.tmX, pl.tmBhi, pl.tmBlo, pl.cn, xnorm, labels, n_end, (int)(row0 / kBM), (int)tiles, pl.n_chunks, pl.n_pass,
+        pl.k, st, count_changes ? 1 : 0, amb_rows, tol_rel, tc::tol_floor_of(pl.d), pl.sx, pl.sx * pl.sb,
+        wait_limits().mbar_iters, out, ld_out);
+  KM_CUDA(cudaGetLastError());
+  return KM_OK;
+}
+
+}  // namespace tcs
 }  // namespace km

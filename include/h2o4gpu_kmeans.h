@@ -204,7 +204,7 @@ typedef struct kmeans_stats {
   int iterations;          /* Lloyd iterations executed                              */
   int n_iter_converged;    /* first iteration after which no label changed, +1; else 0 */
   int relocations;         /* empty-cluster relocations over the whole fit           */
-  int path;                /* 1 fused small-k, 2 SIMT tiles, 3 tcgen05               */
+  int path;                /* 1 fused small-k, 2 SIMT tiles, 3 tcgen05 (of the last fit or transform) */
   int gpu_launches;        /* kernels launched by the last fit (all local devices)   */
   int incremental_iterations; /* iterations (device 0) whose centroid sums were updated from
                                * the rows that changed label instead of recomputed       */

@@ -1154,3 +1154,97 @@ def test_any_row_width_reaches_the_tensor_cores(eng, n, d, k):
         check_step(X, C32.astype(np.float64), h.centroids(), h.labels(), Cn, labn, moved, st["relocations"])
         C = Cn
     h.close()
+
+
+# ---- rows wider than 256 columns with many centroids: both operands streamed ---------------
+@pytest.mark.parametrize("n,d,k", [(20000, 784, 100), (9001, 300, 40), (6000, 1000, 300), (5000, 512, 600),
+                                   (3000, 260, 17)])
+def test_wide_rows_many_centroids_reach_the_tensor_cores(eng, n, d, k):
+    """16-byte aligned rows of more than 256 columns with more than 16 centroids take the tcgen05 kernel
+    that streams both operands in chunks of 64 columns (one pass per 128 or 256 centroids); results as for
+    any other shape, checked against the float64 oracle step by step, and labels against the FMA kernel."""
+    rng = np.random.default_rng(n + d + k)
+    centers = rng.uniform(-4, 4, (max(k // 3, 5), d))
+    X = (centers[rng.integers(0, centers.shape[0], n)] + rng.standard_normal((n, d))).astype(np.float32)
+    init = X[np.sort(rng.choice(n, k, replace=False))].copy()
+    C = init.astype(np.float64)
+    h = eng.ResidentKMeans(dtype=np.float32)
+    h.upload(X)
+    for _ in range(2):
+        C32 = C.astype(np.float32)
+        Cn, labn, _, moved = lloyd.step(X, C32.astype(np.float64), order="descending")
+        h.fit(C32, 1, flags=eng.FIT_NO_FINAL_ASSIGN)
+        st = h.stats()
+        assert st["path"] == 3
+        check_step(X, C32.astype(np.float64), h.centroids(), h.labels(), Cn, labn, moved, st["relocations"])
+        C = Cn
+    h.close()
+    a = one_step(eng, X, init)
+    b = one_step(eng, X, init, flags=eng.FIT_FORCE_SIMT)
+    assert a[2]["path"] == 3 and b[2]["path"] == 2
+    if check_labels(X, init.astype(np.float64), a[1], b[1]) == 0:
+        assert np.array_equal(a[0], b[0])          # integer sums: same labels -> same bits
+
+
+@pytest.mark.parametrize("n,d,k", [(30000, 64, 100), (20000, 128, 300), (4000, 256, 1000), (12000, 784, 100),
+                                   (5000, 48, 33), (3333, 1000, 300)])
+def test_transform_on_the_tensor_cores_matches_exact_distances(eng, tmp_path, n, d, k):
+    """transform (n x k squared distances) of every float32 shape with more than 16 centroids and 16-byte
+    aligned rows of 32 columns or more runs on the streaming tcgen05 kernel with its store epilogue:
+    values against exact float64 distances, and unchanged by row batching."""
+    import os
+    import subprocess
+    import sys
+    rng = np.random.default_rng(n + d + k)
+    centers = rng.uniform(-4, 4, (max(k // 3, 5), d))
+    X = (centers[rng.integers(0, centers.shape[0], n)] + rng.standard_normal((n, d))).astype(np.float32)
+    C = X[np.sort(rng.choice(n, k, replace=False))].copy()
+    h = eng.ResidentKMeans()
+    h.upload(X)
+    h.set_centroids(C)
+    D = h.transform()
+    assert h.stats()["path"] == 3
+    h.close()
+    want = lloyd.transform_sq_exact(X, C.astype(np.float64))
+    floor = np.finfo(np.float32).eps * ((X.astype(np.float64) ** 2).sum(1)[:, None] + (C.astype(np.float64) ** 2).sum(1)[None, :])
+    assert D.shape == want.shape
+    # the centroids are rows of X, so some distances are exactly zero: there only the cancellation floor
+    # counts - the error bound of a score is 2^-19 max(1, 0.45 + d / 190) (|x|^2 + |c|^2), i.e. 16 float32
+    # epsilons of that sum times the row-width factor (the ambiguity threshold of the labelling kernels),
+    # plus the float32 rounding of |x|^2, |c|^2 and their sum
+    bound = 16 * max(1.0, 0.45 + d / 190.0) + 16
+    assert (np.abs(D - want) <= 1e-4 * want + bound * floor).all()
+    code = ("import sys, numpy as np; sys.path.insert(0, %r); import h2o4gpu_b200.engine as e; "
+            "X = np.load(%r); C = np.load(%r); h = e.ResidentKMeans(); h.upload(X); h.set_centroids(C); "
+            "np.save(%r, h.transform())")
+    np.save(tmp_path / "X.npy", X)
+    np.save(tmp_path / "C.npy", C)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, H2O4GPU_KM_TRANSFORM_BATCH_ROWS="1280")
+    subprocess.run([sys.executable, "-c", code % (root, str(tmp_path / "X.npy"), str(tmp_path / "C.npy"),
+                                                  str(tmp_path / "D.npy"))], check=True, env=env)
+    assert np.array_equal(np.load(tmp_path / "D.npy"), D)          # batching changes no value
+
+
+# ---- data far from the origin: the tensor core's accumulation error grows with the row width -----
+@pytest.mark.parametrize("d,k", [(64, 100), (256, 300), (784, 10), (784, 100), (2048, 40)])
+@pytest.mark.parametrize("offset", [6.0, 25.0])
+def test_offset_data_labels_equal_float64_argmin(eng, d, k, offset):
+    """All coordinates near a common offset make |x.c| = |x||c|, the worst case for the fp32 accumulation of
+    the tensor-core products (a one-sided error per K = 16 slice, so it grows with d); the ambiguity
+    threshold scales with the row width and hands the doubtful rows to the exact pass.  With the flat
+    threshold rows of 2048 columns were mislabelled (gaps up to 3e-4 relative).  Labels must equal the
+    float64 argmin except inside the 1e-5 near-tie band."""
+    n = 20000
+    rng = np.random.default_rng(d + k)
+    X = (offset + rng.standard_normal((n, d))).astype(np.float32)
+    C = np.stack([X[rng.choice(n, 50, replace=False)].mean(0) for _ in range(k)]).astype(np.float32)
+    h = eng.ResidentKMeans()
+    h.upload(X)
+    h.fit(C, 1, flags=eng.FIT_NO_FINAL_ASSIGN)
+    lab = h.labels()
+    st = h.stats()
+    h.close()
+    assert st["path"] == 3
+    want = lloyd.assign(X, C.astype(np.float64), dtype=np.float64)
+    check_labels(X, C.astype(np.float64), lab, want)
