@@ -416,50 +416,119 @@ assign_tc_big_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
   }
 }
 
-// Exact re-evaluation for large k: one warp per listed row, lanes split the columns,
-// four centroids at a time (the table is read from L2).
-template <typename T>
-__global__ void __launch_bounds__(256)
-refine_big_kernel(const T* __restrict__ X, int d, const T* __restrict__ C, int k,
+// Exact re-evaluation of the listed rows against all k centroids: direct differences in double on
+// the double copy of the centroid table, lowest index on ties.  A CTA takes two rows at a time: it
+// widens them into shared memory once (integer operations - no float -> double conversion
+// instructions: the first version converted x and c for every pair and spent most of its time
+// there), and its eight warps share the centroids, four per warp and step, so that a centroid element
+// fetched from L1 / L2 serves two rows and a short list still fills the GPU (one warp per row left
+// most SMs idle when a few thousand rows were listed).  The eight partial sums of a step are reduced
+// by trading halves between lanes (9 exchanges instead of 40), which leaves each group of four lanes
+// with one (row, centroid) total; every lane keeps the running minimum of its own slot, the four
+// slots of a row are merged at the end of the warp's share and the eight warps' results in shared
+// memory.  Dynamic shared memory: 16 d bytes.
+constexpr int kRefineBigThreads = 256;
+__global__ void __launch_bounds__(kRefineBigThreads)
+refine_big_kernel(const float* __restrict__ X, int d, const double* __restrict__ Cd, int k,
                   const unsigned int* __restrict__ amb_rows, IterState* st, int* __restrict__ labels,
                   int count_changes) {
+  extern __shared__ __align__(16) double refine_xs[];   // [2][d]
+  __shared__ double s_best[2][kRefineBigThreads / 32];
+  __shared__ int s_idx[2][kRefineBigThreads / 32];
   const unsigned int cnt = st->amb_count;
   const int lane = threadIdx.x & 31;
-  const unsigned int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const unsigned int nwarp = (gridDim.x * blockDim.x) >> 5;
+  const int warp = threadIdx.x >> 5;
+  constexpr int NW = kRefineBigThreads / 32;
+  const double kInf = __longlong_as_double(0x7ff0000000000000LL);
+  // this lane's slot after the reduction: row (bit 4), centroid of the step (bits 3 and 2)
+  const int my_r = (lane >> 4) & 1;
+  const int my_u = ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+  const double* xs0 = refine_xs;
+  const double* xs1 = refine_xs + d;
   unsigned int changed = 0;
-  for (unsigned int e = warp; e < cnt; e += nwarp) {
-    const size_t row = amb_rows[e];
-    const T* x = X + row * (size_t)d;
-    double best = __longlong_as_double(0x7ff0000000000000LL);
+  for (unsigned int e = blockIdx.x * 2; e < cnt; e += gridDim.x * 2) {
+    const bool two = e + 1 < cnt;
+    const size_t r0 = amb_rows[e];
+    const size_t r1 = two ? amb_rows[e + 1] : r0;
+    __syncthreads();   // the previous pair's rows are no longer read
+    for (int t = threadIdx.x; t < d; t += kRefineBigThreads) {
+      refine_xs[t] = widen_exact(X[r0 * (size_t)d + t]);
+      refine_xs[d + t] = widen_exact(X[r1 * (size_t)d + t]);
+    }
+    __syncthreads();
+    double best = kInf;
     int bi = 0x7fffffff;
-    for (int c0 = 0; c0 < k; c0 += 4) {
-      double dot[4] = {0, 0, 0, 0}, cn[4] = {0, 0, 0, 0};
-      for (int t = lane; t < d; t += 32) {
-        const double xv = (double)x[t];
+    for (int c0 = warp * 4; c0 < k; c0 += NW * 4) {
+      double v[8] = {0, 0, 0, 0, 0, 0, 0, 0};   // [row][centroid of the step]
+      for (int t0 = 0; t0 < d; t0 += 256) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          if (c0 + u < k) {
-            const double cv = (double)C[(size_t)(c0 + u) * d + t];
-            dot[u] = fma(xv, cv, dot[u]);
-            cn[u] = fma(cv, cv, cn[u]);
+        for (int i = 0; i < 8; ++i) {
+          const int t = t0 + lane + 32 * i;
+          if (t < d) {
+            const double xa = xs0[t], xb = xs1[t];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              if (c0 + u < k) {
+                const double cv = Cd[(size_t)(c0 + u) * d + t];
+                const double q0 = xa - cv, q1 = xb - cv;
+                v[u] = fma(q0, q0, v[u]);
+                v[4 + u] = fma(q1, q1, v[4 + u]);
+              }
+            }
           }
         }
       }
+      // trade halves: xor 16 separates the rows, xor 8 and xor 4 the centroids; then a butterfly over the quad
+      {
+        const bool up = (lane & 16) != 0;
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        double s = cn[u] - 2.0 * dot[u];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        if (c0 + u < k && s < best) { best = s; bi = c0 + u; }
+        for (int i = 0; i < 4; ++i) {
+          const double keep = up ? v[i + 4] : v[i], send = up ? v[i] : v[i + 4];
+          v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+        }
       }
+      {
+        const bool up = (lane & 8) != 0;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const double keep = up ? v[i + 2] : v[i], send = up ? v[i] : v[i + 2];
+          v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+        }
+      }
+      {
+        const bool up = (lane & 4) != 0;
+        const double keep = up ? v[1] : v[0], send = up ? v[0] : v[1];
+        v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+      }
+      v[0] += __shfl_xor_sync(0xffffffffu, v[0], 2);
+      v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
+      const int c = c0 + my_u;
+      if (c < k && v[0] < best) { best = v[0]; bi = c; }   // ascending c within a slot: strict < keeps the lowest
     }
-    if (lane == 0) {
-      changed += (labels[row] != bi);
-      labels[row] = bi;
+    // merge the four slots of each row (lanes that differ in bits 3 and 2): smaller distance, then lower index
+#pragma unroll
+    for (int o = 8; o >= 4; o >>= 1) {
+      const double ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob < best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if ((lane & 15) == 0) { s_best[my_r][warp] = best; s_idx[my_r][warp] = bi; }
+    __syncthreads();
+    if (warp == 0 && (lane & 15) == 0 && (my_r == 0 || two)) {
+      double b = s_best[my_r][0];
+      int id = s_idx[my_r][0];
+#pragma unroll
+      for (int w = 1; w < NW; ++w) {
+        const double ob = s_best[my_r][w];
+        const int oi = s_idx[my_r][w];
+        if (ob < b || (ob == b && oi < id)) { b = ob; id = oi; }
+      }
+      const size_t row = my_r ? r1 : r0;
+      changed += (labels[row] != id);
+      labels[row] = id;
     }
   }
-  if (count_changes && lane == 0 && changed) atomicAdd(&st->changed, (unsigned long long)changed);
+  if (count_changes && changed) atomicAdd(&st->changed, (unsigned long long)changed);
 }
 
 }  // namespace tcb

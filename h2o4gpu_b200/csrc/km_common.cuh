@@ -214,6 +214,16 @@ __device__ __host__ __forceinline__ double fixed_to_double(const long long* g, d
   return (double)g[1] * (inv * (1.0 / 1073741824.0)) + (double)g[0] * inv;
 }
 
+// float -> double without cvt.f64.f32, which runs at a small fraction of the FMA rate on this part.
+__device__ __forceinline__ double widen_exact(double x) { return x; }
+__device__ __forceinline__ double widen_exact(float x) {
+  // normal numbers exactly; zero and denormals (below 1.2e-38) become zero; the data has
+  // been checked for Inf / NaN
+  const unsigned int u = __float_as_uint(x);
+  const unsigned int hi = (u & 0x80000000u) | (((u & 0x7fffffffu) >> 3) + 0x38000000u);
+  return (u & 0x7f800000u) ? __hiloint2double((int)hi, (int)(u << 29)) : 0.0;
+}
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));

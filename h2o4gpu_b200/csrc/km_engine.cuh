@@ -265,6 +265,18 @@ struct Engine : EngineBase {
     else
       rowdist_kernel<T, 1><<<s.num_sms * 8, 256, 0, s.stream>>>(s.X, s.rows, d, s.labels, cd, s.dist, s.st, force);
   }
+  // exact pass of the tensor-core kernels that keep no candidate list (all centroids of every listed row)
+  int launch_refine_big(Shard<T>& s, bool count_changes) {
+    if constexpr (std::is_same<T, float>::value) {
+      const size_t smem = (size_t)16 * d;
+      if (smem > 48 * 1024)
+        KM_CUDA(cudaFuncSetAttribute(tcb::refine_big_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      tcb::refine_big_kernel<<<s.num_sms * 8, tcb::kRefineBigThreads, smem, s.stream>>>(
+          s.X, d, s.Cd[cur], k, s.amb_rows, s.st, s.labels, count_changes ? 1 : 0);
+      KM_CUDA(cudaGetLastError());
+    }
+    return KM_OK;
+  }
   int allreduce_from(bool from_pure);
   int push_setup(size_t count);
   void push_release();
@@ -1221,8 +1233,7 @@ int Engine<T>::launch_assign(Shard<T>& s, bool use_tc, bool count_changes) {
       launches += 2;
       KM_TRY(tcs::stream_launch(s.tcsp, s.tcp.xnorm, s.labels, s.st, count_changes, s.amb_rows, tc::tol_rel_of(d), s.num_sms,
                                 s.stream));
-      tcb::refine_big_kernel<float><<<s.num_sms * 2, 256, 0, s.stream>>>(s.X, d, s.C[cur], k, s.amb_rows, s.st,
-                                                                        s.labels, count_changes ? 1 : 0);
+      KM_TRY(launch_refine_big(s, count_changes));
       KM_CUDA(cudaGetLastError());
       return KM_OK;
     }
@@ -1230,8 +1241,7 @@ int Engine<T>::launch_assign(Shard<T>& s, bool use_tc, bool count_changes) {
       launches += 2;
       KM_TRY(tcw::wide_launch(s.tcwp, s.tcp.xnorm, s.labels, s.st, count_changes, s.amb_rows, tc::tol_rel_of(d), s.num_sms,
                               s.stream));
-      tcb::refine_big_kernel<float><<<s.num_sms * 2, 256, 0, s.stream>>>(s.X, d, s.C[cur], k, s.amb_rows, s.st,
-                                                                        s.labels, count_changes ? 1 : 0);
+      KM_TRY(launch_refine_big(s, count_changes));
       KM_CUDA(cudaGetLastError());
       return KM_OK;
     }
@@ -1239,8 +1249,7 @@ int Engine<T>::launch_assign(Shard<T>& s, bool use_tc, bool count_changes) {
       launches += 2;
       KM_TRY(tcb::big_launch(s.tcbp, s.tcp.xnorm, s.labels, s.st, count_changes, s.amb_rows, tc::tol_rel_of(d), s.num_sms,
                              s.stream));
-      tcb::refine_big_kernel<float><<<s.num_sms * 2, 256, 0, s.stream>>>(s.X, d, s.C[cur], k, s.amb_rows, s.st,
-                                                                        s.labels, count_changes ? 1 : 0);
+      KM_TRY(launch_refine_big(s, count_changes));
       KM_CUDA(cudaGetLastError());
       return KM_OK;
     }

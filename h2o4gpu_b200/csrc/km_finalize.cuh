@@ -138,15 +138,6 @@ prepare_kernel(const unsigned long long* __restrict__ gcounts, int k, IterState*
 // centroids) and x is widened with integer operations: float -> double conversions run at a
 // small fraction of the FMA rate and were the limit of this kernel (measured again with the table in
 // shared memory: 1e7 x 64 in 0.94 ms with conversions, 0.73 ms with the integer form).
-__device__ __forceinline__ double widen_exact(double x) { return x; }
-__device__ __forceinline__ double widen_exact(float x) {
-  // normal numbers exactly; zero and denormals (below 1.2e-38) become zero; the data has
-  // been checked for Inf / NaN
-  const unsigned int u = __float_as_uint(x);
-  const unsigned int hi = (u & 0x80000000u) | (((u & 0x7fffffffu) >> 3) + 0x38000000u);
-  return (u & 0x7f800000u) ? __hiloint2double((int)hi, (int)(u << 29)) : 0.0;
-}
-
 // SM = true: the whole table (k_smem * d doubles, dynamic shared memory) is copied into shared memory
 // first and the gather by label reads it there - 8 bytes of centroid per 4 bytes of X otherwise go
 // through L1, which then is the limit of the kernel.
