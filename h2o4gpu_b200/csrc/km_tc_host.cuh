@@ -195,16 +195,18 @@ inline int prep(Plan& pl, const float* C, const float* cnorm, cudaStream_t strea
 // which adds 2^-25 (|y|_1 + |b|_1) per score; tol_floor_of(d) = 2^-23 sqrt(d) bounds twice that
 // for a difference through |v|_1 <= sqrt(d) |v|_2.
 // The accumulation term grows with the row width: the tensor core adds every K = 16 slice into the fp32
-// accumulator with truncation, a one-sided error per step.  Measured on the worst case for it (all
-// coordinates near a common offset, so that |x.c| = |x||c|), the largest error of a single score was
-// e1(d) = (0.38 + d / 210) * 2^-19 (|x|^2 + |c|^2): 2^-19.5 at d = 64, 2^-18.4 at 256, 2^-17.1 at 784,
-// 2^-15.6 at 2048, and with the flat 2^-19 rows of 2048 columns were mislabelled (3 of 40,000, gaps up
-// to 3e-4 relative; none seen up to 784 columns).  The errors of two scores that are nearly tied have the
-// same sign (their accumulators differ by the difference of the two |c|^2 only), so their difference is
-// off by at most the larger of the two: tol_rel_of(d) = 2^-19 max(1, 0.45 + d / 190) keeps 10 % above
-// e1(d) from 128 columns on and is the old 2^-19 (1.4 e1) below.
+// accumulator with truncation, a one-sided error per step that is proportional to the accumulator's
+// magnitude.  Measured on the worst case for it (all coordinates near a common offset, so that
+// |x.c| = |x||c| and the accumulator reaches |x|^2 + |c|^2), the largest error of a single score was
+// (0.38 + d / 210) * 2^-19 (|x|^2 + |c|^2): 2^-19.5 at d = 64, 2^-18.4 at 256, 2^-17.1 at 784, 2^-15.6 at 2048
+// - the constant is the split error above (two-sided), the slope the truncation - and with the flat 2^-19
+// rows of 2048 columns were mislabelled (3 of 40,000, gaps up to 3e-4 relative; none seen up to 784
+// columns).  For the difference of two nearly tied scores the split errors add (2 * 0.38); the truncation
+// errors have the sign of their accumulators: equal signs cancel in part, opposite signs mean
+// |acc_j| + |acc_l| = | |c_l|^2 - |c_j|^2 | <= max|c|^2, so their sum stays below the single-score
+// figure.  tol_rel_of(d) = 2^-19 (0.8 + d / 200) keeps 5 % above 2^-19 (0.76 + d / 210).
 constexpr float kTolRel = 1.9073486328125e-06f;
-inline float tol_rel_of(int d) { return kTolRel * std::max(1.0f, 0.45f + (float)d / 190.0f); }
+inline float tol_rel_of(int d) { return kTolRel * (0.8f + (float)d / 200.0f); }
 inline float tol_floor_of(int d) { return 1.1920928955078125e-07f * std::sqrt((float)d); }
 
 inline int launch(Plan& pl, int* labels, IterState* st, bool count_changes, unsigned int* amb_rows, float tol_rel,
