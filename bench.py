@@ -284,8 +284,8 @@ def roofline_of(args_workload, r, hbm_peak, tensor_peak, peak_kind):
     flops = 2.0 * n * k * d
     # DRAM bytes per row of the dominant kernel from the committed ncu captures (profiles/), taken on
     # a smaller case of the same shape and scaled by the rows of a launch (traffic grows in proportion)
-    ncu_bytes_per_row = {("c2", 3): 269.2, ("c3", 3): 527.7, ("c4", 3): 3163.3,
-                         ("c5", 3): 1063.4}.get((args_workload, st["path"]))
+    ncu_bytes_per_row = {("c2", 3): 269.2, ("c3", 3): 527.7, ("c4", 3): 3163.3, ("c5", 3): 1063.4,
+                         ("c4_k100", 3): 3162.5}.get((args_workload, st["path"]))
     traffic = ncu_bytes_per_row * n if ncu_bytes_per_row else None
     tens = {"fp32_equiv_tflops": flops / (a_ms * 1e-3) / 1e12, "issued_tflops": 3 * flops / (a_ms * 1e-3) / 1e12,
             "peak_tflops": tensor_peak, "frac": 3 * flops / (a_ms * 1e-3) / 1e12 / tensor_peak}
