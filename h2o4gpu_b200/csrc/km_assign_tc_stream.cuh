@@ -299,11 +299,17 @@ assign_tc_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
           tmem_wait_ld(v);
           if (out != nullptr) {
             if (row < n) {
-              const size_t r = row - (size_t)tile0 * kBM;
+              const int col0 = p * NPAD + c0;
+              float* op = out + (size_t)col0 * ld_out + (row - (size_t)tile0 * kBM);
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const int col = p * NPAD + c0 + j;
-                if (col < k) out[(size_t)col * ld_out + r] = fabsf(xn + (__uint_as_float(v[j]) + __ldg(cnp + c0 + j)) * inv_sxsb);
+              for (int j4 = 0; j4 < 8; ++j4) {
+                const float4 cn4 = __ldg(reinterpret_cast<const float4*>(cnp + c0 + j4 * 4));
+                const float cn[4] = {cn4.x, cn4.y, cn4.z, cn4.w};
+#pragma unroll
+                for (int qq = 0; qq < 4; ++qq) {
+                  const int j = j4 * 4 + qq;
+                  if (col0 + j < k) op[(size_t)j * ld_out] = fabsf(fmaf(__uint_as_float(v[j]) + cn[qq], inv_sxsb, xn));
+                }
               }
             }
             continue;

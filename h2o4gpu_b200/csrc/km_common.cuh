@@ -14,7 +14,35 @@
 
 #include "../../include/h2o4gpu_kmeans.h"
 
+// Named ranges for timeline tools (NVTX, header-only; without a tool attached a call costs a few
+// nanoseconds).  The reference marks nothing; these make upload / check / init / fit / iteration /
+// assign / transform visible next to the kernels.
+#if defined(__has_include)
+#if __has_include(<nvtx3/nvToolsExt.h>)
+#include <nvtx3/nvToolsExt.h>
+#define KM_HAVE_NVTX 1
+#endif
+#endif
+
 namespace km {
+
+struct TraceRange {
+  explicit TraceRange(const char* name) {
+#ifdef KM_HAVE_NVTX
+    nvtxRangePushA(name);
+#else
+    (void)name;
+#endif
+  }
+  ~TraceRange() {
+#ifdef KM_HAVE_NVTX
+    nvtxRangePop();
+#endif
+  }
+  TraceRange(const TraceRange&) = delete;
+  TraceRange& operator=(const TraceRange&) = delete;
+};
+
 
 // ---- error plumbing -----------------------------------------------------------
 void set_error(const std::string& msg);

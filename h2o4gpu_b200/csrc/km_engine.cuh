@@ -596,6 +596,7 @@ inline void stage_worker(int dev, const unsigned char* src, unsigned char* dst, 
 
 template <typename T>
 int Engine<T>::upload_host_typed(const void* Xv, int src_dtype, size_t rows, size_t cols, char order, bool wait) {
+  TraceRange trace_range("kmeans.upload");
   const size_t esz = dtype_size(src_dtype);
   if (!Xv || rows == 0 || cols == 0 || cols > (1u << 20)) KM_FAIL(KM_EINVAL, "kmeans_upload_host: bad argument");
   if (esz == 0) KM_FAIL(KM_EINVAL, "kmeans_upload_host_typed: unknown element type");
@@ -883,6 +884,7 @@ int Engine<T>::set_sample_weight(const T* host_w, size_t count) {
 // (src/interface_py/h2o4gpu/solvers/utils.py:144-158).
 template <typename T>
 int Engine<T>::check_data() {
+  TraceRange trace_range("kmeans.check_data");
   bool all = true;
   for (auto& s : shards) all = all && s.x_checked;
   if (all) return KM_OK;

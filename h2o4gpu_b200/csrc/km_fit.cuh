@@ -41,6 +41,7 @@ static int ensure_logs(Shard<T>& s, int n) {
 // predict).  Labels change counters are not touched.
 template <typename T>
 int Engine<T>::assign_all(int flags) {
+  TraceRange trace_range("kmeans.assign");
   if (!have_centroids) KM_FAIL(KM_ESTATE, "no centroids set");
   for (auto& s : shards) {
     if (!s.X) KM_FAIL(KM_ESTATE, "no data attached to the handle");
@@ -158,6 +159,7 @@ int Engine<T>::launch_close(Shard<T>& s, int run_if, int it, double inv, bool us
 
 template <typename T>
 int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int flags) {
+  TraceRange trace_range("kmeans.fit");
   if (k_ < 1 || max_iter < 0 || !init) KM_FAIL(KM_EINVAL, "kmeans_fit_resident: bad argument");
   if (shards.empty() || !shards[0].X) KM_FAIL(KM_ESTATE, "kmeans_fit_resident: no data attached");
   if (world_size > 64) KM_FAIL(KM_EINVAL, "at most 64 ranks");
@@ -249,6 +251,7 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
   int it = 0;
   int rc = KM_OK;
   for (; it < max_iter; ++it) {
+    TraceRange iteration_range("kmeans.iteration");   // host side: the launches of one iteration are queued here
     for (size_t i = 0; i < shards.size() && rc == KM_OK; ++i) {
       Shard<T>& s = shards[i];
       DevGuard g(s.dev);
@@ -470,6 +473,7 @@ int Engine<T>::fit(int k_, int max_iter, double threshold, const T* init, int fl
 // differences, double), all local shards; all-reduced over ranks.
 template <typename T>
 int Engine<T>::inertia(double* out) {
+  TraceRange trace_range("kmeans.inertia");
   KM_TRY(inertia_launch());
   return inertia_collect(out);
 }
@@ -519,6 +523,7 @@ int Engine<T>::inertia_collect(double* out) {
 // Squared distances of one shard, column-major with leading dimension ld, to the host.
 template <typename T>
 int Engine<T>::transform_shard(int local, T* out_host, size_t ld) {
+  TraceRange trace_range("kmeans.transform");
   if (local < 0 || local >= (int)shards.size() || !out_host) KM_FAIL(KM_EINVAL, "kmeans_transform_resident: bad argument");
   if (!have_centroids) KM_FAIL(KM_ESTATE, "no centroids set");
   Shard<T>& s = shards[local];

@@ -252,6 +252,7 @@ int fetch_rows(Engine<T>& e, const std::vector<size_t>& rows, std::vector<T>* ou
 template <typename T>
 int init_centroids(Engine<T>& e, int k, int seed, int method, std::vector<T>* out,
                    std::vector<size_t>* picked_rows = nullptr) {
+  TraceRange trace_range("kmeans.init_centroids");
   if (e.shards.empty() || !e.shards[0].X) KM_FAIL(KM_ESTATE, "initialisation: no data attached");
   if (e.world_size != (int)e.shards.size())
     KM_FAIL(KM_ESTATE, "initialisation on the device needs one process owning all shards; pass explicit centroids");
