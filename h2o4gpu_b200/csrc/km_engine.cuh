@@ -100,6 +100,10 @@ struct Shard {
   tcw::WidePlan tcwp; // tensor-core path for few centroids and wide rows
   tcs::StreamPlan tcsp;  // tensor-core path with both operands streamed: wide rows and many centroids, transform
   unsigned int* amb_rows = nullptr;  // rows handed to the exact re-evaluation pass
+  T* xpad = nullptr;                 // rows padded to a multiple of four columns (d % 4 != 0): what TMA can address
+  size_t xpad_cap = 0;               // elements
+  const T* xpad_of = nullptr;
+  size_t xpad_rows = 0;
   size_t amb_cap = 0;
   uint4* amb_near = nullptr;         // per listed row: bit mask of the candidate centroids (small tables)
   size_t amb_near_cap = 0;
@@ -226,12 +230,18 @@ struct Engine : EngineBase {
   // which tensor-core distance kernel labels this shape: 1 table resident (d 32/64, k <= 128), 2 table streamed
   // (d <= 256), 3 few centroids and wide rows, 4 both operands streamed (wider rows, many centroids), 0 none
   int tc_kind() const {
-    if (tcw::wide_shape_ok(k, d)) return 3;
-    if (tc::shape_ok(k, d)) return 1;
-    if (tcb::big_shape_ok(k, d)) return 2;
-    if (tcs::stream_shape_ok(k, d)) return 4;
+    if (tcw::wide_shape_ok(k, dtc())) return 3;
+    if (d % 4 == 0 && tc::shape_ok(k, d)) return 1;
+    if (tcb::big_shape_ok(k, dtc())) return 2;
+    if (tcs::stream_shape_ok(k, dtc())) return 4;
     return 0;
   }
+  // Rows that are not a multiple of 16 bytes cannot be addressed by TMA: the tensor-core kernels then read a
+  // copy of the shard padded with zero columns to dtc() columns (built once per attached matrix; the exact pass,
+  // the sums and everything else keep reading the rows as they are).
+  int dtc() const { return (d + 3) / 4 * 4; }
+  int ensure_xpad(Shard<T>& s);
+  const T* xtc(const Shard<T>& s) const { return d % 4 == 0 ? s.X : s.xpad; }
   int stream_refresh(Shard<T>& s);   // operand table and plan of the streaming kernel for the current centroids
   int tc_refresh(Shard<T>& s);  // split the current centroids for the tensor-core kernel
   int launch_assign(Shard<T>& s, bool use_tc, bool count_changes);
@@ -383,7 +393,7 @@ void Engine<T>::destroy() {
     s.tcbp.release();
     s.tcwp.release();
     s.tcsp.release();
-    km_free(s.amb_rows); km_free(s.amb_near); km_free(s.amb_log);
+    km_free(s.amb_rows); km_free(s.amb_near); km_free(s.amb_log); km_free(s.xpad);
     km_free(s.X_owned); km_free(s.raw); km_free(s.w); km_free(s.labels); km_free(s.dist); km_free(s.gacc);
     km_free(s.pacc); km_free(s.pflush); km_free(s.labels_prev); km_free(s.moved_bits);
     km_free(s.C[0]); km_free(s.C[1]); km_free(s.Cd[0]); km_free(s.Cd[1]); km_free(s.cnorm); km_free(s.shift_k); km_free(s.empties);
@@ -421,6 +431,7 @@ int Engine<T>::attach_device(int local, const T* dX, size_t rows, size_t cols, s
   s.tcbp.ready = false;
   s.tcwp.ready = false;
   s.tcsp.ready = false;
+  s.xpad_of = nullptr;
   if ((int)cols != d) have_centroids = false;
   d = (int)cols;
   n_total = ntot;
@@ -1162,8 +1173,18 @@ template <typename T>
 bool Engine<T>::tc_ok(int flags) const {
   if (!std::is_same<T, float>::value || (flags & KM_FIT_FORCE_SIMT)) return false;
   if (tc_kind() == 0) return false;
-  for (const auto& s : shards)
-    if (s.cc_major != 10 || (reinterpret_cast<uintptr_t>(s.X) & 15) != 0 || !s.x_checked) return false;
+  for (const auto& s : shards) {
+    if (s.cc_major != 10 || !s.x_checked) return false;
+    if (d % 4 == 0) {
+      if ((reinterpret_cast<uintptr_t>(s.X) & 15) != 0) return false;
+    } else if (!(s.xpad && s.xpad_cap >= s.rows * (size_t)dtc())) {
+      // the padded copy must fit beside the shard (with room to spare for the fit's own buffers)
+      size_t free_b = 0, total_b = 0;
+      DevGuard g(s.dev);
+      if (cudaMemGetInfo(&free_b, &total_b) != cudaSuccess) return false;
+      if (free_b < s.rows * (size_t)dtc() * sizeof(T) + ((size_t)1 << 30)) return false;
+    }
+  }
   double xmax = 0;
   for (const auto& s : shards) xmax = std::max(xmax, s.xmax);
   float sx, sb;
@@ -1184,16 +1205,17 @@ int Engine<T>::tc_refresh(Shard<T>& s) {
       KM_CUDA(km_malloc(&s.amb_rows, s.rows * sizeof(unsigned int)));
       s.amb_cap = s.rows;
     }
-    if (tc::shape_ok(k, d) && s.amb_near_cap < s.rows) {
+    if (tc_kind() == 1 && s.amb_near_cap < s.rows) {
       km_free(s.amb_near);
       s.amb_near = nullptr;
       KM_CUDA(km_malloc(&s.amb_near, s.rows * sizeof(uint4)));
       s.amb_near_cap = s.rows;
     }
     const int kind = tc_kind();
+    if (d % 4 != 0) KM_TRY(ensure_xpad(s));
     if (kind == 3) {
-      KM_TRY(tc::ensure_xnorm(s.tcp, s.X, s.rows, d, s.num_sms, s.stream));
-      KM_TRY(tcw::wide_setup(s.tcwp, s.X, s.rows, k, d));
+      KM_TRY(tc::ensure_xnorm(s.tcp, xtc(s), s.rows, dtc(), s.num_sms, s.stream));   // float4 loads: the aligned rows
+      KM_TRY(tcw::wide_setup(s.tcwp, xtc(s), s.rows, k, d, dtc()));
       s.tcwp.sx = tc_sx;
       s.tcwp.sb = tc_sb;
       KM_TRY(tcw::wide_prep(s.tcwp, s.C[cur], s.cnorm, s.stream));
@@ -1205,8 +1227,8 @@ int Engine<T>::tc_refresh(Shard<T>& s) {
       s.tcp.sb = tc_sb;
       KM_TRY(tc::prep(s.tcp, s.C[cur], s.cnorm, s.stream));
     } else {
-      KM_TRY(tc::ensure_xnorm(s.tcp, s.X, s.rows, d, s.num_sms, s.stream));
-      KM_TRY(tcb::big_setup(s.tcbp, s.X, s.rows, k, d));
+      KM_TRY(tc::ensure_xnorm(s.tcp, xtc(s), s.rows, dtc(), s.num_sms, s.stream));   // float4 loads: the aligned rows
+      KM_TRY(tcb::big_setup(s.tcbp, xtc(s), s.rows, k, d, dtc()));
       s.tcbp.sx = tc_sx;
       s.tcbp.sb = tc_sb;
       KM_TRY(tcb::big_prep(s.tcbp, s.C[cur], s.cnorm, s.stream));
@@ -1217,10 +1239,41 @@ int Engine<T>::tc_refresh(Shard<T>& s) {
 }
 
 template <typename T>
+__global__ void __launch_bounds__(256)
+pad_rows_kernel(const T* __restrict__ X, size_t rows, int d, int dp, T* __restrict__ out) {
+  const size_t total = rows * (size_t)dp;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / dp;
+    const int t = (int)(i - r * dp);
+    out[i] = t < d ? X[r * (size_t)d + t] : (T)0;
+  }
+}
+
+template <typename T>
+int Engine<T>::ensure_xpad(Shard<T>& s) {
+  if (s.xpad_of == s.X && s.xpad_rows == s.rows && s.xpad) return KM_OK;
+  const size_t need = s.rows * (size_t)dtc();
+  if (s.xpad_cap < need) {
+    km_free(s.xpad);
+    s.xpad = nullptr;
+    s.xpad_cap = 0;
+    KM_CUDA(km_malloc(&s.xpad, need * sizeof(T)));
+    s.xpad_cap = need;
+  }
+  pad_rows_kernel<T><<<s.num_sms * 16, 256, 0, s.stream>>>(s.X, s.rows, d, dtc(), s.xpad);
+  KM_CUDA(cudaGetLastError());
+  ++launches;
+  s.xpad_of = s.X;
+  s.xpad_rows = s.rows;
+  return KM_OK;
+}
+
+template <typename T>
 int Engine<T>::stream_refresh(Shard<T>& s) {
   if constexpr (std::is_same<T, float>::value) {
-    KM_TRY(tc::ensure_xnorm(s.tcp, s.X, s.rows, d, s.num_sms, s.stream));
-    KM_TRY(tcs::stream_setup(s.tcsp, s.X, s.rows, k, d));
+    if (d % 4 != 0) KM_TRY(ensure_xpad(s));
+    KM_TRY(tc::ensure_xnorm(s.tcp, xtc(s), s.rows, dtc(), s.num_sms, s.stream));   // float4 loads: the aligned rows
+    KM_TRY(tcs::stream_setup(s.tcsp, xtc(s), s.rows, k, d, dtc()));
     s.tcsp.sx = tc_sx;
     s.tcsp.sb = tc_sb;
     KM_TRY(tcs::stream_prep(s.tcsp, s.C[cur], s.cnorm, s.stream));
@@ -1239,7 +1292,7 @@ int Engine<T>::launch_assign(Shard<T>& s, bool use_tc, bool count_changes) {
       KM_CUDA(cudaGetLastError());
       return KM_OK;
     }
-    if (use_tc && tcw::wide_shape_ok(k, d)) {
+    if (use_tc && tc_kind() == 3) {
       launches += 2;
       KM_TRY(tcw::wide_launch(s.tcwp, s.tcp.xnorm, s.labels, s.st, count_changes, s.amb_rows, tc::tol_rel_of(d), s.num_sms,
                               s.stream));
@@ -1247,7 +1300,7 @@ int Engine<T>::launch_assign(Shard<T>& s, bool use_tc, bool count_changes) {
       KM_CUDA(cudaGetLastError());
       return KM_OK;
     }
-    if (use_tc && !tc::shape_ok(k, d)) {
+    if (use_tc && tc_kind() == 2) {
       launches += 2;
       KM_TRY(tcb::big_launch(s.tcbp, s.tcp.xnorm, s.labels, s.st, count_changes, s.amb_rows, tc::tol_rel_of(d), s.num_sms,
                              s.stream));

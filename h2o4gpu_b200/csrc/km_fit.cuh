@@ -48,7 +48,7 @@ int Engine<T>::assign_all(int flags) {
     DevGuard g(s.dev);
     // the same dispatch as the E-step of a fit (launch_assign picks the streaming kernel for few
     // centroids and wide rows, the small-k kernel for narrow ones)
-    const bool use_tc = tc_ok(flags) && (!smallk_ok(false) || tcw::wide_shape_ok(k, d));
+    const bool use_tc = tc_ok(flags) && (!smallk_ok(false) || tc_kind() == 3);
     if (use_tc) {
       KM_TRY(tc_refresh(s));
       KM_CUDA(cudaMemsetAsync(&s.st->amb_count, 0, sizeof(unsigned int), s.stream));
@@ -134,9 +134,9 @@ SplitTable Engine<T>::split_table(Shard<T>& s, bool use_tc) {
   if constexpr (std::is_same<T, float>::value) {
     if (use_tc && tc_kind() == 4)
       tp = SplitTable{s.tcsp.bhi, s.tcsp.blo, s.tcsp.cn, s.tcsp.kpad, s.tcsp.dp, s.tcsp.sb, s.tcsp.sx * s.tcsp.sb};
-    else if (use_tc && tcw::wide_shape_ok(k, d))
+    else if (use_tc && tc_kind() == 3)
       tp = SplitTable{s.tcwp.bhi, s.tcwp.blo, s.tcwp.cn, tcw::kNPad, s.tcwp.dp, s.tcwp.sb, s.tcwp.sx * s.tcwp.sb};
-    else if (use_tc && tc::shape_ok(k, d))
+    else if (use_tc && tc_kind() == 1)
       tp = SplitTable{s.tcp.bhi, s.tcp.blo, s.tcp.cn, s.tcp.npad, 64, s.tcp.sb, s.tcp.sx * s.tcp.sb};
     else if (use_tc)
       tp = SplitTable{s.tcbp.bhi, s.tcbp.blo, s.tcbp.cn, s.tcbp.kpad, s.tcbp.dp, s.tcbp.sb, s.tcbp.sx * s.tcbp.sb};
@@ -551,10 +551,10 @@ int Engine<T>::transform_shard(int local, T* out_host, size_t ld) {
   if constexpr (std::is_same<T, float>::value) {
     // tensor-core kernels with a store epilogue (they need max|x| for the operand scales, i.e. a checked
     // matrix): the wide-row kernel for few centroids, the kernel that streams both operands for the rest
-    if (tcw::wide_shape_ok(k, d) && tc_ok(0)) {
+    if (tc_kind() == 3 && tc_ok(0)) {
       rc = tc_refresh(s);
       wide = rc == KM_OK;
-    } else if (tcs::stream_shape_ok(k, d) && tc_ok(0)) {
+    } else if (tcs::stream_shape_ok(k, dtc()) && tc_ok(0)) {
       if (tc_kind() == 4) {
         rc = tc_refresh(s);
       } else {

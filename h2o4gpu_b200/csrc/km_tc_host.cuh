@@ -275,7 +275,8 @@ inline int big_set_attr(int kpad) {
   return KM_OK;
 }
 
-inline int big_setup(BigPlan& pl, const float* X, size_t rows, int k, int d) {
+// ldx: row pitch of X in elements (d, or d rounded up to four for the padded copy of unaligned rows)
+inline int big_setup(BigPlan& pl, const float* X, size_t rows, int k, int d, int ldx) {
   const int kpad = (k + kNT - 1) / kNT * kNT;
   const int dv = big_variant(d);
   const int dp = dv < 64 ? 64 : dv;
@@ -287,7 +288,7 @@ inline int big_setup(BigPlan& pl, const float* X, size_t rows, int k, int d) {
     KM_CUDA(km_malloc(&pl.cn, (size_t)(kpad + 1) * sizeof(float)));
   }
   pl.kpad = kpad; pl.k = k; pl.d = d; pl.dp = dp; pl.x_base = X; pl.x_rows = rows;
-  KM_TRY(tc::make_map(&pl.tmX, X, rows, d, kBM, 4));
+  KM_TRY(tc::make_map(&pl.tmX, X, rows, ldx, kBM, 4));
   KM_TRY(tc::make_map(&pl.tmBhi, pl.bhi, kpad, dp, kNT, 2));
   KM_TRY(tc::make_map(&pl.tmBlo, pl.blo, kpad, dp, kNT, 2));
   if (dv == 32) KM_TRY(big_set_attr<32>(kpad));
@@ -370,7 +371,7 @@ inline int wide_stages(int d) {
 // float32, at most 16 centroids, rows of 128 or more columns (16-byte aligned rows: d % 4 == 0)
 inline bool wide_shape_ok(int k, int d) { return k >= 1 && k <= kNPad && d >= 128 && d % 4 == 0 && wide_stages(d) > 0; }
 
-inline int wide_setup(WidePlan& pl, const float* X, size_t rows, int k, int d) {
+inline int wide_setup(WidePlan& pl, const float* X, size_t rows, int k, int d, int ldx) {
   if (pl.ready && pl.k == k && pl.d == d && pl.x_base == X && pl.x_rows == rows) return KM_OK;
   const int n_chunks = (d + kChunk - 1) / kChunk;
   const int dp = n_chunks * kChunk;
@@ -382,7 +383,7 @@ inline int wide_setup(WidePlan& pl, const float* X, size_t rows, int k, int d) {
   }
   pl.k = k; pl.d = d; pl.dp = dp; pl.n_chunks = n_chunks; pl.stages = wide_stages(d);
   pl.x_base = X; pl.x_rows = rows;
-  KM_TRY(tc::make_map(&pl.tmX, X, rows, d, kBM, 4));
+  KM_TRY(tc::make_map(&pl.tmX, X, rows, ldx, kBM, 4));
   KM_TRY(tc::make_map(&pl.tmBhi, pl.bhi, kNPad, dp, kNPad, 2));
   KM_TRY(tc::make_map(&pl.tmBlo, pl.blo, kNPad, dp, kNPad, 2));
   KM_CUDA(cudaFuncSetAttribute(assign_tc_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -447,7 +448,7 @@ struct StreamPlan {
 inline bool stream_shape_ok(int k, int d) { return k > 16 && k <= 6144 && d >= 32 && d <= 4096 && d % 4 == 0; }
 inline int stream_npad(int k) { return k <= 128 ? 128 : 256; }
 
-inline int stream_setup(StreamPlan& pl, const float* X, size_t rows, int k, int d) {
+inline int stream_setup(StreamPlan& pl, const float* X, size_t rows, int k, int d, int ldx) {
   if (pl.ready && pl.k == k && pl.d == d && pl.x_base == X && pl.x_rows == rows) return KM_OK;
   const int n_chunks = (d + kSChunk - 1) / kSChunk;
   const int dp = n_chunks * kSChunk;
@@ -462,7 +463,7 @@ inline int stream_setup(StreamPlan& pl, const float* X, size_t rows, int k, int 
   }
   pl.k = k; pl.d = d; pl.dp = dp; pl.n_chunks = n_chunks; pl.npad = npad; pl.n_pass = n_pass; pl.kpad = kpad;
   pl.x_base = X; pl.x_rows = rows;
-  KM_TRY(tc::make_map(&pl.tmX, X, rows, d, kBM, 4));
+  KM_TRY(tc::make_map(&pl.tmX, X, rows, ldx, kBM, 4));
   KM_TRY(tc::make_map(&pl.tmBhi, pl.bhi, kpad, dp, npad, 2));
   KM_TRY(tc::make_map(&pl.tmBlo, pl.blo, kpad, dp, npad, 2));
   if (npad == 128)

@@ -1248,3 +1248,43 @@ def test_offset_data_labels_equal_float64_argmin(eng, d, k, offset):
     assert st["path"] == 3
     want = lloyd.assign(X, C.astype(np.float64), dtype=np.float64)
     check_labels(X, C.astype(np.float64), lab, want)
+
+
+# ---- rows that are not a multiple of 16 bytes: tensor cores through a zero-padded copy --------------
+@pytest.mark.parametrize("n,d,k", [(20000, 50, 100), (9000, 101, 300), (5000, 785, 40), (8000, 786, 12),
+                                   (6000, 30, 64), (4001, 255, 17)])
+def test_unaligned_row_widths_reach_the_tensor_cores(eng, n, d, k):
+    """d % 4 != 0: TMA cannot address the rows, so the tensor-core kernels read a copy of the shard padded
+    with zero columns to the next multiple of four (built once per matrix); sums, exact pass and everything
+    else keep the rows as they are.  Results as for any other shape; labels against the FMA kernel too."""
+    rng = np.random.default_rng(n + d + k)
+    centers = rng.uniform(-4, 4, (max(k // 3, 5), d))
+    X = (centers[rng.integers(0, centers.shape[0], n)] + rng.standard_normal((n, d))).astype(np.float32)
+    init = X[np.sort(rng.choice(n, k, replace=False))].copy()
+    C = init.astype(np.float64)
+    h = eng.ResidentKMeans(dtype=np.float32)
+    h.upload(X)
+    for _ in range(2):
+        C32 = C.astype(np.float32)
+        Cn, labn, _, moved = lloyd.step(X, C32.astype(np.float64), order="descending")
+        h.fit(C32, 1, flags=eng.FIT_NO_FINAL_ASSIGN)
+        st = h.stats()
+        assert st["path"] == 3
+        check_step(X, C32.astype(np.float64), h.centroids(), h.labels(), Cn, labn, moved, st["relocations"])
+        C = Cn
+    # several iterations through the incremental sums as well, then predict and transform on the result
+    h.fit(init, 6)
+    Cfit = h.centroids()
+    lab_fit = h.labels()
+    h.assign()
+    assert np.array_equal(h.labels(), lab_fit)
+    D = h.transform()
+    h.close()
+    want = lloyd.transform_sq_exact(X, Cfit.astype(np.float64))
+    floor = np.finfo(np.float32).eps * ((X.astype(np.float64) ** 2).sum(1)[:, None] + (Cfit.astype(np.float64) ** 2).sum(1)[None, :])
+    assert (np.abs(D - want) <= 1e-4 * want + (16 * (0.8 + d / 200.0) + 16) * floor).all()
+    a = one_step(eng, X, init)
+    b = one_step(eng, X, init, flags=eng.FIT_FORCE_SIMT)
+    assert a[2]["path"] == 3 and b[2]["path"] == 2
+    if check_labels(X, init.astype(np.float64), a[1], b[1]) == 0:
+        assert np.array_equal(a[0], b[0])          # integer sums: same labels -> same bits
