@@ -1288,3 +1288,40 @@ def test_unaligned_row_widths_reach_the_tensor_cores(eng, n, d, k):
     assert a[2]["path"] == 3 and b[2]["path"] == 2
     if check_labels(X, init.astype(np.float64), a[1], b[1]) == 0:
         assert np.array_equal(a[0], b[0])          # integer sums: same labels -> same bits
+
+
+# ---- seeded random shapes across all distance kernels ------------------------------------------
+def _fuzz_shapes():
+    rng = np.random.default_rng(20261126)
+    shapes = []
+    for _ in range(28):
+        d = int(rng.choice([rng.integers(2, 40), rng.integers(40, 300), rng.integers(300, 1300)]))
+        k = int(rng.choice([rng.integers(2, 17), rng.integers(17, 130), rng.integers(130, 700)]))
+        n = int(rng.integers(max(k, 130), 6000))
+        shapes.append((n, d, k))
+    # edge sizes: fewer rows than one tile, one row more than a tile, k = n
+    shapes += [(k0, d0, k0) for k0, d0 in ((37, 64), (129, 300), (200, 785))] + [(129, 128, 40), (257, 784, 10)]
+    return shapes
+
+
+@pytest.mark.parametrize("n,d,k", _fuzz_shapes())
+def test_random_shapes_one_step_matches_oracle(eng, n, d, k):
+    """Whatever kernel a shape selects (fused small-k, FMA tiles, one of the four tensor-core kernels, the padded
+    copy for unaligned rows), one Lloyd step equals the float64 oracle's: labels outside the near-tie band,
+    centroids to 1e-4, relocations counted alike; predict on the result reproduces the labels."""
+    rng = np.random.default_rng(n * 7 + d * 3 + k)
+    centers = rng.uniform(-5, 5, (max(k // 2, 3), d))
+    X = (centers[rng.integers(0, centers.shape[0], n)] + rng.standard_normal((n, d))).astype(np.float32)
+    init = X[np.sort(rng.choice(n, k, replace=False))].copy()
+    h = eng.ResidentKMeans(dtype=np.float32)
+    h.upload(X)
+    Cn, labn, _, moved = lloyd.step(X, init.astype(np.float64), order="descending")
+    h.fit(init, 1, flags=eng.FIT_NO_FINAL_ASSIGN)
+    st = h.stats()
+    check_step(X, init.astype(np.float64), h.centroids(), h.labels(), Cn, labn, moved, st["relocations"])
+    # labels of the new centroids: fit's closing E-step against predict
+    h.fit(init, 2)
+    lab2 = h.labels()
+    h.assign()
+    assert np.array_equal(h.labels(), lab2)
+    h.close()
