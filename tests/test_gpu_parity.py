@@ -509,6 +509,32 @@ def test_multi_gpu_equals_single_gpu(eng):
     h2.close()
 
 
+@pytest.mark.parametrize("n,d,k", [(30001, 128, 300), (20001, 784, 10), (15001, 300, 40), (20001, 50, 100)])
+def test_multi_gpu_other_tensor_core_kernels_equal_single_gpu(eng, n, d, k):
+    """The streamed-table, wide-row and streaming kernels and the padded copy of unaligned rows, several
+    devices driven by one process against one device: centroids and labels bit-identical."""
+    from h2o4gpu_b200.libs import lib_kmeans
+    ndev = lib_kmeans.cdll().kmeans_device_count()
+    if ndev < 2:
+        pytest.skip("one GPU visible")
+    rng = np.random.default_rng(n + d + k)
+    centers = rng.uniform(-4, 4, (max(k // 3, 5), d))
+    X = (centers[rng.integers(0, centers.shape[0], n)] + rng.standard_normal((n, d))).astype(np.float32)
+    init = X[np.sort(rng.choice(n, k, replace=False))].copy()
+    h1 = eng.ResidentKMeans()
+    h1.upload(X)
+    h1.fit(init, 4)
+    h2 = eng.ResidentKMeans(devices=list(range(min(ndev, 4))))
+    h2.upload(X)
+    h2.fit(init, 4)
+    assert h1.stats()["path"] == 3 and h2.stats()["path"] == 3
+    assert h1.stats()["relocations"] == h2.stats()["relocations"]
+    assert np.array_equal(h1.centroids(), h2.centroids())      # integer sums: bit-identical
+    assert np.array_equal(h1.labels(), h2.all_labels())
+    h1.close()
+    h2.close()
+
+
 @pytest.mark.parametrize("n", [2, 5, 9, 41])
 def test_multi_gpu_ragged_row_counts(eng, n):
     """Row counts that a ceil split would leave a device without (9 rows on 8 devices, 5 on 4): the balanced
