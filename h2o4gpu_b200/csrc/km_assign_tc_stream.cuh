@@ -13,7 +13,7 @@
 //   X chunk   TMA (two 128B-swizzled panels of 32 columns, zero fill beyond d) into a ring; converter
 //             warps split it into one of four TMEM A buffers (as in km_assign_tc_wide.cuh)
 //   B chunk   the pass's NPAD rows x 64 columns of the split centroid table, upper and lower halves,
-//             TMA from L2 into a two-stage ring
+//             TMA from L2 into a ring of three stages (N = 128) or two (N = 256)
 //   MMA       12 instructions (M = 128, N = NPAD, K = 16) per chunk into the pass's accumulator
 //   epilogue  after the last chunk: NPAD scores per row, folded into the row's running
 //             (best, second best, index) - or stored as squared distances for transform
@@ -37,7 +37,7 @@ using namespace km::tc;
 constexpr int kSThreads = 512;
 constexpr int kSChunk = 64;        // fp32 columns per chunk
 constexpr int kSNA = 4;            // A buffers in TMEM
-constexpr int kSBStages = 2;       // ring of centroid chunks
+constexpr int kSMaxBStages = 3;    // ring of centroid chunks: three stages with N = 128, two with N = 256
 constexpr int kSMaxXStages = 4;
 constexpr uint32_t kSXStageBytes = kBM * kSChunk * 4;   // 32 KB
 
@@ -47,16 +47,19 @@ template <int NPAD> struct StreamCfg {
   static constexpr int kXStages = NPAD == 128 ? 4 : 2;           // even on purpose
   static constexpr uint32_t kBHalfBytes = (uint32_t)NPAD * 128u;  // one half (hi or lo) of a centroid chunk
   static constexpr uint32_t kBStageBytes = 2u * kBHalfBytes;
+  // one consumer (the issuer), so an odd depth is fine here; a third stage covers the L2 latency of a
+  // chunk while the two before it are multiplied (N = 128: 768 clocks of MMA per chunk)
+  static constexpr int kBStages = NPAD == 128 ? 3 : 2;
 };
 
 enum SBar { S_XFUL = 0, S_XEMP = kSMaxXStages, S_ARDY = 2 * kSMaxXStages, S_AEMP = 2 * kSMaxXStages + kSNA,
-            S_ACF = 2 * kSMaxXStages + 2 * kSNA, S_ACE = S_ACF + 2, S_BFUL = S_ACE + 2, S_BEMP = S_BFUL + kSBStages,
-            S_DRAIN = S_BEMP + kSBStages, S_NBARS = S_DRAIN + 1 };
+            S_ACF = 2 * kSMaxXStages + 2 * kSNA, S_ACE = S_ACF + 2, S_BFUL = S_ACE + 2, S_BEMP = S_BFUL + kSMaxBStages,
+            S_DRAIN = S_BEMP + kSMaxBStages, S_NBARS = S_DRAIN + 1 };
 
 template <int NPAD>
 inline size_t stream_smem_bytes() {
   using Cf = StreamCfg<NPAD>;
-  return 1024 + (size_t)kSBStages * Cf::kBStageBytes + (size_t)Cf::kXStages * kSXStageBytes + S_NBARS * 8 + 64;
+  return 1024 + (size_t)Cf::kBStages * Cf::kBStageBytes + (size_t)Cf::kXStages * kSXStageBytes + S_NBARS * 8 + 64;
 }
 
 // n_chunks = ceil(d / 64); n_pass = ceil(k / NPAD); cn_pad[n_pass * NPAD + 1]: |c|^2 sx sb (+inf in the
@@ -72,6 +75,7 @@ assign_tc_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
   using Cf = StreamCfg<NPAD>;
   constexpr int kXS = Cf::kXStages;
   constexpr int kNAcc = Cf::kNAcc;
+  constexpr int kSBStages = Cf::kBStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_u32 = smem_u32(smem_raw);
   const uint32_t base = (raw_u32 + 1023u) & ~1023u;
@@ -92,7 +96,7 @@ assign_tc_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
     for (int s = 0; s < kSMaxXStages; ++s) { mbar_init(bar(S_XFUL + s), 1); mbar_init(bar(S_XEMP + s), 128); }
     for (int b = 0; b < kSNA; ++b) { mbar_init(bar(S_ARDY + b), 128); mbar_init(bar(S_AEMP + b), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(bar(S_ACF + a), 1); mbar_init(bar(S_ACE + a), 128); }
-    for (int t = 0; t < kSBStages; ++t) { mbar_init(bar(S_BFUL + t), 1); mbar_init(bar(S_BEMP + t), 1); }
+    for (int t = 0; t < kSMaxBStages; ++t) { mbar_init(bar(S_BFUL + t), 1); mbar_init(bar(S_BEMP + t), 1); }
     mbar_init(bar(S_DRAIN), 1);
     *abort_flag = 0;
     abort_flag[3] = (int)wait_iters;
