@@ -22,8 +22,8 @@
 // NPAD = 128 keeps two accumulators (the epilogue of one pass overlaps the next tile's MMAs).
 //
 // Warps: 0 X producer, 1 MMA issuer, 2 B producer, 3 spare, 4-11 converters (two groups of four,
-// alternating chunks), 12-15 epilogue.  Ring depths are even, so a stage always serves the same
-// converter group (a barrier shared by two groups that are not ordered against each other cannot be
+// alternating chunks), 12-15 epilogue.  The X ring and the A buffers have even depths, so a stage always
+// serves the same converter group (a barrier shared by two groups that are not ordered against each other cannot be
 // waited for with a one-bit parity).  Every mbarrier wait is bounded.
 #pragma once
 
