@@ -75,8 +75,10 @@ __device__ __noinline__ void flush_run(long long s, int* a0, size_t pstride, lon
   }
 }
 
-// GS = threads per row (a power of two >= d / 4).  scale30 = 2^(30 - e).
-template <int GS>
+// GS = threads per row, VPT = float4 vectors per thread and row (GS * VPT >= d / 4, GS a power of two):
+// with two vectors per thread the per-row bookkeeping (list entry, label compare, address) is spread
+// over eight elements instead of four.  scale30 = 2^(30 - e).
+template <int GS, int VPT>
 __global__ void __launch_bounds__(kSortThreads, 2)
 sorted_accumulate_kernel(const float* __restrict__ X, size_t n, int d, const int* __restrict__ labels, int k,
                          long long* __restrict__ gsums, unsigned long long* __restrict__ gcounts,
@@ -94,7 +96,9 @@ sorted_accumulate_kernel(const float* __restrict__ X, size_t n, int d, const int
   constexpr int G = kSortThreads / GS;                 // groups walking the sorted list
   const int grp = tid / GS;
   const int l = tid % GS;
-  const bool active = l < dv;
+  bool active[VPT];
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) active[j] = (l + j * GS) < dv;
 
   if (smem_acc)
     for (int i = tid; i < 3 * k * d; i += kSortThreads) acc[i] = 0;
@@ -152,47 +156,55 @@ sorted_accumulate_kernel(const float* __restrict__ X, size_t n, int d, const int
     const int per_grp = (nsorted + G - 1) / G;
     const int p0 = grp * per_grp;
     const int p1 = min(nsorted, p0 + per_grp);
-    long long s[4] = {0, 0, 0, 0};
+    long long s[VPT][4];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0;
     int cur = -1;
     const float* Xt = X + r0 * (size_t)d;
-    constexpr int U = 4;
+    constexpr int U = 4 / VPT;   // rows in flight: four 16-byte loads per thread either way
+    auto flush_all = [&](int c) {
+#pragma unroll
+      for (int j = 0; j < VPT; ++j) {
+        if (active[j]) {
+          int* a0 = acc + (size_t)c * d + (l + j * GS) * 4;
+          long long* g = gsums + (size_t)c * d + (l + j * GS) * 4;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) flush_run(s[j][e], a0 + e, pstride, g + e, smem_acc);
+        }
+        s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0;
+      }
+    };
     for (int p = p0; p < p1; p += U) {
       unsigned ent[U];
-      float4 x[U];
+      float4 x[U][VPT];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         ent[u] = (p + u < p1) ? sorted[p + u] : 0xffffffffu;
-        if (ent[u] != 0xffffffffu && active)
-          x[u] = *reinterpret_cast<const float4*>(Xt + (size_t)(ent[u] & 0xffffu) * d + l * 4);
+#pragma unroll
+        for (int j = 0; j < VPT; ++j)
+          if (ent[u] != 0xffffffffu && active[j])
+            x[u][j] = *reinterpret_cast<const float4*>(Xt + (size_t)(ent[u] & 0xffffu) * d + (l + j * GS) * 4);
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         if (ent[u] == 0xffffffffu) continue;
         const int lab = (int)(ent[u] >> 16);
         if (lab != cur) {
-          if (cur >= 0 && active) {
-            int* a0 = acc + (size_t)cur * d + l * 4;
-            long long* g = gsums + (size_t)cur * d + l * 4;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) flush_run(s[e], a0 + e, pstride, g + e, smem_acc);
-          }
-          s[0] = s[1] = s[2] = s[3] = 0;
+          if (cur >= 0) flush_all(cur);
           cur = lab;
         }
-        if (active) {
-          s[0] += (long long)__float2int_rn(x[u].x * scale30);
-          s[1] += (long long)__float2int_rn(x[u].y * scale30);
-          s[2] += (long long)__float2int_rn(x[u].z * scale30);
-          s[3] += (long long)__float2int_rn(x[u].w * scale30);
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+          if (active[j]) {
+            s[j][0] += (long long)__float2int_rn(x[u][j].x * scale30);
+            s[j][1] += (long long)__float2int_rn(x[u][j].y * scale30);
+            s[j][2] += (long long)__float2int_rn(x[u][j].z * scale30);
+            s[j][3] += (long long)__float2int_rn(x[u][j].w * scale30);
+          }
         }
       }
     }
-    if (cur >= 0 && active) {
-      int* a0 = acc + (size_t)cur * d + l * 4;
-      long long* g = gsums + (size_t)cur * d + l * 4;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) flush_run(s[e], a0 + e, pstride, g + e, smem_acc);
-    }
+    if (cur >= 0) flush_all(cur);
     since_drain += nr;
     __syncthreads();
     if (smem_acc && (since_drain + tile_rows > (size_t)kSortDrainRows || tile + gridDim.x >= n_tiles)) {
